@@ -1,0 +1,283 @@
+/*
+ * tsb200.h — C ABI of libtsb200.so: hand-written sm_100a CUDA kernels for Seq2SeqSharp's GPTDecoder
+ * autoregressive token loop, reached from C# by P/Invoke behind the TensorSharp backend contract
+ * (OpRegistry op names, IAllocator, Storage).
+ *
+ * Conventions (same as the in-tree native bridge TensorSharp.GGML.Native/ggml_ops.cpp:90-135,4683-4722 and
+ * its binding TensorSharp.GGML/GgmlNative.cs:161-331,471-479):
+ *   - every function returns int: 1 = success, 0 = failure; nothing throws across the boundary;
+ *   - TSB200_GetLastError() returns a thread-local message for the calling thread's last failure;
+ *   - plain pointers and sizes only; tensors are described by TSB200Tensor (sizes + element strides, the
+ *     fields of TensorSharp.Tensor: TensorSharp/Tensor.cs:42-57);
+ *   - every entry point selects its device itself (the reference calls a backend from one thread per device:
+ *     Seq2SeqSharp/Tools/BaseSeq2SeqFramework.cs:912) and is safe to call concurrently for different devices;
+ *   - `stream` is a cudaStream_t passed as void*; NULL selects the library's own non-blocking stream of the
+ *     device.  Nothing runs on the legacy NULL stream;
+ *   - there is no CPU fallback: with no usable sm_100 device every compute entry point fails.
+ */
+#ifndef TSB200_H_
+#define TSB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define TSB200_API __declspec(dllexport)
+#else
+#define TSB200_API __attribute__((visibility("default")))
+#endif
+
+/* TensorSharp.DType (TensorSharp/DType.cs:6-13) */
+enum { TSB200_F32 = 0, TSB200_F16 = 1, TSB200_F64 = 2, TSB200_I32 = 3, TSB200_U8 = 4 };
+
+/* A strided view over device memory: the (sizes, strides, storage, offset) of TensorSharp.Tensor with the
+ * offset already applied to `data`.  Outermost dimension first; strides in elements. */
+typedef struct TSB200Tensor {
+  void* data;
+  int32_t dtype;
+  int32_t ndim; /* 1..4 */
+  int64_t sizes[4];
+  int64_t strides[4];
+} TSB200Tensor;
+
+/* ------------------------------------------------------------------------------------------------ lifecycle */
+/* replaces TSGgml_GetLastError (TensorSharp.GGML/GgmlNative.cs:171) */
+TSB200_API const char* TSB200_GetLastError(void);
+/* replaces TSGgml_IsBackendAvailable (GgmlNative.cs:177): 1 when `device` exists and is compute capability 10.x */
+TSB200_API int TSB200_IsAvailable(int device);
+TSB200_API int TSB200_DeviceCount(int* count);
+/* library build facts: "sm_100a;<nvcc version>" */
+TSB200_API const char* TSB200_BuildInfo(void);
+/* number of kernel launches this library has issued on `device` since load (bench bookkeeping) */
+TSB200_API int TSB200_LaunchCount(int device, int64_t* launches);
+
+/* ------------------------------------------------------------------------------------------------ memory
+ * IAllocator.Allocate / Storage.Destroy / Storage.CopyToStorage / CopyFromStorage
+ * (TensorSharp/IAllocator.cs:13-20, TensorSharp/Storage.cs:32-46; device precedent
+ * TensorSharp.CUDA/CudaStorage.cs:10-172).  A failed allocation sets the last error to a message that starts
+ * with "OOM:" so the binding can raise OutOfMemoryException (caught at Seq2SeqSharp/Applications/GPT.cs:269). */
+TSB200_API int TSB200_Alloc(int device, int64_t bytes, void** ptr);
+TSB200_API int TSB200_Free(int device, void* ptr);
+TSB200_API int TSB200_MemcpyH2D(int device, void* dst, const void* src, int64_t bytes, void* stream);
+TSB200_API int TSB200_MemcpyD2H(int device, void* dst, const void* src, int64_t bytes, void* stream);
+TSB200_API int TSB200_MemcpyD2D(int device, void* dst, const void* src, int64_t bytes, void* stream);
+/* cross-device copy; replaces cuMemcpyPeer in TensorSharp.CUDA/KernelOps/CopyOps.cs:47-97 */
+TSB200_API int TSB200_MemcpyPeer(int dst_device, void* dst, int src_device, const void* src, int64_t bytes);
+TSB200_API int TSB200_Synchronize(int device, void* stream);
+/* IAllocator.GetAllocatedMemoryRatio (TensorSharp/IAllocator.cs:19) */
+TSB200_API int TSB200_MemoryInfo(int device, int64_t* free_bytes, int64_t* total_bytes);
+
+/* ------------------------------------------------------------------------------------------------ unfused ops
+ * One entry point per op name the GPT decode path invokes through OpRegistry (the names registered in
+ * TensorSharp.CUDA/CudaBasicOps.cs:81-681).  F32 and F16 tensors; strided views where the reference accepts
+ * them, contiguous-only where the reference itself requires contiguity. */
+/* "copy" (CudaBasicOps.cs:81-163) — same element count, any strides, dtype conversion F32<->F16 allowed */
+TSB200_API int TSB200_Copy(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+/* "fill" (CudaBasicOps.cs:166) */
+TSB200_API int TSB200_Fill(int device, const TSB200Tensor* result, float value, void* stream);
+/* "addmm" (CudaBasicOps.cs:195-262): result = beta*src + alpha*m1*m2; src may be a stride-0 broadcast row */
+TSB200_API int TSB200_Addmm(int device, const TSB200Tensor* result, float beta, const TSB200Tensor* src, float alpha,
+                            const TSB200Tensor* m1, const TSB200Tensor* m2, void* stream);
+/* "addmmbatch" (CudaBasicOps.cs:264-328): 3-D, batch outermost */
+TSB200_API int TSB200_AddmmBatch(int device, const TSB200Tensor* result, float beta, const TSB200Tensor* src,
+                                 float alpha, const TSB200Tensor* m1, const TSB200Tensor* m2, void* stream);
+/* "layernorm" / "rmsnorm" (CudaBasicOps.cs:666,673; kernels TensorSharp.CUDA/DeviceCode/AdvFuncKernels.cs:613-685,
+ * 791-845): rows = all but the last dimension; beta may be NULL */
+TSB200_API int TSB200_LayerNorm(int device, const TSB200Tensor* result, const TSB200Tensor* src,
+                                const TSB200Tensor* gamma, const TSB200Tensor* beta, float eps, void* stream);
+TSB200_API int TSB200_RMSNorm(int device, const TSB200Tensor* result, const TSB200Tensor* src,
+                              const TSB200Tensor* gamma, const TSB200Tensor* beta, float eps, void* stream);
+/* "rope" (CudaBasicOps.cs:616; AdvFuncKernels.cs:1245-1279): interleaved pairs, base 500000,
+ * position = (row % seqLen) + rowOffset.  TSB200_RoPEEx takes the base as an argument. */
+TSB200_API int TSB200_RoPE(int device, const TSB200Tensor* result, const TSB200Tensor* src, int seqLen, int rowOffset,
+                           void* stream);
+TSB200_API int TSB200_RoPEEx(int device, const TSB200Tensor* result, const TSB200Tensor* src, int seqLen,
+                             int rowOffset, float base, void* stream);
+/* "softmax" (CudaBasicOps.cs:655; AdvFuncKernels.cs:1534-1600): over the last dimension, fp32 internally */
+TSB200_API int TSB200_Softmax(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+/* "indexselect" (CudaBasicOps.cs:608; AdvFuncKernels.cs:1214-1243): indices are F32 (or I32), negative = skip row */
+TSB200_API int TSB200_IndexSelect(int device, const TSB200Tensor* result, const TSB200Tensor* src,
+                                  const TSB200Tensor* indices, int isAdd, void* stream);
+/* "addt", "mult" (CudaBasicOps.cs:514,525): broadcasting via stride 0 in either operand */
+TSB200_API int TSB200_Add(int device, const TSB200Tensor* result, const TSB200Tensor* lhs, const TSB200Tensor* rhs,
+                          void* stream);
+TSB200_API int TSB200_Mul(int device, const TSB200Tensor* result, const TSB200Tensor* lhs, const TSB200Tensor* rhs,
+                          void* stream);
+/* "mulv", "divv" (CudaBasicOps.cs:491,493) */
+TSB200_API int TSB200_MulScalar(int device, const TSB200Tensor* result, const TSB200Tensor* src, float value,
+                                void* stream);
+TSB200_API int TSB200_DivScalar(int device, const TSB200Tensor* result, const TSB200Tensor* src, float value,
+                                void* stream);
+/* "relu", "SiLU", "LeakyReLU" (CudaBasicOps.cs:416,443,429) */
+TSB200_API int TSB200_Relu(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+TSB200_API int TSB200_SiLU(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+TSB200_API int TSB200_LeakyReLU(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+/* "float2half", "half2float" (CudaBasicOps.cs:343,346) */
+TSB200_API int TSB200_Float2Half(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+TSB200_API int TSB200_Half2Float(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream);
+/* "argmax" (CudaBasicOps.cs:560; TensorSharp.CUDA/DeviceCode/ReduceDimIndexKernels.cs:25,96-119): along `dim`,
+ * lowest index among equal maxima, index stored as a float (or int32 when result is I32) */
+TSB200_API int TSB200_Argmax(int device, const TSB200Tensor* result, const TSB200Tensor* src, int dim, void* stream);
+/* "buildtrimask" / "buildselftrimask" (CudaBasicOps.cs:645,639; AdvFuncKernels.cs:1414-1437,1383-1412) */
+TSB200_API int TSB200_BuildTriMask(int device, const TSB200Tensor* result, float value, float maskedValue,
+                                   void* stream);
+TSB200_API int TSB200_BuildSelfTriMask(int device, const TSB200Tensor* result, const TSB200Tensor* originalLengths,
+                                       int paddedSeqLen, float value, float maskedValue, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ sampling
+ * Device replacement for the host loop ComputeGraphTensor.TopPSample
+ * (Seq2SeqSharp/Tools/ComputeGraphTensor.cs:2305-2403).  probs [rows, V] F32 contiguous; history [rows,
+ * history_stride] I32 with history_len[row] valid ids (the row's decodedSequence), may be NULL; u [rows] F32
+ * uniform draws standing in for RandomGenerator.floatRandom (Seq2SeqSharp/Tools/RandomGenerator.cs:41-46);
+ * out [rows] I32.  workspace: at least TSB200_TopPWorkspaceBytes(rows, V) bytes of device memory.
+ * Same order as the reference: repeat penalty, drop w <= 0, sort (w desc, index asc), sequential fp32 prefix
+ * sum stopped at the first acc >= topP, pick the first k with acc[k]/acc >= u. */
+TSB200_API int64_t TSB200_TopPWorkspaceBytes(int rows, int V);
+TSB200_API int TSB200_TopPSample(int device, int32_t* out, const float* probs, int rows, int V, float topP,
+                                 float repeatPenalty, const int32_t* history, const int32_t* history_len,
+                                 int history_stride, const float* u, void* workspace, int64_t workspace_bytes,
+                                 void* stream);
+/* u[i] = Philox4x32-10 uniform in [0,1) for (seed, seq_first + i, step); replaces the process-wide
+ * System.Random (RandomGenerator.cs:41-46) with a counter-based stream per sequence */
+TSB200_API int TSB200_PhiloxUniform(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step,
+                                    void* stream);
+
+/* ------------------------------------------------------------------------------------------------ fused ops
+ * Building blocks of the fused decode path (additional op names the reworked layers call when the storage is
+ * device memory of this backend).  dtype = TSB200_F32 or TSB200_F16 for weights/activations; accumulation is
+ * always fp32. */
+enum { TSB200_ACT_NONE = -1, TSB200_ACT_RELU = 0, TSB200_ACT_SILU = 1, TSB200_ACT_LEAKYRELU = 2,
+       TSB200_ACT_GLU_NOACT = 3 /* the reference's "SwiGLU": (xW1+b1)*(xW3+b3), PositionwiseFeedForward.cs:82-89 */,
+       TSB200_ACT_SWIGLU = 4 /* silu(xW1+b1)*(xW3+b3): extension */, TSB200_ACT_GELU = 5 /* erf GELU: extension */ };
+
+/* y[M,N] = act(bias + x[M,K] W[K,N]) (+ residual); W row-major [in,out] as the reference stores it
+ * (Seq2SeqSharp/Layers/FeedForwardLayer.cs:43).  x, y in `dtype`; residual and y_f32 optional:
+ * when y_f32 != NULL the result (plus residual_f32 when given) is written there in fp32 instead of y.
+ * Decode-sized M (<= 16) runs the bandwidth-bound GEMV; larger M the tensor-core GEMM.
+ * Replaces Affine = bias copy + cublasGemmEx (TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-362). */
+TSB200_API int TSB200_LinearBiasAct(int device, int dtype, void* y, float* y_f32, const void* x, const void* W,
+                                    const void* bias, const float* residual_f32, int M, int K, int N, int act,
+                                    void* workspace, int64_t workspace_bytes, void* stream);
+TSB200_API int64_t TSB200_LinearWorkspaceBytes(int M, int K, int N);
+
+/* Fused (residual +) LayerNorm / RMSNorm: x_f32[M,d] (+= delta when given) -> h[M,d] in `dtype`.
+ * norm_type 0 = LayerNorm (beta may be NULL), 1 = RMSNorm.  Replaces gLNormalization / RMSNorm
+ * (AdvFuncKernels.cs:613-685,791-845) plus the preceding "addt". */
+TSB200_API int TSB200_NormResidual(int device, int dtype, void* h, float* x_f32, const void* delta, const void* gamma,
+                                   const void* beta, int norm_type, float eps, int M, int d, void* stream);
+
+/* RoPE on q and k for S new positions per sequence starting at cache length T0, then append k, v to the cache.
+ * q [B,S,H,hd], k/v [B,S,Hkv,hd] in `dtype` (row strides given in elements), cache K/V [B,Hkv,Tmax,hd].
+ * Replaces RoPE x2 + Concat x2 (MultiHeadAttention.cs:141-193, TensorSharp/Core/TensorConcatenation.cs:9-45). */
+TSB200_API int TSB200_RopeAppend(int device, int dtype, void* q, const void* k, const void* v, int64_t q_row_stride,
+                                 int64_t kv_row_stride, void* cacheK, void* cacheV, int B, int S, int H, int Hkv,
+                                 int hd, int T0, int Tmax, int use_rope, float rope_base, void* stream);
+
+/* Split-K flash-decode attention for S = 1: out[B,H,hd] = softmax(q K^T / sqrt(hd)) V over T cached positions,
+ * query head h reading KV head h / (H/Hkv) (GroupQueryAttention.cs:156-165).  Replaces MulBatch + Softmax +
+ * MulBatch (MultiHeadAttention.cs:195-231).  workspace >= TSB200_FlashDecodeWorkspaceBytes(B,H,hd,T). */
+TSB200_API int64_t TSB200_FlashDecodeWorkspaceBytes(int B, int H, int hd, int T);
+TSB200_API int TSB200_FlashDecode(int device, int dtype, void* out, const void* q, int64_t q_row_stride,
+                                  const void* cacheK, const void* cacheV, int B, int H, int Hkv, int hd, int T,
+                                  int Tmax, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Causal attention for prefill (S query positions on an empty cache or after T0 cached positions).
+ * Replaces BuildTriMask + MulBatch + Add + Softmax + MulBatch (Decoder.cs:681-693, MultiHeadAttention.cs:195-231). */
+TSB200_API int TSB200_PrefillAttention(int device, int dtype, void* out, const void* q, int64_t q_row_stride,
+                                       const void* cacheK, const void* cacheV, int B, int S, int H, int Hkv, int hd,
+                                       int T0, int Tmax, void* stream);
+
+/* logits[B,V] F32 -> (optional /temperature) -> softmax -> probs (+= -1 at blocked ids) -> first index of the
+ * row maximum.  Replaces Div + Half2Float + Softmax + Scatter/Add + Argmax (Decoder.cs:720-761;
+ * ReduceDimIndexKernels.cs:96-119).  probs_out may be NULL. */
+TSB200_API int TSB200_SoftmaxArgmax(int device, int32_t* out_ids, float* probs_out, const float* logits, int B, int V,
+                                    float temperature, const int32_t* blocked, int n_blocked, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ GPT engine
+ * The whole token loop of GPT.RunForwardOnSingleDevice / Decoder.GPTDecode / GPTDecoder.Decode
+ * (Seq2SeqSharp/Applications/GPT.cs:212-335, Applications/Decoder.cs:648-794, Networks/GPTDecoder.cs:153-191)
+ * on one device: weights by the reference's dictionary names, a pre-sized in-place KV cache, prefill, and
+ * CUDA-graph decode steps with on-device ArgMax / Top-P. */
+typedef struct TSB200GptConfig {
+  int32_t L, d, H, Hkv, hd, F, V;
+  int32_t norm_type;       /* 0 LayerNorm, 1 RMSNorm (Seq2SeqSharp/Utils/ArchEnums.cs) */
+  int32_t act;             /* TSB200_ACT_* */
+  int32_t pe_type;         /* 0 NoPE, 1 APE, 2 RoPE (Seq2SeqSharp/Utils/PositionEmbedding.cs:18-23) */
+  int32_t attn_type;       /* 0 MultiHeadAttention (packed QKV [d,3d]), 1 GroupQueryAttention */
+  int32_t dtype;           /* TSB200_F32 or TSB200_F16 (weights and activations; accumulation fp32) */
+  float eps;               /* reference: 1e-6 */
+  float rope_base;         /* reference: 500000 */
+  int32_t ape_decode_pos0; /* 1 = reference behaviour: cached decode adds APE row 0 (Decoder.cs:674-677) */
+  int32_t max_batch;       /* KV-cache capacity in sequences */
+  int32_t max_tokens;      /* KV-cache capacity in positions per sequence */
+  int32_t device;
+  /* tensor parallelism (MultiProcessorNetworkWrapper rework): this rank holds heads [H/tp*rank, ..) and FFN
+   * columns [F/tp*rank, ..); the caller supplies the all-reduce through TSB200_GptSetAllReduce. tp_size 1 = off */
+  int32_t tp_rank, tp_size;
+} TSB200GptConfig;
+
+typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOptions.cs:16-39 */
+  int32_t strategy;        /* 0 GreedySearch, 1 Sampling */
+  float topP;
+  float temperature;
+  float repeatPenalty;
+  const int32_t* blocked;  /* host pointer, BlockedTokens */
+  int32_t n_blocked;
+  uint64_t seed;           /* Philox key of the uniform stream; sequence b draws (seed, seq_base + b, step) */
+  uint64_t seq_base;
+} TSB200DecodingOptions;
+
+TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
+TSB200_API int TSB200_GptDestroy(void* gpt);
+/* name = the reference's weight key (IModel.AddWeights/GetWeights, Seq2SeqSharp/Tools/WeightTensor.cs:571-604),
+ * e.g. "GPTDecoder.SelfAttn_3.QKV", "GPTDecoder.PosFFN_3.feedForwardLayer1.m_Whd", "TgtEmbeddings",
+ * "FeedForward_Decoder_0.m_Whd", "PosEmbedding".  data: [rows, cols] row-major FULL (unsharded) tensor in
+ * `dtype` (F32 data is converted when the model is F16), host memory (on_device = 0) or memory of the model's
+ * device (on_device = 1).  With tp_size > 1 the engine keeps only this rank's slice. */
+TSB200_API int TSB200_GptSetWeight(void* gpt, const char* name, const void* data, int dtype, int64_t rows,
+                                   int64_t cols, int on_device);
+/* device pointer of the engine's copy of a weight (for tests and in-place synthetic fill); NULL name lists nothing */
+TSB200_API int TSB200_GptGetWeightPtr(void* gpt, const char* name, void** ptr, int64_t* rows, int64_t* cols);
+/* fill every weight with the seeded synthetic N(0, std) generator (norm gains 1, norm betas 0; biases N(0,std)
+ * when bias_std > 0 else 0), generated on the device */
+TSB200_API int TSB200_GptFillSynthetic(void* gpt, uint64_t seed, float std, float bias_std);
+/* all-reduce callback for tensor parallelism: called on `stream` with a device buffer of `count` fp32 values */
+typedef int (*TSB200AllReduceFn)(void* user, void* buf, int64_t count, void* stream);
+TSB200_API int TSB200_GptSetAllReduce(void* gpt, TSB200AllReduceFn fn, void* user);
+/* clear the KV cache and per-sequence histories */
+TSB200_API int TSB200_GptReset(void* gpt);
+/* Prefill: ids [B,S] host int32 (equal lengths, no padding) -> fills the cache, returns the first generated id
+ * per sequence in out_ids [B] (host).  Decoder.GPTDecode with an empty cache (Decoder.cs:679-697). */
+TSB200_API int TSB200_GptPrefill(void* gpt, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt,
+                                 int32_t* out_ids);
+/* Decode n_steps tokens per sequence, each step feeding back the previous step's id on the device
+ * (Decoder.cs:661-678 + GPT.cs:249-304).  out_ids [B, n_steps] host.  stop_on_eos: 1 = stop early once every
+ * sequence's last id is 0 (GPT.cs:300-303); *steps_done receives the number of steps run. */
+TSB200_API int TSB200_GptDecode(void* gpt, int n_steps, const TSB200DecodingOptions* opt, int stop_on_eos,
+                                int32_t* out_ids, int* steps_done);
+/* logits [B,V] / probs [B,V] (F32, host) of the most recent step */
+TSB200_API int TSB200_GptGetLogits(void* gpt, float* logits, float* probs);
+TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);
+/* device-timed duration (ms, CUDA events on the engine's stream) of the last GptDecode / GptPrefill call and
+ * the number of kernel launches it issued (graph replays count their nodes) */
+TSB200_API int TSB200_GptLastTiming(void* gpt, float* ms, int64_t* launches);
+/* the engine's stream (cudaStream_t) */
+TSB200_API int TSB200_GptStream(void* gpt, void** stream);
+/* algorithmic bytes of one decode step at cache length T for B sequences (weights once + KV read/write +
+ * embeddings + ids) */
+TSB200_API int TSB200_GptStepBytes(void* gpt, int B, int T, int64_t* bytes);
+
+/* ------------------------------------------------------------------------------------------------ synthetic data
+ * Seeded counter-based generator used for weights in tests and benchmarks: element i of tensor `name_hash`
+ * = (sum of eight 16-bit fields of two splitmix64 outputs - 262140) * std / 53510.06..., exactly reproducible
+ * on host and device. */
+TSB200_API int TSB200_FillSynthetic(int device, void* data, int dtype, int64_t n, uint64_t seed, uint64_t name_hash,
+                                    float std, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSB200_H_ */

@@ -1,0 +1,774 @@
+// GPT engine: the token loop of GPT.RunForwardOnSingleDevice / Decoder.GPTDecode / GPTDecoder.Decode
+// (Seq2SeqSharp/Applications/GPT.cs:212-335, Applications/Decoder.cs:648-794, Networks/GPTDecoder.cs:153-191)
+// on one device, built from the fused kernels of this library.
+//
+// Differences from the reference's execution model, none of which change results beyond float rounding:
+//  * weights are packed at load time: GQA's separate Q/K/V matrices become one [d, (H+2Hkv)hd] matrix (one
+//    GEMV/GEMM instead of three), and for the gated FFN W1/W3 are interleaved column-wise so the gate product is
+//    an epilogue;
+//  * the KV cache is pre-sized and appended in place ([B, Hkv, Tmax, hd], un-expanded for GQA) instead of being
+//    re-allocated and re-copied per step (Layers/MultiHeadAttention.cs:173-193);
+//  * the residual stream is kept in fp32; matmul inputs/outputs are in the model dtype; accumulation is fp32;
+//  * a decode step is one CUDA graph: the cache length and the step counter live in device memory so the same
+//    graph is replayed for every token, sampled ids are fed back on the device, and the host reads ids only
+//    when asked (every step only if it must test the reference's stop rule, GPT.cs:300-303).
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+
+namespace tsb {
+
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ E, const T* __restrict__ PE, const int* __restrict__ ids,
+                             int rows, int S, int d, int V, float sf, int pe_mode, int pe_rows, int T0_arg,
+                             const int* __restrict__ dT0) {
+  const int T0 = dT0 ? *dT0 : T0_arg;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    int id = ids[r];
+    if (id < 0 || id >= V) id = 0;
+    const int s = r % S;
+    int pos = (pe_mode == 1) ? s : T0 + s;  // pe_mode 1: the reference peeks APE rows [0, S) (PositionEmbedding.cs:30-33)
+    if (pos >= pe_rows) pos = pe_rows - 1;
+    const T* e = E + (int64_t)id * d;
+    const T* p = (pe_mode != 0) ? PE + (int64_t)pos * d : nullptr;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float v = to_f<T>(e[i]) * sf;
+      if (p) v += to_f<T>(p[i]);
+      x[(int64_t)r * d + i] = v;
+    }
+  }
+}
+
+__global__ void gather_last_kernel(float* __restrict__ xl, const float* __restrict__ x, int B, int S, int d) {
+  for (int b = blockIdx.x; b < B; b += gridDim.x)
+    for (int i = threadIdx.x; i < d; i += blockDim.x) xl[(int64_t)b * d + i] = x[((int64_t)b * S + S - 1) * d + i];
+}
+
+// state[0] = cache length T, state[1] = Philox step counter, state[2] = output slot of this call
+__global__ void commit_kernel(int* __restrict__ ids_cur, const int* __restrict__ ids_new, int* __restrict__ hist,
+                              int* __restrict__ hist_len, int hist_stride, int* __restrict__ out, int B, int* state,
+                              int advance_T) {
+  const int slot = state[2];
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int id = ids_new[b];
+    ids_cur[b] = id;
+    const int l = hist_len[b];
+    if (l < hist_stride) hist[(int64_t)b * hist_stride + l] = id;
+    hist_len[b] = l + 1;
+    out[(int64_t)slot * B + b] = id;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (advance_T) state[0] += 1;
+    state[1] += 1;
+    state[2] = slot + 1;
+  }
+}
+
+template <typename T>
+__global__ void fill_const_kernel(T* p, int64_t n, float v) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = from_f<T>(v);
+}
+
+struct LayerW {
+  void *n1_g = nullptr, *n1_b = nullptr, *wqkv = nullptr, *bqkv = nullptr, *wo = nullptr, *bo = nullptr;
+  void *n2_g = nullptr, *n2_b = nullptr, *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr;
+  void *cK = nullptr, *cV = nullptr;
+};
+
+struct Dest {  // where a logical tensor lives inside the engine's packed buffers
+  void* base = nullptr;
+  int64_t rows = 0, cols = 0, row_stride = 0, col_stride = 1;
+};
+
+struct GraphKey {
+  int B = -1, strategy = -1, splits = -1, n_blocked = -1;
+  float topP = 0, temperature = 0, penalty = 0;
+  uint64_t seed = 0, seq_base = 0, blocked_hash = 0;
+  bool operator==(const GraphKey& o) const {
+    return B == o.B && strategy == o.strategy && splits == o.splits && n_blocked == o.n_blocked && topP == o.topP &&
+           temperature == o.temperature && penalty == o.penalty && seed == o.seed && seq_base == o.seq_base &&
+           blocked_hash == o.blocked_hash;
+  }
+};
+
+struct Gpt {
+  TSB200GptConfig c;
+  DeviceState* st = nullptr;
+  cudaStream_t s = nullptr;
+  int es = 4;  // element size of the model dtype
+  int Nqkv = 0, glu = 0;
+  void *E = nullptr, *PE = nullptr, *nf_g = nullptr, *nf_b = nullptr, *head_w = nullptr, *head_b = nullptr;
+  int pe_rows = 0;
+  std::vector<LayerW> L;
+  float2* rope_tab = nullptr;
+  // activations
+  int64_t act_rows = 0;
+  float* x = nullptr;
+  void *h = nullptr, *qkv = nullptr, *attn = nullptr, *ffn = nullptr;
+  float* xl = nullptr;
+  void* hl = nullptr;
+  float *logits = nullptr, *probs = nullptr, *u = nullptr;
+  int *ids_in = nullptr, *ids_cur = nullptr, *ids_new = nullptr, *hist = nullptr, *hist_len = nullptr, *blocked = nullptr;
+  int* state = nullptr;
+  int* out_dev = nullptr;
+  void *lin_ws = nullptr, *attn_ws = nullptr, *topp_ws = nullptr;
+  int64_t lin_ws_bytes = 0, attn_ws_bytes = 0, topp_ws_bytes = 0;
+  int n_blocked = 0, blocked_cap = 0;
+  int B = 0, T = 0;
+  uint32_t step = 0;
+  bool probs_valid = false;
+  // graph
+  cudaGraphExec_t gexec = nullptr;
+  GraphKey gkey;
+  long long graph_nodes = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = 0.0f;
+  long long last_launches = 0;
+  std::vector<void*> allocs;
+};
+
+static int dev_alloc(Gpt* g, void** p, int64_t bytes, bool zero = true) {
+  if (bytes <= 0) bytes = 256;
+  cudaError_t e = cudaMalloc(p, (size_t)bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    TSB_FAIL("OOM: cudaMalloc of %lld bytes failed: %s", (long long)bytes, cudaGetErrorString(e));
+  }
+  if (zero) TSB_CUDA(cudaMemsetAsync(*p, 0, (size_t)bytes, g->s));
+  g->allocs.push_back(*p);
+  return 1;
+}
+
+static int fill_const(Gpt* g, void* p, int64_t n, float v) {
+  if (g->c.dtype == TSB200_F32) fill_const_kernel<float><<<(int)((n + 255) / 256), 256, 0, g->s>>>((float*)p, n, v);
+  else fill_const_kernel<__half><<<(int)((n + 255) / 256), 256, 0, g->s>>>((__half*)p, n, v);
+  count_launch(g->c.device);
+  return check_launch("fill_const");
+}
+
+static bool starts_with(const std::string& s, const char* p) { return s.compare(0, std::strlen(p), p) == 0; }
+static bool ends_with(const std::string& s, const char* p) {
+  const size_t n = std::strlen(p);
+  return s.size() >= n && s.compare(s.size() - n, n, p) == 0;
+}
+
+// Maps a reference weight key to its place in the engine's buffers.
+static int resolve(Gpt* g, const std::string& name, Dest* out) {
+  const TSB200GptConfig& c = g->c;
+  const int64_t d = c.d, F = c.F, V = c.V, Hd = (int64_t)c.H * c.hd, KVd = (int64_t)c.Hkv * c.hd;
+  auto set = [&](void* base, int64_t rows, int64_t cols, int64_t rs, int64_t cs) {
+    out->base = base; out->rows = rows; out->cols = cols; out->row_stride = rs; out->col_stride = cs;
+    return 1;
+  };
+  auto off = [&](void* base, int64_t elems) { return (void*)((char*)base + elems * g->es); };
+  if (name == "TgtEmbeddings") return set(g->E, V, d, d, 1);
+  if (name == "PosEmbedding") {
+    TSB_CHECK(g->PE, "PosEmbedding given but the model's pe_type is not APE");
+    return set(g->PE, g->pe_rows, d, d, 1);
+  }
+  if (name == "GPTDecoder.layerNorm.m_alpha") return set(g->nf_g, 1, d, d, 1);
+  if (name == "GPTDecoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
+  if (name == "FeedForward_Decoder_0.m_Whd") return set(g->head_w, d, V, V, 1);
+  if (name == "FeedForward_Decoder_0.m_Bd") return set(g->head_b, 1, V, V, 1);
+  TSB_CHECK(starts_with(name, "GPTDecoder."), "unknown weight name '%s'", name.c_str());
+  const std::string rest = name.substr(11);
+  const size_t us = rest.find('_'), dot = rest.find('.');
+  TSB_CHECK(us != std::string::npos && dot != std::string::npos && us < dot, "unknown weight name '%s'", name.c_str());
+  const int k = std::atoi(rest.substr(us + 1, dot - us - 1).c_str());
+  TSB_CHECK(k >= 0 && k < c.L, "layer index out of range in '%s'", name.c_str());
+  LayerW& L = g->L[k];
+  const std::string unit = rest.substr(0, us), field = rest.substr(dot + 1);
+  const int64_t Nq = g->Nqkv;
+  if (unit == "SelfAttn") {
+    if (field == "layerNormQ.m_alpha") return set(L.n1_g, 1, d, d, 1);
+    if (field == "layerNormQ.m_beta") return set(L.n1_b, 1, d, d, 1);
+    if (field == "W0") return set(L.wo, Hd, d, d, 1);
+    if (field == "b0") return set(L.bo, 1, d, d, 1);
+    if (c.attn_type == 0) {
+      if (field == "QKV") return set(L.wqkv, d, Nq, Nq, 1);
+      if (field == "QKVb") return set(L.bqkv, 1, Nq, Nq, 1);
+    } else {
+      if (field == "Q") return set(L.wqkv, d, Hd, Nq, 1);
+      if (field == "Qb") return set(L.bqkv, 1, Hd, Nq, 1);
+      if (field == "K") return set(off(L.wqkv, Hd), d, KVd, Nq, 1);
+      if (field == "Kb") return set(off(L.bqkv, Hd), 1, KVd, Nq, 1);
+      if (field == "V") return set(off(L.wqkv, Hd + KVd), d, KVd, Nq, 1);
+      if (field == "Vb") return set(off(L.bqkv, Hd + KVd), 1, KVd, Nq, 1);
+    }
+  } else if (unit == "PosFFN") {
+    if (field == "layerNorm2.m_alpha") return set(L.n2_g, 1, d, d, 1);
+    if (field == "layerNorm2.m_beta") return set(L.n2_b, 1, d, d, 1);
+    const int64_t w1c = g->glu ? 2 * F : F, cs = g->glu ? 2 : 1;
+    if (field == "feedForwardLayer1.m_Whd") return set(L.w1, d, F, w1c, cs);
+    if (field == "feedForwardLayer1.m_Bd") return set(L.b1, 1, F, w1c, cs);
+    if (g->glu && field == "feedForwardLayer3.m_Whd") return set(off(L.w1, 1), d, F, w1c, cs);
+    if (g->glu && field == "feedForwardLayer3.m_Bd") return set(off(L.b1, 1), 1, F, w1c, cs);
+    if (field == "feedForwardLayer2.m_Whd") return set(L.w2, F, d, d, 1);
+    if (field == "feedForwardLayer2.m_Bd") return set(L.b2, 1, d, d, 1);
+  }
+  TSB_FAIL("unknown weight name '%s'", name.c_str());
+}
+
+static int copy_into(Gpt* g, const Dest& dst, const void* src_dev, int src_dtype) {
+  TSB200Tensor r{}, sv{};
+  r.data = dst.base; r.dtype = g->c.dtype; r.ndim = 2;
+  r.sizes[0] = dst.rows; r.sizes[1] = dst.cols; r.strides[0] = dst.row_stride; r.strides[1] = dst.col_stride;
+  sv.data = const_cast<void*>(src_dev); sv.dtype = src_dtype; sv.ndim = 2;
+  sv.sizes[0] = dst.rows; sv.sizes[1] = dst.cols; sv.strides[0] = dst.cols; sv.strides[1] = 1;
+  return TSB200_Copy(g->c.device, &r, &sv, g->s);
+}
+
+static std::vector<std::string> weight_names(const Gpt* g, bool biases, bool norms, bool matrices) {
+  const TSB200GptConfig& c = g->c;
+  std::vector<std::string> v;
+  auto add = [&](bool on, const std::string& s) { if (on) v.push_back(s); };
+  add(matrices, "TgtEmbeddings");
+  for (int k = 0; k < c.L; ++k) {
+    const std::string a = "GPTDecoder.SelfAttn_" + std::to_string(k) + ".", f = "GPTDecoder.PosFFN_" + std::to_string(k) + ".";
+    add(norms, a + "layerNormQ.m_alpha");
+    if (c.norm_type == 0) add(norms, a + "layerNormQ.m_beta");
+    if (c.attn_type == 0) {
+      add(matrices, a + "QKV");
+      add(biases, a + "QKVb");
+    } else {
+      add(matrices, a + "Q"); add(biases, a + "Qb");
+      add(matrices, a + "K"); add(biases, a + "Kb");
+      add(matrices, a + "V"); add(biases, a + "Vb");
+    }
+    add(matrices, a + "W0");
+    add(biases, a + "b0");
+    add(norms, f + "layerNorm2.m_alpha");
+    if (c.norm_type == 0) add(norms, f + "layerNorm2.m_beta");
+    add(matrices, f + "feedForwardLayer1.m_Whd"); add(biases, f + "feedForwardLayer1.m_Bd");
+    if (g->glu) { add(matrices, f + "feedForwardLayer3.m_Whd"); add(biases, f + "feedForwardLayer3.m_Bd"); }
+    add(matrices, f + "feedForwardLayer2.m_Whd"); add(biases, f + "feedForwardLayer2.m_Bd");
+  }
+  add(norms, "GPTDecoder.layerNorm.m_alpha");
+  if (c.norm_type == 0) add(norms, "GPTDecoder.layerNorm.m_beta");
+  add(matrices, "FeedForward_Decoder_0.m_Whd");
+  add(biases, "FeedForward_Decoder_0.m_Bd");
+  return v;
+}
+
+static int ensure_act(Gpt* g, int64_t rows) {
+  if (rows <= g->act_rows) return 1;
+  const TSB200GptConfig& c = g->c;
+  TSB_CUDA(cudaStreamSynchronize(g->s));
+  auto re = [&](void** p, int64_t bytes) -> int {
+    if (*p) {
+      for (auto& a : g->allocs) if (a == *p) a = nullptr;
+      TSB_CUDA(cudaFree(*p));
+      *p = nullptr;
+    }
+    return dev_alloc(g, p, bytes, false);
+  };
+  const int64_t Hd = (int64_t)c.H * c.hd;
+  TSB_TRY(re((void**)&g->x, rows * c.d * 4));
+  TSB_TRY(re(&g->h, rows * c.d * g->es));
+  TSB_TRY(re(&g->qkv, rows * g->Nqkv * g->es));
+  TSB_TRY(re(&g->attn, rows * Hd * g->es));
+  TSB_TRY(re(&g->ffn, rows * c.F * g->es));
+  g->act_rows = rows;
+  return 1;
+}
+
+static Epilogue make_ep(const void* bias, const float* residual, void* y, float* y32, int act, int glu) {
+  Epilogue e{};
+  e.bias = bias; e.residual = residual; e.y = y32 ? nullptr : y; e.y32 = y32; e.act = act; e.glu = glu;
+  return e;
+}
+
+// One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
+// With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
+static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
+  const TSB200GptConfig& c = g->c;
+  const int dev = c.device, dt = c.dtype, d = c.d, rows = B * S;
+  const int* dT = use_state ? g->state : nullptr;
+  const int Hd = c.H * c.hd, KVd = c.Hkv * c.hd;
+  const int pe_mode = (c.pe_type == 1) ? (c.ape_decode_pos0 ? 1 : 2) : 0;
+  const float sf = (float)std::sqrt((double)d);
+  {
+    const int gsz = rows < g->st->sm_count * 8 ? rows : g->st->sm_count * 8;
+    const int* ids = (S == 1 && use_state) ? g->ids_cur : g->ids_in;
+    if (dt == TSB200_F32)
+      embed_kernel<float><<<gsz, 256, 0, g->s>>>(g->x, (const float*)g->E, (const float*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT);
+    else
+      embed_kernel<__half><<<gsz, 256, 0, g->s>>>(g->x, (const __half*)g->E, (const __half*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT);
+    count_launch(dev);
+    TSB_TRY(check_launch("embed"));
+  }
+  const int act = c.act;
+  for (int k = 0; k < c.L; ++k) {
+    LayerW& L = g->L[k];
+    TSB_TRY(launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
+    TSB_TRY(launch_linear(dev, g->st, dt, g->h, L.wqkv, rows, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    void* qp = g->qkv;
+    void* kp = (char*)g->qkv + (int64_t)Hd * g->es;
+    void* vp = (char*)g->qkv + (int64_t)(Hd + KVd) * g->es;
+    TSB_TRY(launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
+    TSB_TRY(launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
+    TSB_TRY(launch_linear(dev, g->st, dt, g->attn, L.wo, rows, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    TSB_TRY(launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n2_g, c.norm_type == 0 ? L.n2_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
+    TSB_TRY(launch_linear(dev, g->st, dt, g->h, L.w1, rows, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu), g->lin_ws, g->lin_ws_bytes, g->s));
+    TSB_TRY(launch_linear(dev, g->st, dt, g->ffn, L.w2, rows, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+  }
+  const float* xlast = g->x;
+  if (S > 1) {
+    gather_last_kernel<<<B, 256, 0, g->s>>>(g->xl, g->x, B, S, d);
+    count_launch(dev);
+    TSB_TRY(check_launch("gather_last"));
+    xlast = g->xl;
+  }
+  TSB_TRY(launch_norm_residual(dev, g->st, dt, g->hl, const_cast<float*>(xlast), nullptr, g->nf_g, c.norm_type == 0 ? g->nf_b : nullptr, c.norm_type, c.eps, B, d, g->s));
+  TSB_TRY(launch_linear(dev, g->st, dt, g->hl, g->head_w, B, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+  return 1;
+}
+
+// logits -> id (greedy or top-p), then commit: feed back, history, output slot, counters.
+static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool use_state, bool advance_T) {
+  const TSB200GptConfig& c = g->c;
+  const int dev = c.device;
+  const bool sampling = opt->strategy == 1;
+  const int use_temp = (sampling && opt->temperature != 1.0f) ? 1 : 0;
+  TSB_TRY(launch_softmax_argmax(dev, g->st, g->ids_new, sampling ? g->probs : nullptr, g->logits, B, c.V, opt->temperature, use_temp, g->blocked, g->n_blocked, g->s));
+  if (sampling) {
+    TSB_TRY(launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state + 1 : nullptr, g->s));
+    TSB_TRY(launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
+  }
+  commit_kernel<<<1, 256, 0, g->s>>>(g->ids_cur, g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0);
+  count_launch(dev);
+  return check_launch("commit");
+}
+
+static uint64_t hash_blocked(const int32_t* b, int n) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  for (int i = 0; i < n; ++i) {
+    h ^= (uint32_t)b[i];
+    h *= 0x100000001b3ull;
+  }
+  return h;
+}
+
+static int upload_blocked(Gpt* g, const TSB200DecodingOptions* opt) {
+  TSB_CHECK(opt->n_blocked >= 0 && (opt->n_blocked == 0 || opt->blocked), "decoding options: blocked list is null");
+  if (opt->n_blocked > g->blocked_cap) {
+    void* p = nullptr;
+    TSB_TRY(dev_alloc(g, &p, (int64_t)opt->n_blocked * 4 + 256, false));
+    g->blocked = (int*)p;
+    g->blocked_cap = opt->n_blocked + 64;
+    if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  }
+  if (opt->n_blocked) TSB_CUDA(cudaMemcpyAsync(g->blocked, opt->blocked, (size_t)opt->n_blocked * 4, cudaMemcpyHostToDevice, g->s));
+  g->n_blocked = opt->n_blocked;
+  return 1;
+}
+
+static int set_state(Gpt* g, int out_slot) {
+  const int hst[3] = {g->T, (int)g->step, out_slot};
+  TSB_CUDA(cudaMemcpyAsync(g->state, hst, sizeof(hst), cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));  // hst is on the stack
+  return 1;
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
+  TSB_CHECK(cfg && out, "gpt_create: null argument");
+  *out = nullptr;
+  const TSB200GptConfig& c = *cfg;
+  TSB_CHECK(c.L > 0 && c.d > 0 && c.H > 0 && c.hd > 0 && c.F > 0 && c.V > 0, "gpt_create: bad dimensions");
+  TSB_CHECK(c.dtype == TSB200_F32 || c.dtype == TSB200_F16, "gpt_create: dtype must be F32 or F16");
+  TSB_CHECK(c.norm_type == 0 || c.norm_type == 1, "gpt_create: norm_type must be 0 or 1");
+  TSB_CHECK(c.act >= 0 && c.act <= 5, "gpt_create: unknown activation %d", c.act);
+  TSB_CHECK(c.pe_type >= 0 && c.pe_type <= 2, "gpt_create: unknown position embedding type");
+  TSB_CHECK(c.attn_type == 0 || c.attn_type == 1, "gpt_create: attn_type must be 0 (MHA) or 1 (GQA)");
+  TSB_CHECK(c.tp_size <= 1, "gpt_create: tensor parallel degree %d is not supported by this build", c.tp_size);
+  TSB_CHECK(c.max_batch > 0 && c.max_batch <= 1024 && c.max_tokens > 0, "gpt_create: bad cache capacity");
+  DeviceState* st;
+  TSB_TRY(use_device(c.device, &st));
+  Gpt* g = new Gpt();
+  g->c = c;
+  if (c.attn_type == 0) g->c.Hkv = c.H;
+  if (g->c.Hkv <= 0 || g->c.H % g->c.Hkv != 0) {
+    delete g;
+    TSB_FAIL("gpt_create: H must be divisible by Hkv");
+  }
+  g->st = st;
+  g->s = st->stream;
+  g->es = c.dtype == TSB200_F16 ? 2 : 4;
+  g->glu = (c.act == TSB200_ACT_GLU_NOACT || c.act == TSB200_ACT_SWIGLU) ? 1 : 0;
+  const TSB200GptConfig& cc = g->c;
+  const int64_t d = cc.d, F = cc.F, V = cc.V, Hd = (int64_t)cc.H * cc.hd, KVd = (int64_t)cc.Hkv * cc.hd;
+  g->Nqkv = (int)(Hd + 2 * KVd);
+  const int es = g->es;
+  auto fail = [&]() { TSB200_GptDestroy(g); return 0; };
+#define G_ALLOC(p, bytes) if (!dev_alloc(g, (void**)&(p), (bytes))) return fail()
+  G_ALLOC(g->E, V * d * es);
+  if (cc.pe_type == 1) {
+    g->pe_rows = cc.max_tokens + 2;  // rows = max length + 2 as in the reference (Applications/GPT.cs:128)
+    G_ALLOC(g->PE, (int64_t)g->pe_rows * d * es);
+  }
+  G_ALLOC(g->nf_g, d * es);
+  G_ALLOC(g->nf_b, d * es);
+  G_ALLOC(g->head_w, d * V * es);
+  G_ALLOC(g->head_b, V * es);
+  g->L.resize(cc.L);
+  const int64_t cache_elems = (int64_t)cc.max_batch * cc.Hkv * cc.max_tokens * cc.hd;
+  for (int k = 0; k < cc.L; ++k) {
+    LayerW& L = g->L[k];
+    G_ALLOC(L.n1_g, d * es); G_ALLOC(L.n1_b, d * es); G_ALLOC(L.n2_g, d * es); G_ALLOC(L.n2_b, d * es);
+    G_ALLOC(L.wqkv, d * g->Nqkv * es); G_ALLOC(L.bqkv, (int64_t)g->Nqkv * es);
+    G_ALLOC(L.wo, Hd * d * es); G_ALLOC(L.bo, d * es);
+    G_ALLOC(L.w1, d * F * es * (g->glu ? 2 : 1)); G_ALLOC(L.b1, F * es * (g->glu ? 2 : 1));
+    G_ALLOC(L.w2, F * d * es); G_ALLOC(L.b2, d * es);
+    G_ALLOC(L.cK, cache_elems * es); G_ALLOC(L.cV, cache_elems * es);
+    if (!fill_const(g, L.n1_g, d, 1.0f) || !fill_const(g, L.n2_g, d, 1.0f)) return fail();
+  }
+  if (!fill_const(g, g->nf_g, d, 1.0f)) return fail();
+  if (cc.pe_type == 2) {
+    G_ALLOC(g->rope_tab, (int64_t)cc.max_tokens * (cc.hd / 2) * sizeof(float2));
+    if (!launch_rope_table(cc.device, st, g->rope_tab, cc.max_tokens, cc.hd, (double)cc.rope_base, g->s)) return fail();
+  }
+  const int MB = cc.max_batch;
+  G_ALLOC(g->xl, (int64_t)MB * d * 4);
+  G_ALLOC(g->hl, (int64_t)MB * d * es);
+  G_ALLOC(g->logits, (int64_t)MB * V * 4);
+  G_ALLOC(g->probs, (int64_t)MB * V * 4);
+  G_ALLOC(g->u, (int64_t)MB * 4);
+  G_ALLOC(g->ids_cur, (int64_t)MB * 4);
+  G_ALLOC(g->ids_new, (int64_t)MB * 4);
+  G_ALLOC(g->hist, (int64_t)MB * cc.max_tokens * 4);
+  G_ALLOC(g->hist_len, (int64_t)MB * 4);
+  G_ALLOC(g->state, 64);
+  G_ALLOC(g->out_dev, (int64_t)MB * (cc.max_tokens + 1) * 4);
+  G_ALLOC(g->blocked, 1024);
+  g->blocked_cap = 256;
+  int64_t maxN = V > 2 * F ? V : 2 * F;
+  if (g->Nqkv > maxN) maxN = g->Nqkv;
+  g->lin_ws_bytes = linear_workspace_bytes(8, (int)(F > d ? F : d), (int)maxN);
+  G_ALLOC(g->lin_ws, g->lin_ws_bytes);
+  g->attn_ws_bytes = attn_workspace_bytes(MB, cc.H, cc.hd, cc.max_tokens);
+  G_ALLOC(g->attn_ws, g->attn_ws_bytes);
+  g->topp_ws_bytes = TSB200_TopPWorkspaceBytes(MB, cc.V);
+  G_ALLOC(g->topp_ws, g->topp_ws_bytes);
+#undef G_ALLOC
+  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device)) return fail();
+  if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) {
+    set_last_error("gpt_create: cudaEventCreate failed");
+    return fail();
+  }
+  if (!ensure_act(g, MB)) return fail();
+  if (cudaStreamSynchronize(g->s) != cudaSuccess) {
+    set_last_error("gpt_create: initialisation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return fail();
+  }
+  *out = g;
+  return 1;
+}
+
+int TSB200_GptDestroy(void* h) {
+  if (!h) return 1;
+  Gpt* g = (Gpt*)h;
+  cudaSetDevice(g->c.device);
+  if (g->s) cudaStreamSynchronize(g->s);
+  if (g->gexec) cudaGraphExecDestroy(g->gexec);
+  if (g->ev0) cudaEventDestroy(g->ev0);
+  if (g->ev1) cudaEventDestroy(g->ev1);
+  for (void* p : g->allocs)
+    if (p) cudaFree(p);
+  delete g;
+  return 1;
+}
+
+int TSB200_GptSetWeight(void* h, const char* name, const void* data, int dtype, int64_t rows, int64_t cols, int on_device) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && name && data, "gpt_set_weight: null argument");
+  TSB_CHECK(dtype == TSB200_F32 || dtype == TSB200_F16, "gpt_set_weight: data must be F32 or F16");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  Dest dst;
+  TSB_TRY(resolve(g, name, &dst));
+  TSB_CHECK(rows * cols == dst.rows * dst.cols && (cols == dst.cols || rows * cols == dst.cols),
+            "gpt_set_weight: '%s' expects [%lld, %lld], got [%lld, %lld]", name, (long long)dst.rows, (long long)dst.cols,
+            (long long)rows, (long long)cols);
+  const int64_t bytes = rows * cols * (dtype == TSB200_F16 ? 2 : 4);
+  const void* src = data;
+  void* tmp = nullptr;
+  if (!on_device) {
+    cudaError_t e = cudaMalloc(&tmp, (size_t)bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      TSB_FAIL("OOM: staging buffer of %lld bytes: %s", (long long)bytes, cudaGetErrorString(e));
+    }
+    if (cudaMemcpyAsync(tmp, data, (size_t)bytes, cudaMemcpyHostToDevice, g->s) != cudaSuccess) {
+      cudaFree(tmp);
+      TSB_FAIL("gpt_set_weight: host to device copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    src = tmp;
+  }
+  int ok = copy_into(g, dst, src, dtype);
+  if (ok && cudaStreamSynchronize(g->s) != cudaSuccess) {
+    set_last_error("gpt_set_weight: %s", cudaGetErrorString(cudaGetLastError()));
+    ok = 0;
+  }
+  if (tmp) cudaFree(tmp);
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  return ok;
+}
+
+int TSB200_GptGetWeightPtr(void* h, const char* name, void** ptr, int64_t* rows, int64_t* cols) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && name && ptr, "gpt_get_weight_ptr: null argument");
+  Dest dst;
+  TSB_TRY(resolve(g, name, &dst));
+  TSB_CHECK(dst.col_stride == 1 && dst.row_stride == dst.cols, "gpt_get_weight_ptr: '%s' is stored packed with other tensors", name);
+  *ptr = dst.base;
+  if (rows) *rows = dst.rows;
+  if (cols) *cols = dst.cols;
+  return 1;
+}
+
+int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_fill_synthetic: null engine");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  std::vector<std::string> names = weight_names(g, bias_std > 0.0f, false, true);
+  if (g->PE) names.push_back("PosEmbedding");
+  int64_t max_elems = 0;
+  for (auto& n : names) {
+    Dest dst;
+    TSB_TRY(resolve(g, n, &dst));
+    if (dst.rows * dst.cols > max_elems) max_elems = dst.rows * dst.cols;
+  }
+  void* tmp = nullptr;
+  cudaError_t e = cudaMalloc(&tmp, (size_t)max_elems * g->es);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    TSB_FAIL("OOM: synthetic staging buffer: %s", cudaGetErrorString(e));
+  }
+  int ok = 1;
+  for (auto& n : names) {
+    Dest dst;
+    ok = resolve(g, n, &dst);
+    if (!ok) break;
+    const bool is_bias = ends_with(n, "m_Bd") || ends_with(n, "QKVb") || ends_with(n, ".Qb") || ends_with(n, ".Kb") ||
+                         ends_with(n, ".Vb") || ends_with(n, ".b0");
+    ok = launch_synthetic(g->c.device, g->st, tmp, g->c.dtype, dst.rows * dst.cols, seed, fnv1a64(n.c_str()),
+                          is_bias ? bias_std : std, g->s);
+    if (!ok) break;
+    ok = copy_into(g, dst, tmp, g->c.dtype);
+    if (!ok) break;
+  }
+  if (ok && cudaStreamSynchronize(g->s) != cudaSuccess) {
+    set_last_error("gpt_fill_synthetic: %s", cudaGetErrorString(cudaGetLastError()));
+    ok = 0;
+  }
+  cudaFree(tmp);
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  return ok;
+}
+
+int TSB200_GptSetAllReduce(void* h, TSB200AllReduceFn fn, void* user) {
+  (void)h; (void)fn; (void)user;
+  TSB_FAIL("gpt_set_all_reduce: tensor parallelism is not supported by this build");
+}
+
+int TSB200_GptReset(void* h) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_reset: null engine");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  g->B = 0;
+  g->T = 0;
+  g->step = 0;
+  g->probs_valid = false;
+  TSB_CUDA(cudaMemsetAsync(g->hist_len, 0, (size_t)g->c.max_batch * 4, g->s));
+  return 1;
+}
+
+int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ids && opt, "gpt_prefill: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(g->T == 0, "gpt_prefill: the cache is not empty (call TSB200_GptReset first)");
+  TSB_CHECK(B > 0 && B <= c.max_batch, "gpt_prefill: batch %d exceeds capacity %d", B, c.max_batch);
+  TSB_CHECK(S > 0 && S < c.max_tokens, "OOM: prompt of %d tokens exceeds the KV-cache capacity %d", S, c.max_tokens);
+  for (int64_t i = 0; i < (int64_t)B * S; ++i) TSB_CHECK(ids[i] >= 0 && ids[i] < c.V, "gpt_prefill: token id %d out of range", ids[i]);
+  TSB_TRY(ensure_act(g, (int64_t)B * S));
+  void* ids_dev = nullptr;
+  TSB_CUDA(cudaMalloc(&ids_dev, (size_t)B * S * 4));
+  g->ids_in = (int*)ids_dev;
+  int ok = 1;
+  do {
+    if (cudaMemcpyAsync(ids_dev, ids, (size_t)B * S * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: id upload failed"); break; }
+    // history = the prompt (the reference passes the whole sequence as decodedSequence: Decoder.cs:761)
+    if (cudaMemcpy2DAsync(g->hist, (size_t)c.max_tokens * 4, ids_dev, (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history copy failed"); break; }
+    std::vector<int> lens(B, S);
+    if (cudaMemcpyAsync(g->hist_len, lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history length upload failed"); break; }
+    cudaStreamSynchronize(g->s);
+    g->B = B;
+    g->step = 0;
+    if (!(ok = upload_blocked(g, opt))) break;
+    if (!(ok = set_state(g, 0))) break;
+    const long long l0 = g->st->launches;
+    cudaEventRecord(g->ev0, g->s);
+    if (!(ok = enqueue_forward(g, B, S, 0, false, 1))) break;
+    g->T = S;
+    if (!(ok = enqueue_sample(g, B, opt, true, false))) break;
+    cudaEventRecord(g->ev1, g->s);
+    if (cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: %s", cudaGetErrorString(cudaGetLastError())); break; }
+    cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1);
+    g->last_launches = g->st->launches - l0;
+    g->step = 1;
+    g->probs_valid = (opt->strategy == 1);
+    if (out_ids && cudaMemcpy(out_ids, g->out_dev, (size_t)B * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: id download failed"); break; }
+  } while (0);
+  g->ids_in = nullptr;
+  cudaFree(ids_dev);
+  return ok;
+}
+
+int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int stop_on_eos, int32_t* out_ids, int* steps_done) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && opt, "gpt_decode: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(g->T > 0 && g->B > 0, "gpt_decode: prefill first");
+  TSB_CHECK(n_steps >= 0, "gpt_decode: negative step count");
+  // the step that generates token n appends position T + n - 1
+  TSB_CHECK(g->T + n_steps <= c.max_tokens, "OOM: KV-cache capacity %d exceeded (%d cached + %d steps)", c.max_tokens, g->T, n_steps);
+  if (steps_done) *steps_done = 0;
+  if (n_steps == 0) return 1;
+  const int B = g->B;
+  TSB_TRY(upload_blocked(g, opt));
+  TSB_TRY(set_state(g, 0));
+  // split count for the attention kernel: fixed per graph, chosen for the longest cache this call reaches
+  int Tp = 256;
+  while (Tp < g->T + n_steps) Tp <<= 1;
+  GraphKey key;
+  key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, B, c.H, c.Hkv, Tp);
+  key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
+  key.topP = opt->topP; key.temperature = opt->temperature; key.penalty = opt->repeatPenalty;
+  key.seed = opt->seed; key.seq_base = opt->seq_base;
+  if (!g->gexec || !(g->gkey == key)) {
+    if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+    cudaGraph_t graph = nullptr;
+    const long long l0 = g->st->launches;
+    TSB_CUDA(cudaStreamBeginCapture(g->s, cudaStreamCaptureModeThreadLocal));
+    int ok = enqueue_forward(g, B, 1, g->T, true, key.splits) && enqueue_sample(g, B, opt, true, true);
+    cudaError_t e = cudaStreamEndCapture(g->s, &graph);
+    if (!ok || e != cudaSuccess) {
+      if (graph) cudaGraphDestroy(graph);
+      cudaGetLastError();
+      if (ok) set_last_error("gpt_decode: graph capture failed: %s", cudaGetErrorString(e));
+      return 0;
+    }
+    g->graph_nodes = g->st->launches - l0;
+    g->st->launches = l0;  // captured launches have not run yet; replays are counted below
+    e = cudaGraphInstantiate(&g->gexec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+      g->gexec = nullptr;
+      TSB_FAIL("gpt_decode: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    }
+    g->gkey = key;
+  }
+  std::vector<int> last(B);
+  int done = 0;
+  TSB_CUDA(cudaEventRecord(g->ev0, g->s));
+  for (int i = 0; i < n_steps; ++i) {
+    TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
+    count_launch(c.device, g->graph_nodes);
+    ++done;
+    if (stop_on_eos) {
+      // the reference reads the ids back every token to test its stop rule (Decoder.cs:769-782, GPT.cs:300-303)
+      TSB_CUDA(cudaMemcpyAsync(last.data(), g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
+      TSB_CUDA(cudaStreamSynchronize(g->s));
+      bool all_eos = true;
+      for (int b = 0; b < B; ++b) all_eos = all_eos && (last[b] == 0);
+      if (all_eos) break;
+    }
+  }
+  TSB_CUDA(cudaEventRecord(g->ev1, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));
+  TSB_CUDA(cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1));
+  g->last_launches = g->graph_nodes * done;
+  g->T += done;
+  g->step += (uint32_t)done;
+  g->probs_valid = (opt->strategy == 1);
+  if (steps_done) *steps_done = done;
+  if (out_ids) {
+    std::vector<int> tmp((size_t)done * B);
+    TSB_CUDA(cudaMemcpy(tmp.data(), g->out_dev, tmp.size() * 4, cudaMemcpyDeviceToHost));
+    for (int b = 0; b < B; ++b)
+      for (int i = 0; i < n_steps; ++i) out_ids[(int64_t)b * n_steps + i] = i < done ? tmp[(size_t)i * B + b] : 0;
+  }
+  return 1;
+}
+
+int TSB200_GptGetLogits(void* h, float* logits, float* probs) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_get_logits: null engine");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  TSB_CHECK(g->B > 0, "gpt_get_logits: nothing has run yet");
+  const size_t n = (size_t)g->B * g->c.V;
+  if (logits) TSB_CUDA(cudaMemcpy(logits, g->logits, n * 4, cudaMemcpyDeviceToHost));
+  if (probs) {
+    if (!g->probs_valid) {
+      TSB_TRY(launch_softmax_argmax(g->c.device, g->st, nullptr, g->probs, g->logits, g->B, g->c.V, 1.0f, 0, g->blocked, g->n_blocked, g->s));
+      TSB_CUDA(cudaStreamSynchronize(g->s));
+    }
+    TSB_CUDA(cudaMemcpy(probs, g->probs, n * 4, cudaMemcpyDeviceToHost));
+  }
+  return 1;
+}
+
+int TSB200_GptCacheLength(void* h, int* T) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && T, "gpt_cache_length: null argument");
+  *T = g->T;
+  return 1;
+}
+
+int TSB200_GptLastTiming(void* h, float* ms, int64_t* launches) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_last_timing: null engine");
+  if (ms) *ms = g->last_ms;
+  if (launches) *launches = g->last_launches;
+  return 1;
+}
+
+int TSB200_GptStream(void* h, void** stream) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && stream, "gpt_stream: null argument");
+  *stream = (void*)g->s;
+  return 1;
+}
+
+int TSB200_GptStepBytes(void* h, int B, int T, int64_t* bytes) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && bytes, "gpt_step_bytes: null argument");
+  const TSB200GptConfig& c = g->c;
+  const int64_t d = c.d, F = c.F, V = c.V, Hd = (int64_t)c.H * c.hd, KVd = (int64_t)c.Hkv * c.hd, s = g->es;
+  const int64_t p_attn = d * (Hd + 2 * KVd) + Hd * d;
+  const int64_t p_ffn = (g->glu ? 3 : 2) * d * F;
+  const int64_t b_attn = (Hd + 2 * KVd) + d, b_ffn = (g->glu ? 2 : 1) * F + d;
+  const int64_t n_norm = (c.norm_type == 0 ? 2 : 1) * d * 2;
+  int64_t total = s * (c.L * (p_attn + p_ffn) + d * V);
+  total += s * (c.L * (b_attn + b_ffn + n_norm) + V + (c.norm_type == 0 ? 2 : 1) * d);
+  total += (int64_t)B * c.L * 2 * KVd * T * s;  // KV read
+  total += (int64_t)B * c.L * 2 * KVd * s;      // KV write
+  total += (int64_t)B * d * s;                  // embedding rows
+  total += (int64_t)B * 4;                      // ids out
+  *bytes = total;
+  return 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,448 @@
+// RoPE, fused RoPE + KV-cache append, split-K flash-decode attention and causal prefill attention.
+//
+// Cache layout (this backend's own, laid out for streaming): K and V are both [B, Hkv, Tmax, hd], token-major,
+// un-expanded for GQA — the reference materialises K as [B*H, hd, T] and V as [B*H, T, hd] with the KV heads
+// repeated H/Hkv times and re-copies the whole cache every step (Seq2SeqSharp/Layers/GroupQueryAttention.cs:156-188,
+// TensorSharp/Core/TensorConcatenation.cs:9-45).  Query head h reads KV head h / (H/Hkv).
+//
+// RoPE follows TensorSharp/TensorApplyCPU.cs:1148-1178 (same math as TensorSharp.CUDA/DeviceCode/
+// AdvFuncKernels.cs:1245-1279 without fast-math): interleaved pairs (2i, 2i+1), theta_i = base^(-2i/hd) rounded to
+// float, angle = theta_i * position in float, cos/sin evaluated in double and rounded to float.
+#include "kernels.cuh"
+
+namespace tsb {
+
+__device__ __forceinline__ void rope_cs(int i, int cols, int m, double base, float& c, float& s) {
+  const float theta = (float)pow(base, -2.0 * i / cols);
+  const float tm = theta * (float)m;
+  c = (float)cos((double)tm);
+  s = (float)sin((double)tm);
+}
+
+// Unfused "rope": rows flattened [.., seqLen], position = (row % seqLen) + rowOffset.
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t rows, int cols, int seqLen, int rowOffset,
+                            double base) {
+  const int64_t pairs = rows * (cols / 2);
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t j = p / (cols / 2);
+    const int i = (int)(p % (cols / 2));
+    const int m = (int)(j % seqLen) + rowOffset;
+    float c, s;
+    rope_cs(i, cols, m, base, c, s);
+    const float a = to_f<T>(in[j * cols + 2 * i]), b = to_f<T>(in[j * cols + 2 * i + 1]);
+    out[j * cols + 2 * i] = from_f<T>(a * c - b * s);
+    out[j * cols + 2 * i + 1] = from_f<T>(b * c + a * s);
+  }
+}
+
+// cos/sin table [Tmax, hd/2] (float2) built once per model so the decode path does no transcendental work.
+__global__ void rope_table_kernel(float2* __restrict__ tab, int Tmax, int hd, double base) {
+  const int64_t n = (int64_t)Tmax * (hd / 2);
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(p / (hd / 2)), i = (int)(p % (hd / 2));
+    float c, s;
+    rope_cs(i, hd, m, base, c, s);
+    tab[p] = make_float2(c, s);
+  }
+}
+
+// q [B,S,H,hd] rotated in place; k rotated and stored with v into the cache at positions T0 + s.
+// One thread per pair.  tab may be NULL (then cos/sin are evaluated here).
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int64_t q_rs,
+                                   int64_t kv_rs, T* __restrict__ cK, T* __restrict__ cV, int B, int S, int H, int Hkv, int hd,
+                                   int T0_arg, const int* __restrict__ dT0, int Tmax, int use_rope, double base,
+                                   const float2* __restrict__ tab) {
+  const int T0 = dT0 ? *dT0 : T0_arg;  // the engine keeps the cache length on the device so one CUDA graph serves every step
+  const int hp = hd / 2;
+  const int64_t per_row = (int64_t)(H + 2 * Hkv) * hp;
+  const int64_t n = (int64_t)B * S * per_row;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = p / per_row;  // b*S + s
+    int rem = (int)(p % per_row);
+    const int b = (int)(row / S), s = (int)(row % S);
+    const int pos = T0 + s;
+    if (pos >= Tmax) continue;  // capacity is checked on the host; never write past the cache
+    const int head = rem / hp, i = rem % hp;
+    float c = 1.0f, sn = 0.0f;
+    if (use_rope && head < H + Hkv) {
+      if (tab) {
+        const float2 cs = tab[(int64_t)pos * hp + i];
+        c = cs.x;
+        sn = cs.y;
+      } else {
+        rope_cs(i, hd, pos, base, c, sn);
+      }
+    }
+    if (head < H) {
+      T* qp = q + row * q_rs + (int64_t)head * hd + 2 * i;
+      const float a = to_f<T>(qp[0]), bb = to_f<T>(qp[1]);
+      if (use_rope) {
+        qp[0] = from_f<T>(a * c - bb * sn);
+        qp[1] = from_f<T>(bb * c + a * sn);
+      }
+    } else if (head < H + Hkv) {
+      const int g = head - H;
+      const T* kp = k + row * kv_rs + (int64_t)g * hd + 2 * i;
+      const float a = to_f<T>(kp[0]), bb = to_f<T>(kp[1]);
+      T* dst = cK + (((int64_t)b * Hkv + g) * Tmax + pos) * hd + 2 * i;
+      dst[0] = from_f<T>(use_rope ? a * c - bb * sn : a);
+      dst[1] = from_f<T>(use_rope ? bb * c + a * sn : bb);
+    } else {
+      const int g = head - H - Hkv;
+      const T* vp = v + row * kv_rs + (int64_t)g * hd + 2 * i;
+      T* dst = cV + (((int64_t)b * Hkv + g) * Tmax + pos) * hd + 2 * i;
+      dst[0] = vp[0];
+      dst[1] = vp[1];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+// One CTA handles one (sequence b, query position s, group of G query heads sharing a KV head, split of the key
+// range).  Lanes are grouped LPT = hd*sizeof(T)/16 per cached token, each lane owning 16 bytes (EPL elements) of
+// the K row and the V row, so every load is a 128-bit coalesced read and K/V are read exactly once for all G
+// heads.  Each lane group runs an online softmax over its own token subsequence; the partial (max, sum, acc)
+// states are merged through shared memory, and across splits by attn_combine_kernel.
+// Scores: (q . k) * (1/sqrt(hd)) in fp32; softmax in fp32; P.V accumulated in fp32
+// (the reference promotes Q and K to fp32 for the scores as well: MultiHeadAttention.cs:203-221).
+template <typename T> struct Vec16;
+template <> struct Vec16<__half> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ void load(const __half* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void get(float* f) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  float4 raw;
+  __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void get(float* f) const {
+    f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w;
+  }
+};
+
+constexpr int kAttnThreads = 128;
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* __restrict__ out, float* __restrict__ part,
+                                                            const T* __restrict__ q, int64_t q_rs,
+                                                            const T* __restrict__ cK, const T* __restrict__ cV, int S, int H,
+                                                            int Hkv, int hd, int T0_arg, const int* __restrict__ dT0, int Tmax,
+                                                            int splits, float scale) {
+  constexpr int EPL = Vec16<T>::N;
+  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int lpt = hd / EPL;              // lanes per token (power of two, <= 32)
+  const int tpw = 32 / lpt;              // tokens per warp iteration
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int sub = lane / lpt, li = lane % lpt;
+  const int nwarps = kAttnThreads / 32;
+  const int split = blockIdx.x;
+  const int groups_per_kv = (H / Hkv) / G;
+  const int kvh = blockIdx.y / groups_per_kv;
+  const int h0 = kvh * (H / Hkv) + (blockIdx.y % groups_per_kv) * G;
+  const int row = blockIdx.z;  // b*S + s
+  const int b = row / S, s = row % S;
+  const int Tk = min(T0 + s + 1, Tmax);  // causal: keys 0 .. T0+s
+  const int per_split = (Tk + splits - 1) / splits;
+  const int t_beg = split * per_split, t_end = min(Tk, t_beg + per_split);
+
+  float qf[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    Vec16<T> qv;
+    qv.load(q + (int64_t)row * q_rs + (int64_t)(h0 + g) * hd + li * EPL);
+    qv.get(qf[g]);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qf[g][e] *= scale;
+  }
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
+  }
+  const T* Kb = cK + ((int64_t)b * Hkv + kvh) * Tmax * hd + li * EPL;
+  const T* Vb = cV + ((int64_t)b * Hkv + kvh) * Tmax * hd + li * EPL;
+  const int stride = nwarps * tpw;
+  for (int tb = t_beg + w * tpw; tb < t_end; tb += stride) {
+    // all lanes of the warp iterate together (shuffles below need full participation); `live` masks the tail
+    const int t = tb + sub;
+    const bool live = t < t_end;
+    float kf[EPL], vf[EPL];
+    if (live) {
+      Vec16<T> kv, vv;
+      kv.load(Kb + (int64_t)t * hd);
+      vv.load(Vb + (int64_t)t * hd);
+      kv.get(kf);
+      vv.get(vf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) kf[e] = vf[e] = 0.0f;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float d = 0.0f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
+      for (int o = lpt >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (live) {
+        const float mn = fmaxf(m[g], d);
+        const float corr = __expf(m[g] - mn);  // exp(-inf) = 0 on the first token
+        const float p = __expf(d - mn);
+        l[g] = l[g] * corr + p;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+        m[g] = mn;
+      }
+    }
+  }
+  // merge the nwarps*tpw lane-group states through shared memory
+  extern __shared__ float sm[];  // [nstates][G][hd + 2]
+  const int nstates = nwarps * tpw;
+  const int st = w * tpw + sub;
+  const int rec = hd + 2;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float* r = sm + ((int64_t)st * G + g) * rec;
+    if (li == 0) {
+      r[0] = m[g];
+      r[1] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) r[2 + li * EPL + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += kAttnThreads) {
+    const int g = idx / hd, e = idx % hd;
+    float mx = -INFINITY;
+    for (int i = 0; i < nstates; ++i) mx = fmaxf(mx, sm[((int64_t)i * G + g) * rec]);
+    float L = 0.0f, A = 0.0f;
+    for (int i = 0; i < nstates; ++i) {
+      const float* r = sm + ((int64_t)i * G + g) * rec;
+      const float c = (r[0] == -INFINITY) ? 0.0f : __expf(r[0] - mx);
+      L += r[1] * c;
+      A += r[2 + e] * c;
+    }
+    const int h = h0 + g;
+    if (splits == 1) {
+      out[((int64_t)row * H + h) * hd + e] = from_f<T>(L > 0.0f ? A / L : 0.0f);
+    } else {
+      float* pr = part + (((int64_t)row * H + h) * splits + split) * rec;
+      if (e == 0) {
+        pr[0] = mx;
+        pr[1] = L;
+      }
+      pr[2 + e] = A;
+    }
+  }
+}
+
+template <typename T>
+__global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict__ part, int hd, int splits) {
+  const int64_t rh = blockIdx.x;  // row*H + h
+  const int rec = hd + 2;
+  const float* p = part + rh * splits * rec;
+  float mx = -INFINITY;
+  for (int i = 0; i < splits; ++i) mx = fmaxf(mx, p[i * rec]);
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+    float L = 0.0f, A = 0.0f;
+    for (int i = 0; i < splits; ++i) {
+      const float c = (p[i * rec] == -INFINITY) ? 0.0f : __expf(p[i * rec] - mx);
+      L += p[i * rec + 1] * c;
+      A += p[i * rec + 2 + e] * c;
+    }
+    out[rh * hd + e] = from_f<T>(L > 0.0f ? A / L : 0.0f);
+  }
+}
+
+static int pick_splits(DeviceState* st, int B, int Hkv_groups, int T) {
+  // enough CTAs to cover the SMs about twice, at least 256 keys per split
+  const int64_t base = (int64_t)B * Hkv_groups;
+  int s = (int)((2LL * st->sm_count + base - 1) / base);
+  const int max_by_len = (T + 255) / 256;
+  if (s > max_by_len) s = max_by_len;
+  if (s < 1) s = 1;
+  if (s > 64) s = 64;
+  return s;
+}
+
+int64_t attn_workspace_bytes(int B, int H, int hd, int T) {
+  (void)T;
+  return (int64_t)B * H * 64 * (hd + 2) * sizeof(float);
+}
+
+template <typename T>
+static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_t q_rs, const T* cK, const T* cV, int B, int S,
+                         int H, int Hkv, int hd, int T0, const int* dT0, int Tmax, int splits_hint, float* ws, int64_t ws_bytes,
+                         cudaStream_t s) {
+  constexpr int EPL = Vec16<T>::N;
+  const int lpt = hd / EPL;
+  TSB_CHECK(hd % EPL == 0 && lpt >= 1 && lpt <= 32 && (lpt & (lpt - 1)) == 0,
+            "attention: head_dim %d unsupported for this dtype (hd*sizeof(T)/16 must be a power of two <= 32)", hd);
+  TSB_CHECK(H % Hkv == 0, "attention: H must be divisible by Hkv");
+  TSB_CHECK(dT0 || T0 + S <= Tmax, "attention: cache capacity exceeded (%d + %d > %d)", T0, S, Tmax);
+  TSB_CHECK(q_rs % EPL == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)cK % 16) == 0 && ((uintptr_t)cV % 16) == 0,
+            "attention: pointers and row strides must be 16-byte aligned");
+  const int group = H / Hkv;
+  int G = 1;
+  if (group % 8 == 0) G = 8;
+  else if (group % 4 == 0) G = 4;
+  else if (group % 2 == 0) G = 2;
+  const int ygroups = Hkv * (group / G);
+  int splits = (S == 1) ? (splits_hint > 0 ? splits_hint : pick_splits(st, B, ygroups, T0 + 1)) : 1;
+  if (splits > 1) {
+    const int64_t need = (int64_t)B * S * H * splits * (hd + 2) * sizeof(float);
+    if (!ws || ws_bytes < need) splits = 1;
+  }
+  const int tpw = 32 / lpt;
+  const size_t smem = (size_t)(kAttnThreads / 32) * tpw * G * (hd + 2) * sizeof(float);
+  TSB_CHECK(smem <= 48 * 1024, "attention: shared memory need %zu exceeds 48 KB", smem);
+  dim3 grid(splits, ygroups, B * S);
+  const float scale = 1.0f / sqrtf((float)hd);
+#define TSB_ATTN(GG) attn_kernel<T, GG><<<grid, kAttnThreads, smem, s>>>(out, ws, q, q_rs, cK, cV, S, H, Hkv, hd, T0, dT0, Tmax, splits, scale)
+  switch (G) {
+    case 8: TSB_ATTN(8); break;
+    case 4: TSB_ATTN(4); break;
+    case 2: TSB_ATTN(2); break;
+    default: TSB_ATTN(1); break;
+  }
+#undef TSB_ATTN
+  count_launch(device);
+  TSB_TRY(check_launch("attention"));
+  if (splits > 1) {
+    attn_combine_kernel<T><<<B * S * H, hd < 128 ? 64 : 128, 0, s>>>(out, ws, hd, splits);
+    count_launch(device);
+    TSB_TRY(check_launch("attention_combine"));
+  }
+  return 1;
+}
+
+int attn_pick_splits(DeviceState* st, int B, int H, int Hkv, int T) {
+  const int group = H / Hkv;
+  int G = 1;
+  if (group % 8 == 0) G = 8;
+  else if (group % 4 == 0) G = 4;
+  else if (group % 2 == 0) G = 2;
+  return pick_splits(st, B, Hkv * (group / G), T);
+}
+
+int launch_attention(int device, DeviceState* st, int dtype, void* out, const void* q, int64_t q_rs, const void* cK,
+                     const void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0, int Tmax, int splits_hint,
+                     void* ws, int64_t ws_bytes, cudaStream_t s) {
+  if (B == 0 || S == 0) return 1;
+  if (dtype == TSB200_F32)
+    return launch_attn_t<float>(device, st, (float*)out, (const float*)q, q_rs, (const float*)cK, (const float*)cV, B, S, H, Hkv,
+                                hd, T0, dT0, Tmax, splits_hint, (float*)ws, ws_bytes, s);
+  if (dtype == TSB200_F16)
+    return launch_attn_t<__half>(device, st, (__half*)out, (const __half*)q, q_rs, (const __half*)cK, (const __half*)cV, B, S, H,
+                                 Hkv, hd, T0, dT0, Tmax, splits_hint, (float*)ws, ws_bytes, s);
+  TSB_FAIL("attention: unsupported dtype %d", dtype);
+}
+
+int launch_rope_table(int device, DeviceState* st, float2* tab, int Tmax, int hd, double base, cudaStream_t s) {
+  const int64_t n = (int64_t)Tmax * (hd / 2);
+  const int g = (int)((n + 255) / 256 < (int64_t)st->sm_count * 8 ? (n + 255) / 256 : (int64_t)st->sm_count * 8);
+  rope_table_kernel<<<g > 0 ? g : 1, 256, 0, s>>>(tab, Tmax, hd, base);
+  count_launch(device);
+  return check_launch("rope_table");
+}
+
+int launch_rope_append(int device, DeviceState* st, int dtype, void* q, const void* k, const void* v, int64_t q_rs,
+                       int64_t kv_rs, void* cK, void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0,
+                       int Tmax, int use_rope, double base, const float2* tab, cudaStream_t s) {
+  if (B == 0 || S == 0) return 1;
+  TSB_CHECK(hd % 2 == 0, "rope_append: head_dim must be even");
+  TSB_CHECK(dT0 || (T0 >= 0 && T0 + S <= Tmax), "rope_append: cache capacity exceeded (%d + %d > %d)", T0, S, Tmax);
+  const int64_t n = (int64_t)B * S * (H + 2 * Hkv) * (hd / 2);
+  int64_t g = (n + 255) / 256;
+  if (g > (int64_t)st->sm_count * 16) g = (int64_t)st->sm_count * 16;
+  if (dtype == TSB200_F32)
+    rope_append_kernel<float><<<(int)g, 256, 0, s>>>((float*)q, (const float*)k, (const float*)v, q_rs, kv_rs, (float*)cK,
+                                                     (float*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab);
+  else if (dtype == TSB200_F16)
+    rope_append_kernel<__half><<<(int)g, 256, 0, s>>>((__half*)q, (const __half*)k, (const __half*)v, q_rs, kv_rs, (__half*)cK,
+                                                      (__half*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab);
+  else
+    TSB_FAIL("rope_append: unsupported dtype %d", dtype);
+  count_launch(device);
+  return check_launch("rope_append");
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int TSB200_RoPEEx(int device, const TSB200Tensor* result, const TSB200Tensor* src, int seqLen, int rowOffset, float base,
+                  void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_TRY(check_tensor(result, "result"));
+  TSB_TRY(check_tensor(src, "src"));
+  TSB_CHECK(result->dtype == src->dtype, "rope: dtype mismatch");
+  // the reference requires contiguous tensors here (AdvFuncKernels.cs:3198-3205)
+  TSB_CHECK(is_contiguous(result) && is_contiguous(src) && numel(result) == numel(src), "rope: tensors must be contiguous and equal-sized");
+  const int cols = (int)src->sizes[src->ndim - 1];
+  TSB_CHECK(cols > 0 && cols % 2 == 0 && seqLen > 0, "rope: even column count and positive seqLen required");
+  const int64_t rows = numel(src) / cols;
+  if (rows == 0) return 1;
+  cudaStream_t s = pick_stream(st, stream);
+  int64_t g = (rows * (cols / 2) + 255) / 256;
+  if (g > (int64_t)st->sm_count * 8) g = (int64_t)st->sm_count * 8;
+  if (src->dtype == TSB200_F32) rope_kernel<float><<<(int)g, 256, 0, s>>>((float*)result->data, (const float*)src->data, rows, cols, seqLen, rowOffset, (double)base);
+  else if (src->dtype == TSB200_F16) rope_kernel<__half><<<(int)g, 256, 0, s>>>((__half*)result->data, (const __half*)src->data, rows, cols, seqLen, rowOffset, (double)base);
+  else TSB_FAIL("rope: unsupported dtype %d", src->dtype);
+  count_launch(device);
+  return check_launch("rope");
+}
+
+int TSB200_RoPE(int device, const TSB200Tensor* result, const TSB200Tensor* src, int seqLen, int rowOffset, void* stream) {
+  return TSB200_RoPEEx(device, result, src, seqLen, rowOffset, 500000.0f, stream);
+}
+
+int TSB200_RopeAppend(int device, int dtype, void* q, const void* k, const void* v, int64_t q_row_stride,
+                      int64_t kv_row_stride, void* cacheK, void* cacheV, int B, int S, int H, int Hkv, int hd, int T0,
+                      int Tmax, int use_rope, float rope_base, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(q && k && v && cacheK && cacheV, "rope_append: null pointer");
+  return launch_rope_append(device, st, dtype, q, k, v, q_row_stride, kv_row_stride, cacheK, cacheV, B, S, H, Hkv, hd, T0,
+                            nullptr, Tmax, use_rope, (double)rope_base, nullptr, pick_stream(st, stream));
+}
+
+int64_t TSB200_FlashDecodeWorkspaceBytes(int B, int H, int hd, int T) { return attn_workspace_bytes(B, H, hd, T); }
+
+int TSB200_FlashDecode(int device, int dtype, void* out, const void* q, int64_t q_row_stride, const void* cacheK,
+                       const void* cacheV, int B, int H, int Hkv, int hd, int T, int Tmax, void* workspace,
+                       int64_t workspace_bytes, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(out && q && cacheK && cacheV, "flash_decode: null pointer");
+  TSB_CHECK(T >= 1, "flash_decode: empty cache");
+  return launch_attention(device, st, dtype, out, q, q_row_stride, cacheK, cacheV, B, 1, H, Hkv, hd, T - 1, nullptr, Tmax, 0,
+                          workspace, workspace_bytes, pick_stream(st, stream));
+}
+
+int TSB200_PrefillAttention(int device, int dtype, void* out, const void* q, int64_t q_row_stride, const void* cacheK,
+                            const void* cacheV, int B, int S, int H, int Hkv, int hd, int T0, int Tmax, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(out && q && cacheK && cacheV, "prefill_attention: null pointer");
+  return launch_attention(device, st, dtype, out, q, q_row_stride, cacheK, cacheV, B, S, H, Hkv, hd, T0, nullptr, Tmax, 0,
+                          nullptr, 0, pick_stream(st, stream));
+}
+
+}  // extern "C"

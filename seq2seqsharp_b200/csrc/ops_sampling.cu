@@ -1,0 +1,515 @@
+// Softmax, ArgMax, fused logits softmax + ArgMax, Top-P sort-and-sample and the Philox uniform stream.
+//
+//  * "softmax"  : row max -> exp(x - max) -> / sum, fp32 internally (TensorSharp/TensorApplyCPU.cs:1230-1268;
+//                 TensorSharp.CUDA/DeviceCode/AdvFuncKernels.cs:1534-1600).
+//  * "argmax"   : lowest index among equal maxima (TensorApplyCPU.cs:339-360;
+//                 TensorSharp.CUDA/DeviceCode/ReduceDimIndexKernels.cs:25,96-119 scans one thread per row — here a
+//                 whole CTA reduces (value, index) pairs with warp shuffles and the same tie rule).
+//  * Top-P      : device version of the host loop ComputeGraphTensor.TopPSample
+//                 (Seq2SeqSharp/Tools/ComputeGraphTensor.cs:2305-2403); see topp_kernel.
+#include "kernels.cuh"
+
+namespace tsb {
+
+struct ValIdx {
+  float v;
+  int i;
+};
+// "a beats b": strictly greater value, or equal value and lower index (first-max rule).
+__device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ ValIdx warp_argmax(ValIdx x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ValIdx y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  return x;
+}
+__device__ __forceinline__ ValIdx block_argmax(ValIdx x, ValIdx* red /* 32 */) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  x = warp_argmax(x);
+  __syncthreads();
+  if (lane == 0) red[w] = x;
+  __syncthreads();
+  ValIdx r;
+  r.v = -INFINITY;
+  r.i = 0x7fffffff;
+  if (lane < nw) r = red[lane];
+  return warp_argmax(r);
+}
+
+// ------------------------------------------------------------------------------------------------ softmax
+template <typename T>
+__global__ void __launch_bounds__(1024) softmax_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t rows, int cols,
+                                                       int64_t in_row_stride, int64_t in_col_stride) {
+  __shared__ float red[32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* x = in + r * in_row_stride;
+    T* y = out + r * (int64_t)cols;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) mx = fmaxf(mx, to_f<T>(x[(int64_t)i * in_col_stride]));
+    mx = block_max(mx, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) s += expf(to_f<T>(x[(int64_t)i * in_col_stride]) - mx);
+    s = block_sum(s, red);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+      y[i] = from_f<T>(expf(to_f<T>(x[(int64_t)i * in_col_stride]) - mx) / s);
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ argmax
+// src viewed as [outer, n, inner] with the reduced dimension in the middle.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256) argmax_kernel(TO* __restrict__ out, const T* __restrict__ in, int64_t outer, int n,
+                                                     int64_t inner, int64_t so, int64_t sn, int64_t si) {
+  __shared__ ValIdx red[32];
+  for (int64_t r = blockIdx.x; r < outer * inner; r += gridDim.x) {
+    const int64_t o = r / inner, ii = r % inner;
+    const T* x = in + o * so + ii * si;
+    ValIdx best;
+    best.v = -INFINITY;
+    best.i = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      ValIdx c;
+      c.v = to_f<T>(x[(int64_t)i * sn]);
+      c.i = i;
+      if (best.i == 0x7fffffff || c.v > best.v) best = c;  // strictly greater, as the reference scan
+    }
+    best = block_argmax(best, red);
+    if (threadIdx.x == 0) out[r] = (TO)(best.i == 0x7fffffff ? 0 : best.i);
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ fused softmax + argmax
+// logits [B,V] fp32 -> probs (optionally stored) -> first index of the row maximum of the PROBABILITIES, which is
+// what the reference compares (Decoder.cs:732-761): logits that differ can round to equal probabilities, and
+// the lowest index must then win.  Blocked ids get p += -1 (Decoder.cs:744-752).
+__global__ void __launch_bounds__(1024) softmax_argmax_kernel(int* __restrict__ out_ids, float* __restrict__ probs,
+                                                              const float* __restrict__ logits, int V, float inv_temp_div,
+                                                              int use_temp, const int* __restrict__ blocked, int n_blocked) {
+  __shared__ float red[32];
+  __shared__ ValIdx redi[32];
+  const int r = blockIdx.x;
+  const float* z = logits + (int64_t)r * V;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = z[i];
+    if (use_temp) v = v / inv_temp_div;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, red);
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = z[i];
+    if (use_temp) v = v / inv_temp_div;
+    s += expf(v - mx);
+  }
+  s = block_sum(s, red);
+  ValIdx best;
+  best.v = -INFINITY;
+  best.i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = z[i];
+    if (use_temp) v = v / inv_temp_div;
+    float p = expf(v - mx) / s;
+    for (int j = 0; j < n_blocked; ++j)
+      if (blocked[j] == i) p += -1.0f;
+    if (probs) probs[(int64_t)r * V + i] = p;
+    ValIdx c;
+    c.v = p;
+    c.i = i;
+    best = better(best, c);
+  }
+  best = block_argmax(best, redi);
+  if (threadIdx.x == 0 && out_ids) out_ids[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+// ------------------------------------------------------------------------------------------------ Philox4x32-10
+__host__ __device__ inline void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
+    const uint32_t n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    const uint32_t n3 = (uint32_t)p0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+// key = (seed lo, seed hi), counter = (step, 0, seq lo, seq hi); u = (x0 >> 8) * 2^-24 in [0,1)
+__host__ __device__ inline float philox_uniform(uint64_t seed, uint64_t seq, uint32_t step) {
+  uint32_t c[4] = {step, 0u, (uint32_t)seq, (uint32_t)(seq >> 32)};
+  philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+  return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+}
+__global__ void philox_kernel(float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step_arg, const int* dstep) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t step = dstep ? (uint32_t)*dstep : step_arg;
+  if (i < n) u[i] = philox_uniform(seed, seq_first + (uint64_t)i, step);
+}
+
+// ------------------------------------------------------------------------------------------------ Top-P
+// One CTA of 1024 threads per row.  Workspace per row (uint32 words): keyA[V] keyB[V] idxA[V] idxB[V] last[V].
+//  1. key[j] = bits(w_j) for w_j > 0 else 0, where w_j = probs[j] * (float)pow(dist/len, repeatPenalty) for ids
+//     already in the row's history (dist counted from the LAST occurrence), computed as the reference does:
+//     float ratio -> double pow -> float -> float multiply.
+//  2. stable LSD radix sort, 4 x 8 bits, descending by key: equal keys keep ascending index order, which is the
+//     reference's SortedDictionary<float, List<int>> iterated in reverse with insertion-ordered lists.
+//  3. one lane accumulates acc += w sequentially in fp32 (the reference's rounding order) and stops at the first
+//     acc >= topP; accumulated values are kept.
+//  4. all threads search the first k with acc[k] / acc_final >= u.
+constexpr int kTopPThreads = 1024;
+constexpr int kTopPWarps = kTopPThreads / 32;
+constexpr int kScanChunk = 4096;
+
+struct ToppSmem {
+  uint32_t hist[kTopPWarps][256];  // per-warp digit counters / offsets
+  uint32_t warp_tot[32];
+  float chunk[kScanChunk];
+  int n_cand;
+  float acc_final;
+  int stop;
+  int best_k;
+};
+
+// The buffers are written earlier in the same kernel, so they are deliberately NOT const __restrict__ (no
+// non-coherent read-only loads).
+__device__ __forceinline__ void radix_pass(const uint32_t* kin, const uint32_t* iin, uint32_t* kout, uint32_t* iout, int n,
+                                           int shift, bool first, ToppSmem& sm) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int per_warp = ((n + kTopPWarps - 1) / kTopPWarps + 31) & ~31;
+  const int beg = w * per_warp, end = min(n, beg + per_warp);
+  for (int i = threadIdx.x; i < kTopPWarps * 256; i += blockDim.x) (&sm.hist[0][0])[i] = 0;
+  __syncthreads();
+  // A: per-warp histogram of the (descending) digit
+  for (int base = beg; base < end; base += 32) {
+    const int j = base + lane;
+    const bool ok = j < end;
+    const uint32_t key = ok ? kin[j] : 0u;
+    const uint32_t dg = ok ? (255u - ((key >> shift) & 255u)) : 256u;
+    const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+    if (ok && lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  // B: exclusive scan in (digit-major, warp-minor) order
+  {
+    uint32_t v[8];
+    uint32_t tsum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int li = threadIdx.x * 8 + e;  // li = digit * 32 + warp
+      v[e] = sm.hist[li & 31][li >> 5];
+      tsum += v[e];
+    }
+    uint32_t incl = tsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) sm.warp_tot[w] = incl;
+    __syncthreads();
+    if (w == 0) {
+      uint32_t t = sm.warp_tot[lane];
+      uint32_t ti = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u2 = __shfl_up_sync(0xffffffffu, ti, o);
+        if (lane >= o) ti += u2;
+      }
+      sm.warp_tot[lane] = ti - t;
+    }
+    __syncthreads();
+    uint32_t run = sm.warp_tot[w] + incl - tsum;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int li = threadIdx.x * 8 + e;
+      sm.hist[li & 31][li >> 5] = run;
+      run += v[e];
+    }
+  }
+  __syncthreads();
+  // C: stable scatter
+  for (int base = beg; base < end; base += 32) {
+    const int j = base + lane;
+    const bool ok = j < end;
+    const uint32_t key = ok ? kin[j] : 0u;
+    const uint32_t idx = ok ? (first ? (uint32_t)j : iin[j]) : 0u;
+    const uint32_t dg = ok ? (255u - ((key >> shift) & 255u)) : 256u;
+    const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+    const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+    uint32_t pos = 0;
+    if (ok) pos = sm.hist[w][dg] + rank;
+    __syncwarp();
+    if (ok) {
+      kout[pos] = key;
+      iout[pos] = idx;
+      if (lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* __restrict__ out, const float* __restrict__ probs, int V,
+                                                            float topP, float repeatPenalty,
+                                                            const int* __restrict__ history,
+                                                            const int* __restrict__ history_len, int history_stride,
+                                                            const float* __restrict__ u, uint32_t* ws) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ToppSmem& sm = *reinterpret_cast<ToppSmem*>(smem_raw);
+  const int r = blockIdx.x;
+  uint32_t* keyA = ws + (size_t)r * 5 * V;
+  uint32_t* keyB = keyA + V;
+  uint32_t* idxA = keyB + V;
+  uint32_t* idxB = idxA + V;
+  int* last = reinterpret_cast<int*>(idxB + V);
+  const float* p = probs + (size_t)r * V;
+  const int* hist = history ? history + (size_t)r * history_stride : nullptr;
+  const int len = (history && history_len) ? history_len[r] : 0;
+
+  // 1. keys (+ repeat penalty on the last occurrence of each id in the history)
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    const float w = p[j];
+    keyA[j] = (w > 0.0f) ? __float_as_uint(w) : 0u;
+  }
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= 0 && t < V) last[t] = -1;
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= 0 && t < V) atomicMax(&last[t], q);
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= 0 && t < V && last[t] == q) {
+      float w = p[t];
+      if (w > 0.0f) {
+        const float ratio = (float)(len - q) / (float)len;
+        const float rp = (float)pow((double)ratio, (double)repeatPenalty);
+        w = w * rp;
+        keyA[t] = __float_as_uint(w);  // may become +0: stays in the list with weight 0, as in the reference
+        if (w == 0.0f) keyA[t] = 0u;   // a zero weight sorts with the dropped entries; it adds nothing to acc
+      }
+    }
+  }
+  __syncthreads();
+
+  // 2. sort descending, stable
+  radix_pass(keyA, nullptr, keyB, idxB, V, 0, true, sm);
+  radix_pass(keyB, idxB, keyA, idxA, V, 8, false, sm);
+  radix_pass(keyA, idxA, keyB, idxB, V, 16, false, sm);
+  radix_pass(keyB, idxB, keyA, idxA, V, 24, false, sm);
+  // sorted: keyA / idxA
+
+  // 3. sequential fp32 prefix sum by one lane, staged through shared memory in chunks
+  if (threadIdx.x == 0) {
+    sm.n_cand = 0;
+    sm.acc_final = 0.0f;
+    sm.stop = 0;
+    sm.best_k = 0x7fffffff;
+  }
+  __syncthreads();
+  float* accs = reinterpret_cast<float*>(keyB);  // accumulated values, reusing a sort buffer
+  for (int base = 0; base < V; base += kScanChunk) {
+    const int m = min(kScanChunk, V - base);
+    for (int i = threadIdx.x; i < m; i += blockDim.x) sm.chunk[i] = __uint_as_float(keyA[base + i]);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float acc = sm.acc_final;
+      int i = 0;
+      for (; i < m; ++i) {
+        const float w = sm.chunk[i];
+        if (!(w > 0.0f)) {  // end of the valid (w > 0) entries
+          sm.stop = 1;
+          break;
+        }
+        acc += w;
+        sm.chunk[i] = acc;
+        if (acc >= topP) {
+          ++i;
+          sm.stop = 1;
+          break;
+        }
+      }
+      sm.acc_final = acc;
+      sm.n_cand = base + i;
+    }
+    __syncthreads();
+    const int done = min(m, sm.n_cand - base);
+    for (int i = threadIdx.x; i < done; i += blockDim.x) accs[base + i] = sm.chunk[i];
+    if (sm.stop) break;
+    __syncthreads();
+  }
+  __syncthreads();
+
+  // 4. first k with acc[k] / acc_final >= u
+  const int n = sm.n_cand;
+  const float tot = sm.acc_final, uu = u[r];
+  int mine = 0x7fffffff;
+  for (int k = threadIdx.x; k < n; k += blockDim.x)
+    if (accs[k] / tot >= uu) {
+      mine = k;
+      break;
+    }
+  if (mine != 0x7fffffff) atomicMin(&sm.best_k, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = (sm.best_k == 0x7fffffff) ? 0 : (int)idxA[sm.best_k];
+}
+
+int init_topp_attrs(int device) {
+  static bool attr_set[kMaxDevices] = {false};
+  if (!attr_set[device]) {
+    TSB_CUDA(cudaFuncSetAttribute(topp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ToppSmem)));
+    attr_set[device] = true;
+  }
+  return 1;
+}
+
+int launch_softmax_argmax(int device, DeviceState* st, int* out_ids, float* probs, const float* logits, int B, int V,
+                          float temperature, int use_temp, const int* blocked_dev, int n_blocked, cudaStream_t s) {
+  (void)st;
+  if (B == 0) return 1;
+  softmax_argmax_kernel<<<B, 1024, 0, s>>>(out_ids, probs, logits, V, temperature, use_temp, blocked_dev, n_blocked);
+  count_launch(device);
+  return check_launch("softmax_argmax");
+}
+
+int launch_topp(int device, DeviceState* st, int* out, const float* probs, int rows, int V, float topP, float repeatPenalty,
+                const int* history, const int* history_len, int history_stride, const float* u, void* ws, cudaStream_t s) {
+  (void)st;
+  if (rows == 0) return 1;
+  TSB_TRY(init_topp_attrs(device));
+  topp_kernel<<<rows, kTopPThreads, sizeof(ToppSmem), s>>>(out, probs, V, topP, repeatPenalty, history, history_len,
+                                                           history_stride, u, (uint32_t*)ws);
+  count_launch(device);
+  return check_launch("topp");
+}
+
+int launch_philox(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step, const int* dstep,
+                  cudaStream_t s) {
+  if (n == 0) return 1;
+  philox_kernel<<<(n + 127) / 128, 128, 0, s>>>(u, n, seed, seq_first, step, dstep);
+  count_launch(device);
+  return check_launch("philox");
+}
+
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int TSB200_Softmax(int device, const TSB200Tensor* result, const TSB200Tensor* src, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_TRY(check_tensor(result, "result"));
+  TSB_TRY(check_tensor(src, "src"));
+  TSB_CHECK(result->dtype == src->dtype, "softmax: dtype mismatch");
+  TSB_CHECK(numel(result) == numel(src) && is_contiguous(result), "softmax: result must be contiguous and match src");
+  const int cols = (int)src->sizes[src->ndim - 1];
+  const int64_t rows = cols ? numel(src) / cols : 0;
+  if (rows == 0) return 1;
+  int64_t rs = cols, cs = 1;
+  if (!is_contiguous(src)) {
+    TSB_CHECK(src->ndim == 2, "softmax: non-contiguous src must be a 2-D view");
+    rs = src->strides[0];
+    cs = src->strides[1];
+  }
+  cudaStream_t s = pick_stream(st, stream);
+  const int g = (int)(rows < (int64_t)st->sm_count * 4 ? rows : (int64_t)st->sm_count * 4);
+  const int th = cols >= 4096 ? 1024 : (cols >= 512 ? 256 : 64);
+  if (src->dtype == TSB200_F32) softmax_kernel<float><<<g, th, 0, s>>>((float*)result->data, (const float*)src->data, rows, cols, rs, cs);
+  else if (src->dtype == TSB200_F16) softmax_kernel<__half><<<g, th, 0, s>>>((__half*)result->data, (const __half*)src->data, rows, cols, rs, cs);
+  else TSB_FAIL("softmax: unsupported dtype %d", src->dtype);
+  count_launch(device);
+  return check_launch("softmax");
+}
+
+int TSB200_Argmax(int device, const TSB200Tensor* result, const TSB200Tensor* src, int dim, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_TRY(check_tensor(result, "result"));
+  TSB_TRY(check_tensor(src, "src"));
+  if (dim < 0) dim = src->ndim - 1;
+  TSB_CHECK(dim < src->ndim, "argmax: dim out of range");
+  TSB_CHECK(is_contiguous(result), "argmax: result must be contiguous");
+  const int n = (int)src->sizes[dim];
+  TSB_CHECK(n > 0, "argmax: empty dimension");
+  // collapse to [outer, n, inner]; needs the outer and inner groups to be uniformly strided
+  int64_t outer = 1, inner = 1, so = 0, si = 1;
+  for (int i = 0; i < dim; ++i) outer *= src->sizes[i];
+  for (int i = dim + 1; i < src->ndim; ++i) inner *= src->sizes[i];
+  if (is_contiguous(src)) {
+    so = (int64_t)n * inner;
+    si = 1;
+  } else {
+    TSB_CHECK(src->ndim == 2, "argmax: non-contiguous src must be a 2-D view");
+    so = dim == 1 ? src->strides[0] : 0;
+    si = dim == 0 ? src->strides[1] : 1;
+  }
+  const int64_t sn = src->strides[dim];
+  TSB_CHECK(numel(result) == outer * inner, "argmax: result must have the reduced dimension of size 1");
+  cudaStream_t s = pick_stream(st, stream);
+  const int64_t work = outer * inner;
+  const int g = (int)(work < (int64_t)st->sm_count * 8 ? work : (int64_t)st->sm_count * 8);
+#define TSB_AM(T, TO) argmax_kernel<T, TO><<<g, 256, 0, s>>>((TO*)result->data, (const T*)src->data, outer, n, inner, so, sn, si)
+  if (src->dtype == TSB200_F32 && result->dtype == TSB200_F32) TSB_AM(float, float);
+  else if (src->dtype == TSB200_F32 && result->dtype == TSB200_I32) TSB_AM(float, int);
+  else if (src->dtype == TSB200_F16 && result->dtype == TSB200_F16) TSB_AM(__half, __half);
+  else if (src->dtype == TSB200_F16 && result->dtype == TSB200_F32) TSB_AM(__half, float);
+  else if (src->dtype == TSB200_F16 && result->dtype == TSB200_I32) TSB_AM(__half, int);
+  else TSB_FAIL("argmax: unsupported dtypes src=%d result=%d", src->dtype, result->dtype);
+#undef TSB_AM
+  count_launch(device);
+  return check_launch("argmax");
+}
+
+int TSB200_SoftmaxArgmax(int device, int32_t* out_ids, float* probs_out, const float* logits, int B, int V,
+                         float temperature, const int32_t* blocked, int n_blocked, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(logits && (out_ids || probs_out), "softmax_argmax: null pointer");
+  TSB_CHECK(B >= 0 && V > 0, "softmax_argmax: bad shape");
+  TSB_CHECK(n_blocked == 0 || blocked, "softmax_argmax: blocked list is null");
+  return launch_softmax_argmax(device, st, out_ids, probs_out, logits, B, V, temperature, temperature != 1.0f ? 1 : 0,
+                               blocked, n_blocked, pick_stream(st, stream));
+}
+
+int64_t TSB200_TopPWorkspaceBytes(int rows, int V) { return (int64_t)rows * V * 5 * 4; }
+
+int TSB200_TopPSample(int device, int32_t* out, const float* probs, int rows, int V, float topP, float repeatPenalty,
+                      const int32_t* history, const int32_t* history_len, int history_stride, const float* u,
+                      void* workspace, int64_t workspace_bytes, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(out && probs && u && workspace, "topp: null pointer");
+  TSB_CHECK(rows >= 0 && V > 0, "topp: bad shape");
+  TSB_CHECK(workspace_bytes >= TSB200_TopPWorkspaceBytes(rows, V), "topp: workspace too small (%lld < %lld)",
+            (long long)workspace_bytes, (long long)TSB200_TopPWorkspaceBytes(rows, V));
+  TSB_CHECK(!history || history_len, "topp: history given without history_len");
+  return launch_topp(device, st, out, probs, rows, V, topP, repeatPenalty, history, history_len, history_stride, u,
+                     workspace, pick_stream(st, stream));
+}
+
+int TSB200_PhiloxUniform(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(u && n >= 0, "philox: bad arguments");
+  return launch_philox(device, u, n, seed, seq_first, step, nullptr, pick_stream(st, stream));
+}
+
+}  // extern "C"
