@@ -1,0 +1,281 @@
+"""Host-side mirror of the reference's GPT application for the B200 backend.
+
+Names follow Seq2SeqSharp: `DecodingOptions` (Seq2SeqSharp/Applications/DecodingOptions.cs:16-39),
+`GPT.RunForwardOnSingleDevice` (Seq2SeqSharp/Applications/GPT.cs:212-335), weight keys as stored by
+IModel.AddWeights (Seq2SeqSharp/Tools/WeightTensor.cs:571-604).  The work is done by the GPT engine of
+libtsb200.so through the C ABI; this module only marshals.  There is no CPU path.
+"""
+import ctypes as C
+from dataclasses import dataclass, field
+from enum import IntEnum
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import _native as N
+from .synthetic import synth
+
+
+class DecodingStrategyEnums(IntEnum):  # Seq2SeqSharp/Utils/DecodingStrategyEnums.cs
+    GreedySearch = 0
+    Sampling = 1
+
+
+class NormEnums(IntEnum):
+    LayerNorm = 0
+    RMSNorm = 1
+
+
+class ActivateFuncEnums(IntEnum):  # Seq2SeqSharp/Utils/ActivateFuncEnums.cs:5-12 (+ two extensions)
+    ReLU = 0
+    SiLU = 1
+    LeakyReLU = 2
+    SwiGLU = 3        # the reference's SwiGLU: (xW1+b1) * (xW3+b3), no SiLU (PositionwiseFeedForward.cs:82-116)
+    SwiGLU_SiLU = 4   # extension: silu(xW1+b1) * (xW3+b3)
+    GELU = 5          # extension: erf GELU
+
+
+class PositionEmbeddingEnums(IntEnum):  # Seq2SeqSharp/Utils/PositionEmbedding.cs:18-23
+    NoPE = 0
+    APE = 1
+    RoPE = 2
+
+
+class MultiHeadAttentionTypeEnums(IntEnum):
+    MHA = 0
+    GQA = 1
+
+
+@dataclass
+class DecodingOptions:
+    MaxTgtSentLength: int = 256
+    RepeatPenalty: float = 2.0
+    BeamSearchSize: int = 1
+    Temperature: float = 1.0
+    TopP: float = 1.0
+    DecodingStrategy: DecodingStrategyEnums = DecodingStrategyEnums.GreedySearch
+    BlockedTokens: Optional[List[int]] = None
+    # counter-based uniform stream replacing the process-wide System.Random (Tools/RandomGenerator.cs:41-46)
+    Seed: int = 0
+    SeqBase: int = 0
+
+
+@dataclass
+class GPTConfig:
+    """Shape and behaviour switches of GPTDecoder (Seq2SeqSharp/Networks/GPTDecoder.cs:40-133)."""
+    L: int
+    d: int
+    H: int
+    hd: int
+    F: int
+    V: int
+    Hkv: int = 0
+    norm: NormEnums = NormEnums.LayerNorm
+    act: ActivateFuncEnums = ActivateFuncEnums.ReLU
+    pe: PositionEmbeddingEnums = PositionEmbeddingEnums.RoPE
+    attn: MultiHeadAttentionTypeEnums = MultiHeadAttentionTypeEnums.MHA
+    dtype: str = "float32"          # "float32" | "float16"
+    eps: float = 1e-6               # Layers/LayerNormalization.cs:36, RMSNormalization.cs:26
+    rope_base: float = 500000.0     # TensorSharp/TensorApplyCPU.cs:1162
+    ape_decode_pos0: bool = True    # Decoder.cs:674-677 adds APE row 0 in cached decode
+    name: str = ""
+
+    def kv_heads(self):
+        return self.Hkv if (self.attn == MultiHeadAttentionTypeEnums.GQA and self.Hkv) else self.H
+
+    def is_glu(self):
+        return self.act in (ActivateFuncEnums.SwiGLU, ActivateFuncEnums.SwiGLU_SiLU)
+
+    def weight_shapes(self, max_pos: int = 0) -> Dict[str, tuple]:
+        """Reference weight keys -> [rows, cols] (every linear has a bias; LM head is separate from the embedding)."""
+        d, F, V, Hd, KVd = self.d, self.F, self.V, self.H * self.hd, self.kv_heads() * self.hd
+        s = {"TgtEmbeddings": (V, d)}
+        if self.pe == PositionEmbeddingEnums.APE and max_pos:
+            s["PosEmbedding"] = (max_pos, d)
+        for k in range(self.L):
+            a, f = "GPTDecoder.SelfAttn_%d." % k, "GPTDecoder.PosFFN_%d." % k
+            s[a + "layerNormQ.m_alpha"] = (1, d)
+            if self.norm == NormEnums.LayerNorm:
+                s[a + "layerNormQ.m_beta"] = (1, d)
+            if self.attn == MultiHeadAttentionTypeEnums.MHA:
+                s[a + "QKV"] = (d, 3 * Hd)
+                s[a + "QKVb"] = (1, 3 * Hd)
+            else:
+                s[a + "Q"], s[a + "Qb"] = (d, Hd), (1, Hd)
+                s[a + "K"], s[a + "Kb"] = (d, KVd), (1, KVd)
+                s[a + "V"], s[a + "Vb"] = (d, KVd), (1, KVd)
+            s[a + "W0"], s[a + "b0"] = (Hd, d), (1, d)
+            s[f + "layerNorm2.m_alpha"] = (1, d)
+            if self.norm == NormEnums.LayerNorm:
+                s[f + "layerNorm2.m_beta"] = (1, d)
+            s[f + "feedForwardLayer1.m_Whd"], s[f + "feedForwardLayer1.m_Bd"] = (d, F), (1, F)
+            if self.is_glu():
+                s[f + "feedForwardLayer3.m_Whd"], s[f + "feedForwardLayer3.m_Bd"] = (d, F), (1, F)
+            s[f + "feedForwardLayer2.m_Whd"], s[f + "feedForwardLayer2.m_Bd"] = (F, d), (1, d)
+        s["GPTDecoder.layerNorm.m_alpha"] = (1, d)
+        if self.norm == NormEnums.LayerNorm:
+            s["GPTDecoder.layerNorm.m_beta"] = (1, d)
+        s["FeedForward_Decoder_0.m_Whd"], s["FeedForward_Decoder_0.m_Bd"] = (d, V), (1, V)
+        return s
+
+    def matmul_params(self):
+        d, F, V, Hd, KVd = self.d, self.F, self.V, self.H * self.hd, self.kv_heads() * self.hd
+        return self.L * (d * (Hd + 2 * KVd) + Hd * d + (3 if self.is_glu() else 2) * d * F) + d * V
+
+
+def is_bias(name: str) -> bool:
+    return name.endswith(("m_Bd", "QKVb", ".Qb", ".Kb", ".Vb", ".b0"))
+
+
+def is_norm(name: str) -> bool:
+    return name.endswith(("m_alpha", "m_beta"))
+
+
+def synthetic_weights(cfg: GPTConfig, seed: int, std: float = 0.02, bias_std: float = 0.0, max_pos: int = 0):
+    """Seeded weights keyed by the reference names: matrices ~ N(0, std); norm gains 1, betas 0; biases 0 (the
+    reference default) or N(0, bias_std).  Values are float32; for a float16 model they are rounded to half once
+    (round-to-nearest-even) and returned as float32 holding the rounded values, so the oracle sees what the device sees."""
+    out = {}
+    for name, shape in cfg.weight_shapes(max_pos).items():
+        if name.endswith("m_alpha"):
+            w = np.ones(shape, dtype=np.float32)
+        elif name.endswith("m_beta"):
+            w = np.zeros(shape, dtype=np.float32)
+        elif is_bias(name):
+            w = synth(name, shape, seed, bias_std) if bias_std > 0 else np.zeros(shape, dtype=np.float32)
+        else:
+            w = synth(name, shape, seed, std)
+        if cfg.dtype == "float16":
+            w = w.astype(np.float16).astype(np.float32)
+        out[name] = w
+    return out
+
+
+class GPT:
+    """One GPT replica on one device (the reference builds one per device id through
+    MultiProcessorNetworkWrapper.GetNetworkOnDevice, Seq2SeqSharp/Applications/GPT.cs:138-146)."""
+
+    def __init__(self, cfg: GPTConfig, device_id: int = 0, max_batch: int = 1, max_tokens: int = 512):
+        self.cfg = cfg
+        self.device_id = device_id
+        self.max_batch = max_batch
+        self.max_tokens = max_tokens
+        c = N.GptConfig()
+        c.L, c.d, c.H, c.Hkv, c.hd, c.F, c.V = cfg.L, cfg.d, cfg.H, cfg.kv_heads(), cfg.hd, cfg.F, cfg.V
+        c.norm_type, c.act, c.pe_type, c.attn_type = int(cfg.norm), int(cfg.act), int(cfg.pe), int(cfg.attn)
+        c.dtype = N.F16 if cfg.dtype == "float16" else N.F32
+        c.eps, c.rope_base = cfg.eps, cfg.rope_base
+        c.ape_decode_pos0 = 1 if cfg.ape_decode_pos0 else 0
+        c.max_batch, c.max_tokens, c.device = max_batch, max_tokens, device_id
+        c.tp_rank, c.tp_size = 0, 1
+        self._h = C.c_void_p()
+        N.call("TSB200_GptCreate", C.byref(c), C.byref(self._h))
+        self._keep = None
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            N.lib().TSB200_GptDestroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def pos_embedding_rows(self):
+        return self.max_tokens + 2
+
+    # ---- weights -----------------------------------------------------------------------------------
+    def LoadWeights(self, weights: Dict[str, np.ndarray]):
+        """IModel.GetWeights equivalent: full tensors by reference key (float32 or float16 numpy arrays)."""
+        for name, w in weights.items():
+            w = np.ascontiguousarray(w)
+            if w.dtype == np.float16:
+                dt = N.F16
+            else:
+                w = w.astype(np.float32, copy=False)
+                dt = N.F32
+            rows, cols = (w.shape if w.ndim == 2 else (1, w.size))
+            N.call("TSB200_GptSetWeight", self._h, name.encode(), w.ctypes.data_as(C.c_void_p), dt, rows, cols, 0)
+
+    def FillSynthetic(self, seed: int, std: float = 0.02, bias_std: float = 0.0):
+        """Same values as synthetic_weights(), generated on the device (for models too large to stage from the host)."""
+        N.call("TSB200_GptFillSynthetic", self._h, seed, std, bias_std)
+
+    # ---- token loop --------------------------------------------------------------------------------
+    def _opts(self, o: DecodingOptions):
+        c = N.DecodingOptionsC()
+        c.strategy = int(o.DecodingStrategy)
+        c.topP, c.temperature, c.repeatPenalty = o.TopP, o.Temperature, o.RepeatPenalty
+        bl = list(o.BlockedTokens or [])
+        arr = (C.c_int32 * max(1, len(bl)))(*bl)
+        c.blocked = C.cast(arr, C.POINTER(C.c_int32))
+        c.n_blocked = len(bl)
+        c.seed, c.seq_base = o.Seed, o.SeqBase
+        self._keep = arr
+        return c
+
+    def Reset(self):
+        N.call("TSB200_GptReset", self._h)
+
+    def Prefill(self, tokens, opts: DecodingOptions):
+        ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        if ids.ndim != 2:
+            raise ValueError("tokens must be [batch, prompt_len] with equal prompt lengths")
+        B, S = ids.shape
+        out = np.zeros(B, dtype=np.int32)
+        c = self._opts(opts)
+        N.call("TSB200_GptPrefill", self._h, ids.ctypes.data_as(C.c_void_p), B, S, C.byref(c),
+               out.ctypes.data_as(C.c_void_p))
+        self._B = B
+        return out
+
+    def Decode(self, n_steps: int, opts: DecodingOptions, stop_on_eos: bool = False):
+        out = np.zeros((self._B, n_steps), dtype=np.int32)
+        done = C.c_int(0)
+        c = self._opts(opts)
+        N.call("TSB200_GptDecode", self._h, n_steps, C.byref(c), 1 if stop_on_eos else 0,
+               out.ctypes.data_as(C.c_void_p), C.byref(done))
+        return out[:, :done.value]
+
+    def RunForwardOnSingleDevice(self, tokens, decodingOptions: DecodingOptions, stop_on_eos: bool = True):
+        """tokens [B, promptLen] -> generated ids [B, n] with n <= MaxTgtSentLength - promptLen: the loop
+        `for (i = promptLen; i < MaxTgtSentLength; i++)` with the all-sequences-ended-with-EOS stop rule
+        (GPT.cs:249-304).  Raises TSB200OutOfMemory where the reference returns NetworkResultStatus.OOM."""
+        ids = np.asarray(tokens, dtype=np.int32)
+        B, S = ids.shape
+        n_new = decodingOptions.MaxTgtSentLength - S
+        if n_new <= 0:
+            return np.zeros((B, 0), dtype=np.int32)
+        self.Reset()
+        first = self.Prefill(ids, decodingOptions)
+        if n_new == 1 or (stop_on_eos and bool(np.all(first == 0))):
+            return first[:, None]
+        rest = self.Decode(n_new - 1, decodingOptions, stop_on_eos=stop_on_eos)
+        return np.concatenate([first[:, None], rest], axis=1)
+
+    # ---- inspection --------------------------------------------------------------------------------
+    def Logits(self, want_probs=True):
+        B, V = self._B, self.cfg.V
+        lg = np.empty((B, V), dtype=np.float32)
+        pr = np.empty((B, V), dtype=np.float32) if want_probs else None
+        N.call("TSB200_GptGetLogits", self._h, lg.ctypes.data_as(C.c_void_p),
+               pr.ctypes.data_as(C.c_void_p) if pr is not None else None)
+        return lg, pr
+
+    def CacheLength(self):
+        t = C.c_int(0)
+        N.call("TSB200_GptCacheLength", self._h, C.byref(t))
+        return t.value
+
+    def LastTiming(self):
+        ms, n = C.c_float(0), C.c_int64(0)
+        N.call("TSB200_GptLastTiming", self._h, C.byref(ms), C.byref(n))
+        return ms.value, n.value
+
+    def StepBytes(self, B, T):
+        b = C.c_int64(0)
+        N.call("TSB200_GptStepBytes", self._h, B, T, C.byref(b))
+        return b.value
