@@ -264,6 +264,19 @@ TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);
 /* device-timed duration (ms, CUDA events on the engine's stream) of the last GptDecode / GptPrefill call and
  * the number of kernel launches it issued (graph replays count their nodes) */
 TSB200_API int TSB200_GptLastTiming(void* gpt, float* ms, int64_t* launches);
+/* One decode step with HOST buffers: uploads last_ids [B] (pinned staging), runs the step, downloads the new ids
+ * [B].  This is the per-token host round trip the reference makes (ids built on the host each step,
+ * TensorUtils.CreateTokensEmbeddings; ids read back, Decoder.cs:769-782): B*4 bytes each way. */
+TSB200_API int TSB200_GptStepHost(void* gpt, const int32_t* last_ids, const TSB200DecodingOptions* opt,
+                                  int32_t* out_ids);
+/* per-step device durations of the last TSB200_GptDecode call (CUDA events between graph launches) */
+TSB200_API int TSB200_GptEnableStepTiming(void* gpt, int enable);
+TSB200_API int TSB200_GptGetStepTimes(void* gpt, float* ms, int n, int* n_out);
+/* Runs n_steps decode steps un-captured with CUDA events around every launch group and returns, per kernel class
+ * (0 embed, 1 norm, 2 linear (GEMV/GEMM), 3 rope+append, 4 attention, 5 sampling, 6 commit), the summed device
+ * time in ms and the number of launch groups.  n_classes >= 8. */
+TSB200_API int TSB200_GptProfileDecode(void* gpt, int n_steps, const TSB200DecodingOptions* opt, float* class_ms,
+                                       int64_t* class_groups, int n_classes);
 /* the engine's stream (cudaStream_t) */
 TSB200_API int TSB200_GptStream(void* gpt, void** stream);
 /* algorithmic bytes of one decode step at cache length T for B sequences (weights once + KV read/write +

@@ -191,6 +191,9 @@ class OracleGPT:
     def reset(self):
         lib().orc_reset(self._h)
 
+    def cache_len(self):
+        return int(lib().orc_cache_len(self._h))
+
     def step(self, ids, temperature=1.0, blocked=()):
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         B, S = ids.shape

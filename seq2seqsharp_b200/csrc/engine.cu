@@ -129,7 +129,43 @@ struct Gpt {
   float last_ms = 0.0f;
   long long last_launches = 0;
   std::vector<void*> allocs;
+  // instrumentation (TSB200_GptProfileDecode): events around every launch group, by kernel class
+  bool prof = false;
+  std::vector<cudaEvent_t> prof_ev;
+  std::vector<int> prof_cls;
+  size_t prof_n = 0;
+  // per-step events of the last GptDecode (TSB200_GptEnableStepTiming)
+  bool step_timing = false;
+  std::vector<cudaEvent_t> step_ev;
+  int step_ev_n = 0;
+  int* pin_ids = nullptr;  // pinned host staging for TSB200_GptStepHost
 };
+
+enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_COUNT = 8 };
+
+static void prof_begin(Gpt* g) {
+  if (!g->prof) return;
+  if (g->prof_ev.size() < 2 * (g->prof_n + 1)) {
+    const size_t old = g->prof_ev.size();
+    g->prof_ev.resize(old + 512);
+    for (size_t i = old; i < g->prof_ev.size(); ++i) cudaEventCreate(&g->prof_ev[i]);
+  }
+  cudaEventRecord(g->prof_ev[2 * g->prof_n], g->s);
+}
+static void prof_end(Gpt* g, int cls) {
+  if (!g->prof) return;
+  cudaEventRecord(g->prof_ev[2 * g->prof_n + 1], g->s);
+  if (g->prof_cls.size() <= g->prof_n) g->prof_cls.resize(g->prof_n + 512);
+  g->prof_cls[g->prof_n] = cls;
+  ++g->prof_n;
+}
+#define PROF(cls, call)          \
+  do {                           \
+    prof_begin(g);               \
+    const int _ok = (call);      \
+    prof_end(g, cls);            \
+    if (!_ok) return 0;          \
+  } while (0)
 
 static int dev_alloc(Gpt* g, void** p, int64_t bytes, bool zero = true) {
   if (bytes <= 0) bytes = 256;
@@ -292,6 +328,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   const int pe_mode = (c.pe_type == 1) ? (c.ape_decode_pos0 ? 1 : 2) : 0;
   const float sf = (float)std::sqrt((double)d);
   {
+    prof_begin(g);
     const int gsz = rows < g->st->sm_count * 8 ? rows : g->st->sm_count * 8;
     const int* ids = (S == 1 && use_state) ? g->ids_cur : g->ids_in;
     if (dt == TSB200_F32)
@@ -299,22 +336,23 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     else
       embed_kernel<__half><<<gsz, 256, 0, g->s>>>(g->x, (const __half*)g->E, (const __half*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT);
     count_launch(dev);
+    prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
   }
   const int act = c.act;
   for (int k = 0; k < c.L; ++k) {
     LayerW& L = g->L[k];
-    TSB_TRY(launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
-    TSB_TRY(launch_linear(dev, g->st, dt, g->h, L.wqkv, rows, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
+    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->h, L.wqkv, rows, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
     void* qp = g->qkv;
     void* kp = (char*)g->qkv + (int64_t)Hd * g->es;
     void* vp = (char*)g->qkv + (int64_t)(Hd + KVd) * g->es;
-    TSB_TRY(launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
-    TSB_TRY(launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
-    TSB_TRY(launch_linear(dev, g->st, dt, g->attn, L.wo, rows, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
-    TSB_TRY(launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n2_g, c.norm_type == 0 ? L.n2_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
-    TSB_TRY(launch_linear(dev, g->st, dt, g->h, L.w1, rows, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu), g->lin_ws, g->lin_ws_bytes, g->s));
-    TSB_TRY(launch_linear(dev, g->st, dt, g->ffn, L.w2, rows, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
+    PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
+    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->attn, L.wo, rows, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n2_g, c.norm_type == 0 ? L.n2_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
+    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->h, L.w1, rows, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu), g->lin_ws, g->lin_ws_bytes, g->s));
+    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->ffn, L.w2, rows, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
   }
   const float* xlast = g->x;
   if (S > 1) {
@@ -323,8 +361,8 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     TSB_TRY(check_launch("gather_last"));
     xlast = g->xl;
   }
-  TSB_TRY(launch_norm_residual(dev, g->st, dt, g->hl, const_cast<float*>(xlast), nullptr, g->nf_g, c.norm_type == 0 ? g->nf_b : nullptr, c.norm_type, c.eps, B, d, g->s));
-  TSB_TRY(launch_linear(dev, g->st, dt, g->hl, g->head_w, B, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+  PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->hl, const_cast<float*>(xlast), nullptr, g->nf_g, c.norm_type == 0 ? g->nf_b : nullptr, c.norm_type, c.eps, B, d, g->s));
+  PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->hl, g->head_w, B, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
   return 1;
 }
 
@@ -334,13 +372,15 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
   const int dev = c.device;
   const bool sampling = opt->strategy == 1;
   const int use_temp = (sampling && opt->temperature != 1.0f) ? 1 : 0;
-  TSB_TRY(launch_softmax_argmax(dev, g->st, g->ids_new, sampling ? g->probs : nullptr, g->logits, B, c.V, opt->temperature, use_temp, g->blocked, g->n_blocked, g->s));
+  PROF(KC_SAMPLE, launch_softmax_argmax(dev, g->st, g->ids_new, sampling ? g->probs : nullptr, g->logits, B, c.V, opt->temperature, use_temp, g->blocked, g->n_blocked, g->s));
   if (sampling) {
-    TSB_TRY(launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state + 1 : nullptr, g->s));
-    TSB_TRY(launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
+    PROF(KC_SAMPLE, launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state + 1 : nullptr, g->s));
+    PROF(KC_SAMPLE, launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
   }
+  prof_begin(g);
   commit_kernel<<<1, 256, 0, g->s>>>(g->ids_cur, g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0);
   count_launch(dev);
+  prof_end(g, KC_COMMIT);
   return check_launch("commit");
 }
 
@@ -371,6 +411,46 @@ static int set_state(Gpt* g, int out_slot) {
   const int hst[3] = {g->T, (int)g->step, out_slot};
   TSB_CUDA(cudaMemcpyAsync(g->state, hst, sizeof(hst), cudaMemcpyHostToDevice, g->s));
   TSB_CUDA(cudaStreamSynchronize(g->s));  // hst is on the stack
+  return 1;
+}
+
+// Captures (or reuses) the CUDA graph of one decode step for the current batch and decoding options.
+static int ensure_graph(Gpt* g, const TSB200DecodingOptions* opt, int n_steps) {
+  const TSB200GptConfig& c = g->c;
+  const int B = g->B;
+  // split count for the attention kernel: fixed per graph, chosen for the longest cache this call reaches
+  int Tp = 256;
+  while (Tp < g->T + n_steps) Tp <<= 1;
+  GraphKey key;
+  key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, B, c.H, c.Hkv, Tp);
+  key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
+  key.topP = opt->topP; key.temperature = opt->temperature; key.penalty = opt->repeatPenalty;
+  key.seed = opt->seed; key.seq_base = opt->seq_base;
+  if (g->gexec && g->gkey == key) return 1;
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  cudaGraph_t graph = nullptr;
+  const long long l0 = g->st->launches;
+  const bool prof = g->prof;
+  g->prof = false;
+  TSB_CUDA(cudaStreamBeginCapture(g->s, cudaStreamCaptureModeThreadLocal));
+  int ok = enqueue_forward(g, B, 1, g->T, true, key.splits) && enqueue_sample(g, B, opt, true, true);
+  cudaError_t e = cudaStreamEndCapture(g->s, &graph);
+  g->prof = prof;
+  if (!ok || e != cudaSuccess) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    if (ok) set_last_error("gpt_decode: graph capture failed: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  g->graph_nodes = g->st->launches - l0;
+  g->st->launches = l0;  // captured launches have not run yet; replays are counted when launched
+  e = cudaGraphInstantiate(&g->gexec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    g->gexec = nullptr;
+    TSB_FAIL("gpt_decode: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+  }
+  g->gkey = key;
   return 1;
 }
 
@@ -482,6 +562,9 @@ int TSB200_GptDestroy(void* h) {
   if (g->gexec) cudaGraphExecDestroy(g->gexec);
   if (g->ev0) cudaEventDestroy(g->ev0);
   if (g->ev1) cudaEventDestroy(g->ev1);
+  for (auto e : g->prof_ev) cudaEventDestroy(e);
+  for (auto e : g->step_ev) cudaEventDestroy(e);
+  if (g->pin_ids) cudaFreeHost(g->pin_ids);
   for (void* p : g->allocs)
     if (p) cudaFree(p);
   delete g;
@@ -649,44 +732,27 @@ int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int
   const int B = g->B;
   TSB_TRY(upload_blocked(g, opt));
   TSB_TRY(set_state(g, 0));
-  // split count for the attention kernel: fixed per graph, chosen for the longest cache this call reaches
-  int Tp = 256;
-  while (Tp < g->T + n_steps) Tp <<= 1;
-  GraphKey key;
-  key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, B, c.H, c.Hkv, Tp);
-  key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
-  key.topP = opt->topP; key.temperature = opt->temperature; key.penalty = opt->repeatPenalty;
-  key.seed = opt->seed; key.seq_base = opt->seq_base;
-  if (!g->gexec || !(g->gkey == key)) {
-    if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
-    cudaGraph_t graph = nullptr;
-    const long long l0 = g->st->launches;
-    TSB_CUDA(cudaStreamBeginCapture(g->s, cudaStreamCaptureModeThreadLocal));
-    int ok = enqueue_forward(g, B, 1, g->T, true, key.splits) && enqueue_sample(g, B, opt, true, true);
-    cudaError_t e = cudaStreamEndCapture(g->s, &graph);
-    if (!ok || e != cudaSuccess) {
-      if (graph) cudaGraphDestroy(graph);
-      cudaGetLastError();
-      if (ok) set_last_error("gpt_decode: graph capture failed: %s", cudaGetErrorString(e));
-      return 0;
-    }
-    g->graph_nodes = g->st->launches - l0;
-    g->st->launches = l0;  // captured launches have not run yet; replays are counted below
-    e = cudaGraphInstantiate(&g->gexec, graph, 0);
-    cudaGraphDestroy(graph);
-    if (e != cudaSuccess) {
-      g->gexec = nullptr;
-      TSB_FAIL("gpt_decode: cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
-    }
-    g->gkey = key;
-  }
+  TSB_TRY(ensure_graph(g, opt, n_steps));
   std::vector<int> last(B);
   int done = 0;
+  if (g->step_timing) {
+    while ((int)g->step_ev.size() < n_steps + 1) {
+      cudaEvent_t e;
+      TSB_CUDA(cudaEventCreate(&e));
+      g->step_ev.push_back(e);
+    }
+  }
+  g->step_ev_n = 0;
   TSB_CUDA(cudaEventRecord(g->ev0, g->s));
+  if (g->step_timing) TSB_CUDA(cudaEventRecord(g->step_ev[0], g->s));
   for (int i = 0; i < n_steps; ++i) {
     TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
     count_launch(c.device, g->graph_nodes);
     ++done;
+    if (g->step_timing) {
+      TSB_CUDA(cudaEventRecord(g->step_ev[i + 1], g->s));
+      g->step_ev_n = i + 1;
+    }
     if (stop_on_eos) {
       // the reference reads the ids back every token to test its stop rule (Decoder.cs:769-782, GPT.cs:300-303)
       TSB_CUDA(cudaMemcpyAsync(last.data(), g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
@@ -768,6 +834,91 @@ int TSB200_GptStepBytes(void* h, int B, int T, int64_t* bytes) {
   total += (int64_t)B * d * s;                  // embedding rows
   total += (int64_t)B * 4;                      // ids out
   *bytes = total;
+  return 1;
+}
+
+int TSB200_GptEnableStepTiming(void* h, int enable) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_enable_step_timing: null engine");
+  g->step_timing = enable != 0;
+  return 1;
+}
+
+int TSB200_GptGetStepTimes(void* h, float* ms, int n, int* n_out) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ms && n_out, "gpt_get_step_times: null argument");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  const int m = g->step_ev_n < n ? g->step_ev_n : n;
+  for (int i = 0; i < m; ++i) TSB_CUDA(cudaEventElapsedTime(&ms[i], g->step_ev[i], g->step_ev[i + 1]));
+  *n_out = m;
+  return 1;
+}
+
+int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && last_ids && opt && out_ids, "gpt_step_host: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(g->T > 0 && g->B > 0, "gpt_step_host: prefill first");
+  TSB_CHECK(g->T + 1 <= c.max_tokens, "OOM: KV-cache capacity %d exceeded", c.max_tokens);
+  const int B = g->B;
+  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)c.max_batch * 8, cudaHostAllocDefault));
+  TSB_TRY(upload_blocked(g, opt));
+  if (!g->gexec) TSB_TRY(set_state(g, 0));
+  TSB_TRY(ensure_graph(g, opt, 1));
+  for (int b = 0; b < B; ++b) {
+    TSB_CHECK(last_ids[b] >= 0 && last_ids[b] < c.V, "gpt_step_host: token id %d out of range", last_ids[b]);
+    g->pin_ids[b] = last_ids[b];
+  }
+  const int hst[3] = {g->T, (int)g->step, 0};
+  int* pin_state = g->pin_ids + c.max_batch;  // second half of the pinned block
+  pin_state[0] = hst[0]; pin_state[1] = hst[1]; pin_state[2] = hst[2];
+  TSB_CUDA(cudaMemcpyAsync(g->ids_cur, g->pin_ids, (size_t)B * 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaMemcpyAsync(g->state, pin_state, 12, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
+  count_launch(c.device, g->graph_nodes);
+  TSB_CUDA(cudaMemcpyAsync(g->pin_ids, g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));
+  for (int b = 0; b < B; ++b) out_ids[b] = g->pin_ids[b];
+  g->T += 1;
+  g->step += 1;
+  g->probs_valid = (opt->strategy == 1);
+  g->last_launches = g->graph_nodes;
+  return 1;
+}
+
+int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, float* class_ms, int64_t* class_groups,
+                            int n_classes) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && opt && class_ms && class_groups, "gpt_profile_decode: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(n_classes >= KC_COUNT, "gpt_profile_decode: need room for %d classes", (int)KC_COUNT);
+  TSB_CHECK(g->T > 0 && g->B > 0, "gpt_profile_decode: prefill first");
+  TSB_CHECK(g->T + n_steps <= c.max_tokens, "OOM: KV-cache capacity %d exceeded", c.max_tokens);
+  for (int i = 0; i < n_classes; ++i) { class_ms[i] = 0.0f; class_groups[i] = 0; }
+  TSB_TRY(upload_blocked(g, opt));
+  TSB_TRY(set_state(g, 0));
+  int Tp = 256;
+  while (Tp < g->T + n_steps) Tp <<= 1;
+  const int splits = attn_pick_splits(g->st, g->B, c.H, c.Hkv, Tp);
+  g->prof = true;
+  g->prof_n = 0;
+  int ok = 1;
+  for (int i = 0; i < n_steps && ok; ++i) ok = enqueue_forward(g, g->B, 1, g->T, true, splits) && enqueue_sample(g, g->B, opt, true, true);
+  g->prof = false;
+  cudaError_t e = cudaStreamSynchronize(g->s);
+  if (!ok) return 0;
+  TSB_CUDA(e);
+  for (size_t i = 0; i < g->prof_n; ++i) {
+    float ms = 0.0f;
+    TSB_CUDA(cudaEventElapsedTime(&ms, g->prof_ev[2 * i], g->prof_ev[2 * i + 1]));
+    class_ms[g->prof_cls[i]] += ms;
+    class_groups[g->prof_cls[i]] += 1;
+  }
+  g->T += n_steps;
+  g->step += (uint32_t)n_steps;
+  g->probs_valid = (opt->strategy == 1);
   return 1;
 }
 

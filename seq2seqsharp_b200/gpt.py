@@ -256,6 +256,34 @@ class GPT:
         rest = self.Decode(n_new - 1, decodingOptions, stop_on_eos=stop_on_eos)
         return np.concatenate([first[:, None], rest], axis=1)
 
+    def StepHost(self, last_ids, opts: DecodingOptions):
+        """One decode step with host buffers: ids in -> ids out (what the reference does per token)."""
+        ids = np.ascontiguousarray(last_ids, dtype=np.int32)
+        out = np.empty_like(ids)
+        c = self._opts(opts)
+        N.call("TSB200_GptStepHost", self._h, ids.ctypes.data_as(C.c_void_p), C.byref(c), out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def EnableStepTiming(self, on=True):
+        N.call("TSB200_GptEnableStepTiming", self._h, 1 if on else 0)
+
+    def StepTimes(self, n):
+        ms = np.zeros(n, dtype=np.float32)
+        got = C.c_int(0)
+        N.call("TSB200_GptGetStepTimes", self._h, ms.ctypes.data_as(C.c_void_p), n, C.byref(got))
+        return ms[:got.value]
+
+    KERNEL_CLASSES = ("embed", "norm", "linear", "rope_append", "attention", "sampling", "commit")
+
+    def ProfileDecode(self, n_steps, opts: DecodingOptions):
+        """{class: (ms_total, launch_groups)} over n_steps un-captured decode steps (CUDA events per launch group)."""
+        ms = np.zeros(8, dtype=np.float32)
+        groups = np.zeros(8, dtype=np.int64)
+        c = self._opts(opts)
+        N.call("TSB200_GptProfileDecode", self._h, n_steps, C.byref(c), ms.ctypes.data_as(C.c_void_p),
+               groups.ctypes.data_as(C.c_void_p), 8)
+        return {k: (float(ms[i]), int(groups[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
+
     # ---- inspection --------------------------------------------------------------------------------
     def Logits(self, want_probs=True):
         B, V = self._B, self.cfg.V

@@ -210,3 +210,33 @@ def test_device_synthetic_fill_equals_host_generator(cuda, oracle):
     np.testing.assert_array_equal(la, lb)
     a.close()
     b.close()
+
+
+def test_step_host_and_profile_paths_agree_with_graph_decode(cuda):
+    """The host-buffer step (ids uploaded and read back every token) and the instrumented un-captured path must produce
+    the same ids as the graph-replayed device loop."""
+    cfg = ARCHS[1]
+    w = synthetic_weights(cfg, 4, std=0.05)
+    prompt = prompt_ids(6, 2, 12, cfg.V)
+    opts = DecodingOptions(MaxTgtSentLength=64, DecodingStrategy=DS.Sampling, TopP=0.9, BlockedTokens=[0], Seed=5)
+    gpt = GPT(cfg, max_batch=2, max_tokens=64)
+    gpt.LoadWeights(w)
+    gpt.Reset()
+    first = gpt.Prefill(prompt, opts)
+    a = gpt.Decode(20, opts)
+    gpt.Reset()
+    first2 = gpt.Prefill(prompt, opts)
+    np.testing.assert_array_equal(first, first2)
+    last, b = first2, []
+    for _ in range(10):
+        last = gpt.StepHost(last, opts)
+        b.append(last.copy())
+    prof = gpt.ProfileDecode(4, opts)
+    assert prof["linear"][1] == 4 * (4 * cfg.L + 1) and prof["linear"][0] > 0
+    c = gpt.Decode(6, opts)
+    np.testing.assert_array_equal(np.stack(b, axis=1), a[:, :10])
+    np.testing.assert_array_equal(c, a[:, 14:20])
+    gpt.EnableStepTiming(True)
+    gpt.Decode(5, opts)
+    assert len(gpt.StepTimes(5)) == 5 and (gpt.StepTimes(5) > 0).all()
+    gpt.close()
