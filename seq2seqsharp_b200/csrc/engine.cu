@@ -862,7 +862,7 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   TSB_CHECK(g->T > 0 && g->B > 0, "gpt_step_host: prefill first");
   TSB_CHECK(g->T + 1 <= c.max_tokens, "OOM: KV-cache capacity %d exceeded", c.max_tokens);
   const int B = g->B;
-  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)c.max_batch * 8, cudaHostAllocDefault));
+  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)c.max_batch * 4 + 64, cudaHostAllocDefault));
   TSB_TRY(upload_blocked(g, opt));
   if (!g->gexec) TSB_TRY(set_state(g, 0));
   TSB_TRY(ensure_graph(g, opt, 1));
