@@ -163,6 +163,23 @@ TSB200_API int TSB200_LinearBiasAct(int device, int dtype, void* y, float* y_f32
                                     void* workspace, int64_t workspace_bytes, void* stream);
 TSB200_API int64_t TSB200_LinearWorkspaceBytes(int M, int K, int N);
 
+/* The engine's weight layout for decode: contiguous 16 KB tiles [32 rows][256 (F16) or 128 (F32) columns], column-tile
+ * major, zero padded, so that a CTA streams one contiguous byte range with TMA bulk copies.  PackWeight converts a
+ * row-major [K,N] matrix (F32 or F16 source) into `packed` (PackedWeightBytes bytes). */
+TSB200_API int64_t TSB200_PackedWeightBytes(int dtype, int K, int N);
+TSB200_API int TSB200_PackWeight(int device, int dtype, void* packed, const void* W, int src_dtype, int K, int N,
+                                 void* stream);
+/* y = act(bias + prologue(x) Wp) (+ residual) on packed weights.  norm_type -1: x [M,K] in `dtype`; 0 / 1: the input
+ * is the fp32 residual stream x_f32 [M,K] and LayerNorm / RMSNorm (gamma, beta, eps) is applied first, fused into the
+ * kernel (M <= 4 only).  M <= 4 runs the TMA-fed streaming GEMV; larger M the fallback kernels.  Replaces
+ * LayerNorm/RMSNorm + Affine + activation/gate/residual of one layer (PositionwiseFeedForward.cs:72-98,
+ * MultiHeadAttention.cs:130-137,234-237). */
+TSB200_API int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N);
+TSB200_API int TSB200_LinearPacked(int device, int dtype, void* y, float* y_f32, const void* x, const float* x_f32,
+                                   const void* gamma, const void* beta, int norm_type, float eps, const void* Wp,
+                                   const void* bias, const float* residual_f32, int M, int K, int N, int act,
+                                   void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Fused (residual +) LayerNorm / RMSNorm: x_f32[M,d] (+= delta when given) -> h[M,d] in `dtype`.
  * norm_type 0 = LayerNorm (beta may be NULL), 1 = RMSNorm.  Replaces gLNormalization / RMSNorm
  * (AdvFuncKernels.cs:613-685,791-845) plus the preceding "addt". */

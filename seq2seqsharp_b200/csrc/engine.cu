@@ -79,9 +79,12 @@ struct LayerW {
   void *cK = nullptr, *cV = nullptr;
 };
 
-struct Dest {  // where a logical tensor lives inside the engine's packed buffers
+struct Dest {  // where a logical tensor lives inside the engine's buffers
   void* base = nullptr;
   int64_t rows = 0, cols = 0, row_stride = 0, col_stride = 1;
+  // matrices of linear layers live in the tiled layout of gemv_stream.cu: logical column j -> packed column c0 + j*cs
+  bool packed = false;
+  int64_t c0 = 0, cs = 1;
 };
 
 struct GraphKey {
@@ -139,6 +142,8 @@ struct Gpt {
   std::vector<cudaEvent_t> step_ev;
   int step_ev_n = 0;
   int* pin_ids = nullptr;  // pinned host staging for TSB200_GptStepHost
+  int* err_flag = nullptr; // device word raised by a kernel whose bounded wait ran out
+  bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
 };
 
 enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_COUNT = 8 };
@@ -201,6 +206,11 @@ static int resolve(Gpt* g, const std::string& name, Dest* out) {
     return 1;
   };
   auto off = [&](void* base, int64_t elems) { return (void*)((char*)base + elems * g->es); };
+  auto setp = [&](void* base, int64_t rows, int64_t cols, int64_t c0, int64_t cs) {
+    out->base = base; out->rows = rows; out->cols = cols; out->packed = true; out->c0 = c0; out->cs = cs;
+    return 1;
+  };
+  out->packed = false;
   if (name == "TgtEmbeddings") return set(g->E, V, d, d, 1);
   if (name == "PosEmbedding") {
     TSB_CHECK(g->PE, "PosEmbedding given but the model's pe_type is not APE");
@@ -208,7 +218,7 @@ static int resolve(Gpt* g, const std::string& name, Dest* out) {
   }
   if (name == "GPTDecoder.layerNorm.m_alpha") return set(g->nf_g, 1, d, d, 1);
   if (name == "GPTDecoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
-  if (name == "FeedForward_Decoder_0.m_Whd") return set(g->head_w, d, V, V, 1);
+  if (name == "FeedForward_Decoder_0.m_Whd") return setp(g->head_w, d, V, 0, 1);
   if (name == "FeedForward_Decoder_0.m_Bd") return set(g->head_b, 1, V, V, 1);
   TSB_CHECK(starts_with(name, "GPTDecoder."), "unknown weight name '%s'", name.c_str());
   const std::string rest = name.substr(11);
@@ -222,34 +232,37 @@ static int resolve(Gpt* g, const std::string& name, Dest* out) {
   if (unit == "SelfAttn") {
     if (field == "layerNormQ.m_alpha") return set(L.n1_g, 1, d, d, 1);
     if (field == "layerNormQ.m_beta") return set(L.n1_b, 1, d, d, 1);
-    if (field == "W0") return set(L.wo, Hd, d, d, 1);
+    if (field == "W0") return setp(L.wo, Hd, d, 0, 1);
     if (field == "b0") return set(L.bo, 1, d, d, 1);
     if (c.attn_type == 0) {
-      if (field == "QKV") return set(L.wqkv, d, Nq, Nq, 1);
+      if (field == "QKV") return setp(L.wqkv, d, Nq, 0, 1);
       if (field == "QKVb") return set(L.bqkv, 1, Nq, Nq, 1);
     } else {
-      if (field == "Q") return set(L.wqkv, d, Hd, Nq, 1);
+      if (field == "Q") return setp(L.wqkv, d, Hd, 0, 1);
       if (field == "Qb") return set(L.bqkv, 1, Hd, Nq, 1);
-      if (field == "K") return set(off(L.wqkv, Hd), d, KVd, Nq, 1);
+      if (field == "K") return setp(L.wqkv, d, KVd, Hd, 1);
       if (field == "Kb") return set(off(L.bqkv, Hd), 1, KVd, Nq, 1);
-      if (field == "V") return set(off(L.wqkv, Hd + KVd), d, KVd, Nq, 1);
+      if (field == "V") return setp(L.wqkv, d, KVd, Hd + KVd, 1);
       if (field == "Vb") return set(off(L.bqkv, Hd + KVd), 1, KVd, Nq, 1);
     }
   } else if (unit == "PosFFN") {
     if (field == "layerNorm2.m_alpha") return set(L.n2_g, 1, d, d, 1);
     if (field == "layerNorm2.m_beta") return set(L.n2_b, 1, d, d, 1);
     const int64_t w1c = g->glu ? 2 * F : F, cs = g->glu ? 2 : 1;
-    if (field == "feedForwardLayer1.m_Whd") return set(L.w1, d, F, w1c, cs);
+    if (field == "feedForwardLayer1.m_Whd") return setp(L.w1, d, F, 0, cs);
     if (field == "feedForwardLayer1.m_Bd") return set(L.b1, 1, F, w1c, cs);
-    if (g->glu && field == "feedForwardLayer3.m_Whd") return set(off(L.w1, 1), d, F, w1c, cs);
+    if (g->glu && field == "feedForwardLayer3.m_Whd") return setp(L.w1, d, F, 1, cs);
     if (g->glu && field == "feedForwardLayer3.m_Bd") return set(off(L.b1, 1), 1, F, w1c, cs);
-    if (field == "feedForwardLayer2.m_Whd") return set(L.w2, F, d, d, 1);
+    if (field == "feedForwardLayer2.m_Whd") return setp(L.w2, F, d, 0, 1);
     if (field == "feedForwardLayer2.m_Bd") return set(L.b2, 1, d, d, 1);
   }
   TSB_FAIL("unknown weight name '%s'", name.c_str());
 }
 
 static int copy_into(Gpt* g, const Dest& dst, const void* src_dev, int src_dtype) {
+  if (dst.packed)
+    return launch_pack(g->c.device, g->st, g->c.dtype, dst.base, src_dtype, src_dev, (int)dst.rows, (int)dst.cols, (int)dst.rows,
+                       (int)dst.c0, (int)dst.cs, g->s);
   TSB200Tensor r{}, sv{};
   r.data = dst.base; r.dtype = g->c.dtype; r.ndim = 2;
   r.sizes[0] = dst.rows; r.sizes[1] = dst.cols; r.strides[0] = dst.row_stride; r.strides[1] = dst.col_stride;
@@ -318,6 +331,32 @@ static Epilogue make_ep(const void* bias, const float* residual, void* y, float*
   return e;
 }
 
+// One linear layer of the engine on packed weights.  With `ng` the input is the fp32 residual stream and the layer's
+// LayerNorm / RMSNorm comes first: fused into the streaming GEMV as a prologue for decode-sized row counts, a
+// separate launch (into g->h) otherwise.
+static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid, const void* ng, const void* nb, void* h_tmp,
+                         const void* Wp, int K, int N, const Epilogue& ep) {
+  const TSB200GptConfig& c = g->c;
+  const int dev = c.device, dt = c.dtype;
+  if (rows <= 4) {
+    prof_begin(g);
+    const int r = launch_gemv_stream(dev, g->st, dt, Wp, ng ? (const void*)x_resid : x_T, ng ? (c.norm_type == 0 ? 2 : 1) : 0, ng,
+                                     c.norm_type == 0 ? nb : nullptr, c.eps, rows, K, N, ep, g->err_flag, g->pdl, g->lin_ws,
+                                     g->lin_ws_bytes, g->s);
+    if (r != 2) {
+      prof_end(g, KC_LINEAR);
+      return r;
+    }
+  }
+  if (ng) {
+    PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, h_tmp, const_cast<float*>(x_resid), nullptr, ng, c.norm_type == 0 ? nb : nullptr,
+                                       c.norm_type, c.eps, rows, K, g->s));
+    x_T = h_tmp;
+  }
+  PROF(KC_LINEAR, launch_linear(dev, g->st, dt, x_T, Wp, rows, K, N, ep, g->lin_ws, g->lin_ws_bytes, g->s, true));
+  return 1;
+}
+
 // One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
 // With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
 static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
@@ -342,17 +381,15 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   const int act = c.act;
   for (int k = 0; k < c.L; ++k) {
     LayerW& L = g->L[k];
-    PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
-    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->h, L.wqkv, rows, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n1_g, L.n1_b, g->h, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
     void* qp = g->qkv;
     void* kp = (char*)g->qkv + (int64_t)Hd * g->es;
     void* vp = (char*)g->qkv + (int64_t)(Hd + KVd) * g->es;
     PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
     PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
-    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->attn, L.wo, rows, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
-    PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.n2_g, c.norm_type == 0 ? L.n2_b : nullptr, c.norm_type, c.eps, rows, d, g->s));
-    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->h, L.w1, rows, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu), g->lin_ws, g->lin_ws_bytes, g->s));
-    PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->ffn, L.w2, rows, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+    TSB_TRY(engine_linear(g, rows, g->attn, nullptr, nullptr, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0)));
+    TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n2_g, L.n2_b, g->h, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu)));
+    TSB_TRY(engine_linear(g, rows, g->ffn, nullptr, nullptr, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0)));
   }
   const float* xlast = g->x;
   if (S > 1) {
@@ -361,8 +398,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     TSB_TRY(check_launch("gather_last"));
     xlast = g->xl;
   }
-  PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->hl, const_cast<float*>(xlast), nullptr, g->nf_g, c.norm_type == 0 ? g->nf_b : nullptr, c.norm_type, c.eps, B, d, g->s));
-  PROF(KC_LINEAR, launch_linear(dev, g->st, dt, g->hl, g->head_w, B, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0), g->lin_ws, g->lin_ws_bytes, g->s));
+  TSB_TRY(engine_linear(g, B, nullptr, xlast, g->nf_g, g->nf_b, g->hl, g->head_w, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0)));
   return 1;
 }
 
@@ -382,6 +418,17 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
   count_launch(dev);
   prof_end(g, KC_COMMIT);
   return check_launch("commit");
+}
+
+// A kernel whose bounded wait ran out raises the device error word; surface it as a failure of the call.
+static int check_err_flag(Gpt* g) {
+  int e = 0;
+  TSB_CUDA(cudaMemcpy(&e, g->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (e) {
+    cudaMemset(g->err_flag, 0, sizeof(int));
+    TSB_FAIL("a kernel gave up waiting on a shared-memory barrier (internal error); results of this call are invalid");
+  }
+  return 1;
 }
 
 static uint64_t hash_blocked(const int32_t* b, int n) {
@@ -498,17 +545,17 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   }
   G_ALLOC(g->nf_g, d * es);
   G_ALLOC(g->nf_b, d * es);
-  G_ALLOC(g->head_w, d * V * es);
+  G_ALLOC(g->head_w, packed_bytes(cc.dtype, (int)d, (int)V));
   G_ALLOC(g->head_b, V * es);
   g->L.resize(cc.L);
   const int64_t cache_elems = (int64_t)cc.max_batch * cc.Hkv * cc.max_tokens * cc.hd;
   for (int k = 0; k < cc.L; ++k) {
     LayerW& L = g->L[k];
     G_ALLOC(L.n1_g, d * es); G_ALLOC(L.n1_b, d * es); G_ALLOC(L.n2_g, d * es); G_ALLOC(L.n2_b, d * es);
-    G_ALLOC(L.wqkv, d * g->Nqkv * es); G_ALLOC(L.bqkv, (int64_t)g->Nqkv * es);
-    G_ALLOC(L.wo, Hd * d * es); G_ALLOC(L.bo, d * es);
-    G_ALLOC(L.w1, d * F * es * (g->glu ? 2 : 1)); G_ALLOC(L.b1, F * es * (g->glu ? 2 : 1));
-    G_ALLOC(L.w2, F * d * es); G_ALLOC(L.b2, d * es);
+    G_ALLOC(L.wqkv, packed_bytes(cc.dtype, (int)d, g->Nqkv)); G_ALLOC(L.bqkv, (int64_t)g->Nqkv * es);
+    G_ALLOC(L.wo, packed_bytes(cc.dtype, (int)Hd, (int)d)); G_ALLOC(L.bo, d * es);
+    G_ALLOC(L.w1, packed_bytes(cc.dtype, (int)d, (int)(F * (g->glu ? 2 : 1)))); G_ALLOC(L.b1, F * es * (g->glu ? 2 : 1));
+    G_ALLOC(L.w2, packed_bytes(cc.dtype, (int)F, (int)d)); G_ALLOC(L.b2, d * es);
     G_ALLOC(L.cK, cache_elems * es); G_ALLOC(L.cV, cache_elems * es);
     if (!fill_const(g, L.n1_g, d, 1.0f) || !fill_const(g, L.n2_g, d, 1.0f)) return fail();
   }
@@ -534,13 +581,21 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   int64_t maxN = V > 2 * F ? V : 2 * F;
   if (g->Nqkv > maxN) maxN = g->Nqkv;
   g->lin_ws_bytes = linear_workspace_bytes(8, (int)(F > d ? F : d), (int)maxN);
+  {
+    const int shapes[5][2] = {{(int)d, g->Nqkv}, {(int)Hd, (int)d}, {(int)d, (int)(F * (g->glu ? 2 : 1))}, {(int)F, (int)d}, {(int)d, (int)V}};
+    for (auto& sh : shapes) {
+      const int64_t b = stream_workspace_bytes(cc.dtype, 4, sh[0], sh[1], st->sm_count);
+      if (b > g->lin_ws_bytes) g->lin_ws_bytes = b;
+    }
+  }
   G_ALLOC(g->lin_ws, g->lin_ws_bytes);
+  G_ALLOC(g->err_flag, 64);
   g->attn_ws_bytes = attn_workspace_bytes(MB, cc.H, cc.hd, cc.max_tokens);
   G_ALLOC(g->attn_ws, g->attn_ws_bytes);
   g->topp_ws_bytes = TSB200_TopPWorkspaceBytes(MB, cc.V);
   G_ALLOC(g->topp_ws, g->topp_ws_bytes);
 #undef G_ALLOC
-  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device)) return fail();
+  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device)) return fail();
   if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) {
     set_last_error("gpt_create: cudaEventCreate failed");
     return fail();
@@ -611,7 +666,7 @@ int TSB200_GptGetWeightPtr(void* h, const char* name, void** ptr, int64_t* rows,
   TSB_CHECK(g && name && ptr, "gpt_get_weight_ptr: null argument");
   Dest dst;
   TSB_TRY(resolve(g, name, &dst));
-  TSB_CHECK(dst.col_stride == 1 && dst.row_stride == dst.cols, "gpt_get_weight_ptr: '%s' is stored packed with other tensors", name);
+  TSB_CHECK(!dst.packed && dst.col_stride == 1 && dst.row_stride == dst.cols, "gpt_get_weight_ptr: '%s' is stored in the engine's packed layout", name);
   *ptr = dst.base;
   if (rows) *rows = dst.rows;
   if (cols) *cols = dst.cols;
@@ -765,6 +820,7 @@ int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int
   TSB_CUDA(cudaEventRecord(g->ev1, g->s));
   TSB_CUDA(cudaStreamSynchronize(g->s));
   TSB_CUDA(cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1));
+  TSB_TRY(check_err_flag(g));
   g->last_launches = g->graph_nodes * done;
   g->T += done;
   g->step += (uint32_t)done;

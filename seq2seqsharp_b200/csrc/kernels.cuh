@@ -15,8 +15,20 @@ struct Epilogue {
 
 int launch_norm_residual(int device, DeviceState* st, int dtype, void* h, float* x, const void* delta, const void* gamma,
                          const void* beta, int norm_type, float eps, int M, int d, cudaStream_t s);
+// `packed`: W is in the engine's tiled layout (see gemv_stream.cu) instead of row-major [K,N]
 int launch_linear(int device, DeviceState* st, int dtype, const void* x, const void* W, int M, int K, int N,
-                  const Epilogue& ep, void* ws, int64_t ws_bytes, cudaStream_t s);
+                  const Epilogue& ep, void* ws, int64_t ws_bytes, cudaStream_t s, bool packed);
+// streaming GEMV on packed weights, M <= 4; xmode 0: x is T [M,K]; 1/2: x is the fp32 residual stream and RMSNorm /
+// LayerNorm (gamma, beta, eps) is applied as a prologue.  Returns 1 ok, 0 error, 2 shape not handled.
+int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, const void* x, int xmode, const void* gamma,
+                       const void* beta, float eps, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws,
+                       int64_t ws_bytes, cudaStream_t s);
+int64_t stream_workspace_bytes(int dtype, int M, int K, int N, int sm_count);
+int64_t packed_bytes(int dtype, int K, int N);
+int packed_tile_cols(int dtype);
+int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols, int K,
+                int c0, int cs, cudaStream_t s);
+int init_stream_attrs(int device);
 int64_t linear_workspace_bytes(int M, int K, int N);
 int launch_attention(int device, DeviceState* st, int dtype, void* out, const void* q, int64_t q_rs, const void* cK,
                      const void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0, int Tmax, int splits_hint,

@@ -268,10 +268,10 @@ __global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict
 }
 
 static int pick_splits(DeviceState* st, int B, int Hkv_groups, int T) {
-  // enough CTAs to cover the SMs about twice, at least 256 keys per split
+  // enough CTAs to cover the SMs about twice, at least 32 keys per split (a CTA covers 8..16 keys per iteration)
   const int64_t base = (int64_t)B * Hkv_groups;
   int s = (int)((2LL * st->sm_count + base - 1) / base);
-  const int max_by_len = (T + 255) / 256;
+  const int max_by_len = (T + 31) / 32;
   if (s > max_by_len) s = max_by_len;
   if (s < 1) s = 1;
   if (s > 64) s = 64;

@@ -64,7 +64,7 @@ constexpr int kGemvUnroll = 4;
 template <typename T, int M>
 __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const T* __restrict__ x, const T* __restrict__ W, int K, int N,
                                                             int kchunk, int ksplit, float* partials, unsigned int* counters,
-                                                            Epilogue ep) {
+                                                            Epilogue ep, int packedKB) {
   constexpr int VEC = WVec<T>::N;
   constexpr int NT = 32 * VEC;
   extern __shared__ float smem[];  // phase 1: xs[M][kchunk]; phase 2: red[warps][M][NT]
@@ -87,13 +87,14 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const T* __restrict_
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[m][e] = 0.0f;
 
-  const T* wp = W + c0;
+  // row-major [K,N] (packedKB == 0) or the engine's tiled layout [ct][kb][32][NT] (packedKB = tiles along K)
+  const T* wp = packedKB ? W + (int64_t)ct * packedKB * (32 * NT) + lane * VEC : W + c0;
   for (int k = k0 + w; k < k1; k += kGemvWarps * kGemvUnroll) {
     WVec<T> wv[kGemvUnroll];
 #pragma unroll
     for (int u = 0; u < kGemvUnroll; ++u) {
       const int kk = k + u * kGemvWarps;
-      if (kk < k1 && col_ok) wv[u].load(wp + (int64_t)kk * N);
+      if (kk < k1 && (col_ok || packedKB)) wv[u].load(packedKB ? wp + (int64_t)kk * NT : wp + (int64_t)kk * N);
       else wv[u].zero();
     }
 #pragma unroll
@@ -181,6 +182,7 @@ struct GemmArgs {
   int64_t s_m, s_n, s_b;      // src (beta term / bias broadcast)
   int64_t c_m, c_n, c_b;
   float alpha, beta;
+  int b_packedKB, b_NT;       // B in the engine's tiled layout when b_packedKB > 0
 };
 
 template <typename T, bool EPI>
@@ -202,7 +204,11 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g, Epilogue 
     for (int i = threadIdx.x; i < 64 * 16; i += 256) {
       const int kk = i / 64, nn = i % 64;
       const int k = k0 + kk, n = n0 + nn;
-      Bs[kk][nn] = (k < g.K && n < g.N) ? to_f<T>(B[k * g.b_k + n * g.b_n]) : 0.0f;
+      float bv = 0.0f;
+      if (k < g.K && n < g.N)
+        bv = g.b_packedKB ? to_f<T>(B[((int64_t)(n / g.b_NT) * g.b_packedKB + k / 32) * (32 * g.b_NT) + (int64_t)(k % 32) * g.b_NT + n % g.b_NT])
+                          : to_f<T>(B[k * g.b_k + n * g.b_n]);
+      Bs[kk][nn] = bv;
     }
     __syncthreads();
 #pragma unroll
@@ -315,7 +321,7 @@ int init_linear_attrs(int device) {
 
 template <typename T, int M>
 static int launch_gemv_m(int device, DeviceState* st, const T* x, const T* W, int K, int N, const Epilogue& ep, void* ws,
-                         int64_t ws_bytes, cudaStream_t s) {
+                         int64_t ws_bytes, cudaStream_t s, int packedKB) {
   constexpr int NT = 32 * WVec<T>::N;
   GemvPlan p = plan_gemv<T>(st, M, K, N);
   const int64_t cnt_bytes = ((int64_t)p.ctiles * 4 + 255) & ~255LL;
@@ -329,7 +335,7 @@ static int launch_gemv_m(int device, DeviceState* st, const T* x, const T* W, in
   unsigned int* counters = reinterpret_cast<unsigned int*>(ws);
   float* partials = ws ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + cnt_bytes) : nullptr;
   dim3 grid(p.ctiles, p.ksplit);
-  gemv_kernel<T, M><<<grid, kGemvThreads, p.smem, s>>>(x, W, K, N, p.kchunk, p.ksplit, partials, counters, ep);
+  gemv_kernel<T, M><<<grid, kGemvThreads, p.smem, s>>>(x, W, K, N, p.kchunk, p.ksplit, partials, counters, ep, packedKB);
   count_launch(device);
   return check_launch("gemv");
 }
@@ -347,10 +353,11 @@ static int launch_generic(int device, const GemmArgs& g, const Epilogue* ep, cud
 
 // y = epilogue(x[M,K] W[K,N]); x, W contiguous.  counters in `ws` must be zero on first use (they self-reset).
 int launch_linear(int device, DeviceState* st, int dtype, const void* x, const void* W, int M, int K, int N,
-                  const Epilogue& ep, void* ws, int64_t ws_bytes, cudaStream_t s) {
+                  const Epilogue& ep, void* ws, int64_t ws_bytes, cudaStream_t s, bool packed) {
   if (M == 0) return 1;
   const int vec = dtype == TSB200_F16 ? 8 : 4;
-  const bool gemv_ok = (N % vec == 0) && (((uintptr_t)W % 16) == 0) && M <= 16;
+  const int packedKB = packed ? (K + 31) / 32 : 0;
+  const bool gemv_ok = (packed || N % vec == 0) && (((uintptr_t)W % 16) == 0) && M <= 16;
   if (gemv_ok) {
     for (int m0 = 0; m0 < M; m0 += 8) {
       const int mb = M - m0 < 8 ? M - m0 : 8;
@@ -359,7 +366,7 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
       if (e2.residual) e2.residual += (int64_t)m0 * No;
       if (e2.y32) e2.y32 += (int64_t)m0 * No;
       if (e2.y) e2.y = (char*)e2.y + (int64_t)m0 * No * (dtype == TSB200_F16 ? 2 : 4);
-#define TSB_GEMV(T, MM) launch_gemv_m<T, MM>(device, st, (const T*)x + (int64_t)m0 * K, (const T*)W, K, N, e2, ws, ws_bytes, s)
+#define TSB_GEMV(T, MM) launch_gemv_m<T, MM>(device, st, (const T*)x + (int64_t)m0 * K, (const T*)W, K, N, e2, ws, ws_bytes, s, packedKB)
 #define TSB_GEMV_SW(T)                                  \
   switch (mb) {                                         \
     case 1: TSB_TRY(TSB_GEMV(T, 1)); break;             \
@@ -382,6 +389,8 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
   g.M = M; g.N = N; g.K = K; g.batch = 1;
   g.a_m = K; g.a_k = 1; g.b_k = N; g.b_n = 1;
   g.alpha = 1.0f; g.beta = 0.0f;
+  g.b_packedKB = packedKB;
+  g.b_NT = 32 * vec;
   if (dtype == TSB200_F16) return launch_generic<__half>(device, g, &ep, s);
   return launch_generic<float>(device, g, &ep, s);
 }
@@ -459,7 +468,7 @@ int TSB200_LinearBiasAct(int device, int dtype, void* y, float* y_f32, const voi
     const int64_t z = workspace_bytes < 65536 ? workspace_bytes : 65536;
     TSB_CUDA(cudaMemsetAsync(workspace, 0, (size_t)z, s));
   }
-  return launch_linear(device, st, dtype, x, W, M, K, N, ep, workspace, workspace_bytes, s);
+  return launch_linear(device, st, dtype, x, W, M, K, N, ep, workspace, workspace_bytes, s, false);
 }
 
 }  // extern "C"

@@ -23,14 +23,23 @@ def _stream():
 
 
 def _time(fn, iters):
-    fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
+    """Average device time of one call: `iters` calls are captured into one CUDA graph (so host launch overhead is
+    not on the clock) and the graph is timed with CUDA events on the launching stream."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
         fn()
-    e1.record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
 
 
@@ -38,7 +47,7 @@ def case_gemv(a):
     dt = torch.float16 if a.dtype == "f16" else torch.float32
     nd = N.F16 if a.dtype == "f16" else N.F32
     # several weight matrices are cycled so that consecutive launches never find their weights in L2
-    n_mats = max(2, int(300e6 // (a.K * a.N * (2 if a.dtype == "f16" else 4))) + 1)
+    n_mats = max(3, int(1.2e9 // (a.K * a.N * (2 if a.dtype == "f16" else 4))) + 1)
     Ws = [(torch.randn(a.K, a.N, device="cuda") * 0.02).to(dt) for _ in range(n_mats)]
     x = torch.randn(a.M, a.K, device="cuda").to(dt)
     b = torch.zeros(a.N, device="cuda", dtype=dt)
@@ -56,6 +65,41 @@ def case_gemv(a):
     ms = _time(run, a.iters)
     nbytes = a.K * a.N * W_es(a) + a.N * W_es(a)
     print("gemv M=%d K=%d N=%d %s: %.3f ms/launch, %.1f GB/s algorithmic (%d matrices cycled)" % (a.M, a.K, a.N, a.dtype, ms, nbytes / ms / 1e6, n_mats))
+
+
+def case_gemv_packed(a):
+    """The engine's TMA-fed streaming GEMV on packed tiles (M <= 4), optionally with the fused RMSNorm prologue."""
+    dt = torch.float16 if a.dtype == "f16" else torch.float32
+    nd = N.F16 if a.dtype == "f16" else N.F32
+    es = W_es(a)
+    pb = N.lib().TSB200_PackedWeightBytes(nd, a.K, a.N)
+    n_mats = max(3, int(1.2e9 // pb) + 1)
+    W = (torch.randn(a.K, a.N, device="cuda") * 0.02).to(dt)
+    Wps = []
+    for _ in range(n_mats):
+        Wp = torch.empty(pb, dtype=torch.uint8, device="cuda")
+        N.call("TSB200_PackWeight", 0, nd, Wp.data_ptr(), W.data_ptr(), nd, a.K, a.N, _stream())
+        Wps.append(Wp)
+    x = torch.randn(a.M, a.K, device="cuda").to(dt)
+    x32 = torch.randn(a.M, a.K, device="cuda")
+    gamma = torch.ones(a.K, device="cuda", dtype=dt)
+    b = torch.zeros(a.N, device="cuda", dtype=dt)
+    y = torch.empty(a.M, a.N, device="cuda", dtype=dt)
+    wsb = N.lib().TSB200_LinearPackedWorkspaceBytes(nd, a.M, a.K, a.N)
+    ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+    i = [0]
+
+    def run():
+        Wp = Wps[i[0] % n_mats]
+        i[0] += 1
+        N.call("TSB200_LinearPacked", 0, nd, y.data_ptr(), None, None if a.norm else x.data_ptr(), x32.data_ptr() if a.norm else None,
+               gamma.data_ptr() if a.norm else None, None, 1 if a.norm else -1, 1e-6, Wp.data_ptr(), b.data_ptr(), None, a.M, a.K, a.N,
+               N.ACT_NONE, ws.data_ptr(), wsb, _stream())
+
+    ms = _time(run, a.iters)
+    nbytes = a.K * a.N * es + a.N * es
+    print("gemv_packed M=%d K=%d N=%d %s norm=%d: %.4f ms/launch, %.1f GB/s algorithmic (%d matrices cycled)" % (
+        a.M, a.K, a.N, a.dtype, a.norm, ms, nbytes / ms / 1e6, n_mats))
 
 
 def W_es(a):
@@ -87,7 +131,15 @@ def case_topp(a):
     g = torch.Generator(device="cuda").manual_seed(0)
     p = torch.softmax(torch.randn(a.rows, a.V, device="cuda", generator=g) * a.spread, dim=-1)
     u = torch.rand(a.rows, generator=torch.Generator().manual_seed(1))
-    ms = _time(lambda: Ops.TopPSample(p, a.topP, 0.0, None, u), a.iters)
+    out = torch.empty(a.rows, dtype=torch.int32, device="cuda")
+    wsb = N.lib().TSB200_TopPWorkspaceBytes(a.rows, a.V)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    ud = u.cuda()
+    hist = torch.arange(1, a.hist + 1, dtype=torch.int32, device="cuda").repeat(a.rows, 1).contiguous() if a.hist else None
+    hlen = torch.full((a.rows,), a.hist, dtype=torch.int32, device="cuda") if a.hist else None
+    ms = _time(lambda: N.call("TSB200_TopPSample", 0, out.data_ptr(), p.data_ptr(), a.rows, a.V, a.topP, 2.0 if a.hist else 0.0,
+                              hist.data_ptr() if a.hist else None, hlen.data_ptr() if a.hist else None, a.hist, ud.data_ptr(),
+                              ws.data_ptr(), wsb, _stream()), a.iters)
     print("topp rows=%d V=%d topP=%g: %.3f ms/launch" % (a.rows, a.V, a.topP, ms))
 
 
@@ -109,7 +161,8 @@ def case_attention(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemv", "decode", "topp", "attention"])
+    ap.add_argument("case", choices=["gemv", "gemv_packed", "decode", "topp", "attention"])
+    ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--N", type=int, default=22016)
@@ -122,6 +175,7 @@ def main():
     ap.add_argument("--V", type=int, default=32000)
     ap.add_argument("--topP", type=float, default=0.95)
     ap.add_argument("--spread", type=float, default=0.05)
+    ap.add_argument("--hist", type=int, default=0)
     ap.add_argument("--B", type=int, default=4)
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=8)
@@ -131,7 +185,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("kernel_cases needs a GPU (no CPU fallback)")
     torch.cuda.set_device(0)
-    {"gemv": case_gemv, "decode": case_decode, "topp": case_topp, "attention": case_attention}[a.case](a)
+    {"gemv": case_gemv, "gemv_packed": case_gemv_packed, "decode": case_decode, "topp": case_topp, "attention": case_attention}[a.case](a)
 
 
 if __name__ == "__main__":

@@ -194,3 +194,71 @@ def test_softmax_argmax_fused(cuda, oracle):
     # temperature
     N.call("TSB200_SoftmaxArgmax", 0, ids.data_ptr(), probs.data_ptr(), dev(z).data_ptr(), B, V, 0.7, None, 0, stream())
     np.testing.assert_allclose(host(probs), oracle.softmax(z / np.float32(0.7)), atol=1e-7, rtol=5e-5)
+
+
+def linear_packed(x, W, bias, act, norm=None, residual=None, dtype=torch.float32, want_f32=False):
+    """norm = (norm_type, gamma, beta, eps): x is then the fp32 residual stream."""
+    M, K = x.shape
+    Nn = W.shape[1]
+    nd = N.F16 if dtype == torch.float16 else N.F32
+    glu = act in (N.ACT_GLU_NOACT, N.ACT_SWIGLU)
+    No = Nn // 2 if glu else Nn
+    pb = N.lib().TSB200_PackedWeightBytes(nd, K, Nn)
+    Wp = torch.empty(pb, dtype=torch.uint8, device="cuda")
+    N.call("TSB200_PackWeight", 0, nd, Wp.data_ptr(), W.data_ptr(), N.F16 if W.dtype == torch.float16 else N.F32, K, Nn, stream())
+    y = torch.empty(M, No, device="cuda", dtype=dtype)
+    y32 = torch.empty(M, No, device="cuda", dtype=torch.float32) if want_f32 else None
+    wsb = N.lib().TSB200_LinearPackedWorkspaceBytes(nd, M, K, Nn)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    nt, g, b, eps = norm if norm is not None else (-1, None, None, 0.0)
+    N.call("TSB200_LinearPacked", 0, nd, y.data_ptr(), y32.data_ptr() if want_f32 else None,
+           x.data_ptr() if norm is None else None, x.data_ptr() if norm is not None else None,
+           g.data_ptr() if g is not None else None, b.data_ptr() if b is not None else None, nt, eps, Wp.data_ptr(),
+           bias.data_ptr() if bias is not None else None, residual.data_ptr() if residual is not None else None, M, K, Nn, act,
+           ws.data_ptr(), wsb, stream())
+    return y32 if want_f32 else y
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float16, 4e-3)])
+@pytest.mark.parametrize("M,K,Nn", [(1, 512, 1536), (1, 4096, 6144), (2, 768, 3072), (4, 2048, 8192), (1, 11008, 4096),
+                                    (1, 64, 96), (3, 100, 40), (1, 4096, 32000), (1, 96, 1009), (6, 256, 512), (20, 130, 72)])
+def test_linear_packed_streaming_gemv(cuda, oracle, dtype, tol, M, K, Nn):
+    """The TMA-fed stream-K GEMV on packed tiles (M <= 4) and the packed fallbacks (M > 4), every epilogue."""
+    rng = np.random.default_rng(M * 17 + K + Nn)
+    x = dev(rng.standard_normal((M, K)).astype(np.float32), dtype)
+    W = dev((rng.standard_normal((K, Nn)) * 0.05).astype(np.float32), dtype)
+    b = dev((rng.standard_normal((1, Nn)) * 0.1).astype(np.float32), dtype)
+    ref = oracle.addmm(1.0, host(b), 1.0, host(x), host(W))
+    scale = max(1.0, float(np.abs(ref).max()))
+    np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype)), ref, atol=tol * scale)
+    np.testing.assert_allclose(host(linear_packed(x, W, None, N.ACT_RELU, dtype=dtype)), oracle.act(ref - host(b), 0), atol=tol * scale)
+    np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_GELU, dtype=dtype)), oracle.act(ref, 5), atol=tol * scale)
+    res = dev(rng.standard_normal((M, Nn)).astype(np.float32))
+    np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_NONE, residual=res, dtype=dtype, want_f32=True)), ref + host(res), atol=tol * scale)
+    if Nn % 2 == 0:
+        a, g = ref[:, 0::2], ref[:, 1::2]
+        np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_GLU_NOACT, dtype=dtype)), a * g, atol=tol * scale * scale)
+        np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_SWIGLU, dtype=dtype)), oracle.act(a, 1) * g, atol=tol * scale * scale)
+    # determinism of the stream-K reduction
+    first = host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype))
+    for _ in range(3):
+        np.testing.assert_array_equal(host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype)), first)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float16, 6e-3)])
+@pytest.mark.parametrize("norm_type", [0, 1])
+@pytest.mark.parametrize("M,K,Nn", [(1, 512, 1536), (3, 768, 2304), (1, 4096, 6144), (4, 100, 264)])
+def test_linear_packed_with_fused_norm(cuda, oracle, dtype, tol, norm_type, M, K, Nn):
+    rng = np.random.default_rng(K + norm_type)
+    x = dev((rng.standard_normal((M, K)) * 1.7 + 0.2).astype(np.float32))
+    W = dev((rng.standard_normal((K, Nn)) * 0.05).astype(np.float32), dtype)
+    b = dev((rng.standard_normal((1, Nn)) * 0.1).astype(np.float32), dtype)
+    g = dev((1 + 0.1 * rng.standard_normal(K)).astype(np.float32), dtype)
+    be = dev((0.1 * rng.standard_normal(K)).astype(np.float32), dtype)
+    h = oracle.layernorm(host(x), host(g), host(be), 1e-6) if norm_type == 0 else oracle.rmsnorm(host(x), host(g), None, 1e-6)
+    if dtype == torch.float16:
+        h = h.astype(np.float16).astype(np.float32)   # the normalised activations are rounded to the model dtype
+    ref = oracle.addmm(1.0, host(b), 1.0, h, host(W))
+    scale = max(1.0, float(np.abs(ref).max()))
+    out = linear_packed(x, W, b, N.ACT_NONE, norm=(norm_type, g, be if norm_type == 0 else None, 1e-6), dtype=dtype)
+    np.testing.assert_allclose(host(out), ref, atol=tol * scale)
