@@ -140,6 +140,23 @@ TSB200_API int TSB200_TopPSample(int device, int32_t* out, const float* probs, i
                                  float repeatPenalty, const int32_t* history, const int32_t* history_len,
                                  int history_stride, const float* u, void* workspace, int64_t workspace_bytes,
                                  void* stream);
+/* Top-P sampling for callers that must not allocate device memory.  (No counterpart in the reference: its TopPSample
+ * runs on the host.)  Some hosts of this library cannot call cudaMalloc on the sampling path: a serving loop that has
+ * given all remaining device memory to its own pool (the reference reserves a fixed share of the GPU up front and
+ * treats any later allocation failure as out-of-memory), or a per-token loop where the implicit device-wide
+ * synchronisation of an allocation would stall every stream.  This variant takes the same inputs and writes the same
+ * output as TSB200_TopPSample but sorts inside a 5 MiB scratch block built into the library, so it calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *   - Limit: rows * V <= 262144 (e.g. 4 rows of a 65536-word vocabulary, 8 rows of 32000).  Larger requests fail with a
+ *     message naming the limit; use TSB200_TopPSample with your own workspace for those.
+ *   - The first call on each device looks up the scratch block's device address and opts the kernel into its shared
+ *     memory size; make that first call before starting any stream capture.
+ *   - All calls on a device share the one scratch block, which keeps whatever the previous call left in it; nothing
+ *     in it needs clearing (the kernel writes every word before reading it), but two calls that overlap on the GPU
+ *     (different streams, or different host threads) race on it.  Serialise them. */
+TSB200_API int TSB200_TopPSampleStatic(int device, int32_t* out, const float* probs, int rows, int V, float topP,
+                                       float repeatPenalty, const int32_t* history, const int32_t* history_len,
+                                       int history_stride, const float* u, void* stream);
 /* u[i] = Philox4x32-10 uniform in [0,1) for (seed, seq_first + i, step); replaces the process-wide
  * System.Random (RandomGenerator.cs:41-46) with a counter-based stream per sequence */
 TSB200_API int TSB200_PhiloxUniform(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step,

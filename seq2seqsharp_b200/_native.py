@@ -103,6 +103,7 @@ def lib():
         "TSB200_BuildSelfTriMask": (i32, [i32, TP, TP, i32, f32, f32, vp]),
         "TSB200_TopPWorkspaceBytes": (i64, [i32, i32]),
         "TSB200_TopPSample": (i32, [i32, vp, vp, i32, i32, f32, f32, vp, vp, i32, vp, vp, i64, vp]),
+        "TSB200_TopPSampleStatic": (i32, [i32, vp, vp, i32, i32, f32, f32, vp, vp, i32, vp, vp]),
         "TSB200_PhiloxUniform": (i32, [i32, vp, i32, u64, u64, u32, vp]),
         "TSB200_LinearBiasAct": (i32, [i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp]),
         "TSB200_LinearWorkspaceBytes": (i64, [i32, i32, i32]),

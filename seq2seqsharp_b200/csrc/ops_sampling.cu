@@ -513,3 +513,41 @@ int TSB200_PhiloxUniform(int device, float* u, int n, uint64_t seed, uint64_t se
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ Top-P without any allocation
+// Scratch for TSB200_TopPSampleStatic: a fixed block of device memory that is part of the library image.  Every GPU
+// that loads the library holds these 5 MiB until the process exits.
+namespace tsb {
+constexpr int64_t kStaticToppBytes = 4LL * 65536 * 20;  // up to rows * V = 262144 probabilities per call (5 x uint32 each)
+static __device__ __align__(256) unsigned char g_topp_static_scratch[kStaticToppBytes];
+// Host code must not hand `g_topp_static_scratch` itself to a kernel: on the host that name is only a stand-in for the
+// symbol.  The real device address is looked up once per device, with that device current, and cached here.
+static void* g_topp_static_addr[kMaxDevices] = {};
+
+static int topp_static_setup(int device) {
+  if (g_topp_static_addr[device]) return 1;
+  void* p = nullptr;
+  TSB_CUDA(cudaGetSymbolAddress(&p, g_topp_static_scratch));
+  TSB_CHECK(p != nullptr, "topp_static: the scratch symbol has no device address");
+  TSB_TRY(init_topp_attrs(device));
+  g_topp_static_addr[device] = p;
+  return 1;
+}
+}  // namespace tsb
+
+extern "C" int TSB200_TopPSampleStatic(int device, int32_t* out, const float* probs, int rows, int V, float topP,
+                                        float repeatPenalty, const int32_t* history, const int32_t* history_len,
+                                        int history_stride, const float* u, void* stream) {
+  DeviceState* st;
+  TSB_TRY(use_device(device, &st));
+  TSB_CHECK(out && probs && u, "topp_static: null pointer");
+  TSB_CHECK(rows >= 0 && V > 0, "topp_static: bad shape");
+  TSB_CHECK(!history || history_len, "topp_static: history given without history_len");
+  const int64_t need = TSB200_TopPWorkspaceBytes(rows, V);
+  TSB_CHECK(need <= kStaticToppBytes,
+            "topp_static: rows*V = %lld exceeds the built-in scratch (at most %lld probabilities per call); use "
+            "TSB200_TopPSample with a caller-provided workspace", (long long)rows * V, (long long)(kStaticToppBytes / 20));
+  TSB_TRY(topp_static_setup(device));  // first call on this device: address lookup + kernel attribute, no allocation
+  return launch_topp(device, st, out, probs, rows, V, topP, repeatPenalty, history, history_len, history_stride, u,
+                     g_topp_static_addr[device], pick_stream(st, stream));
+}
