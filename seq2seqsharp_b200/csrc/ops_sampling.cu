@@ -169,7 +169,8 @@ __global__ void philox_kernel(float* u, int n, uint64_t seed, uint64_t seq_first
 //  4. all threads search the first k with acc[k] / acc_final >= u.
 constexpr int kTopPThreads = 1024;
 constexpr int kTopPWarps = kTopPThreads / 32;
-constexpr int kScanChunk = 4096;
+constexpr int kScanChunk = 1024;   // head of the prefix sum staged in shared memory
+constexpr int kRadixUnroll = 8;
 
 struct ToppSmem {
   uint32_t hist[kTopPWarps][256];  // per-warp digit counters / offsets
@@ -179,6 +180,11 @@ struct ToppSmem {
   float acc_final;
   int stop;
   int best_k;
+  int n_valid;
+  int ov_idx, stop_idx;   // first index of the window whose sum left the binade / reached topP
+  int k_next;
+  uint32_t acc_bits;
+  int2 warp_pair[32];
 };
 
 // The buffers are written earlier in the same kernel, so they are deliberately NOT const __restrict__ (no
@@ -190,15 +196,24 @@ __device__ __forceinline__ void radix_pass(const uint32_t* kin, const uint32_t* 
   const int beg = w * per_warp, end = min(n, beg + per_warp);
   for (int i = threadIdx.x; i < kTopPWarps * 256; i += blockDim.x) (&sm.hist[0][0])[i] = 0;
   __syncthreads();
-  // A: per-warp histogram of the (descending) digit
-  for (int base = beg; base < end; base += 32) {
-    const int j = base + lane;
-    const bool ok = j < end;
-    const uint32_t key = ok ? kin[j] : 0u;
-    const uint32_t dg = ok ? (255u - ((key >> shift) & 255u)) : 256u;
-    const uint32_t peers = __match_any_sync(0xffffffffu, dg);
-    if (ok && lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
-    __syncwarp();
+  // A: per-warp histogram of the (descending) digit; kRadixUnroll loads are in flight per lane
+  for (int base0 = beg; base0 < end; base0 += 32 * kRadixUnroll) {
+    uint32_t keys[kRadixUnroll];
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      keys[q] = j < end ? kin[j] : 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      if (base0 + q * 32 >= end) break;
+      const bool ok = j < end;
+      const uint32_t dg = ok ? (255u - ((keys[q] >> shift) & 255u)) : 256u;
+      const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+      if (ok && lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+      __syncwarp();
+    }
   }
   __syncthreads();
   // B: exclusive scan in (digit-major, warp-minor) order
@@ -240,25 +255,236 @@ __device__ __forceinline__ void radix_pass(const uint32_t* kin, const uint32_t* 
   }
   __syncthreads();
   // C: stable scatter
-  for (int base = beg; base < end; base += 32) {
-    const int j = base + lane;
-    const bool ok = j < end;
-    const uint32_t key = ok ? kin[j] : 0u;
-    const uint32_t idx = ok ? (first ? (uint32_t)j : iin[j]) : 0u;
-    const uint32_t dg = ok ? (255u - ((key >> shift) & 255u)) : 256u;
-    const uint32_t peers = __match_any_sync(0xffffffffu, dg);
-    const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-    uint32_t pos = 0;
-    if (ok) pos = sm.hist[w][dg] + rank;
-    __syncwarp();
-    if (ok) {
-      kout[pos] = key;
-      iout[pos] = idx;
-      if (lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+  for (int base0 = beg; base0 < end; base0 += 32 * kRadixUnroll) {
+    uint32_t keys[kRadixUnroll], idxs[kRadixUnroll];
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      keys[q] = j < end ? kin[j] : 0u;
+      idxs[q] = j < end ? (first ? (uint32_t)j : iin[j]) : 0u;
     }
-    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      if (base0 + q * 32 >= end) break;
+      const bool ok = j < end;
+      const uint32_t dg = ok ? (255u - ((keys[q] >> shift) & 255u)) : 256u;
+      const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+      const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+      uint32_t pos = 0;
+      if (ok) pos = sm.hist[w][dg] + rank;
+      __syncwarp();
+      if (ok) {
+        kout[pos] = keys[q];
+        iout[pos] = idxs[q];
+        if (lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+      }
+      __syncwarp();
+    }
   }
   __syncthreads();
+}
+
+// ---- exact parallel evaluation of   acc = 0; for k: acc = fl32(acc + w[k])   for sorted positive w ------------------
+// While acc stays inside one binade [2^e, 2^(e+1)) it is a multiple of ulp = 2^(e-23) and fl32(acc + w) equals
+// acc + ulp * (q + r), where w/ulp = q + f and r rounds f to nearest, ties to even of (acc/ulp + q).  So in units of
+// ulp every element is the map A -> A + inc[A & 1] with two integer increments, these maps compose associatively, and
+// a block-wide scan of the composed maps gives every partial sum of a window bit-exactly.  The first element whose
+// sum leaves the binade (A >= 2^24) is added with one ordinary fp32 add (the hardware rounds on the coarser grid) and
+// the next window starts from there.  The first kHead elements, where binades change every few elements, are added
+// one by one from shared memory.
+struct IncPair {
+  int i0, i1;  // increment when the incoming A is even / odd
+};
+__device__ __forceinline__ int sat_add(int a, int b) { return min(a + b, 1 << 29); }
+__device__ __forceinline__ IncPair compose(IncPair f, IncPair g) {  // first f, then g
+  IncPair h;
+  h.i0 = sat_add(f.i0, (f.i0 & 1) ? g.i1 : g.i0);
+  h.i1 = sat_add(f.i1, ((1 + f.i1) & 1) ? g.i1 : g.i0);
+  return h;
+}
+__device__ __forceinline__ void split_float(uint32_t bits, int& e, uint32_t& m) {
+  const uint32_t E = bits >> 23;
+  if (E == 0) {
+    e = -126;
+    m = bits & 0x7fffffu;
+  } else {
+    e = (int)E - 127;
+    m = (bits & 0x7fffffu) | 0x800000u;
+  }
+}
+__device__ __forceinline__ IncPair inc_of(uint32_t wbits, int e) {
+  int ew;
+  uint32_t m;
+  split_float(wbits, ew, m);
+  const int shift = e - ew;
+  IncPair r;
+  if (shift <= 0) {  // w is in the same (or a higher) binade: the sum leaves the binade at once
+    r.i0 = r.i1 = 1 << 29;
+    return r;
+  }
+  if (shift >= 32) {
+    r.i0 = r.i1 = 0;
+    return r;
+  }
+  const uint32_t q = m >> shift, rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+  const int up = rem > half ? 1 : 0, tie = rem == half ? 1 : 0;
+  r.i0 = (int)q + up + (tie & (int)(q & 1u));          // A even: A+q is odd iff q is odd
+  r.i1 = (int)q + up + (tie & (int)((q & 1u) ^ 1u));   // A odd
+  return r;
+}
+constexpr int kHead = 1024;
+constexpr int kPerThread = 8;
+
+__device__ void exact_prefix(const uint32_t* keys, float* accs, int n_valid, float topP, ToppSmem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  // ---- head: plain sequential adds out of shared memory, eight at a time
+  const int nh = min(n_valid, kHead);
+  for (int i = tid; i < nh; i += blockDim.x) sm.chunk[i] = __uint_as_float(keys[i]);
+  __syncthreads();
+  if (tid == 0) {
+    float acc = 0.0f;
+    int i = 0, stop = 0;
+    while (i < nh && !stop) {
+      float v[8];
+      const int c = min(8, nh - i);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = j < c ? sm.chunk[i + j] : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < c && !stop) {
+          acc += v[j];
+          sm.chunk[i + j] = acc;
+          if (acc >= topP) {
+            stop = 1;
+            sm.n_cand = i + j + 1;
+          }
+        }
+      }
+      i += c;
+    }
+    if (!stop) sm.n_cand = nh;
+    sm.stop = stop || (nh == n_valid);
+    sm.acc_final = acc;
+    sm.k_next = nh;
+    sm.acc_bits = __float_as_uint(acc);
+  }
+  __syncthreads();
+  for (int i = tid; i < sm.n_cand && i < nh; i += blockDim.x) accs[i] = sm.chunk[i];
+  // ---- windows of blockDim * kPerThread elements
+  while (true) {
+    __syncthreads();
+    if (sm.stop) break;
+    const int k0 = sm.k_next;
+    int e;
+    uint32_t A0;
+    split_float(sm.acc_bits, e, A0);
+    if (tid == 0) {
+      sm.ov_idx = 0x7fffffff;
+      sm.stop_idx = 0x7fffffff;
+    }
+    const int base = k0 + tid * kPerThread;
+    uint32_t wb[kPerThread];
+    IncPair f[kPerThread], F;
+    F.i0 = F.i1 = 0;
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+      wb[j] = (base + j < n_valid) ? keys[base + j] : 0u;
+      if (wb[j]) f[j] = inc_of(wb[j], e);
+      else f[j].i0 = f[j].i1 = 0;
+      F = compose(F, f[j]);
+    }
+    // inclusive scan of the per-thread maps across the block
+    IncPair incl = F;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      IncPair prev;
+      prev.i0 = __shfl_up_sync(0xffffffffu, incl.i0, o);
+      prev.i1 = __shfl_up_sync(0xffffffffu, incl.i1, o);
+      if (lane >= o) incl = compose(prev, incl);
+    }
+    if (lane == 31) sm.warp_pair[w] = make_int2(incl.i0, incl.i1);
+    __syncthreads();
+    if (w == 0) {
+      const int2 t = sm.warp_pair[lane];
+      IncPair x;
+      x.i0 = t.x;
+      x.i1 = t.y;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        IncPair prev;
+        prev.i0 = __shfl_up_sync(0xffffffffu, x.i0, o);
+        prev.i1 = __shfl_up_sync(0xffffffffu, x.i1, o);
+        if (lane >= o) x = compose(prev, x);
+      }
+      sm.warp_pair[lane] = make_int2(x.i0, x.i1);  // inclusive over warps
+    }
+    __syncthreads();
+    // exclusive map for this thread = (all earlier warps) then (earlier lanes of this warp)
+    IncPair excl;
+    excl.i0 = excl.i1 = 0;
+    if (w > 0) {
+      const int2 t = sm.warp_pair[w - 1];
+      excl.i0 = t.x;
+      excl.i1 = t.y;
+    }
+    {
+      IncPair lane_prev;
+      lane_prev.i0 = __shfl_up_sync(0xffffffffu, incl.i0, 1);
+      lane_prev.i1 = __shfl_up_sync(0xffffffffu, incl.i1, 1);
+      if (lane > 0) excl = compose(excl, lane_prev);
+    }
+    int A = sat_add((int)A0, (A0 & 1u) ? excl.i1 : excl.i0);
+    const uint32_t ebits = (uint32_t)(e + 126) << 23;
+    float outv[kPerThread];
+    int n_ok = 0;
+    bool live = A < (1 << 24);
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+      if (live && base + j < n_valid) {
+        A = sat_add(A, (A & 1) ? f[j].i1 : f[j].i0);
+        if (A >= (1 << 24)) {
+          atomicMin(&sm.ov_idx, base + j);
+          live = false;
+        } else {
+          const float v = __uint_as_float(ebits + (uint32_t)A);
+          outv[j] = v;
+          n_ok = j + 1;
+          if (v >= topP) {
+            atomicMin(&sm.stop_idx, base + j);
+            live = false;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j)
+      if (j < n_ok) accs[base + j] = outv[j];
+    __syncthreads();
+    if (tid == 0) {
+      const int wend = min(n_valid, k0 + (int)blockDim.x * kPerThread);
+      const int ov = sm.ov_idx, st = sm.stop_idx;
+      if (st < ov) {  // reached topP inside the valid part of the window
+        sm.n_cand = st + 1;
+        sm.stop = 1;
+      } else if (ov < wend) {  // element `ov` carries the sum into the next binade: one ordinary fp32 add
+        const float prev = (ov == k0) ? __uint_as_float(sm.acc_bits) : accs[ov - 1];
+        const float acc = prev + __uint_as_float(keys[ov]);
+        accs[ov] = acc;
+        sm.acc_bits = __float_as_uint(acc);
+        sm.k_next = ov + 1;
+        sm.n_cand = ov + 1;
+        if (acc >= topP || ov + 1 >= n_valid) sm.stop = 1;
+      } else {
+        sm.k_next = wend;
+        sm.n_cand = wend;
+        sm.acc_bits = __float_as_uint(accs[wend - 1]);
+        if (wend >= n_valid) sm.stop = 1;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) sm.acc_final = sm.n_cand > 0 ? accs[sm.n_cand - 1] : 0.0f;
 }
 
 __global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* __restrict__ out, const float* __restrict__ probs, int V,
@@ -315,45 +541,21 @@ __global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* __restrict__ ou
   radix_pass(keyB, idxB, keyA, idxA, V, 24, false, sm);
   // sorted: keyA / idxA
 
-  // 3. sequential fp32 prefix sum by one lane, staged through shared memory in chunks
+  // 3. fp32 prefix sum with the reference's left-to-right rounding, computed exactly but in parallel (see exact_prefix)
   if (threadIdx.x == 0) {
     sm.n_cand = 0;
     sm.acc_final = 0.0f;
     sm.stop = 0;
     sm.best_k = 0x7fffffff;
+    sm.n_valid = 0;
   }
   __syncthreads();
+  // number of entries with w > 0 (they sort first)
+  for (int j = threadIdx.x; j < V; j += blockDim.x)
+    if (keyA[j] != 0u && (j + 1 == V || keyA[j + 1] == 0u)) sm.n_valid = j + 1;
+  __syncthreads();
   float* accs = reinterpret_cast<float*>(keyB);  // accumulated values, reusing a sort buffer
-  for (int base = 0; base < V; base += kScanChunk) {
-    const int m = min(kScanChunk, V - base);
-    for (int i = threadIdx.x; i < m; i += blockDim.x) sm.chunk[i] = __uint_as_float(keyA[base + i]);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float acc = sm.acc_final;
-      int i = 0;
-      for (; i < m; ++i) {
-        const float w = sm.chunk[i];
-        if (!(w > 0.0f)) {  // end of the valid (w > 0) entries
-          sm.stop = 1;
-          break;
-        }
-        acc += w;
-        sm.chunk[i] = acc;
-        if (acc >= topP) {
-          ++i;
-          sm.stop = 1;
-          break;
-        }
-      }
-      sm.acc_final = acc;
-      sm.n_cand = base + i;
-    }
-    __syncthreads();
-    const int done = min(m, sm.n_cand - base);
-    for (int i = threadIdx.x; i < done; i += blockDim.x) accs[base + i] = sm.chunk[i];
-    if (sm.stop) break;
-    __syncthreads();
-  }
+  exact_prefix(keyA, accs, sm.n_valid, topP, sm);
   __syncthreads();
 
   // 4. first k with acc[k] / acc_final >= u
