@@ -191,6 +191,9 @@ TSB200_API int TSB200_PackWeight(int device, int dtype, void* packed, const void
  * kernel (M <= 4 only).  M <= 4 runs the TMA-fed streaming GEMV; larger M the fallback kernels.  Replaces
  * LayerNorm/RMSNorm + Affine + activation/gate/residual of one layer (PositionwiseFeedForward.cs:72-98,
  * MultiHeadAttention.cs:130-137,234-237). */
+/* profiling aid: when set to a device buffer of grid*8 int64, every CTA of the streaming GEMV stamps %globaltimer at
+ * start / dependency resolved / x staged / first tile landed / last tile consumed / done.  NULL switches it off. */
+TSB200_API int TSB200_DebugSetGemvTrace(void* device_buffer);
 TSB200_API int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N);
 TSB200_API int TSB200_LinearPacked(int device, int dtype, void* y, float* y_f32, const void* x, const float* x_f32,
                                    const void* gamma, const void* beta, int norm_type, float eps, const void* Wp,

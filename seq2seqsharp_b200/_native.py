@@ -109,6 +109,7 @@ def lib():
         "TSB200_LinearWorkspaceBytes": (i64, [i32, i32, i32]),
         "TSB200_PackedWeightBytes": (i64, [i32, i32, i32]),
         "TSB200_PackWeight": (i32, [i32, i32, vp, vp, i32, i32, i32, vp]),
+        "TSB200_DebugSetGemvTrace": (i32, [vp]),
         "TSB200_LinearPackedWorkspaceBytes": (i64, [i32, i32, i32, i32]),
         "TSB200_LinearPacked": (i32, [i32, i32, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp]),
         "TSB200_NormResidual": (i32, [i32, i32, vp, vp, vp, vp, vp, i32, f32, i32, i32, vp]),

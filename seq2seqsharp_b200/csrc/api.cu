@@ -17,6 +17,11 @@ void set_last_error(const char* fmt, ...) {
 }
 const char* last_error() { return g_last_error.c_str(); }
 
+static thread_local bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+PdlScope::PdlScope(bool on) : prev(g_pdl) { g_pdl = on; }
+PdlScope::~PdlScope() { g_pdl = prev; }
+
 static DeviceState g_dev[kMaxDevices];
 static std::mutex g_dev_mu;
 

@@ -56,6 +56,36 @@ inline cudaStream_t pick_stream(DeviceState* st, void* stream) { return stream ?
 void count_launch(int device, long long n = 1);
 int check_launch(const char* what);
 
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// Kernels of a decode step are chained with programmatic stream serialization: a kernel may become resident while its
+// predecessor is still running.  It calls pdl_wait() before it touches anything an earlier kernel wrote (a no-op when
+// the launch carried no such attribute) and pdl_trigger() as early as possible so that its own successor can be
+// scheduled.  The engine switches the attribute on for the launches it issues (PdlScope); stand-alone ops never use it.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+bool pdl_enabled();
+struct PdlScope {
+  bool prev;
+  explicit PdlScope(bool on);
+  ~PdlScope();
+};
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- dtype helpers ----------------------------------------------------------------------------------
 inline size_t dtype_size(int dt) {
   switch (dt) {

@@ -13,6 +13,7 @@
 //    graph is replayed for every token, sampled ids are fed back on the device, and the host reads ids only
 //    when asked (every step only if it must test the reference's stop rule, GPT.cs:300-303).
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -22,9 +23,11 @@
 namespace tsb {
 
 template <typename T>
-__global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ E, const T* __restrict__ PE, const int* __restrict__ ids,
+__global__ void embed_kernel(float* x, const T* E, const T* PE, const int* ids,
                              int rows, int S, int d, int V, float sf, int pe_mode, int pe_rows, int T0_arg,
-                             const int* __restrict__ dT0) {
+                             const int* dT0) {
+  pdl_trigger();
+  pdl_wait();
   const int T0 = dT0 ? *dT0 : T0_arg;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     int id = ids[r];
@@ -42,15 +45,17 @@ __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ E, con
   }
 }
 
-__global__ void gather_last_kernel(float* __restrict__ xl, const float* __restrict__ x, int B, int S, int d) {
+__global__ void gather_last_kernel(float* xl, const float* x, int B, int S, int d) {
   for (int b = blockIdx.x; b < B; b += gridDim.x)
     for (int i = threadIdx.x; i < d; i += blockDim.x) xl[(int64_t)b * d + i] = x[((int64_t)b * S + S - 1) * d + i];
 }
 
 // state[0] = cache length T, state[1] = Philox step counter, state[2] = output slot of this call
-__global__ void commit_kernel(int* __restrict__ ids_cur, const int* __restrict__ ids_new, int* __restrict__ hist,
-                              int* __restrict__ hist_len, int hist_stride, int* __restrict__ out, int B, int* state,
+__global__ void commit_kernel(int* ids_cur, const int* ids_new, int* hist,
+                              int* hist_len, int hist_stride, int* out, int B, int* state,
                               int advance_T) {
+  pdl_trigger();
+  pdl_wait();
   const int slot = state[2];
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
     const int id = ids_new[b];
@@ -360,6 +365,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
 // One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
 // With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
 static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
+  PdlScope pdl_scope(g->pdl && S == 1);
   const TSB200GptConfig& c = g->c;
   const int dev = c.device, dt = c.dtype, d = c.d, rows = B * S;
   const int* dT = use_state ? g->state : nullptr;
@@ -371,9 +377,9 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     const int gsz = rows < g->st->sm_count * 8 ? rows : g->st->sm_count * 8;
     const int* ids = (S == 1 && use_state) ? g->ids_cur : g->ids_in;
     if (dt == TSB200_F32)
-      embed_kernel<float><<<gsz, 256, 0, g->s>>>(g->x, (const float*)g->E, (const float*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT);
+      TSB_CUDA(launch_k(embed_kernel<float>, dim3(gsz), dim3(256), 0, g->s, g->x, (const float*)g->E, (const float*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT));
     else
-      embed_kernel<__half><<<gsz, 256, 0, g->s>>>(g->x, (const __half*)g->E, (const __half*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT);
+      TSB_CUDA(launch_k(embed_kernel<__half>, dim3(gsz), dim3(256), 0, g->s, g->x, (const __half*)g->E, (const __half*)g->PE, ids, rows, S, d, c.V, sf, pe_mode, g->pe_rows, T0, dT));
     count_launch(dev);
     prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
@@ -404,6 +410,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
 
 // logits -> id (greedy or top-p), then commit: feed back, history, output slot, counters.
 static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool use_state, bool advance_T) {
+  PdlScope pdl_scope(g->pdl && advance_T);
   const TSB200GptConfig& c = g->c;
   const int dev = c.device;
   const bool sampling = opt->strategy == 1;
@@ -414,7 +421,7 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
     PROF(KC_SAMPLE, launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
   }
   prof_begin(g);
-  commit_kernel<<<1, 256, 0, g->s>>>(g->ids_cur, g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0);
+  TSB_CUDA(launch_k(commit_kernel, dim3(1), dim3(256), 0, g->s, g->ids_cur, (const int*)g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0));
   count_launch(dev);
   prof_end(g, KC_COMMIT);
   return check_launch("commit");
@@ -532,6 +539,10 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   g->s = st->stream;
   g->es = c.dtype == TSB200_F16 ? 2 : 4;
   g->glu = (c.act == TSB200_ACT_GLU_NOACT || c.act == TSB200_ACT_SWIGLU) ? 1 : 0;
+  {
+    const char* e = getenv("TSB200_PDL");  // "0" switches programmatic dependent launch off (A/B measurements)
+    g->pdl = !(e && e[0] == '0');
+  }
   const TSB200GptConfig& cc = g->c;
   const int64_t d = cc.d, F = cc.F, V = cc.V, Hd = (int64_t)cc.H * cc.hd, KVd = (int64_t)cc.Hkv * cc.hd;
   g->Nqkv = (int)(Hd + 2 * KVd);

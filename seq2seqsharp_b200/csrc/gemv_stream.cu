@@ -65,6 +65,16 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ long long gtimer() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(slot)                                                                     \
+  do {                                                                                  \
+    if (a.trace && (tid & 31) == 0 && ((tid >> 5) == 0 || (tid >> 5) == kConsumerWarps)) \
+      a.trace[(size_t)blockIdx.x * 8 + (slot)] = gtimer();                              \
+  } while (0)
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T> struct TileVec;
@@ -105,6 +115,7 @@ struct StreamArgs {
   float* partials;       // [CT][max_contrib][M][NT]
   unsigned int* counters;  // [CT], zero on entry, self-resetting
   int* error_flag;       // set to 1 on a wait timeout
+  long long* trace;      // optional [grid][8] globaltimer stamps (profiling aid), null in normal use
   Epilogue ep;
 };
 
@@ -124,6 +135,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
   __shared__ float s_stat[2 * 4 * 8];
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  if (w == 0) TRACE(0);  // CTA start
   const long long U = (long long)a.KB * a.CT;
   const long long G = gridDim.x;
   const int u_begin = (int)(U * blockIdx.x / G), u_end = (int)(U * (blockIdx.x + 1) / G);
@@ -171,26 +183,50 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
 
   // ---------------- consumer warps
   grid_dep_wait();  // activations and outputs of earlier kernels are visible from here on
-  // prologue: stage x (optionally normalised) in shared memory as T
+  if (w == 0) TRACE(1);  // dependency resolved
+  // prologue: stage x (optionally normalised) in shared memory as T.  Loads are gathered into registers in batches
+  // before anything is stored (a store to shared memory between two global loads would serialise their latencies).
+  constexpr int XB = 8;  // loads in flight per thread
   if (a.xmode == 0) {
-    const T* x = reinterpret_cast<const T*>(a.x);
-    for (int i = tid; i < M * Kp; i += 256) {
-      const int m = i / Kp, k = i % Kp;
-      xs[i] = (k < a.K) ? x[(size_t)m * a.K + k] : from_f<T>(0.0f);
+    const T* __restrict__ x = reinterpret_cast<const T*>(a.x);
+    const int K = a.K;
+    for (int m = 0; m < M; ++m) {
+      for (int k0 = 0; k0 < Kp; k0 += 256 * XB) {
+        T v[XB];
+#pragma unroll
+        for (int j = 0; j < XB; ++j) {
+          const int k = k0 + j * 256 + tid;
+          const T xv = x[(size_t)m * K + (k < K ? k : 0)];  // plain (coherent) load, clamped index
+          v[j] = (k < K) ? xv : from_f<T>(0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < XB; ++j) {
+          const int k = k0 + j * 256 + tid;
+          if (k < Kp) xs[m * Kp + k] = v[j];
+        }
+      }
     }
   } else {
-    const float* x = reinterpret_cast<const float*>(a.x);
+    const float* __restrict__ x = reinterpret_cast<const float*>(a.x);
     const T* gamma = reinterpret_cast<const T*>(a.gamma);
-    const T* beta = reinterpret_cast<const T*>(a.beta);
+    // A guarded load may be hoisted above its guard by the compiler; so that every address a thread can form is
+    // valid, a missing beta aliases gamma and is switched off by a factor instead of by a null test.
+    const float beta_on = a.beta ? 1.0f : 0.0f;
+    const T* beta = a.beta ? reinterpret_cast<const T*>(a.beta) : gamma;
     const int K = a.K;
-#pragma unroll
+    constexpr int XR = 48;  // row elements kept in registers per thread: rows up to 256*48 = 12288
     for (int m = 0; m < M; ++m) {
+      float xr[XR];
+#pragma unroll
+      for (int j = 0; j < XR; ++j) {
+        const int k = j * 256 + tid;
+        const float xv = __ldcg(x + (size_t)m * K + (k < K ? k : 0));  // L2-coherent load (written by the previous kernel), clamped index
+        xr[j] = (k < K) ? xv : 0.0f;
+      }
       // statistics over the row: sum (LayerNorm) or sum of squares (RMSNorm), then centred squares for LayerNorm
       float s1 = 0.0f;
-      for (int k = tid; k < K; k += 256) {
-        const float v = x[(size_t)m * K + k];
-        s1 += (a.xmode == 2) ? v : v * v;
-      }
+#pragma unroll
+      for (int j = 0; j < XR; ++j) s1 += (a.xmode == 2) ? xr[j] : xr[j] * xr[j];
       s1 = warp_sum(s1);
       if (lane == 0) s_stat[m * 8 + w] = s1;
       consumer_sync();
@@ -201,8 +237,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
       if (a.xmode == 2) {
         mean = tot / K;
         float s2 = 0.0f;
-        for (int k = tid; k < K; k += 256) {
-          const float e = x[(size_t)m * K + k] - mean;
+#pragma unroll
+        for (int j = 0; j < XR; ++j) {
+          const float e = (j * 256 + tid < K) ? xr[j] - mean : 0.0f;
           s2 += e * e;
         }
         s2 = warp_sum(s2);
@@ -215,13 +252,22 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
       } else {
         inv = sqrtf(tot / (float)K + a.eps);  // rms
       }
-      for (int k = tid; k < Kp; k += 256) {
-        float v = 0.0f;
-        if (k < K) {
-          v = to_f<T>(gamma[k]) * ((x[(size_t)m * K + k] - mean) / inv);
-          if (beta) v += to_f<T>(beta[k]);
+#pragma unroll
+      for (int j0 = 0; j0 < XR; j0 += XB) {
+        if (j0 * 256 >= Kp) break;
+        float gv[XB], bv[XB];
+#pragma unroll
+        for (int j = 0; j < XB; ++j) {
+          const int k = (j0 + j) * 256 + tid;
+          const int kc = k < K ? k : 0;  // clamped: always in range
+          gv[j] = to_f<T>(gamma[kc]);
+          bv[j] = beta_on * to_f<T>(beta[kc]);
         }
-        xs[m * Kp + k] = from_f<T>(v);
+#pragma unroll
+        for (int j = 0; j < XB; ++j) {
+          const int k = (j0 + j) * 256 + tid;
+          if (k < Kp) xs[m * Kp + k] = from_f<T>((k < K) ? gv[j] * ((xr[j0 + j] - mean) / inv) + bv[j] : 0.0f);
+        }
       }
     }
   }
@@ -242,6 +288,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
   // awaited and every named barrier is still reached by all eight warps); results are then garbage and the host
   // sees the error flag.
   bool dead = false;
+  if (w == 0) TRACE(2);  // x staged
   constexpr int RPW = kKT / kConsumerWarps;  // rows of a tile per warp (consecutive rows, so x is one vector load)
   for (int u = u_begin; u < u_end; ++u) {
     if (*(volatile int*)&s_err) dead = true;
@@ -249,6 +296,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
       s_err = 1;
       dead = true;
     }
+    if (w == 0 && u == u_begin) TRACE(3);  // first tile landed
     const unsigned char* tile = stage_mem + (size_t)s * kTileBytes;
     TileVec<T> wv[RPW];
 #pragma unroll
@@ -279,6 +327,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
       ++ct;
     }
     const bool seg_end = (cur_kb == a.KB - 1) || (u == u_end - 1);
+    if (w == 0 && u == u_end - 1) TRACE(4);  // last tile consumed
     if (!seg_end) continue;
     // ---- end of this CTA's share of column tile ct: reduce over warps, then finish or hand over a partial
 #pragma unroll
@@ -366,6 +415,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
     consumer_sync();  // red is reused by the next segment
     seg_begin = u + 1;
   }
+  if (w == 0) TRACE(5);  // done
   if (tid == 0 && *(volatile int*)&s_err && a.error_flag) *a.error_flag = 1;
 }
 
@@ -465,7 +515,7 @@ static int launch_stream_m(int device, DeviceState* st, const StreamPlan& p, Str
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
   TSB_CUDA(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<T, M>, a));
   count_launch(device);
   return 1;
@@ -497,14 +547,19 @@ static int launch_stream_t(int device, DeviceState* st, StreamArgs& a, int M, bo
   return 2;
 }
 
+static long long* g_gemv_trace = nullptr;  // set through TSB200_DebugSetGemvTrace (profiling aid)
+void set_gemv_trace(long long* p) { g_gemv_trace = p; }
+
 // Returns 1 on success, 0 on error, 2 when the shape is not handled by this kernel (caller falls back).
 int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, const void* x, int xmode, const void* gamma,
                        const void* beta, float eps, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws,
                        int64_t ws_bytes, cudaStream_t s) {
   if (M < 1 || M > 4) return 2;
+  if (xmode != 0 && K > 12288) return 2;  // the norm prologue keeps a row in registers
   StreamArgs a{};
   a.Wp = Wp; a.x = x; a.gamma = gamma; a.beta = beta; a.xmode = xmode; a.eps = eps; a.K = K; a.N = N;
   a.error_flag = error_flag;
+  a.trace = g_gemv_trace;
   a.ep = ep;
   if (dtype == TSB200_F16) return launch_stream_t<__half>(device, st, a, M, pdl, ws, ws_bytes, s);
   return launch_stream_t<float>(device, st, a, M, pdl, ws, ws_bytes, s);
@@ -531,6 +586,11 @@ using namespace tsb;
 extern "C" {
 
 int64_t TSB200_PackedWeightBytes(int dtype, int K, int N) { return packed_bytes(dtype, K, N); }
+
+int TSB200_DebugSetGemvTrace(void* device_buffer) {
+  set_gemv_trace(reinterpret_cast<long long*>(device_buffer));
+  return 1;
+}
 
 int TSB200_PackWeight(int device, int dtype, void* packed, const void* W, int src_dtype, int K, int N, void* stream) {
   DeviceState* st;

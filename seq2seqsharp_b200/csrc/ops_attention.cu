@@ -50,10 +50,12 @@ __global__ void rope_table_kernel(float2* __restrict__ tab, int Tmax, int hd, do
 // q [B,S,H,hd] rotated in place; k rotated and stored with v into the cache at positions T0 + s.
 // One thread per pair.  tab may be NULL (then cos/sin are evaluated here).
 template <typename T>
-__global__ void rope_append_kernel(T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int64_t q_rs,
-                                   int64_t kv_rs, T* __restrict__ cK, T* __restrict__ cV, int B, int S, int H, int Hkv, int hd,
-                                   int T0_arg, const int* __restrict__ dT0, int Tmax, int use_rope, double base,
-                                   const float2* __restrict__ tab) {
+__global__ void rope_append_kernel(T* q, const T* k, const T* v, int64_t q_rs,
+                                   int64_t kv_rs, T* cK, T* cV, int B, int S, int H, int Hkv, int hd,
+                                   int T0_arg, const int* dT0, int Tmax, int use_rope, double base,
+                                   const float2* tab) {
+  pdl_trigger();
+  pdl_wait();
   const int T0 = dT0 ? *dT0 : T0_arg;  // the engine keeps the cache length on the device so one CUDA graph serves every step
   const int hp = hd / 2;
   const int64_t per_row = (int64_t)(H + 2 * Hkv) * hp;
@@ -134,12 +136,14 @@ template <> struct Vec16<float> {
 constexpr int kAttnThreads = 128;
 
 template <typename T, int G>
-__global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* __restrict__ out, float* __restrict__ part,
-                                                            const T* __restrict__ q, int64_t q_rs,
-                                                            const T* __restrict__ cK, const T* __restrict__ cV, int S, int H,
-                                                            int Hkv, int hd, int T0_arg, const int* __restrict__ dT0, int Tmax,
+__global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* out, float* part,
+                                                            const T* q, int64_t q_rs,
+                                                            const T* cK, const T* cV, int S, int H,
+                                                            int Hkv, int hd, int T0_arg, const int* dT0, int Tmax,
                                                             int splits, float scale) {
   constexpr int EPL = Vec16<T>::N;
+  pdl_trigger();
+  pdl_wait();
   const int T0 = dT0 ? *dT0 : T0_arg;
   const int lpt = hd / EPL;              // lanes per token (power of two, <= 32)
   const int tpw = 32 / lpt;              // tokens per warp iteration
@@ -250,7 +254,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* __restrict__ out,
 }
 
 template <typename T>
-__global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict__ part, int hd, int splits) {
+__global__ void attn_combine_kernel(T* out, const float* part, int hd, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t rh = blockIdx.x;  // row*H + h
   const int rec = hd + 2;
   const float* p = part + rh * splits * rec;
@@ -311,7 +317,7 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   TSB_CHECK(smem <= 48 * 1024, "attention: shared memory need %zu exceeds 48 KB", smem);
   dim3 grid(splits, ygroups, B * S);
   const float scale = 1.0f / sqrtf((float)hd);
-#define TSB_ATTN(GG) attn_kernel<T, GG><<<grid, kAttnThreads, smem, s>>>(out, ws, q, q_rs, cK, cV, S, H, Hkv, hd, T0, dT0, Tmax, splits, scale)
+#define TSB_ATTN(GG) TSB_CUDA(launch_k(attn_kernel<T, GG>, grid, dim3(kAttnThreads), smem, s, out, ws, q, q_rs, cK, cV, S, H, Hkv, hd, T0, dT0, Tmax, splits, scale))
   switch (G) {
     case 8: TSB_ATTN(8); break;
     case 4: TSB_ATTN(4); break;
@@ -322,7 +328,7 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   count_launch(device);
   TSB_TRY(check_launch("attention"));
   if (splits > 1) {
-    attn_combine_kernel<T><<<B * S * H, hd < 128 ? 64 : 128, 0, s>>>(out, ws, hd, splits);
+    TSB_CUDA(launch_k(attn_combine_kernel<T>, dim3(B * S * H), dim3(hd < 128 ? 64 : 128), 0, s, out, (const float*)ws, hd, splits));
     count_launch(device);
     TSB_TRY(check_launch("attention_combine"));
   }
@@ -369,11 +375,11 @@ int launch_rope_append(int device, DeviceState* st, int dtype, void* q, const vo
   int64_t g = (n + 255) / 256;
   if (g > (int64_t)st->sm_count * 16) g = (int64_t)st->sm_count * 16;
   if (dtype == TSB200_F32)
-    rope_append_kernel<float><<<(int)g, 256, 0, s>>>((float*)q, (const float*)k, (const float*)v, q_rs, kv_rs, (float*)cK,
-                                                     (float*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab);
+    TSB_CUDA(launch_k(rope_append_kernel<float>, dim3((int)g), dim3(256), 0, s, (float*)q, (const float*)k, (const float*)v, q_rs, kv_rs,
+                      (float*)cK, (float*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab));
   else if (dtype == TSB200_F16)
-    rope_append_kernel<__half><<<(int)g, 256, 0, s>>>((__half*)q, (const __half*)k, (const __half*)v, q_rs, kv_rs, (__half*)cK,
-                                                      (__half*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab);
+    TSB_CUDA(launch_k(rope_append_kernel<__half>, dim3((int)g), dim3(256), 0, s, (__half*)q, (const __half*)k, (const __half*)v, q_rs,
+                      kv_rs, (__half*)cK, (__half*)cV, B, S, H, Hkv, hd, T0, dT0, Tmax, use_rope, base, tab));
   else
     TSB_FAIL("rope_append: unsupported dtype %d", dtype);
   count_launch(device);

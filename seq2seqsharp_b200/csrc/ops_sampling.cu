@@ -91,11 +91,13 @@ __global__ void __launch_bounds__(256) argmax_kernel(TO* __restrict__ out, const
 // logits [B,V] fp32 -> probs (optionally stored) -> first index of the row maximum of the PROBABILITIES, which is
 // what the reference compares (Decoder.cs:732-761): logits that differ can round to equal probabilities, and
 // the lowest index must then win.  Blocked ids get p += -1 (Decoder.cs:744-752).
-__global__ void __launch_bounds__(1024) softmax_argmax_kernel(int* __restrict__ out_ids, float* __restrict__ probs,
-                                                              const float* __restrict__ logits, int V, float inv_temp_div,
-                                                              int use_temp, const int* __restrict__ blocked, int n_blocked) {
+__global__ void __launch_bounds__(1024) softmax_argmax_kernel(int* out_ids, float* probs,
+                                                              const float* logits, int V, float inv_temp_div,
+                                                              int use_temp, const int* blocked, int n_blocked) {
   __shared__ float red[32];
   __shared__ ValIdx redi[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* z = logits + (int64_t)r * V;
   float mx = -INFINITY;
@@ -152,6 +154,8 @@ __host__ __device__ inline float philox_uniform(uint64_t seed, uint64_t seq, uin
   return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
 }
 __global__ void philox_kernel(float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step_arg, const int* dstep) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t step = dstep ? (uint32_t)*dstep : step_arg;
   if (i < n) u[i] = philox_uniform(seed, seq_first + (uint64_t)i, step);
@@ -487,13 +491,15 @@ __device__ void exact_prefix(const uint32_t* keys, float* accs, int n_valid, flo
   if (tid == 0) sm.acc_final = sm.n_cand > 0 ? accs[sm.n_cand - 1] : 0.0f;
 }
 
-__global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* __restrict__ out, const float* __restrict__ probs, int V,
+__global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* out, const float* probs, int V,
                                                             float topP, float repeatPenalty,
-                                                            const int* __restrict__ history,
-                                                            const int* __restrict__ history_len, int history_stride,
-                                                            const float* __restrict__ u, uint32_t* ws) {
+                                                            const int* history,
+                                                            const int* history_len, int history_stride,
+                                                            const float* u, uint32_t* ws) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   ToppSmem& sm = *reinterpret_cast<ToppSmem*>(smem_raw);
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   uint32_t* keyA = ws + (size_t)r * 5 * V;
   uint32_t* keyB = keyA + V;
@@ -585,7 +591,7 @@ int launch_softmax_argmax(int device, DeviceState* st, int* out_ids, float* prob
                           float temperature, int use_temp, const int* blocked_dev, int n_blocked, cudaStream_t s) {
   (void)st;
   if (B == 0) return 1;
-  softmax_argmax_kernel<<<B, 1024, 0, s>>>(out_ids, probs, logits, V, temperature, use_temp, blocked_dev, n_blocked);
+  TSB_CUDA(launch_k(softmax_argmax_kernel, dim3(B), dim3(1024), 0, s, out_ids, probs, logits, V, temperature, use_temp, blocked_dev, n_blocked));
   count_launch(device);
   return check_launch("softmax_argmax");
 }
@@ -595,8 +601,8 @@ int launch_topp(int device, DeviceState* st, int* out, const float* probs, int r
   (void)st;
   if (rows == 0) return 1;
   TSB_TRY(init_topp_attrs(device));
-  topp_kernel<<<rows, kTopPThreads, sizeof(ToppSmem), s>>>(out, probs, V, topP, repeatPenalty, history, history_len,
-                                                           history_stride, u, (uint32_t*)ws);
+  TSB_CUDA(launch_k(topp_kernel, dim3(rows), dim3(kTopPThreads), sizeof(ToppSmem), s, out, probs, V, topP, repeatPenalty, history,
+                    history_len, history_stride, u, (uint32_t*)ws));
   count_launch(device);
   return check_launch("topp");
 }
@@ -604,7 +610,7 @@ int launch_topp(int device, DeviceState* st, int* out, const float* probs, int r
 int launch_philox(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step, const int* dstep,
                   cudaStream_t s) {
   if (n == 0) return 1;
-  philox_kernel<<<(n + 127) / 128, 128, 0, s>>>(u, n, seed, seq_first, step, dstep);
+  TSB_CUDA(launch_k(philox_kernel, dim3((n + 127) / 128), dim3(128), 0, s, u, n, seed, seq_first, step, dstep));
   count_launch(device);
   return check_launch("philox");
 }

@@ -38,7 +38,14 @@ def _ref(d):
 
 
 def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The caller's current torch stream.  On torch's legacy default stream (handle 0) the library would fall back to
+    its own non-blocking stream, which does not order itself after torch's work, so pending torch work is waited for
+    first."""
+    h = torch.cuda.current_stream().cuda_stream
+    if h == 0:
+        torch.cuda.synchronize()
+        return None
+    return C.c_void_p(h)
 
 
 def _dev(t):

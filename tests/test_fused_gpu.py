@@ -23,7 +23,8 @@ def host(t):
 
 
 def stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    from seq2seqsharp_b200.ops import _stream as ops_stream
+    return ops_stream()
 
 
 def linear(x, W, bias, act, residual=None, dtype=torch.float32, want_f32=False):

@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    from seq2seqsharp_b200.ops import _stream as ops_stream
+    return ops_stream()
 
 
 def _case(seed, rows, V, spread):
