@@ -431,6 +431,7 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
 static int check_err_flag(Gpt* g) {
   int e = 0;
   TSB_CUDA(cudaMemcpy(&e, g->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  e |= tc_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
     TSB_FAIL("a kernel gave up waiting on a shared-memory barrier (internal error); results of this call are invalid");
@@ -606,7 +607,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   g->topp_ws_bytes = TSB200_TopPWorkspaceBytes(MB, cc.V);
   G_ALLOC(g->topp_ws, g->topp_ws_bytes);
 #undef G_ALLOC
-  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device)) return fail();
+  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device) || !init_tc_attrs(cc.device)) return fail();
   if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) {
     set_last_error("gpt_create: cudaEventCreate failed");
     return fail();
@@ -774,6 +775,7 @@ int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200Dec
     cudaEventRecord(g->ev1, g->s);
     if (cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: %s", cudaGetErrorString(cudaGetLastError())); break; }
     cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1);
+    if (!(ok = check_err_flag(g))) break;
     g->last_launches = g->st->launches - l0;
     g->step = 1;
     g->probs_valid = (opt->strategy == 1);

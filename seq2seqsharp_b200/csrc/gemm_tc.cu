@@ -1,0 +1,346 @@
+// Tensor-core GEMM for prefill and large-batch decode: y[M,N] = epilogue(x[M,K] * W[K,N]), fp16 in, fp32 accumulate.
+//
+// sm_100a design (5th-generation tensor cores):
+//  * operands are staged in shared memory by TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle, completion
+//    on mbarriers): A = activations [M,K] row-major (K-major operand, box 64 k x 128 rows), B = the engine's packed
+//    weight tiles [ct][kb][32 k][256 n] read in place through a 4-D tensor map (MN-major operand, box 64 n x 32 k x
+//    2 kb), so decode GEMV and GEMM share ONE copy of the weights;
+//  * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=128, K=16) with the accumulator in
+//    tensor memory (TMEM, 128 lanes x 128 fp32 columns), tcgen05.commit hands shared-memory stages back to the
+//    producer and signals the epilogue;
+//  * four epilogue warps read the accumulator with tcgen05.ld (32 lanes x 32 columns per instruction) and apply the
+//    same fused epilogue as the GEMV: bias first, activation, gate product on interleaved columns, fp32 residual;
+//  * warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..7 = epilogue.
+// Rows beyond M and K beyond the tensor are zero-filled by TMA, N is padded by the packed layout.
+// Every mbarrier wait is bounded; on timeout an error word is raised, TMEM is freed and the kernel returns.
+//
+// Replaces cublasGemmEx (TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-362, fp16 accumulate there) plus the bias
+// copy, activation and residual kernels around it.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "kernels.cuh"
+
+namespace tsb {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64;
+constexpr int kTcStages = 4;
+constexpr int kTcThreads = 256;
+constexpr int kABytes = kBM * kBK * 2;  // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;  // 16 KB
+constexpr unsigned kTcSpin = 1u << 22;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, unsigned parity) {
+  const uint32_t a = s_u32(bar);
+  for (unsigned i = 0; i < kTcSpin; ++i) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(s_u32(dst)),
+      "l"(map), "r"(s_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          s_u32(dst)),
+      "l"(map), "r"(s_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in 16-byte units,
+// version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Raised by a kernel whose bounded wait ran out; read and cleared by tc_take_error().
+__device__ int g_tc_error;
+
+struct TcArgs {
+  int M, N, K;        // logical sizes (N = packed column count actually used, multiple of 8)
+  int KB;             // packed 32-row tiles along K
+  int* error_flag;
+  Epilogue ep;
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                                const __grid_constant__ CUtensorMap mapB, TcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // carve: [stages][A 16K][B 16K] (1024-byte aligned for the 128B swizzle atoms), then barriers
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + kTcStages * kABytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kTcStages * (kABytes + kBBytes));
+  uint64_t* empty = full + kTcStages;
+  uint64_t* acc_ready = empty + kTcStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  __shared__ int s_err;
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int k_iters = (a.K + kBK - 1) / kBK;
+
+  if (tid == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      tc_mbar_init(&full[s], 1);
+      tc_mbar_init(&empty[s], 1);
+    }
+    tc_mbar_init(acc_ready, 1);
+    s_err = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (w == 2) {  // TMEM allocation: 128 columns of fp32 accumulator (one warp, whole-warp instruction)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(kBN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (w == 0 && lane == 0) {
+    // ---------------- TMA producer
+    const int ct = n_tile >> 1, n_in = (n_tile & 1) * 128;
+    for (int it = 0; it < k_iters; ++it) {
+      const int s = it % kTcStages, r = it / kTcStages;
+      if (it >= kTcStages && !tc_mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
+        s_err = 1;
+        break;
+      }
+      tc_mbar_expect_tx(&full[s], kABytes + kBBytes);
+      tma_load_2d(sA + s * kABytes, &mapA, it * kBK, m_tile * kBM, &full[s]);
+      // B: two 64-column halves of the 128-column tile, each [2 kb][32 k][64 n] = 8 KB
+      tma_load_4d(sB + s * kBBytes, &mapB, n_in, 0, it * 2, ct, &full[s]);
+      tma_load_4d(sB + s * kBBytes + 8192, &mapB, n_in + 64, 0, it * 2, ct, &full[s]);
+    }
+  } else if (w == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = 128, M = 128
+    const uint32_t idesc = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                           ((uint32_t)(kBM >> 4) << 24);
+    for (int it = 0; it < k_iters; ++it) {
+      const int s = it % kTcStages, r = it / kTcStages;
+      if (!tc_mbar_wait(&full[s], (unsigned)(r & 1))) {
+        s_err = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_base = s_u32(sA + s * kABytes), b_base = s_u32(sB + s * kBBytes);
+#pragma unroll
+      for (int kk = 0; kk < kBK / 16; ++kk) {
+        // A (K-major, SW128): rows of 128 B, 8-row atoms 1024 B apart; 16 k = 32 B along the row
+        const uint64_t ad = make_desc(a_base + kk * 32, 16, 1024);
+        // B (MN-major, SW128): 64-n atoms [8 k][128 B]; k groups of 8 are 1024 B apart (SBO), the second 64-n half is
+        // 8192 B away (LBO); 16 k = two atoms = 2048 B
+        const uint64_t bd = make_desc(b_base + kk * 2048, 8192, 1024);
+        umma_f16(tmem_acc, ad, bd, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(&empty[s]);  // frees the stage when these MMAs have read it
+    }
+    umma_commit(acc_ready);    // accumulator complete
+  } else if (w >= 4) {
+    // ---------------- epilogue: warp (w - 4) owns TMEM lanes 32*(w-4) .. +31 = rows of the tile
+    const int q = w - 4;
+    const bool ok = tc_mbar_wait(acc_ready, 0);
+    if (!ok) s_err = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = m_tile * kBM + q * 32 + lane;
+    const __half* bias = reinterpret_cast<const __half*>(a.ep.bias);
+    const int n0 = n_tile * kBN;
+    const int No = a.ep.glu ? a.N / 2 : a.N;
+#pragma unroll 1
+    for (int c = 0; c < kBN; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+      if (!ok || row >= a.M) continue;
+      if (!a.ep.glu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = n0 + c + j;
+          if (col < a.N) {
+            float x = __uint_as_float(v[j]) + (bias ? __half2float(bias[col]) : 0.0f);
+            switch (a.ep.act) {
+              case TSB200_ACT_RELU: x = x < 0.0f ? 0.0f : x; break;
+              case TSB200_ACT_SILU: x = x / (1.0f + expf(-x)); break;
+              case TSB200_ACT_LEAKYRELU: x = x < 0.0f ? 0.01f * x : x; break;
+              case TSB200_ACT_GELU: x = 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); break;
+              default: break;
+            }
+            const size_t o = (size_t)row * a.N + col;
+            if (a.ep.residual) x += a.ep.residual[o];
+            if (a.ep.y32) a.ep.y32[o] = x;
+            else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int col = n0 + c + j;
+          if (col + 1 < a.N) {
+            float av = __uint_as_float(v[j]) + (bias ? __half2float(bias[col]) : 0.0f);
+            const float gv = __uint_as_float(v[j + 1]) + (bias ? __half2float(bias[col + 1]) : 0.0f);
+            if (a.ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
+            float x = av * gv;
+            const size_t o = (size_t)row * No + (col >> 1);
+            if (a.ep.residual) x += a.ep.residual[o];
+            if (a.ep.y32) a.ep.y32[o] = x;
+            else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (w == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kBN) : "memory");
+  }
+  if (tid == 0 && s_err) {
+    g_tc_error = 1;
+    if (a.error_flag) *a.error_flag = 1;
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+int init_tc_attrs(int device) {
+  static bool done[kMaxDevices] = {};
+  if (done[device]) return 1;
+  TSB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kTcStages * (kABytes + kBBytes) + 1024 + 256));
+  done[device] = true;
+  return 1;
+}
+
+// 1 when a tensor-core GEMM on the current device gave up waiting since the last call (and clears the mark).
+int tc_take_error() {
+  int e = 0;
+  if (cudaMemcpyFromSymbol(&e, g_tc_error, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (e) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_tc_error, &z, sizeof(int));
+  }
+  return e;
+}
+
+// Returns 1 ok, 0 error, 2 not handled (caller falls back to the generic kernel).
+int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                   int* error_flag, cudaStream_t s) {
+  (void)st;
+  {
+    static int enabled = -1;
+    if (enabled < 0) {
+      const char* e = getenv("TSB200_TC");  // "0" routes large-M linears to the CUDA-core fallback (A/B measurements)
+      enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (!enabled) return 2;
+  }
+  if (K % 8 != 0 || ((uintptr_t)x % 16) != 0 || ((uintptr_t)Wp % 16) != 0) return 2;
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return 2;
+  TSB_TRY(init_tc_attrs(device));
+  const int KB = (K + 31) / 32, CT = (N + 255) / 256;
+  CUtensorMap mapA, mapB;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t el[2] = {1, 1};
+    const CUresult r = enc(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, el,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TSB_CHECK(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled(A) failed with %d", (int)r);
+  }
+  {
+    // packed tiles as a 4-D tensor: (n_in 256, k_in 32, kb KB, ct CT)
+    const cuuint64_t dims[4] = {256, 32, (cuuint64_t)KB, (cuuint64_t)CT};
+    const cuuint64_t strides[3] = {512, 16384, (cuuint64_t)KB * 16384};
+    const cuuint32_t box[4] = {64, 32, 2, 1};
+    const cuuint32_t el[4] = {1, 1, 1, 1};
+    const CUresult r = enc(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(Wp), dims, strides, box, el,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TSB_CHECK(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled(B) failed with %d", (int)r);
+  }
+  TcArgs a{};
+  a.M = M; a.N = N; a.K = K; a.KB = KB; a.error_flag = error_flag; a.ep = ep;
+  dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM);
+  TSB_CHECK(grid.y <= 65535, "gemm_tc: too many row tiles");
+  const size_t smem = kTcStages * (kABytes + kBBytes) + 1024 + 256;
+  gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(mapA, mapB, a);
+  count_launch(device);
+  return check_launch("gemm_tc");
+}
+
+}  // namespace tsb

@@ -29,6 +29,11 @@ int packed_tile_cols(int dtype);
 int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols, int K,
                 int c0, int cs, cudaStream_t s);
 int init_stream_attrs(int device);
+// tcgen05/TMEM GEMM on packed fp16 weights (gemm_tc.cu): 1 ok, 0 error, 2 shape not handled
+int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                   int* error_flag, cudaStream_t s);
+int init_tc_attrs(int device);
+int tc_take_error();
 int64_t linear_workspace_bytes(int M, int K, int N);
 int launch_attention(int device, DeviceState* st, int dtype, void* out, const void* q, int64_t q_rs, const void* cK,
                      const void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0, int Tmax, int splits_hint,

@@ -357,6 +357,10 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
   if (M == 0) return 1;
   const int vec = dtype == TSB200_F16 ? 8 : 4;
   const int packedKB = packed ? (K + 31) / 32 : 0;
+  if (packed && dtype == TSB200_F16 && M > 16) {
+    const int r = launch_gemm_tc(device, st, x, W, M, K, N, ep, nullptr, s);
+    if (r != 2) return r;
+  }
   const bool gemv_ok = (packed || N % vec == 0) && (((uintptr_t)W % 16) == 0) && M <= 16;
   if (gemv_ok) {
     for (int m0 = 0; m0 < M; m0 += 8) {

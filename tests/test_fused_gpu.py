@@ -263,3 +263,27 @@ def test_linear_packed_with_fused_norm(cuda, oracle, dtype, tol, norm_type, M, K
     scale = max(1.0, float(np.abs(ref).max()))
     out = linear_packed(x, W, b, N.ACT_NONE, norm=(norm_type, g, be if norm_type == 0 else None, 1e-6), dtype=dtype)
     np.testing.assert_allclose(host(out), ref, atol=tol * scale)
+
+
+@pytest.mark.parametrize("M,K,Nn", [(64, 64, 128), (128, 512, 256), (200, 96, 264), (17, 4096, 6144), (512, 768, 2304),
+                                    (130, 1376, 512), (64, 2048, 1000), (300, 160, 96)])
+def test_linear_packed_tensor_core_gemm(cuda, oracle, M, K, Nn):
+    """M > 16 on fp16 packed weights runs the tcgen05/TMEM GEMM (TMA-fed, accumulator in tensor memory): every epilogue,
+    ragged M (rows zero-filled by TMA), K not a multiple of the 64-wide k block, N not a multiple of the tile."""
+    dtype, tol = torch.float16, 4e-3
+    rng = np.random.default_rng(M + K + Nn)
+    x = dev((rng.standard_normal((M, K)) * 0.5).astype(np.float32), dtype)
+    W = dev((rng.standard_normal((K, Nn)) * 0.05).astype(np.float32), dtype)
+    b = dev((rng.standard_normal((1, Nn)) * 0.1).astype(np.float32), dtype)
+    ref = oracle.addmm(1.0, host(b), 1.0, host(x), host(W))
+    scale = max(1.0, float(np.abs(ref).max()))
+    np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype)), ref, atol=tol * scale)
+    np.testing.assert_allclose(host(linear_packed(x, W, None, N.ACT_SILU, dtype=dtype)), oracle.act(ref - host(b), 1), atol=tol * scale)
+    res = dev(rng.standard_normal((M, Nn)).astype(np.float32))
+    np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_NONE, residual=res, dtype=dtype, want_f32=True)), ref + host(res), atol=tol * scale)
+    if Nn % 2 == 0:
+        a, g = ref[:, 0::2], ref[:, 1::2]
+        np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_GLU_NOACT, dtype=dtype)), a * g, atol=tol * scale * scale)
+        np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_SWIGLU, dtype=dtype)), oracle.act(a, 1) * g, atol=tol * scale * scale)
+    first = host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype))
+    np.testing.assert_array_equal(host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype)), first)
