@@ -251,8 +251,10 @@ typedef struct TSB200GptConfig {
   int32_t max_batch;       /* KV-cache capacity in sequences */
   int32_t max_tokens;      /* KV-cache capacity in positions per sequence */
   int32_t device;
-  /* tensor parallelism (MultiProcessorNetworkWrapper rework): this rank holds heads [H/tp*rank, ..) and FFN
-   * columns [F/tp*rank, ..); the caller supplies the all-reduce through TSB200_GptSetAllReduce. tp_size 1 = off */
+  /* tensor parallelism (MultiProcessorNetworkWrapper rework): H, Hkv, F above are the FULL model's; this rank keeps
+   * query heads [H/tp*rank, ..), KV heads [Hkv/tp*rank, ..) and FFN columns [F/tp*rank, ..) and sums the partial
+   * results of the out-projection and of the down-projection over the ranks of the communicator given to
+   * TSB200_GptSetComm (one all-reduce each per layer).  tp_size <= 1 = off */
   int32_t tp_rank, tp_size;
 } TSB200GptConfig;
 
@@ -281,9 +283,14 @@ TSB200_API int TSB200_GptGetWeightPtr(void* gpt, const char* name, void** ptr, i
 /* fill every weight with the seeded synthetic N(0, std) generator (norm gains 1, norm betas 0; biases N(0,std)
  * when bias_std > 0 else 0), generated on the device */
 TSB200_API int TSB200_GptFillSynthetic(void* gpt, uint64_t seed, float std, float bias_std);
-/* all-reduce callback for tensor parallelism: called on `stream` with a device buffer of `count` fp32 values */
-typedef int (*TSB200AllReduceFn)(void* user, void* buf, int64_t count, void* stream);
-TSB200_API int TSB200_GptSetAllReduce(void* gpt, TSB200AllReduceFn fn, void* user);
+/* communicator for a tensor-parallel engine (one process per GPU): rank 0 creates a 128-byte id, hands it to the
+ * other ranks by any host channel, every rank calls CommInitRank.  NCCL over NVLink/NVSwitch, opened at run time.
+ * Replaces the cuMemcpyPeer exchanges of TensorSharp.CUDA/KernelOps/CopyOps.cs:47-97 (the reference has no collective). */
+TSB200_API int TSB200_CommGetUniqueId(void* id128);
+TSB200_API int TSB200_CommInitRank(const void* id128, int rank, int nranks, int device, void** comm);
+TSB200_API int TSB200_CommDestroy(void* comm);
+TSB200_API int TSB200_AllReduceSumF32(void* comm, float* buf, int64_t count, void* stream);
+TSB200_API int TSB200_GptSetComm(void* gpt, void* comm);
 /* clear the KV cache and per-sequence histories */
 TSB200_API int TSB200_GptReset(void* gpt);
 /* Prefill: ids [B,S] host int32 (equal lengths, no padding) -> fills the cache, returns the first generated id

@@ -123,7 +123,11 @@ def lib():
         "TSB200_GptSetWeight": (i32, [vp, C.c_char_p, vp, i32, i64, i64, i32]),
         "TSB200_GptGetWeightPtr": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(i64), C.POINTER(i64)]),
         "TSB200_GptFillSynthetic": (i32, [vp, u64, f32, f32]),
-        "TSB200_GptSetAllReduce": (i32, [vp, vp, vp]),
+        "TSB200_CommGetUniqueId": (i32, [vp]),
+        "TSB200_CommInitRank": (i32, [vp, i32, i32, i32, C.POINTER(vp)]),
+        "TSB200_CommDestroy": (i32, [vp]),
+        "TSB200_AllReduceSumF32": (i32, [vp, vp, i64, vp]),
+        "TSB200_GptSetComm": (i32, [vp, vp]),
         "TSB200_GptReset": (i32, [vp]),
         "TSB200_GptPrefill": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), i32, vp, C.POINTER(i32)]),

@@ -73,6 +73,13 @@ __global__ void commit_kernel(int* ids_cur, const int* ids_new, int* hist,
   }
 }
 
+// x += delta, after the all-reduce of a row-parallel layer's partial sums (tensor parallelism)
+__global__ void residual_add_kernel(float* x, const float* delta, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] += delta[i];
+}
+
 template <typename T>
 __global__ void fill_const_kernel(T* p, int64_t n, float v) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = from_f<T>(v);
@@ -90,6 +97,10 @@ struct Dest {  // where a logical tensor lives inside the engine's buffers
   // matrices of linear layers live in the tiled layout of gemv_stream.cu: logical column j -> packed column c0 + j*cs
   bool packed = false;
   int64_t c0 = 0, cs = 1;
+  // tensor parallelism: the caller hands over the FULL tensor [full_rows, full_cols]; this rank keeps the block that
+  // starts at (sr0, sc0).  skip: the tensor belongs to another rank entirely (bias of a row-parallel layer).
+  int64_t full_rows = 0, full_cols = 0, sr0 = 0, sc0 = 0;
+  bool skip = false;
 };
 
 struct GraphKey {
@@ -109,6 +120,10 @@ struct Gpt {
   cudaStream_t s = nullptr;
   int es = 4;  // element size of the model dtype
   int Nqkv = 0, glu = 0;
+  int tp = 1, tp_rank = 0;     // tensor-parallel degree and rank; c.H / c.Hkv / c.F hold this rank's share
+  int fullH = 0, fullHkv = 0, fullF = 0;
+  void* comm = nullptr;        // communicator for the two all-reduces per layer (TSB200_GptSetComm)
+  float* ar_buf = nullptr;     // fp32 [rows, d] partial sums handed to the all-reduce
   void *E = nullptr, *PE = nullptr, *nf_g = nullptr, *nf_b = nullptr, *head_w = nullptr, *head_b = nullptr;
   int pe_rows = 0;
   std::vector<LayerW> L;
@@ -151,7 +166,7 @@ struct Gpt {
   bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
 };
 
-enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_COUNT = 8 };
+enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_COUNT = 8 };
 
 static void prof_begin(Gpt* g) {
   if (!g->prof) return;
@@ -202,8 +217,41 @@ static bool ends_with(const std::string& s, const char* p) {
   return s.size() >= n && s.compare(s.size() - n, n, p) == 0;
 }
 
-// Maps a reference weight key to its place in the engine's buffers.
-static int resolve(Gpt* g, const std::string& name, Dest* out) {
+// Maps a reference weight key to its place in the engine's buffers.  g->c holds this rank's LOCAL head and FFN counts;
+// the slice of the full tensor that lands here is described by (full_rows, full_cols, sr0, sc0).  The packed MHA
+// QKV matrix is sliced in three parts (q, k, v): `part` selects one, *nparts tells how many there are.
+static int resolve_local(Gpt* g, const std::string& name, Dest* out);
+static int resolve(Gpt* g, const std::string& name, Dest* out, int part = 0, int* nparts = nullptr) {
+  if (nparts) *nparts = 1;
+  *out = Dest();
+  TSB_TRY(resolve_local(g, name, out));
+  const TSB200GptConfig& c = g->c;
+  const int64_t tp = g->tp, r = g->tp_rank;
+  out->full_rows = out->rows;
+  out->full_cols = out->cols;
+  if (tp <= 1) return 1;
+  const int64_t Hd = (int64_t)c.H * c.hd, KVd = (int64_t)c.Hkv * c.hd, F = c.F;
+  auto ends = [&](const char* suf) { return ends_with(name, suf); };
+  const bool is_vec = out->rows == 1 && !out->packed;
+  if (ends(".W0")) { out->full_rows = Hd * tp; out->sr0 = r * Hd; }
+  else if (ends("feedForwardLayer2.m_Whd")) { out->full_rows = F * tp; out->sr0 = r * F; }
+  else if (ends(".b0") || ends("feedForwardLayer2.m_Bd")) { out->skip = (r != 0); }
+  else if (ends(".QKV") || ends(".QKVb")) {
+    if (nparts) *nparts = 3;
+    out->full_cols = 3 * Hd * tp;
+    out->cols = Hd;
+    out->sc0 = part * Hd * tp + r * Hd;
+    if (out->packed) out->c0 = part * Hd;
+    else out->base = (char*)out->base + part * Hd * g->es;
+  }
+  else if (ends(".Q") || ends(".Qb")) { out->full_cols = Hd * tp; out->sc0 = r * Hd; }
+  else if (ends(".K") || ends(".Kb") || ends(".V") || ends(".Vb")) { out->full_cols = KVd * tp; out->sc0 = r * KVd; }
+  else if (ends("feedForwardLayer1.m_Whd") || ends("feedForwardLayer1.m_Bd") || ends("feedForwardLayer3.m_Whd") ||
+           ends("feedForwardLayer3.m_Bd")) { out->full_cols = F * tp; out->sc0 = r * F; }
+  (void)is_vec;
+  return 1;
+}
+static int resolve_local(Gpt* g, const std::string& name, Dest* out) {
   const TSB200GptConfig& c = g->c;
   const int64_t d = c.d, F = c.F, V = c.V, Hd = (int64_t)c.H * c.hd, KVd = (int64_t)c.Hkv * c.hd;
   auto set = [&](void* base, int64_t rows, int64_t cols, int64_t rs, int64_t cs) {
@@ -264,15 +312,19 @@ static int resolve(Gpt* g, const std::string& name, Dest* out) {
   TSB_FAIL("unknown weight name '%s'", name.c_str());
 }
 
+// src_dev points at the FULL tensor [dst.full_rows, dst.full_cols]; this rank's block is copied / packed.
 static int copy_into(Gpt* g, const Dest& dst, const void* src_dev, int src_dtype) {
+  if (dst.skip) return 1;
+  const int ses = src_dtype == TSB200_F16 ? 2 : 4;
+  const void* src = (const char*)src_dev + (dst.sr0 * dst.full_cols + dst.sc0) * ses;
   if (dst.packed)
-    return launch_pack(g->c.device, g->st, g->c.dtype, dst.base, src_dtype, src_dev, (int)dst.rows, (int)dst.cols, (int)dst.rows,
-                       (int)dst.c0, (int)dst.cs, g->s);
+    return launch_pack(g->c.device, g->st, g->c.dtype, dst.base, src_dtype, src, (int)dst.rows, (int)dst.cols, (int)dst.full_cols,
+                       (int)dst.rows, (int)dst.c0, (int)dst.cs, g->s);
   TSB200Tensor r{}, sv{};
   r.data = dst.base; r.dtype = g->c.dtype; r.ndim = 2;
   r.sizes[0] = dst.rows; r.sizes[1] = dst.cols; r.strides[0] = dst.row_stride; r.strides[1] = dst.col_stride;
-  sv.data = const_cast<void*>(src_dev); sv.dtype = src_dtype; sv.ndim = 2;
-  sv.sizes[0] = dst.rows; sv.sizes[1] = dst.cols; sv.strides[0] = dst.cols; sv.strides[1] = 1;
+  sv.data = const_cast<void*>(src); sv.dtype = src_dtype; sv.ndim = 2;
+  sv.sizes[0] = dst.rows; sv.sizes[1] = dst.cols; sv.strides[0] = dst.full_cols; sv.strides[1] = 1;
   return TSB200_Copy(g->c.device, &r, &sv, g->s);
 }
 
@@ -326,6 +378,7 @@ static int ensure_act(Gpt* g, int64_t rows) {
   TSB_TRY(re(&g->qkv, rows * g->Nqkv * g->es));
   TSB_TRY(re(&g->attn, rows * Hd * g->es));
   TSB_TRY(re(&g->ffn, rows * c.F * g->es));
+  if (g->tp > 1) TSB_TRY(re((void**)&g->ar_buf, rows * c.d * 4));
   g->act_rows = rows;
   return 1;
 }
@@ -362,6 +415,29 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
   return 1;
 }
 
+// x += in[rows,K] * Wp[K,d] + bias: the out-projection of attention and the FFN down-projection.  Under tensor
+// parallelism each rank holds K/tp rows of the weight, so its product is a partial sum: it goes to a scratch buffer
+// (bias only on rank 0), one all-reduce sums it over the ranks, and the residual add follows
+// (MultiProcessorNetworkWrapper rework: one all-reduce after the out-projection, one after the down-projection).
+static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp, int K, const void* bias) {
+  const int d = g->c.d;
+  if (g->tp <= 1) return engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+  TSB_CHECK(g->comm, "tensor parallel engine has no communicator (call TSB200_GptSetComm)");
+  TSB_TRY(engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, nullptr, nullptr, g->ar_buf, TSB200_ACT_NONE, 0)));
+  prof_begin(g);
+  int ok = comm_all_reduce_f32(g->comm, g->ar_buf, (int64_t)rows * d, g->s);
+  prof_end(g, KC_ALLREDUCE);
+  TSB_TRY(ok);
+  prof_begin(g);
+  const int64_t n = (int64_t)rows * d;
+  int64_t gsz = (n + 255) / 256;
+  if (gsz > (int64_t)g->st->sm_count * 8) gsz = (int64_t)g->st->sm_count * 8;
+  TSB_CUDA(launch_k(residual_add_kernel, dim3((int)gsz), dim3(256), 0, g->s, g->x, (const float*)g->ar_buf, n));
+  count_launch(g->c.device);
+  prof_end(g, KC_NORM);
+  return check_launch("residual_add");
+}
+
 // One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
 // With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
 static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
@@ -393,9 +469,9 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     void* vp = (char*)g->qkv + (int64_t)(Hd + KVd) * g->es;
     PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
     PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
-    TSB_TRY(engine_linear(g, rows, g->attn, nullptr, nullptr, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0)));
+    TSB_TRY(row_parallel_linear(g, rows, g->attn, L.wo, Hd, L.bo));
     TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n2_g, L.n2_b, g->h, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu)));
-    TSB_TRY(engine_linear(g, rows, g->ffn, nullptr, nullptr, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0)));
+    TSB_TRY(row_parallel_linear(g, rows, g->ffn, L.w2, c.F, L.b2));
   }
   const float* xlast = g->x;
   if (S > 1) {
@@ -525,13 +601,23 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   TSB_CHECK(c.act >= 0 && c.act <= 5, "gpt_create: unknown activation %d", c.act);
   TSB_CHECK(c.pe_type >= 0 && c.pe_type <= 2, "gpt_create: unknown position embedding type");
   TSB_CHECK(c.attn_type == 0 || c.attn_type == 1, "gpt_create: attn_type must be 0 (MHA) or 1 (GQA)");
-  TSB_CHECK(c.tp_size <= 1, "gpt_create: tensor parallel degree %d is not supported by this build", c.tp_size);
+  const int tp = c.tp_size > 1 ? c.tp_size : 1;
+  TSB_CHECK(tp == 1 || (c.tp_rank >= 0 && c.tp_rank < tp), "gpt_create: tp_rank %d out of range for tp_size %d", c.tp_rank, tp);
+  {
+    const int hkv = c.attn_type == 0 ? c.H : c.Hkv;
+    TSB_CHECK(tp == 1 || (c.H % tp == 0 && hkv % tp == 0 && c.F % tp == 0),
+              "gpt_create: tensor parallel degree %d must divide the query heads (%d), KV heads (%d) and FFN width (%d)", tp, c.H, hkv, c.F);
+  }
   TSB_CHECK(c.max_batch > 0 && c.max_batch <= 1024 && c.max_tokens > 0, "gpt_create: bad cache capacity");
   DeviceState* st;
   TSB_TRY(use_device(c.device, &st));
   Gpt* g = new Gpt();
   g->c = c;
   if (c.attn_type == 0) g->c.Hkv = c.H;
+  g->tp = tp;
+  g->tp_rank = tp > 1 ? c.tp_rank : 0;
+  g->fullH = g->c.H; g->fullHkv = g->c.Hkv; g->fullF = g->c.F;
+  g->c.H /= tp; g->c.Hkv /= tp; g->c.F /= tp;  // from here on the config holds this rank's share
   if (g->c.Hkv <= 0 || g->c.H % g->c.Hkv != 0) {
     delete g;
     TSB_FAIL("gpt_create: H must be divisible by Hkv");
@@ -578,6 +664,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   }
   const int MB = cc.max_batch;
   G_ALLOC(g->xl, (int64_t)MB * d * 4);
+  if (tp > 1) G_ALLOC(g->ar_buf, (int64_t)MB * d * 4);
   G_ALLOC(g->hl, (int64_t)MB * d * es);
   G_ALLOC(g->logits, (int64_t)MB * V * 4);
   G_ALLOC(g->probs, (int64_t)MB * V * 4);
@@ -644,10 +731,11 @@ int TSB200_GptSetWeight(void* h, const char* name, const void* data, int dtype, 
   TSB_CHECK(dtype == TSB200_F32 || dtype == TSB200_F16, "gpt_set_weight: data must be F32 or F16");
   TSB_TRY(use_device(g->c.device, nullptr));
   Dest dst;
-  TSB_TRY(resolve(g, name, &dst));
-  TSB_CHECK(rows * cols == dst.rows * dst.cols && (cols == dst.cols || rows * cols == dst.cols),
-            "gpt_set_weight: '%s' expects [%lld, %lld], got [%lld, %lld]", name, (long long)dst.rows, (long long)dst.cols,
-            (long long)rows, (long long)cols);
+  int nparts = 1;
+  TSB_TRY(resolve(g, name, &dst, 0, &nparts));
+  TSB_CHECK(rows * cols == dst.full_rows * dst.full_cols && (cols == dst.full_cols || rows * cols == dst.full_cols),
+            "gpt_set_weight: '%s' expects the full tensor [%lld, %lld], got [%lld, %lld]", name, (long long)dst.full_rows,
+            (long long)dst.full_cols, (long long)rows, (long long)cols);
   const int64_t bytes = rows * cols * (dtype == TSB200_F16 ? 2 : 4);
   const void* src = data;
   void* tmp = nullptr;
@@ -663,7 +751,10 @@ int TSB200_GptSetWeight(void* h, const char* name, const void* data, int dtype, 
     }
     src = tmp;
   }
-  int ok = copy_into(g, dst, src, dtype);
+  int ok = 1;
+  for (int part = 0; part < nparts && ok; ++part) {
+    ok = resolve(g, name, &dst, part, nullptr) && copy_into(g, dst, src, dtype);
+  }
   if (ok && cudaStreamSynchronize(g->s) != cudaSuccess) {
     set_last_error("gpt_set_weight: %s", cudaGetErrorString(cudaGetLastError()));
     ok = 0;
@@ -695,7 +786,7 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
   for (auto& n : names) {
     Dest dst;
     TSB_TRY(resolve(g, n, &dst));
-    if (dst.rows * dst.cols > max_elems) max_elems = dst.rows * dst.cols;
+    if (dst.full_rows * dst.full_cols > max_elems) max_elems = dst.full_rows * dst.full_cols;
   }
   void* tmp = nullptr;
   cudaError_t e = cudaMalloc(&tmp, (size_t)max_elems * g->es);
@@ -706,14 +797,15 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
   int ok = 1;
   for (auto& n : names) {
     Dest dst;
-    ok = resolve(g, n, &dst);
+    int nparts = 1;
+    ok = resolve(g, n, &dst, 0, &nparts);
     if (!ok) break;
     const bool is_bias = ends_with(n, "m_Bd") || ends_with(n, "QKVb") || ends_with(n, ".Qb") || ends_with(n, ".Kb") ||
                          ends_with(n, ".Vb") || ends_with(n, ".b0");
-    ok = launch_synthetic(g->c.device, g->st, tmp, g->c.dtype, dst.rows * dst.cols, seed, fnv1a64(n.c_str()),
+    // the FULL logical tensor is generated (every rank produces the same values) and this rank's block is kept
+    ok = launch_synthetic(g->c.device, g->st, tmp, g->c.dtype, dst.full_rows * dst.full_cols, seed, fnv1a64(n.c_str()),
                           is_bias ? bias_std : std, g->s);
-    if (!ok) break;
-    ok = copy_into(g, dst, tmp, g->c.dtype);
+    for (int part = 0; part < nparts && ok; ++part) ok = resolve(g, n, &dst, part, nullptr) && copy_into(g, dst, tmp, g->c.dtype);
     if (!ok) break;
   }
   if (ok && cudaStreamSynchronize(g->s) != cudaSuccess) {
@@ -725,9 +817,14 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
   return ok;
 }
 
-int TSB200_GptSetAllReduce(void* h, TSB200AllReduceFn fn, void* user) {
-  (void)h; (void)fn; (void)user;
-  TSB_FAIL("gpt_set_all_reduce: tensor parallelism is not supported by this build");
+int TSB200_GptSetComm(void* h, void* comm) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_set_comm: null engine");
+  TSB_CHECK(!comm || (comm_nranks(comm) == g->tp && comm_rank(comm) == g->tp_rank),
+            "gpt_set_comm: communicator is rank %d of %d but the engine is rank %d of %d", comm_rank(comm), comm_nranks(comm), g->tp_rank, g->tp);
+  g->comm = comm;
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  return 1;
 }
 
 int TSB200_GptReset(void* h) {

@@ -421,14 +421,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
 
 // ---- packing: row-major logical columns [c0 + j*cs] of a [K, Np] matrix into the tiled layout -----------------------
 template <typename TD, typename TS>
-__global__ void pack_tiles_kernel(TD* __restrict__ dst, const TS* __restrict__ src, int rows, int cols, int KB, int NT, int c0,
-                                  int cs) {
+__global__ void pack_tiles_kernel(TD* __restrict__ dst, const TS* __restrict__ src, int rows, int cols, int src_ld, int KB,
+                                  int NT, int c0, int cs) {
   const long long n = (long long)rows * cols;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const int k = (int)(i / cols), j = (int)(i % cols);
     const int c = c0 + j * cs;
     const long long tile = (long long)(c / NT) * KB + (k / kKT);
-    dst[tile * (kKT * NT) + (long long)(k % kKT) * NT + (c % NT)] = from_f<TD>(to_f<TS>(src[i]));
+    dst[tile * (kKT * NT) + (long long)(k % kKT) * NT + (c % NT)] = from_f<TD>(to_f<TS>(src[(long long)k * src_ld + j]));
   }
 }
 
@@ -439,15 +439,15 @@ int64_t packed_bytes(int dtype, int K, int N) {
   return KB * CT * kTileBytes;
 }
 
-int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols, int K,
-                int c0, int cs, cudaStream_t s) {
+int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols,
+                int src_ld, int K, int c0, int cs, cudaStream_t s) {
   const int NT = packed_tile_cols(dst_dtype);
   const int KB = (K + kKT - 1) / kKT;
   const long long n = (long long)rows * cols;
   if (n == 0) return 1;
   long long g = (n + 255) / 256;
   if (g > (long long)st->sm_count * 16) g = (long long)st->sm_count * 16;
-#define TSB_PACK(TD, TS) pack_tiles_kernel<TD, TS><<<(int)g, 256, 0, s>>>((TD*)dst, (const TS*)src, rows, cols, KB, NT, c0, cs)
+#define TSB_PACK(TD, TS) pack_tiles_kernel<TD, TS><<<(int)g, 256, 0, s>>>((TD*)dst, (const TS*)src, rows, cols, src_ld, KB, NT, c0, cs)
   if (dst_dtype == TSB200_F16 && src_dtype == TSB200_F16) TSB_PACK(__half, __half);
   else if (dst_dtype == TSB200_F16 && src_dtype == TSB200_F32) TSB_PACK(__half, float);
   else if (dst_dtype == TSB200_F32 && src_dtype == TSB200_F32) TSB_PACK(float, float);
@@ -599,7 +599,7 @@ int TSB200_PackWeight(int device, int dtype, void* packed, const void* W, int sr
   TSB_CHECK(dtype == TSB200_F32 || dtype == TSB200_F16, "pack_weight: unsupported dtype %d", dtype);
   cudaStream_t s = pick_stream(st, stream);
   TSB_CUDA(cudaMemsetAsync(packed, 0, (size_t)packed_bytes(dtype, K, N), s));
-  return launch_pack(device, st, dtype, packed, src_dtype, W, K, N, K, 0, 1, s);
+  return launch_pack(device, st, dtype, packed, src_dtype, W, K, N, N, K, 0, 1, s);
 }
 
 int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N) {

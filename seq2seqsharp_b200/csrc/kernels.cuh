@@ -26,8 +26,12 @@ int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, c
 int64_t stream_workspace_bytes(int dtype, int M, int K, int N, int sm_count);
 int64_t packed_bytes(int dtype, int K, int N);
 int packed_tile_cols(int dtype);
-int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols, int K,
-                int c0, int cs, cudaStream_t s);
+int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols,
+                int src_ld, int K, int c0, int cs, cudaStream_t s);
+// NCCL binding (comm.cu)
+int comm_all_reduce_f32(void* comm, float* buf, int64_t count, cudaStream_t s);
+int comm_nranks(void* comm);
+int comm_rank(void* comm);
 int init_stream_attrs(int device);
 // tcgen05/TMEM GEMM on packed fp16 weights (gemm_tc.cu): 1 ok, 0 error, 2 shape not handled
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,

@@ -151,12 +151,44 @@ def synthetic_weights(cfg: GPTConfig, seed: int, std: float = 0.02, bias_std: fl
     return out
 
 
+def tp_shard_weights(cfg: GPTConfig, weights: Dict[str, np.ndarray], rank: int, n: int) -> Dict[str, np.ndarray]:
+    """This rank's share of every weight under n-way tensor parallelism — the same rule the engine applies when it is
+    handed full tensors (csrc/engine.cu: resolve): query heads, KV heads and FFN columns are cut into n contiguous blocks;
+    Q/K/V/W1/W3 (and their biases) are column blocks, W0/W2 are row blocks, the biases of W0/W2 stay on rank 0 only,
+    everything else (embeddings, norms, LM head) is replicated."""
+    Hd, KVd, F = cfg.H * cfg.hd, cfg.kv_heads() * cfg.hd, cfg.F
+    hq, hk, f = Hd // n, KVd // n, F // n
+    out = {}
+    for name, w in weights.items():
+        w = np.asarray(w)
+        if name.endswith(".W0"):
+            w = w[rank * hq:(rank + 1) * hq]
+        elif name.endswith("feedForwardLayer2.m_Whd"):
+            w = w[rank * f:(rank + 1) * f]
+        elif name.endswith((".b0", "feedForwardLayer2.m_Bd")):
+            w = w if rank == 0 else np.zeros_like(w)
+        elif name.endswith((".QKV", ".QKVb")):
+            w = np.concatenate([w[:, p * Hd + rank * hq:p * Hd + (rank + 1) * hq] for p in range(3)], axis=1)
+        elif name.endswith((".Q", ".Qb")):
+            w = w[:, rank * hq:(rank + 1) * hq]
+        elif name.endswith((".K", ".Kb", ".V", ".Vb")):
+            w = w[:, rank * hk:(rank + 1) * hk]
+        elif name.endswith(("feedForwardLayer1.m_Whd", "feedForwardLayer1.m_Bd", "feedForwardLayer3.m_Whd", "feedForwardLayer3.m_Bd")):
+            w = w[:, rank * f:(rank + 1) * f]
+        out[name] = np.ascontiguousarray(w)
+    return out
+
+
 class GPT:
     """One GPT replica on one device (the reference builds one per device id through
     MultiProcessorNetworkWrapper.GetNetworkOnDevice, Seq2SeqSharp/Applications/GPT.cs:138-146)."""
 
-    def __init__(self, cfg: GPTConfig, device_id: int = 0, max_batch: int = 1, max_tokens: int = 512):
+    def __init__(self, cfg: GPTConfig, device_id: int = 0, max_batch: int = 1, max_tokens: int = 512, tp_rank: int = 0,
+                 tp_size: int = 1):
+        """tp_size > 1: this process holds rank `tp_rank` of a tensor-parallel group (one process per GPU); weights are
+        still handed over as FULL tensors, the engine keeps its share; call InitComm() before running."""
         self.cfg = cfg
+        self._comm = C.c_void_p()
         self.device_id = device_id
         self.max_batch = max_batch
         self.max_tokens = max_tokens
@@ -167,15 +199,32 @@ class GPT:
         c.eps, c.rope_base = cfg.eps, cfg.rope_base
         c.ape_decode_pos0 = 1 if cfg.ape_decode_pos0 else 0
         c.max_batch, c.max_tokens, c.device = max_batch, max_tokens, device_id
-        c.tp_rank, c.tp_size = 0, 1
+        c.tp_rank, c.tp_size = tp_rank, tp_size
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         self._h = C.c_void_p()
         N.call("TSB200_GptCreate", C.byref(c), C.byref(self._h))
         self._keep = None
+
+    def InitComm(self, group=None):
+        """Creates the NCCL communicator of the tensor-parallel group: rank 0 makes the id, torch.distributed (any
+        backend) carries its 128 bytes to the other ranks."""
+        import torch.distributed as dist
+        buf = (C.c_ubyte * 128)()
+        if self.tp_rank == 0:
+            N.call("TSB200_CommGetUniqueId", buf)
+        box = [bytes(buf)]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        ident = (C.c_ubyte * 128).from_buffer_copy(box[0])
+        N.call("TSB200_CommInitRank", ident, self.tp_rank, self.tp_size, self.device_id, C.byref(self._comm))
+        N.call("TSB200_GptSetComm", self._h, self._comm)
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
             N.lib().TSB200_GptDestroy(self._h)
             self._h = C.c_void_p()
+        if getattr(self, "_comm", None) and self._comm.value:
+            N.lib().TSB200_CommDestroy(self._comm)
+            self._comm = C.c_void_p()
 
     def __del__(self):
         try:
@@ -273,7 +322,7 @@ class GPT:
         N.call("TSB200_GptGetStepTimes", self._h, ms.ctypes.data_as(C.c_void_p), n, C.byref(got))
         return ms[:got.value]
 
-    KERNEL_CLASSES = ("embed", "norm", "linear", "rope_append", "attention", "sampling", "commit")
+    KERNEL_CLASSES = ("embed", "norm", "linear", "rope_append", "attention", "sampling", "commit", "allreduce")
 
     def ProfileDecode(self, n_steps, opts: DecodingOptions):
         """{class: (ms_total, launch_groups)} over n_steps un-captured decode steps (CUDA events per launch group)."""

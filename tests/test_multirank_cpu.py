@@ -87,3 +87,86 @@ def test_a_failing_rank_is_reported_to_all_ranks():
     res = _run(fail_on=1)
     for rank, status, msg in res:
         assert status == "err" and "rank 1" in msg and "OOM" in msg
+
+
+# ---- tensor-parallel sharding rule (the one the engine applies) checked on CPU ranks with a gloo all-reduce -------------
+def _tp_layer_partial(cfg, w, x, k=0):
+    """One decoder layer on THIS rank's shard, numpy: returns the partial sums of the two row-parallel projections
+    (before the all-reduce) so the caller can reduce them.  x [rows, d] is replicated.  Prefill of S = rows tokens, B = 1."""
+    import math
+    from oracle.np_oracle import act, layernorm, rmsnorm, rope, softmax
+    f32 = np.float32
+    a, f = "GPTDecoder.SelfAttn_%d" % k, "GPTDecoder.PosFFN_%d" % k
+
+    def norm(v, prefix):
+        g = w[prefix + ".m_alpha"].reshape(-1)
+        return layernorm(v, g, w[prefix + ".m_beta"].reshape(-1), cfg.eps) if int(cfg.norm) == 0 else rmsnorm(v, g, cfg.eps)
+
+    S, hd = x.shape[0], cfg.hd
+    h = norm(x, a + ".layerNormQ")
+    q = (h @ w[a + ".Q"] + w[a + ".Qb"]).reshape(S, -1, hd).transpose(1, 0, 2)
+    kk = (h @ w[a + ".K"] + w[a + ".Kb"]).reshape(S, -1, hd).transpose(1, 0, 2)
+    vv = (h @ w[a + ".V"] + w[a + ".Vb"]).reshape(S, -1, hd).transpose(1, 0, 2)
+    pos = np.arange(S)
+    q, kk = rope(q, pos, cfg.rope_base), rope(kk, pos, cfg.rope_base)
+    grp = q.shape[0] // kk.shape[0]
+    sc = (q @ np.repeat(kk, grp, 0).transpose(0, 2, 1)) * f32(1 / math.sqrt(hd))
+    sc = sc + np.where(pos[None, :] <= pos[:, None], f32(0), f32(-30000.0))
+    o = (softmax(sc.astype(f32)) @ np.repeat(vv, grp, 0)).transpose(1, 0, 2).reshape(S, -1)
+    return (o @ w[a + ".W0"] + w[a + ".b0"]).astype(f32), h, f
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import dataclasses
+        import torch
+        from oracle.np_oracle import NpGPT, act
+        from seq2seqsharp_b200.gpt import (ActivateFuncEnums as A, GPTConfig, MultiHeadAttentionTypeEnums as M, NormEnums as Nm,
+                                           PositionEmbeddingEnums as P, synthetic_weights, tp_shard_weights)
+        cfg = GPTConfig(L=1, d=64, H=4, Hkv=2, hd=16, F=96, V=53, norm=Nm.RMSNorm, act=A.SwiGLU, pe=P.RoPE, attn=M.GQA)
+        w = synthetic_weights(cfg, 5, std=0.1, bias_std=0.05)
+        ws = tp_shard_weights(cfg, w, rank, world)
+        local = dataclasses.replace(cfg, H=cfg.H // world, Hkv=cfg.Hkv // world, F=cfg.F // world)
+        rng = np.random.default_rng(0)
+        x = rng.standard_normal((5, cfg.d)).astype(np.float32)
+
+        def allreduce(v):
+            t = torch.from_numpy(v.copy())
+            dist.all_reduce(t)
+            return t.numpy()
+
+        part, _, f = _tp_layer_partial(local, ws, x)
+        x1 = x + allreduce(part)                                   # one all-reduce after the out-projection
+        from oracle.np_oracle import rmsnorm
+        h2 = rmsnorm(x1, ws[f + ".layerNorm2.m_alpha"].reshape(-1), cfg.eps)
+        u = act(3, (h2 @ ws[f + ".feedForwardLayer1.m_Whd"] + ws[f + ".feedForwardLayer1.m_Bd"]).astype(np.float32))
+        u = u * (h2 @ ws[f + ".feedForwardLayer3.m_Whd"] + ws[f + ".feedForwardLayer3.m_Bd"])
+        x2 = x1 + allreduce((u @ ws[f + ".feedForwardLayer2.m_Whd"] + ws[f + ".feedForwardLayer2.m_Bd"]).astype(np.float32))  # and one after the down-projection
+        # unsharded reference on the same rank
+        full, _, _ = _tp_layer_partial(cfg, w, x)
+        y1 = x + full
+        g2 = rmsnorm(y1, w[f + ".layerNorm2.m_alpha"].reshape(-1), cfg.eps)
+        v = act(3, (g2 @ w[f + ".feedForwardLayer1.m_Whd"] + w[f + ".feedForwardLayer1.m_Bd"]).astype(np.float32))
+        v = v * (g2 @ w[f + ".feedForwardLayer3.m_Whd"] + w[f + ".feedForwardLayer3.m_Bd"])
+        y2 = y1 + (v @ w[f + ".feedForwardLayer2.m_Whd"] + w[f + ".feedForwardLayer2.m_Bd"])
+        q.put((rank, float(np.abs(x2 - y2).max()), float(np.abs(y2).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_tensor_parallel_sharding_rule_sums_to_the_unsharded_layer():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, scale in res:
+        assert err <= 1e-5 * max(1.0, scale), "rank %d: sharded layer differs from the unsharded one by %g" % (rank, err)
