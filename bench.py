@@ -97,14 +97,15 @@ class ClockSampler:
         return out
 
 
-def linear_bytes_per_step(cfg):
-    """Algorithmic bytes of every linear layer of one decode step: each weight and bias read once."""
+def linear_bytes_per_step(cfg, shards=1):
+    """Algorithmic bytes of every linear layer of one decode step on ONE GPU: each weight and bias read once; under
+    tensor parallelism the layer matrices are cut `shards` ways and the LM head is replicated."""
     es = 2 if cfg.dtype == "float16" else 4
     d, F, V, Hd, KVd = cfg.d, cfg.F, cfg.V, cfg.H * cfg.hd, cfg.kv_heads() * cfg.hd
     nq = Hd + 2 * KVd
     f1 = (2 if cfg.is_glu() else 1) * F
     per_layer = d * nq + nq + Hd * d + d + d * f1 + f1 + F * d + d
-    return es * (cfg.L * per_layer + d * V + V)
+    return es * (cfg.L * per_layer // shards + d * V + V)
 
 
 class CpuSample:
@@ -207,12 +208,15 @@ def run_b200(args):
     K, W = args.steps, max(args.warmup, 3)
     n_prof = 8
     max_tokens = S + W + 2 * K + n_prof + 16
-    gpt = GPT(cfg, device_id=local, max_batch=B, max_tokens=max_tokens)
+    tp = args.parallelism == "tp" and world > 1
+    gpt = GPT(cfg, device_id=local, max_batch=B, max_tokens=max_tokens, tp_rank=rank if tp else 0, tp_size=world if tp else 1)
     gpt.FillSynthetic(SEED, 0.02, 0.0)
-    prompt = prompt_ids(SEED + rank, B, S, cfg.V)
+    if tp:
+        gpt.InitComm()
+    prompt = prompt_ids(SEED + (0 if tp else rank), B, S, cfg.V)
     opts = DecodingOptions(MaxTgtSentLength=max_tokens, BlockedTokens=[0], TopP=topP, Temperature=1.0, RepeatPenalty=2.0,
                            DecodingStrategy=DecodingStrategyEnums.Sampling if strat == "topp" else DecodingStrategyEnums.GreedySearch,
-                           Seed=SEED, SeqBase=rank * B)
+                           Seed=SEED, SeqBase=0 if tp else rank * B)
 
     def barrier():
         torch.cuda.synchronize()
@@ -274,27 +278,29 @@ def run_b200(args):
     # ---- roofline of the dominant kernel class (the decode GEMV): CUDA events around every launch, un-captured
     prof = gpt.ProfileDecode(n_prof, opts)
     lin_ms, lin_groups = prof["linear"]
-    lin_bytes = linear_bytes_per_step(cfg)
+    lin_bytes = linear_bytes_per_step(cfg, world if tp else 1)
     hbm, which = peaks()
     achieved = (lin_bytes * n_prof / 1e9) / (lin_ms / 1e3) if lin_ms > 0 else 0.0
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "gemv_traffic.json")
-    if os.path.exists(tp):
-        with open(tp) as fh:
+    traffic_path = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+    if os.path.exists(traffic_path):
+        with open(traffic_path) as fh:
             tj = json.load(fh)
         # dram bytes per algorithmic byte measured by ncu on the same kernel, scaled to one launch of this workload
         traffic = tj.get("dram_bytes_per_algorithmic_byte", 0) * lin_bytes / max(1, lin_groups // n_prof) or None
     step_bytes = gpt.StepBytes(B, T_mid)
-    tokens = world * B * K
+    seqs = B if tp else world * B      # sequences decoded by the whole job
+    tokens = seqs * K
     value = tokens / (ms / 1e3)
     line = {
         "metric": "decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "f16" if cfg.dtype == "float16" else "f32", "data": "synthetic",
         "config": {"workload": args.workload, "model": name, "batch_per_gpu": B, "prompt_len": S, "context_at_timing": T_mid,
-                   "decoding": strat, "topP": topP, "parallelism": "batch-sharded replicas x%d" % world,
+                   "decoding": strat, "topP": topP,
+                   "parallelism": ("tensor-parallel x%d (heads and FFN sharded, 2 all-reduces per layer)" % world) if tp else "batch-sharded replicas x%d" % world,
                    "l2": "inputs larger than L2: %.0f MB of weights+KV streamed per step vs 126 MB L2" % (step_bytes / 1e6)},
-        "e2e": {"value": world * B * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": B * 4 + 12, "d2h_bytes_per_step": B * 4},
+        "e2e": {"value": seqs * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": B * 4 + 12, "d2h_bytes_per_step": B * 4},
         "gpu_launches": int(n_launch),
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel (all linear layers of a decode step)", "achieved": achieved,
@@ -304,7 +310,7 @@ def run_b200(args):
         "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes * K / 1e9 / (ms / 1e3),
                           "frac_of_hbm_peak": step_bytes * K / 1e9 / (ms / 1e3) / hbm},
         "p50_ms_per_token": float(np.median(step_ms)) if len(step_ms) else None,
-        "prefill": {"tokens_per_s": world * B * S / (prefill_ms / 1e3), "ms": prefill_ms},
+        "prefill": {"tokens_per_s": seqs * S / (prefill_ms / 1e3), "ms": prefill_ms},
         "kernel_classes_ms_per_step": {k: v[0] / n_prof for k, v in prof.items()},
         "host_wall_ms_per_step": 1e3 * t_wall / K,
     }
@@ -333,6 +339,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c5_b1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
+                    help="N > 1: 'replicas' = batch-sharded independent sequences (weak scaling, the default); "
+                         "'tp' = one model sharded over the GPUs with two all-reduces per layer (strong scaling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
