@@ -108,9 +108,54 @@ __device__ int g_tc_error;
 struct TcArgs {
   int M, N, K;        // logical sizes (N = packed column count actually used, multiple of 8)
   int KB;             // packed 32-row tiles along K
+  int ksplit;         // CTAs sharing one output tile along K (grid.z); > 1 only when there are few tiles (small M)
+  float* partials;    // [ksplit][M][Npad] raw fp32 accumulators, Npad = gridDim.x * 128
+  unsigned int* counters;  // one per output tile, zero on entry, self-resetting
   int* error_flag;
   Epilogue ep;
 };
+
+// Fused epilogue for 32 consecutive columns of one row: bias first, activation, gate product on interleaved
+// (a_j, g_j) column pairs, fp32 residual, store in fp16 or fp32.
+__device__ __forceinline__ void tc_finish(const TcArgs& a, int row, int col0, const float* v) {
+  const __half* bias = reinterpret_cast<const __half*>(a.ep.bias);
+  if (!a.ep.glu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int col = col0 + j;
+      if (col < a.N) {
+        float x = v[j] + (bias ? __half2float(bias[col]) : 0.0f);
+        switch (a.ep.act) {
+          case TSB200_ACT_RELU: x = x < 0.0f ? 0.0f : x; break;
+          case TSB200_ACT_SILU: x = x / (1.0f + expf(-x)); break;
+          case TSB200_ACT_LEAKYRELU: x = x < 0.0f ? 0.01f * x : x; break;
+          case TSB200_ACT_GELU: x = 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); break;
+          default: break;
+        }
+        const size_t o = (size_t)row * a.N + col;
+        if (a.ep.residual) x += a.ep.residual[o];
+        if (a.ep.y32) a.ep.y32[o] = x;
+        else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+      }
+    }
+  } else {
+    const int No = a.N / 2;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const int col = col0 + j;
+      if (col + 1 < a.N) {
+        float av = v[j] + (bias ? __half2float(bias[col]) : 0.0f);
+        const float gv = v[j + 1] + (bias ? __half2float(bias[col + 1]) : 0.0f);
+        if (a.ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
+        float x = av * gv;
+        const size_t o = (size_t)row * No + (col >> 1);
+        if (a.ep.residual) x += a.ep.residual[o];
+        if (a.ep.y32) a.ep.y32[o] = x;
+        else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+      }
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                                 const __grid_constant__ CUtensorMap mapB, TcArgs a) {
@@ -127,7 +172,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y;
-  const int k_iters = (a.K + kBK - 1) / kBK;
+  const int k_total = (a.K + kBK - 1) / kBK;
+  const int k_per = (k_total + a.ksplit - 1) / a.ksplit;
+  const int k_begin = blockIdx.z * k_per;
+  const int k_iters = max(0, min(k_total, k_begin + k_per) - k_begin);  // k blocks of this CTA
+  __shared__ int s_last;
 
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
@@ -157,10 +206,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         break;
       }
       tc_mbar_expect_tx(&full[s], kABytes + kBBytes);
-      tma_load_2d(sA + s * kABytes, &mapA, it * kBK, m_tile * kBM, &full[s]);
+      tma_load_2d(sA + s * kABytes, &mapA, (k_begin + it) * kBK, m_tile * kBM, &full[s]);
       // B: two 64-column halves of the 128-column tile, each [2 kb][32 k][64 n] = 8 KB
-      tma_load_4d(sB + s * kBBytes, &mapB, n_in, 0, it * 2, ct, &full[s]);
-      tma_load_4d(sB + s * kBBytes + 8192, &mapB, n_in + 64, 0, it * 2, ct, &full[s]);
+      tma_load_4d(sB + s * kBBytes, &mapB, n_in, 0, (k_begin + it) * 2, ct, &full[s]);
+      tma_load_4d(sB + s * kBBytes + 8192, &mapB, n_in + 64, 0, (k_begin + it) * 2, ct, &full[s]);
     }
   } else if (w == 1 && lane == 0) {
     // ---------------- MMA issuer
@@ -194,47 +243,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     if (!ok) s_err = 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int row = m_tile * kBM + q * 32 + lane;
-    const __half* bias = reinterpret_cast<const __half*>(a.ep.bias);
     const int n0 = n_tile * kBN;
-    const int No = a.ep.glu ? a.N / 2 : a.N;
+    const bool live = ok && row < a.M;
+    const size_t Npad = (size_t)gridDim.x * kBN;
 #pragma unroll 1
     for (int c = 0; c < kBN; c += 32) {
       uint32_t v[32];
       tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-      if (!ok || row >= a.M) continue;
-      if (!a.ep.glu) {
+      if (!live) continue;
+      if (a.ksplit == 1) {
+        float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = n0 + c + j;
-          if (col < a.N) {
-            float x = __uint_as_float(v[j]) + (bias ? __half2float(bias[col]) : 0.0f);
-            switch (a.ep.act) {
-              case TSB200_ACT_RELU: x = x < 0.0f ? 0.0f : x; break;
-              case TSB200_ACT_SILU: x = x / (1.0f + expf(-x)); break;
-              case TSB200_ACT_LEAKYRELU: x = x < 0.0f ? 0.01f * x : x; break;
-              case TSB200_ACT_GELU: x = 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); break;
-              default: break;
-            }
-            const size_t o = (size_t)row * a.N + col;
-            if (a.ep.residual) x += a.ep.residual[o];
-            if (a.ep.y32) a.ep.y32[o] = x;
-            else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
-          }
-        }
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        tc_finish(a, row, n0 + c, f);
       } else {
+        // raw partial sums of this K slice; the last CTA of the tile adds the slices in a fixed order
+        float4* dst = reinterpret_cast<float4*>(a.partials + ((size_t)blockIdx.z * a.M + row) * Npad + n0 + c);
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const int col = n0 + c + j;
-          if (col + 1 < a.N) {
-            float av = __uint_as_float(v[j]) + (bias ? __half2float(bias[col]) : 0.0f);
-            const float gv = __uint_as_float(v[j + 1]) + (bias ? __half2float(bias[col + 1]) : 0.0f);
-            if (a.ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
-            float x = av * gv;
-            const size_t o = (size_t)row * No + (col >> 1);
-            if (a.ep.residual) x += a.ep.residual[o];
-            if (a.ep.y32) a.ep.y32[o] = x;
-            else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+        for (int j = 0; j < 8; ++j)
+          dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                               __uint_as_float(v[4 * j + 3]));
+      }
+    }
+    if (a.ksplit > 1) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (w == 4 && lane == 0) {
+        const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned int prev = atomicAdd(&a.counters[tile], 1u);
+        s_last = (prev == (unsigned int)(a.ksplit - 1));
+        if (s_last) a.counters[tile] = 0u;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_last && live) {
+        __threadfence();
+#pragma unroll 1
+        for (int c = 0; c < kBN; c += 32) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = 0.0f;
+          for (int z = 0; z < a.ksplit; ++z) {
+            const float4* src = reinterpret_cast<const float4*>(a.partials + ((size_t)z * a.M + row) * Npad + n0 + c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = __ldcg(src + j);
+              f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
+            }
           }
+          tc_finish(a, row, n0 + c, f);
         }
       }
     }
@@ -295,9 +351,15 @@ int tc_take_error() {
 }
 
 // Returns 1 ok, 0 error, 2 not handled (caller falls back to the generic kernel).
+int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count) {
+  const int64_t tiles = (int64_t)((N + kBN - 1) / kBN) * ((M + kBM - 1) / kBM);
+  if (tiles >= sm_count) return 0;
+  const int64_t ks = (2 * sm_count + tiles - 1) / tiles;
+  return 4096 + tiles * 4 + ks * M * (int64_t)((N + kBN - 1) / kBN) * kBN * 4;
+}
+
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
-                   int* error_flag, cudaStream_t s) {
-  (void)st;
+                   int* error_flag, void* ws, int64_t ws_bytes, cudaStream_t s) {
   {
     static int enabled = -1;
     if (enabled < 0) {
@@ -335,8 +397,30 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
   }
   TcArgs a{};
   a.M = M; a.N = N; a.K = K; a.KB = KB; a.error_flag = error_flag; a.ep = ep;
-  dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM);
+  dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM, 1);
   TSB_CHECK(grid.y <= 65535, "gemm_tc: too many row tiles");
+  // few output tiles (decode-sized M): share each tile's K range among several CTAs so that all SMs stream weights
+  a.ksplit = 1;
+  {
+    const int64_t tiles = (int64_t)grid.x * grid.y;
+    const int k_total = (K + kBK - 1) / kBK;
+    if (tiles < st->sm_count && k_total >= 8 && ws) {
+      int ks = (int)((2 * st->sm_count + tiles - 1) / tiles);
+      if (ks > k_total / 4) ks = k_total / 4;
+      if (ks > 1) {
+        const int k_per = (k_total + ks - 1) / ks;
+        ks = (k_total + k_per - 1) / k_per;  // no empty slice
+        const int64_t cnt = ((tiles * 4 + 255) & ~255LL);
+        const int64_t need = cnt + (int64_t)ks * M * grid.x * kBN * 4;
+        if (ks > 1 && ws_bytes >= need) {
+          a.ksplit = ks;
+          a.counters = reinterpret_cast<unsigned int*>(ws);
+          a.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + cnt);
+          grid.z = ks;
+        }
+      }
+    }
+  }
   const size_t smem = kTcStages * (kABytes + kBBytes) + 1024 + 256;
   gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(mapA, mapB, a);
   count_launch(device);

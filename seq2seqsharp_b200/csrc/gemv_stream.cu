@@ -604,7 +604,9 @@ int TSB200_PackWeight(int device, int dtype, void* packed, const void* W, int sr
 
 int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N) {
   const int64_t a = stream_workspace_bytes(dtype, M > 4 ? 4 : (M < 1 ? 1 : M), K, N, 160);
-  const int64_t b = linear_workspace_bytes(M, K, N);
+  int64_t b = linear_workspace_bytes(M, K, N);
+  const int64_t c = dtype == TSB200_F16 && M > 16 ? gemm_tc_workspace_bytes(M, N, 132) : 0;
+  if (c > b) b = c;
   return (a > b ? a : b) + 256;
 }
 

@@ -35,7 +35,8 @@ int comm_rank(void* comm);
 int init_stream_attrs(int device);
 // tcgen05/TMEM GEMM on packed fp16 weights (gemm_tc.cu): 1 ok, 0 error, 2 shape not handled
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
-                   int* error_flag, cudaStream_t s);
+                   int* error_flag, void* ws, int64_t ws_bytes, cudaStream_t s);
+int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count);
 int init_tc_attrs(int device);
 int tc_take_error();
 int64_t linear_workspace_bytes(int M, int K, int N);

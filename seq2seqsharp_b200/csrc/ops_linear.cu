@@ -358,7 +358,7 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
   const int vec = dtype == TSB200_F16 ? 8 : 4;
   const int packedKB = packed ? (K + 31) / 32 : 0;
   if (packed && dtype == TSB200_F16 && M > 16) {
-    const int r = launch_gemm_tc(device, st, x, W, M, K, N, ep, nullptr, s);
+    const int r = launch_gemm_tc(device, st, x, W, M, K, N, ep, nullptr, ws, ws_bytes, s);
     if (r != 2) return r;
   }
   const bool gemv_ok = (packed || N % vec == 0) && (((uintptr_t)W % 16) == 0) && M <= 16;
