@@ -10,6 +10,7 @@ path), timing is the max over ranks.
 Workloads (synthetic seeded weights and prompts of the named shapes; no dataset is involved):
     c5_b1   Llama-7B-class fp16, B=1,  prompt 512, Top-P 0.95     (headline: latency-bound decode)
     c5_b64  same model, B=64
+    c5_b4 / c5_b8  same model, B=4 / B=8 (still one persistent launch per step on the fp16 tensor-core variant)
     c3_b1 / c3_b32  Llama-1B-class fp16, prompt 1024, greedy
     c1      tiny fp32 model, B=1, prompt 32, greedy
 """
@@ -32,6 +33,8 @@ WORKLOADS = {
     #            config name               B   prompt  strategy  topP
     "c5_b1": ("c5_llama7b_fp16", 1, 512, "topp", 0.95),
     "c5_b64": ("c5_llama7b_fp16", 64, 512, "topp", 0.95),
+    "c5_b4": ("c5_llama7b_fp16", 4, 512, "topp", 0.95),
+    "c5_b8": ("c5_llama7b_fp16", 8, 512, "topp", 0.95),
     "c3_b1": ("c3_llama1b_fp16", 1, 1024, "greedy", 1.0),
     "c3_b32": ("c3_llama1b_fp16", 32, 1024, "greedy", 1.0),
     "c2_b8": ("c2_gpt2small_fp16", 8, 128, "topp", 0.9),
@@ -276,9 +279,18 @@ def run_b200(args):
     e2e_s = max_over_ranks(e2e_s)
 
     # ---- roofline of the dominant kernel class (the decode GEMV): CUDA events around every launch, un-captured
+    T_prof = gpt.CacheLength() + n_prof // 2
     prof = gpt.ProfileDecode(n_prof, opts)
     lin_ms, lin_groups = prof["linear"]
     lin_bytes = linear_bytes_per_step(cfg, world if tp else 1)
+    dominant = "gemv_stream_kernel / gemm_tc_kernel (all linear layers of a decode step)"
+    if prof["decode_stack"][1] > 0:
+        # batch <= 4: one persistent launch per step runs every linear plus RoPE, cache append and attention; its
+        # algorithmic bytes are the weights once plus the KV cache read and the appended rows
+        lin_ms, lin_groups = prof["decode_stack"]
+        es = 2 if cfg.dtype == "float16" else 4
+        lin_bytes += B * cfg.L * 2 * cfg.kv_heads() * cfg.hd * (T_prof + 1) * es
+        dominant = "decode_stack_kernel (persistent: all linears, RoPE, cache append and attention of a decode step)"
     hbm, which = peaks()
     achieved = (lin_bytes * n_prof / 1e9) / (lin_ms / 1e3) if lin_ms > 0 else 0.0
     traffic = None
@@ -303,7 +315,7 @@ def run_b200(args):
         "e2e": {"value": seqs * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": B * 4 + 12, "d2h_bytes_per_step": B * 4},
         "gpu_launches": int(n_launch),
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
-        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (all linear layers of a decode step)", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved,
                      "peak": hbm, "peak_source": which, "unit": "GB/s", "frac": achieved / hbm,
                      "traffic": traffic, "algorithmic_bytes_per_launch": lin_bytes / max(1, lin_groups // n_prof),
                      "launches_per_step": lin_groups // n_prof},

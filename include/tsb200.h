@@ -269,6 +269,12 @@ typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOpti
   uint64_t seq_base;
 } TSB200DecodingOptions;
 
+/* Profiling aid: when `device_buffer` is not NULL the persistent decode-step kernel (batch <= 4) writes four
+ * %globaltimer stamps per CTA and operation into it ([SMs][operations][8] int64, followed by [SMs][8] cycle counters of the MMA warp: dependency met, input staged, last
+ * weight tile consumed, operation left); NULL switches it off.  The operations of a step are, per layer: QKV,
+ * attention, out-projection, FFN up, FFN down; then the LM head (5*L + 1).  No counterpart in the reference. */
+TSB200_API int TSB200_GptDebugStackTrace(void* gpt, void* device_buffer);
+
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);
 /* name = the reference's weight key (IModel.AddWeights/GetWeights, Seq2SeqSharp/Tools/WeightTensor.cs:571-604),

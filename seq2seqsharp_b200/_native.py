@@ -138,6 +138,7 @@ def lib():
         "TSB200_GptStepHost": (i32, [vp, vp, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptEnableStepTiming": (i32, [vp, i32]),
         "TSB200_GptGetStepTimes": (i32, [vp, vp, i32, C.POINTER(i32)]),
+        "TSB200_GptDebugStackTrace": (i32, [vp, vp]),
         "TSB200_GptProfileDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), vp, vp, i32]),
         "TSB200_GptStepBytes": (i32, [vp, i32, i32, C.POINTER(i64)]),
         "TSB200_FillSynthetic": (i32, [i32, vp, i32, i64, u64, u64, f32, vp]),

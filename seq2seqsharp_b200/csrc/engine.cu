@@ -164,9 +164,19 @@ struct Gpt {
   int* pin_ids = nullptr;  // pinned host staging for TSB200_GptStepHost
   int* err_flag = nullptr; // device word raised by a kernel whose bounded wait ran out
   bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
+  // persistent decode-step kernel (decode_stack.cu): the program of operations and its scratch
+  bool use_stack = true;
+  std::vector<StackOp> stack_host;
+  StackOp* stack_dev = nullptr;
+  int stack_B = 0;
+  const void* stack_key = nullptr;   // activation buffer the program was built for
+  void *stack_partials = nullptr, *stack_counters = nullptr, *stack_attn = nullptr;
+  int stack_max_B = 4;
+  int64_t stack_counter_bytes = 0;
+  long long* stack_trace = nullptr;  // optional timestamps (TSB200_GptDebugStackTrace)
 };
 
-enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_COUNT = 8 };
+enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_STACK = 8, KC_COUNT = 9 };
 
 static void prof_begin(Gpt* g) {
   if (!g->prof) return;
@@ -438,6 +448,55 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
   return check_launch("residual_add");
 }
 
+// Builds (or reuses) the operation list of the persistent decode-step kernel for B sequences: per layer QKV (norm
+// prologue), attention, out-projection (+residual), FFN up (norm prologue, activation / gate), FFN down (+residual),
+// then the LM head behind the final norm.
+static int ensure_stack(Gpt* g, int B) {
+  const TSB200GptConfig& c = g->c;
+  g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
+  if (!g->use_stack || B > g->stack_max_B || g->tp != 1) return 1;
+  if (g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) return 1;
+  const int d = c.d, Hd = c.H * c.hd;
+  const int nmode = c.norm_type == 0 ? 2 : 1;
+  std::vector<StackOp> ops;
+  auto lin = [&](int xmode, const void* x, const void* ng, const void* nb, const void* Wp, int K, int N, const Epilogue& ep) {
+    StackOp o{};
+    o.type = 0; o.xmode = xmode; o.Wp = Wp; o.x = x; o.gamma = ng; o.beta = (c.norm_type == 0) ? nb : nullptr; o.eps = c.eps;
+    o.K = K; o.N = N; o.ep = ep;
+    ops.push_back(o);
+  };
+  for (int k = 0; k < c.L; ++k) {
+    LayerW& L = g->L[k];
+    lin(nmode, g->x, L.n1_g, L.n1_b, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0));
+    StackOp at{};
+    at.type = 1; at.x = g->qkv; at.cK = L.cK; at.cV = L.cV; at.ep.y = g->attn;
+    ops.push_back(at);
+    lin(0, g->attn, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+    lin(nmode, g->x, L.n2_g, L.n2_b, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, c.act, g->glu));
+    lin(0, g->ffn, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+  }
+  lin(nmode, g->x, g->nf_g, g->nf_b, g->head_w, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0));
+  if (!g->stack_partials) {
+    StackConfig sc{};
+    sc.dtype = c.dtype; sc.M = c.max_batch < g->stack_max_B ? c.max_batch : g->stack_max_B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd;
+    int64_t pb, cb, ab;
+    decode_stack_scratch(sc, ops.data(), (int)ops.size(), g->st->sm_count, &pb, &cb, &ab);
+    TSB_TRY(dev_alloc(g, &g->stack_partials, pb, false));
+    TSB_TRY(dev_alloc(g, &g->stack_counters, cb, true));
+    TSB_TRY(dev_alloc(g, &g->stack_attn, ab, false));
+    g->stack_counter_bytes = cb;
+    void* p = nullptr;
+    TSB_TRY(dev_alloc(g, &p, (int64_t)ops.size() * sizeof(StackOp), false));
+    g->stack_dev = (StackOp*)p;
+  }
+  TSB_CUDA(cudaMemcpyAsync(g->stack_dev, ops.data(), ops.size() * sizeof(StackOp), cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));  // `ops` is pageable host memory
+  g->stack_host.swap(ops);
+  g->stack_B = B;
+  g->stack_key = g->x;
+  return 1;
+}
+
 // One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
 // With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
 static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
@@ -459,6 +518,18 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     count_launch(dev);
     prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
+  }
+  if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->tp == 1 && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
+    StackConfig sc{};
+    sc.dtype = dt; sc.M = B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd; sc.Tmax = c.max_tokens; sc.qkv_rs = g->Nqkv;
+    sc.use_rope = c.pe_type == 2; sc.rope_tab = g->rope_tab; sc.dT = dT;
+    prof_begin(g);
+    const int r = launch_decode_stack(dev, g->st, sc, g->stack_dev, g->stack_host.data(), (int)g->stack_host.size(),
+                                      g->stack_partials, g->stack_counters, g->stack_attn, g->err_flag, g->stack_trace, g->pdl, g->s);
+    if (r != 2) {
+      prof_end(g, KC_STACK);
+      return r;
+    }
   }
   const int act = c.act;
   for (int k = 0; k < c.L; ++k) {
@@ -510,6 +581,7 @@ static int check_err_flag(Gpt* g) {
   e |= tc_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
+    if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
     TSB_FAIL("a kernel gave up waiting on a shared-memory barrier (internal error); results of this call are invalid");
   }
   return 1;
@@ -552,6 +624,7 @@ static int ensure_graph(Gpt* g, const TSB200DecodingOptions* opt, int n_steps) {
   // split count for the attention kernel: fixed per graph, chosen for the longest cache this call reaches
   int Tp = 256;
   while (Tp < g->T + n_steps) Tp <<= 1;
+  TSB_TRY(ensure_stack(g, B));
   GraphKey key;
   key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, B, c.H, c.Hkv, Tp);
   key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
@@ -629,6 +702,8 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   {
     const char* e = getenv("TSB200_PDL");  // "0" switches programmatic dependent launch off (A/B measurements)
     g->pdl = !(e && e[0] == '0');
+    e = getenv("TSB200_STACK");            // "0": one launch per operation instead of the persistent decode-step kernel
+    g->use_stack = !(e && e[0] == '0');
   }
   const TSB200GptConfig& cc = g->c;
   const int64_t d = cc.d, F = cc.F, V = cc.V, Hd = (int64_t)cc.H * cc.hd, KVd = (int64_t)cc.Hkv * cc.hd;
@@ -695,7 +770,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   g->topp_ws_bytes = TSB200_TopPWorkspaceBytes(MB, cc.V);
   G_ALLOC(g->topp_ws, g->topp_ws_bytes);
 #undef G_ALLOC
-  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device) || !init_tc_attrs(cc.device)) return fail();
+  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device) || !init_tc_attrs(cc.device) || !init_stack_attrs(cc.device)) return fail();
   if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) {
     set_last_error("gpt_create: cudaEventCreate failed");
     return fail();
@@ -1054,6 +1129,14 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   return 1;
 }
 
+int TSB200_GptDebugStackTrace(void* h, void* device_buffer) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_debug_stack_trace: null handle");
+  g->stack_trace = reinterpret_cast<long long*>(device_buffer);
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }  // the pointer is a kernel argument of the captured step
+  return 1;
+}
+
 int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, float* class_ms, int64_t* class_groups,
                             int n_classes) {
   Gpt* g = (Gpt*)h;
@@ -1069,6 +1152,7 @@ int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* o
   int Tp = 256;
   while (Tp < g->T + n_steps) Tp <<= 1;
   const int splits = attn_pick_splits(g->st, g->B, c.H, c.Hkv, Tp);
+  TSB_TRY(ensure_stack(g, g->B));
   g->prof = true;
   g->prof_n = 0;
   int ok = 1;

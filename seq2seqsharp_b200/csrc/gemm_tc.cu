@@ -2,9 +2,10 @@
 //
 // sm_100a design (5th-generation tensor cores):
 //  * operands are staged in shared memory by TMA tensor copies (cp.async.bulk.tensor, 128-byte swizzle, completion
-//    on mbarriers): A = activations [M,K] row-major (K-major operand, box 64 k x 128 rows), B = the engine's packed
-//    weight tiles [ct][kb][32 k][256 n] read in place through a 4-D tensor map (MN-major operand, box 64 n x 32 k x
-//    2 kb), so decode GEMV and GEMM share ONE copy of the weights;
+//    on mbarriers): A = activations [M,K] row-major (K-major operand, box 64 k x 128 rows); B = the engine's packed
+//    weight tiles, which are stored pre-swizzled (packed_tile_off), so the 128 columns x 32 k a stage needs from a
+//    tile are one contiguous 8 KB range that a plain bulk copy lands in operand layout (MN-major, SWIZZLE_128B):
+//    decode GEMV and GEMM share ONE copy of the weights;
 //  * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=128, K=16) with the accumulator in
 //    tensor memory (TMEM, 128 lanes x 128 fp32 columns), tcgen05.commit hands shared-memory stages back to the
 //    producer and signals the epilogue;
@@ -59,12 +60,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(s_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
-          s_u32(dst)),
-      "l"(map), "r"(s_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
+__device__ __forceinline__ void tc_bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s_u32(dst)),
+               "l"(src), "r"(bytes), "r"(s_u32(bar))
+               : "memory");
 }
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in 16-byte units,
 // version 1, 128-byte swizzle.
@@ -112,6 +111,7 @@ struct TcArgs {
   float* partials;    // [ksplit][M][Npad] raw fp32 accumulators, Npad = gridDim.x * 128
   unsigned int* counters;  // one per output tile, zero on entry, self-resetting
   int* error_flag;
+  const unsigned char* Wp;  // packed weight tiles
   Epilogue ep;
 };
 
@@ -157,8 +157,7 @@ __device__ __forceinline__ void tc_finish(const TcArgs& a, int row, int col0, co
   }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA,
-                                                                const __grid_constant__ CUtensorMap mapB, TcArgs a) {
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // carve: [stages][A 16K][B 16K] (1024-byte aligned for the 128B swizzle atoms), then barriers
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -198,18 +197,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
   if (w == 0 && lane == 0) {
     // ---------------- TMA producer
-    const int ct = n_tile >> 1, n_in = (n_tile & 1) * 128;
+    // B: this CTA's 128 columns are boxes (2p, 2p+1) of column tile ct: 8 KB contiguous in every packed k tile
+    const unsigned char* wsrc = a.Wp + ((size_t)(n_tile >> 1) * a.KB) * 16384 + (size_t)(n_tile & 1) * 8192;
     for (int it = 0; it < k_iters; ++it) {
       const int s = it % kTcStages, r = it / kTcStages;
       if (it >= kTcStages && !tc_mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
         s_err = 1;
         break;
       }
-      tc_mbar_expect_tx(&full[s], kABytes + kBBytes);
+      const int kb0 = (k_begin + it) * 2;
+      const bool two = kb0 + 1 < a.KB;  // the last 64-k block of an odd tile count has one packed tile only
+      tc_mbar_expect_tx(&full[s], kABytes + (two ? 16384 : 8192));
       tma_load_2d(sA + s * kABytes, &mapA, (k_begin + it) * kBK, m_tile * kBM, &full[s]);
-      // B: two 64-column halves of the 128-column tile, each [2 kb][32 k][64 n] = 8 KB
-      tma_load_4d(sB + s * kBBytes, &mapB, n_in, 0, (k_begin + it) * 2, ct, &full[s]);
-      tma_load_4d(sB + s * kBBytes + 8192, &mapB, n_in + 64, 0, (k_begin + it) * 2, ct, &full[s]);
+      tc_bulk_g2s(sB + s * kBBytes, wsrc + (size_t)kb0 * 16384, 8192, &full[s]);
+      if (two) tc_bulk_g2s(sB + s * kBBytes + 8192, wsrc + (size_t)(kb0 + 1) * 16384, 8192, &full[s]);
     }
   } else if (w == 1 && lane == 0) {
     // ---------------- MMA issuer
@@ -224,13 +225,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_base = s_u32(sA + s * kABytes), b_base = s_u32(sB + s * kBBytes);
+      const int kk_end = ((k_begin + it) * 2 + 1 < a.KB) ? 4 : 2;  // no second packed tile: its stage half was not filled
 #pragma unroll
       for (int kk = 0; kk < kBK / 16; ++kk) {
+        if (kk >= kk_end) break;
         // A (K-major, SW128): rows of 128 B, 8-row atoms 1024 B apart; 16 k = 32 B along the row
         const uint64_t ad = make_desc(a_base + kk * 32, 16, 1024);
-        // B (MN-major, SW128): 64-n atoms [8 k][128 B]; k groups of 8 are 1024 B apart (SBO), the second 64-n half is
-        // 8192 B away (LBO); 16 k = two atoms = 2048 B
-        const uint64_t bd = make_desc(b_base + kk * 2048, 8192, 1024);
+        // B (MN-major, SW128), stage = [k tile 2][64-n box 2][32 k][128 B]: k groups of 8 are 1024 B apart (SBO), the
+        // second 64-n box is 4096 B away (LBO); 16 k = two groups = 2048 B; the second k tile starts at 8192 B
+        const uint64_t bd = make_desc(b_base + (kk >> 1) * 8192 + (kk & 1) * 2048, 4096, 1024);
         umma_f16(tmem_acc, ad, bd, idesc, (it > 0 || kk > 0) ? 1u : 0u);
       }
       umma_commit(&empty[s]);  // frees the stage when these MMAs have read it
@@ -373,7 +376,7 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
   if (!enc) return 2;
   TSB_TRY(init_tc_attrs(device));
   const int KB = (K + 31) / 32, CT = (N + 255) / 256;
-  CUtensorMap mapA, mapB;
+  CUtensorMap mapA;
   {
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
@@ -384,19 +387,9 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     TSB_CHECK(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled(A) failed with %d", (int)r);
   }
-  {
-    // packed tiles as a 4-D tensor: (n_in 256, k_in 32, kb KB, ct CT)
-    const cuuint64_t dims[4] = {256, 32, (cuuint64_t)KB, (cuuint64_t)CT};
-    const cuuint64_t strides[3] = {512, 16384, (cuuint64_t)KB * 16384};
-    const cuuint32_t box[4] = {64, 32, 2, 1};
-    const cuuint32_t el[4] = {1, 1, 1, 1};
-    const CUresult r = enc(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(Wp), dims, strides, box, el,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TSB_CHECK(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled(B) failed with %d", (int)r);
-  }
   TcArgs a{};
   a.M = M; a.N = N; a.K = K; a.KB = KB; a.error_flag = error_flag; a.ep = ep;
+  a.Wp = reinterpret_cast<const unsigned char*>(Wp);
   dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM, 1);
   TSB_CHECK(grid.y <= 65535, "gemm_tc: too many row tiles");
   // few output tiles (decode-sized M): share each tile's K range among several CTAs so that all SMs stream weights
@@ -422,7 +415,7 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
     }
   }
   const size_t smem = kTcStages * (kABytes + kBBytes) + 1024 + 256;
-  gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(mapA, mapB, a);
+  gemm_tc_kernel<<<grid, kTcThreads, smem, s>>>(mapA, a);
   count_launch(device);
   return check_launch("gemm_tc");
 }

@@ -2,7 +2,8 @@
 //
 // Blackwell-first design:
 //  * weights are pre-packed at load time into contiguous 16 KB tiles [KT=32 rows][NT=32*VEC columns] ordered
-//    column-tile-major, so the units a CTA works on are ONE contiguous byte range of HBM;
+//    column-tile-major, so the units a CTA works on are ONE contiguous byte range of HBM (fp16 tiles are stored
+//    in the 128-byte-swizzled box order of packed_tile_off(), which this kernel's 16-byte reads follow);
 //  * each CTA is persistent over a contiguous, evenly sized range of tiles (stream-K: the K dimension of a column
 //    tile may be shared by several CTAs), so all SMs stream the same number of bytes regardless of the shape;
 //  * one producer warp feeds a ring of shared-memory stages with TMA bulk copies (cp.async.bulk, completion on an
@@ -22,85 +23,15 @@
 // kernels of the reference (TensorSharp.CUDA/DeviceCode/AdvFuncKernels.cs:613-685,791-845,
 // TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-362, Seq2SeqSharp/Layers/PositionwiseFeedForward.cs:72-98).
 #include "kernels.cuh"
+#include "stream_common.cuh"
 
 namespace tsb {
 
-constexpr int kKT = 32;                 // rows per packed tile
-constexpr int kTileBytes = 16384;       // kKT * NT * sizeof(T) for both dtypes
-constexpr int kConsumerWarps = 8;
-constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
-constexpr unsigned kSpinLimit = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: returns false when the phase did not complete within the poll limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned limit = kSpinLimit) {
-  const uint32_t a = smem_u32(bar);
-  for (unsigned i = 0; i < limit; ++i) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
-               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ long long gtimer() {
-  long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 #define TRACE(slot)                                                                     \
   do {                                                                                  \
     if (a.trace && (tid & 31) == 0 && ((tid >> 5) == 0 || (tid >> 5) == kConsumerWarps)) \
       a.trace[(size_t)blockIdx.x * 8 + (slot)] = gtimer();                              \
   } while (0)
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-template <typename T> struct TileVec;
-template <> struct TileVec<__half> {
-  static constexpr int N = 8;
-  uint4 raw;
-  __device__ __forceinline__ void lds(const void* p) { raw = *reinterpret_cast<const uint4*>(p); }
-  __device__ __forceinline__ void get(float* f) const {
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 t = __half22float2(h[i]);
-      f[2 * i] = t.x;
-      f[2 * i + 1] = t.y;
-    }
-  }
-};
-template <> struct TileVec<float> {
-  static constexpr int N = 4;
-  float4 raw;
-  __device__ __forceinline__ void lds(const void* p) { raw = *reinterpret_cast<const float4*>(p); }
-  __device__ __forceinline__ void get(float* f) const {
-    f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w;
-  }
-};
-
 struct StreamArgs {
   const void* Wp;        // packed tiles
   const void* x;         // xmode 0: T [M,K]; xmode 1/2: fp32 residual stream [M,K]
@@ -300,7 +231,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(StreamAr
     const unsigned char* tile = stage_mem + (size_t)s * kTileBytes;
     TileVec<T> wv[RPW];
 #pragma unroll
-    for (int rr = 0; rr < RPW; ++rr) wv[rr].lds(tile + ((size_t)(w * RPW + rr) * NT + lane * VEC) * sizeof(T));
+    for (int rr = 0; rr < RPW; ++rr) wv[rr].lds(tile + (size_t)packed_tile_off<T>(w * RPW + rr, lane * VEC) * sizeof(T));
     float xv[M][RPW];
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -428,7 +359,7 @@ __global__ void pack_tiles_kernel(TD* __restrict__ dst, const TS* __restrict__ s
     const int k = (int)(i / cols), j = (int)(i % cols);
     const int c = c0 + j * cs;
     const long long tile = (long long)(c / NT) * KB + (k / kKT);
-    dst[tile * (kKT * NT) + (long long)(k % kKT) * NT + (c % NT)] = from_f<TD>(to_f<TS>(src[(long long)k * src_ld + j]));
+    dst[tile * (kKT * NT) + packed_tile_off<TD>(k % kKT, c % NT)] = from_f<TD>(to_f<TS>(src[(long long)k * src_ld + j]));
   }
 }
 

@@ -24,7 +24,48 @@ int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, c
                        const void* beta, float eps, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws,
                        int64_t ws_bytes, cudaStream_t s);
 int64_t stream_workspace_bytes(int dtype, int M, int K, int N, int sm_count);
+
+// ---- persistent decode-step kernel (decode_stack.cu): one launch runs a whole list of operations ---------------
+struct StackOp {
+  int type;               // 0 linear on packed weights, 1 rope + cache append + attention partials
+  // linear
+  int xmode;              // 0: x is T [M,K]; 1 / 2: RMSNorm / LayerNorm of the fp32 rows x
+  const void* Wp;
+  const void* x;
+  const void* gamma;
+  const void* beta;
+  float eps;
+  int K, N;
+  Epilogue ep;
+  // attention: q|k|v rows of the current token in `x` (row stride qkv_rs elements), this layer's cache, output
+  // rows [M, H*hd] in T at ep.y
+  void* cK;
+  void* cV;
+};
+struct StackConfig {
+  int dtype, M;           // M = sequences (1..4; up to 8 on the fp16 tensor-core kernel)
+  int H, Hkv, hd, Tmax, qkv_rs, use_rope;
+  const float2* rope_tab; // [Tmax, hd/2] cos/sin
+  const int* dT;          // device word holding the cache length before this step
+};
+// Sizes of the scratch areas launch_decode_stack() needs for a program (host copy of the ops).
+void decode_stack_scratch(const StackConfig& c, const StackOp* ops, int n_ops, int sm_count, int64_t* partial_bytes,
+                          int64_t* counter_bytes, int64_t* attn_part_bytes);
+// 1 ok, 0 error, 2 when the program cannot run on this kernel (caller uses the per-op launches).
+int launch_decode_stack(int device, DeviceState* st, const StackConfig& c, const StackOp* ops_dev, const StackOp* ops_host,
+                        int n_ops, void* partials, void* counters, void* attn_part, int* error_flag,
+                        long long* trace, bool pdl, cudaStream_t s);
+int init_stack_attrs(int device);
 int64_t packed_bytes(int dtype, int K, int N);
+// Element offset of (k, c) inside one packed 16 KB tile (k < 32, c < tile columns).  fp32 tiles are plain
+// [32 k][128 columns].  fp16 tiles are stored as the shared-memory image the tensor cores want: four 64-column
+// boxes, each [32 k][128 bytes], the eight 16-byte units of a row XOR-ed with k & 7 (the SWIZZLE_128B pattern), so
+// that ONE linear 16 KB bulk copy lands a tile ready for ldmatrix / tcgen05 descriptors without bank conflicts.
+template <typename T>
+__host__ __device__ __forceinline__ int packed_tile_off(int k, int c) {
+  if (sizeof(T) == 2) return ((c >> 6) << 11) + (k << 6) + ((((c >> 3) & 7) ^ (k & 7)) << 3) + (c & 7);
+  return k * 128 + c;
+}
 int packed_tile_cols(int dtype);
 int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_dtype, const void* src, int rows, int cols,
                 int src_ld, int K, int c0, int cs, cudaStream_t s);

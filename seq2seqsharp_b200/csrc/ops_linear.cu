@@ -94,7 +94,8 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const T* __restrict_
 #pragma unroll
     for (int u = 0; u < kGemvUnroll; ++u) {
       const int kk = k + u * kGemvWarps;
-      if (kk < k1 && (col_ok || packedKB)) wv[u].load(packedKB ? wp + (int64_t)kk * NT : wp + (int64_t)kk * N);
+      if (kk < k1 && (col_ok || packedKB))
+        wv[u].load(packedKB ? wp + (int64_t)(kk >> 5) * (32 * NT) + packed_tile_off<T>(kk & 31, lane * VEC) - lane * VEC : wp + (int64_t)kk * N);
       else wv[u].zero();
     }
 #pragma unroll
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmArgs g, Epilogue 
       const int k = k0 + kk, n = n0 + nn;
       float bv = 0.0f;
       if (k < g.K && n < g.N)
-        bv = g.b_packedKB ? to_f<T>(B[((int64_t)(n / g.b_NT) * g.b_packedKB + k / 32) * (32 * g.b_NT) + (int64_t)(k % 32) * g.b_NT + n % g.b_NT])
+        bv = g.b_packedKB ? to_f<T>(B[((int64_t)(n / g.b_NT) * g.b_packedKB + k / 32) * (32 * g.b_NT) + packed_tile_off<T>(k % 32, n % g.b_NT)])
                           : to_f<T>(B[k * g.b_k + n * g.b_n]);
       Bs[kk][nn] = bv;
     }

@@ -1,0 +1,80 @@
+// Shared device helpers of the streaming kernels: mbarrier / TMA bulk-copy wrappers (every wait bounded), the 16-byte
+// tile vector of each dtype, and the geometry of the packed weight tiles.
+#pragma once
+#include "kernels.cuh"
+
+namespace tsb {
+
+constexpr int kKT = 32;                 // rows per packed tile
+constexpr int kTileBytes = 16384;       // kKT * NT * sizeof(T) for both dtypes
+constexpr int kConsumerWarps = 8;
+constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: returns false when the phase did not complete within the poll limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned limit = kSpinLimit) {
+  const uint32_t a = smem_u32(bar);
+  for (unsigned i = 0; i < limit; ++i) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ long long gtimer() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <typename T> struct TileVec;
+template <> struct TileVec<__half> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ void lds(const void* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void get(float* f) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+template <> struct TileVec<float> {
+  static constexpr int N = 4;
+  float4 raw;
+  __device__ __forceinline__ void lds(const void* p) { raw = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void get(float* f) const {
+    f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w;
+  }
+};
+
+
+}  // namespace tsb

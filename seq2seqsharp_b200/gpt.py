@@ -322,16 +322,21 @@ class GPT:
         N.call("TSB200_GptGetStepTimes", self._h, ms.ctypes.data_as(C.c_void_p), n, C.byref(got))
         return ms[:got.value]
 
-    KERNEL_CLASSES = ("embed", "norm", "linear", "rope_append", "attention", "sampling", "commit", "allreduce")
+    KERNEL_CLASSES = ("embed", "norm", "linear", "rope_append", "attention", "sampling", "commit", "allreduce", "decode_stack")
 
     def ProfileDecode(self, n_steps, opts: DecodingOptions):
         """{class: (ms_total, launch_groups)} over n_steps un-captured decode steps (CUDA events per launch group)."""
-        ms = np.zeros(8, dtype=np.float32)
-        groups = np.zeros(8, dtype=np.int64)
+        n = len(self.KERNEL_CLASSES)
+        ms = np.zeros(n, dtype=np.float32)
+        groups = np.zeros(n, dtype=np.int64)
         c = self._opts(opts)
         N.call("TSB200_GptProfileDecode", self._h, n_steps, C.byref(c), ms.ctypes.data_as(C.c_void_p),
-               groups.ctypes.data_as(C.c_void_p), 8)
+               groups.ctypes.data_as(C.c_void_p), n)
         return {k: (float(ms[i]), int(groups[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
+
+    def DebugStackTrace(self, device_ptr):
+        """Profiling aid: per-CTA, per-operation timestamps of the persistent decode-step kernel (0 switches it off)."""
+        N.call("TSB200_GptDebugStackTrace", self._h, C.c_void_p(device_ptr or None))
 
     # ---- inspection --------------------------------------------------------------------------------
     def Logits(self, want_probs=True):

@@ -232,7 +232,8 @@ def test_step_host_and_profile_paths_agree_with_graph_decode(cuda):
         last = gpt.StepHost(last, opts)
         b.append(last.copy())
     prof = gpt.ProfileDecode(4, opts)
-    assert prof["linear"][1] == 4 * (4 * cfg.L + 1) and prof["linear"][0] > 0
+    # batch <= 4 runs the layer stack as one persistent launch per step; larger batches one launch per linear
+    assert prof["decode_stack"][1] == 4 and prof["decode_stack"][0] > 0 and prof["linear"][1] == 0
     c = gpt.Decode(6, opts)
     np.testing.assert_array_equal(np.stack(b, axis=1), a[:, :10])
     np.testing.assert_array_equal(c, a[:, 14:20])
@@ -240,3 +241,46 @@ def test_step_host_and_profile_paths_agree_with_graph_decode(cuda):
     gpt.Decode(5, opts)
     assert len(gpt.StepTimes(5)) == 5 and (gpt.StepTimes(5) > 0).all()
     gpt.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B", [1, 3, 4, 7])
+@pytest.mark.parametrize("cfg", ARCHS, ids=[c.name for c in ARCHS])
+def test_persistent_step_kernel_matches_per_op_launches(cuda, cfg, B, monkeypatch):
+    """Small batches decode through ONE persistent kernel per step (all linears, RoPE, cache append and attention of the
+    layer stack); TSB200_STACK=0 keeps one launch per operation.  Fed the same ids, both must give the same logits
+    (attention splits differ, so not bitwise: the tolerance of the dtype) and leave the same cache length; the
+    persistent kernel must also be bitwise reproducible run to run."""
+    S, n_new = 19, 12
+    w = synthetic_weights(cfg, 11, std=0.05 if cfg.d < 512 else 0.03, bias_std=0.02, max_pos=66)
+    prompt = prompt_ids(13, B, S, cfg.V)
+    opts = DecodingOptions(MaxTgtSentLength=64, DecodingStrategy=DS.GreedySearch, BlockedTokens=[0])
+
+    def engine(stack):
+        monkeypatch.setenv("TSB200_STACK", "1" if stack else "0")
+        g = GPT(cfg, max_batch=B, max_tokens=64)
+        g.LoadWeights(w)
+        return g
+
+    a, b, a2 = engine(True), engine(False), engine(True)
+    last = a.Prefill(prompt, opts)
+    np.testing.assert_array_equal(last, b.Prefill(prompt, opts))
+    a2.Prefill(prompt, opts)
+    # fp16 models run up to 8 sequences on the tensor-core variant, fp32 models up to 4 on the CUDA-core variant
+    import os
+    tensor_rows = 4 if os.environ.get("TSB200_STACK_MODE") == "fma" else 8   # debug switch: CUDA-core consumers for fp16 too
+    expect = 1 if B <= (tensor_rows if cfg.dtype == "float16" else 4) else 0
+    assert a.ProfileDecode(1, opts)["decode_stack"][1] == expect and b.ProfileDecode(1, opts)["decode_stack"][1] == 0
+    a2.ProfileDecode(1, opts)
+    worst = 0.0
+    for _ in range(n_new):
+        na, nb = a.StepHost(last, opts), b.StepHost(last, opts)
+        a2.StepHost(last, opts)
+        la, lb = a.Logits(want_probs=False)[0], b.Logits(want_probs=False)[0]
+        np.testing.assert_array_equal(la, a2.Logits(want_probs=False)[0])
+        worst = max(worst, rel_err(la, lb))
+        last = na
+    assert worst <= tol_for(cfg), worst
+    assert a.CacheLength() == b.CacheLength() == S + 1 + n_new
+    for g in (a, b, a2):
+        g.close()
