@@ -7,6 +7,8 @@
 //                 whole CTA reduces (value, index) pairs with warp shuffles and the same tie rule).
 //  * Top-P      : device version of the host loop ComputeGraphTensor.TopPSample
 //                 (Seq2SeqSharp/Tools/ComputeGraphTensor.cs:2305-2403); see topp_kernel.
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace tsb {
@@ -189,6 +191,8 @@ struct ToppSmem {
   int k_next;
   uint32_t acc_bits;
   int2 warp_pair[32];
+  uint32_t tot[256];    // cluster sort: this CTA's count per digit (read by the other CTAs of the cluster)
+  uint32_t base[256];   // cluster sort: global offset of this CTA's first key of a digit, minus its local offset
 };
 
 // The buffers are written earlier in the same kernel, so they are deliberately NOT const __restrict__ (no
@@ -344,7 +348,7 @@ __device__ void exact_prefix(const uint32_t* keys, float* accs, int n_valid, flo
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   // ---- head: plain sequential adds out of shared memory, eight at a time
   const int nh = min(n_valid, kHead);
-  for (int i = tid; i < nh; i += blockDim.x) sm.chunk[i] = __uint_as_float(keys[i]);
+  for (int i = tid; i < nh; i += blockDim.x) sm.chunk[i] = __uint_as_float(__ldcg(keys + i));
   __syncthreads();
   if (tid == 0) {
     float acc = 0.0f;
@@ -393,7 +397,7 @@ __device__ void exact_prefix(const uint32_t* keys, float* accs, int n_valid, flo
     F.i0 = F.i1 = 0;
 #pragma unroll
     for (int j = 0; j < kPerThread; ++j) {
-      wb[j] = (base + j < n_valid) ? keys[base + j] : 0u;
+      wb[j] = (base + j < n_valid) ? __ldcg(keys + base + j) : 0u;
       if (wb[j]) f[j] = inc_of(wb[j], e);
       else f[j].i0 = f[j].i1 = 0;
       F = compose(F, f[j]);
@@ -473,7 +477,7 @@ __device__ void exact_prefix(const uint32_t* keys, float* accs, int n_valid, flo
         sm.stop = 1;
       } else if (ov < wend) {  // element `ov` carries the sum into the next binade: one ordinary fp32 add
         const float prev = (ov == k0) ? __uint_as_float(sm.acc_bits) : accs[ov - 1];
-        const float acc = prev + __uint_as_float(keys[ov]);
+        const float acc = prev + __uint_as_float(__ldcg(keys + ov));
         accs[ov] = acc;
         sm.acc_bits = __float_as_uint(acc);
         sm.k_next = ov + 1;
@@ -578,10 +582,248 @@ __global__ void __launch_bounds__(kTopPThreads) topp_kernel(int* out, const floa
   if (threadIdx.x == 0) out[r] = (sm.best_k == 0x7fffffff) ? 0 : (int)idxA[sm.best_k];
 }
 
+
+// ------------------------------------------------------------------------------------------------ Top-P on a cluster
+// The same algorithm with the stable radix sort spread over a thread-block cluster of kToppCluster CTAs (one cluster
+// per row): CTA c ranks the c-th slice of the current key order, the 256 digit totals of every CTA are read through
+// distributed shared memory after a cluster barrier, and the scatter goes to the global ping-pong buffers (L2).
+// A slice is 1/8 of the vocabulary, so the latency-bound ranking chains are 8 times shorter than on one SM.  CTA 0
+// then runs the exact prefix sum and the search.  Keys and indices written by other CTAs are read with L2 loads.
+constexpr int kToppCluster = 8;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t ld_dsmem_u32(const uint32_t* local_ptr, uint32_t cta) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local_ptr), ra, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(cta));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void radix_pass_cluster(const uint32_t* kin, const uint32_t* iin, uint32_t* kout, uint32_t* iout, int n,
+                                                   int shift, bool first, ToppSmem& sm, int crank) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int n_per = ((n + kToppCluster - 1) / kToppCluster + 31) & ~31;
+  const int s_beg = min(n, crank * n_per), s_end = min(n, s_beg + n_per);
+  const int n_loc = s_end - s_beg;
+  const int per_warp = ((n_loc + kTopPWarps - 1) / kTopPWarps + 31) & ~31;
+  const int beg = min(s_end, s_beg + w * per_warp), end = min(s_end, beg + per_warp);
+  for (int i = threadIdx.x; i < kTopPWarps * 256; i += blockDim.x) (&sm.hist[0][0])[i] = 0;
+  __syncthreads();
+  // A: per-warp histogram of the (descending) digit
+  for (int base0 = beg; base0 < end; base0 += 32 * kRadixUnroll) {
+    uint32_t keys[kRadixUnroll];
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      keys[q] = j < end ? __ldcg(kin + j) : 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      if (base0 + q * 32 >= end) break;
+      const bool ok = j < end;
+      const uint32_t dg = ok ? (255u - ((keys[q] >> shift) & 255u)) : 256u;
+      const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+      if (ok && lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  // B: exclusive scan inside the CTA in (digit-major, warp-minor) order
+  {
+    uint32_t v[8];
+    uint32_t tsum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int li = threadIdx.x * 8 + e;  // li = digit * 32 + warp
+      v[e] = sm.hist[li & 31][li >> 5];
+      tsum += v[e];
+    }
+    uint32_t incl = tsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) sm.warp_tot[w] = incl;
+    __syncthreads();
+    if (w == 0) {
+      uint32_t t = sm.warp_tot[lane];
+      uint32_t ti = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u2 = __shfl_up_sync(0xffffffffu, ti, o);
+        if (lane >= o) ti += u2;
+      }
+      sm.warp_tot[lane] = ti - t;
+    }
+    __syncthreads();
+    uint32_t run = sm.warp_tot[w] + incl - tsum;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int li = threadIdx.x * 8 + e;
+      sm.hist[li & 31][li >> 5] = run;
+      run += v[e];
+    }
+  }
+  __syncthreads();
+  // this CTA's keys per digit: difference of the offsets of warp 0
+  if (threadIdx.x < 256) {
+    const int d = threadIdx.x;
+    sm.tot[d] = (d == 255 ? (uint32_t)n_loc : sm.hist[0][d + 1]) - sm.hist[0][d];
+  }
+  cluster_sync_all();  // every CTA's totals are in place (and all reads of the previous pass are done)
+  // C: global base of (digit, this CTA): keys of smaller digits anywhere + keys of this digit in earlier CTAs
+  if (threadIdx.x < 256) {
+    const int d = threadIdx.x;
+    uint32_t all = 0, before = 0;
+#pragma unroll
+    for (int c = 0; c < kToppCluster; ++c) {
+      const uint32_t t = ld_dsmem_u32(&sm.tot[d], (uint32_t)c);
+      all += t;
+      if (c < crank) before += t;
+    }
+    uint32_t incl = all;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) sm.warp_tot[w] = incl;  // 8 warps take part
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    uint32_t wbase = 0;
+    for (int i = 0; i < w; ++i) wbase += sm.warp_tot[i];
+    sm.base[d] = wbase + incl - all + before - sm.hist[0][d];
+  }
+  __syncthreads();
+  // D: stable scatter into the global buffers
+  for (int base0 = beg; base0 < end; base0 += 32 * kRadixUnroll) {
+    uint32_t keys[kRadixUnroll], idxs[kRadixUnroll];
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      keys[q] = j < end ? __ldcg(kin + j) : 0u;
+      idxs[q] = j < end ? (first ? (uint32_t)j : __ldcg(iin + j)) : 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < kRadixUnroll; ++q) {
+      const int j = base0 + q * 32 + lane;
+      if (base0 + q * 32 >= end) break;
+      const bool ok = j < end;
+      const uint32_t dg = ok ? (255u - ((keys[q] >> shift) & 255u)) : 256u;
+      const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+      const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+      uint32_t pos = 0;
+      if (ok) pos = sm.hist[w][dg] + sm.base[dg] + rank;
+      __syncwarp();
+      if (ok) {
+        kout[pos] = keys[q];
+        iout[pos] = idxs[q];
+        if (lane == (__ffs(peers) - 1)) sm.hist[w][dg] += __popc(peers);
+      }
+      __syncwarp();
+    }
+  }
+  cluster_sync_all();  // the scattered keys are visible to the whole cluster; sm.tot may be rewritten
+}
+
+__global__ void __launch_bounds__(kTopPThreads) topp_cluster_kernel(int* out, const float* probs, int V, float topP, float repeatPenalty,
+                                                                    const int* history, const int* history_len, int history_stride,
+                                                                    const float* u, uint32_t* ws) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ToppSmem& sm = *reinterpret_cast<ToppSmem*>(smem_raw);
+  pdl_trigger();
+  pdl_wait();
+  const int crank = (int)cluster_rank();
+  const int r = blockIdx.x / kToppCluster;
+  uint32_t* keyA = ws + (size_t)r * 5 * V;
+  uint32_t* keyB = keyA + V;
+  uint32_t* idxA = keyB + V;
+  uint32_t* idxB = idxA + V;
+  int* last = reinterpret_cast<int*>(idxB + V);
+  const float* p = probs + (size_t)r * V;
+  const int* hist = history ? history + (size_t)r * history_stride : nullptr;
+  const int len = (history && history_len) ? history_len[r] : 0;
+  const int n_per = ((V + kToppCluster - 1) / kToppCluster + 31) & ~31;
+  const int s_beg = min(V, crank * n_per), s_end = min(V, s_beg + n_per);
+
+  // 1. keys of this CTA's slice (+ repeat penalty on the last occurrence of each id of the slice in the history)
+  for (int j = s_beg + threadIdx.x; j < s_end; j += blockDim.x) {
+    const float w = p[j];
+    keyA[j] = (w > 0.0f) ? __float_as_uint(w) : 0u;
+  }
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= s_beg && t < s_end) last[t] = -1;
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= s_beg && t < s_end) atomicMax(&last[t], q);
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < len; q += blockDim.x) {
+    const int t = hist[q];
+    if (t >= s_beg && t < s_end && last[t] == q) {
+      float w = p[t];
+      if (w > 0.0f) {
+        const float ratio = (float)(len - q) / (float)len;
+        const float rp = (float)pow((double)ratio, (double)repeatPenalty);
+        w = w * rp;
+        keyA[t] = (w == 0.0f) ? 0u : __float_as_uint(w);  // a zero weight sorts with the dropped entries
+      }
+    }
+  }
+  __syncthreads();
+
+  // 2. sort descending, stable, over the cluster
+  radix_pass_cluster(keyA, nullptr, keyB, idxB, V, 0, true, sm, crank);
+  radix_pass_cluster(keyB, idxB, keyA, idxA, V, 8, false, sm, crank);
+  radix_pass_cluster(keyA, idxA, keyB, idxB, V, 16, false, sm, crank);
+  radix_pass_cluster(keyB, idxB, keyA, idxA, V, 24, false, sm, crank);
+  if (crank != 0) return;  // the last cluster barrier is behind us: nobody reads this CTA's shared memory any more
+
+  // 3. + 4. on CTA 0: exact fp32 prefix sum and search, as in topp_kernel
+  if (threadIdx.x == 0) {
+    sm.n_cand = 0;
+    sm.acc_final = 0.0f;
+    sm.stop = 0;
+    sm.best_k = 0x7fffffff;
+    sm.n_valid = 0;
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < V; j += blockDim.x)
+    if (__ldcg(keyA + j) != 0u && (j + 1 == V || __ldcg(keyA + j + 1) == 0u)) sm.n_valid = j + 1;
+  __syncthreads();
+  float* accs = reinterpret_cast<float*>(keyB);
+  exact_prefix(keyA, accs, sm.n_valid, topP, sm);
+  __syncthreads();
+  const int n = sm.n_cand;
+  const float tot = sm.acc_final, uu = u[r];
+  int mine = 0x7fffffff;
+  for (int k = threadIdx.x; k < n; k += blockDim.x)
+    if (accs[k] / tot >= uu) {
+      mine = k;
+      break;
+    }
+  if (mine != 0x7fffffff) atomicMin(&sm.best_k, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = (sm.best_k == 0x7fffffff) ? 0 : (int)__ldcg(idxA + sm.best_k);
+}
+
 int init_topp_attrs(int device) {
   static bool attr_set[kMaxDevices] = {false};
   if (!attr_set[device]) {
     TSB_CUDA(cudaFuncSetAttribute(topp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ToppSmem)));
+    TSB_CUDA(cudaFuncSetAttribute(topp_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ToppSmem)));
     attr_set[device] = true;
   }
   return 1;
@@ -601,6 +843,32 @@ int launch_topp(int device, DeviceState* st, int* out, const float* probs, int r
   (void)st;
   if (rows == 0) return 1;
   TSB_TRY(init_topp_attrs(device));
+  static int use_cluster = -1;
+  if (use_cluster < 0) {
+    const char* e = getenv("TSB200_TOPP_CLUSTER");  // "0": one CTA per row (A/B measurements)
+    use_cluster = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (use_cluster && V >= 4096) {
+    // one cluster of kToppCluster CTAs per row
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(rows * kToppCluster);
+    cfg.blockDim = dim3(kTopPThreads);
+    cfg.dynamicSmemBytes = sizeof(ToppSmem);
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = kToppCluster;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    uint32_t* wsp = (uint32_t*)ws;
+    TSB_CUDA(cudaLaunchKernelEx(&cfg, topp_cluster_kernel, out, probs, V, topP, repeatPenalty, history, history_len, history_stride, u, wsp));
+    count_launch(device);
+    return check_launch("topp_cluster");
+  }
   TSB_CUDA(launch_k(topp_kernel, dim3(rows), dim3(kTopPThreads), sizeof(ToppSmem), s, out, probs, V, topP, repeatPenalty, history,
                     history_len, history_stride, u, (uint32_t*)ws));
   count_launch(device);
