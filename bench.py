@@ -299,7 +299,10 @@ def run_b200(args):
         with open(traffic_path) as fh:
             tj = json.load(fh)
         # dram bytes per algorithmic byte measured by ncu on the same kernel, scaled to one launch of this workload
-        traffic = tj.get("dram_bytes_per_algorithmic_byte", 0) * lin_bytes / max(1, lin_groups // n_prof) or None
+        ratio = tj.get("dram_bytes_per_algorithmic_byte", 0)
+        if prof["decode_stack"][1] == 0:
+            ratio = tj.get("per_linear_kernel", {}).get("dram_bytes_per_algorithmic_byte", ratio)
+        traffic = ratio * lin_bytes / max(1, lin_groups // n_prof) or None
     step_bytes = gpt.StepBytes(B, T_mid)
     seqs = B if tp else world * B      # sequences decoded by the whole job
     tokens = seqs * K

@@ -322,7 +322,11 @@ static StackPlan stack_plan_t(const StackConfig& c, const StackOp* ops, int n_op
     const int64_t b = (int64_t)g.CT * mc * c.M * NT * 4;
     if (b > p.partial_bytes) p.partial_bytes = b;
     if (g.CT > p.counter_words) p.counter_words = g.CT;
-    const size_t x = (((size_t)c.M * g.KB * kKT * sizeof(T)) + 127) & ~(size_t)127;
+    // staged k-tiles per row: the whole row, or (mma.sync variant, plain inputs) only the tiles a CTA streams
+    int64_t kt = g.KB;
+    const int64_t per = (g.U + g.Gop - 1) / g.Gop;
+    if (mode == 2 && ops[i].xmode == 0 && ops[i].K % 8 == 0 && per < g.KB) kt = per;
+    const size_t x = (((size_t)c.M * kt * kKT * sizeof(T)) + 127) & ~(size_t)127;
     if (x > xs) xs = x;
   }
   // mode 0 (FMA consumers): the eight warps' sums meet in shared memory; 1 (tcgen05): accumulators live in tensor

@@ -117,12 +117,22 @@ __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned 
   bool more_ahead = true;
   const unsigned char* src;
   while (fetch.next(a, src)) {
-    while (more_ahead && n_ahead < a.l2_ahead + 1) {
+    // the look-ahead cursor never falls behind the fetch cursor
+    while (more_ahead && n_ahead < 1) {
       const unsigned char* p;
       more_ahead = ahead.next(a, p);
-      if (more_ahead) {
-        if (n_ahead > 0 || a.l2_ahead > 0) bulk_prefetch_l2(p, kTileBytes);
-        ++n_ahead;
+      if (more_ahead) ++n_ahead;
+    }
+    if (round > 0 && a.l2_ahead > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u, 1u)) {
+      // the ring is full (the consumers are in a dependency wait): let HBM work for this CTA meanwhile by asking L2
+      // for the tiles that come next, then block
+      while (more_ahead && n_ahead < a.l2_ahead + 1) {
+        const unsigned char* p;
+        more_ahead = ahead.next(a, p);
+        if (more_ahead) {
+          bulk_prefetch_l2(p, kTileBytes);
+          ++n_ahead;
+        }
       }
     }
     if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
@@ -198,6 +208,33 @@ __device__ __forceinline__ void stage_plain_vec(T* xs, const T* x, int M, int K,
       for (int j = 0; j < 8; ++j) {
         const int i = v0 + j * 256 + tid;
         if (i < nvp) dst[i] = v[j];
+      }
+    }
+  }
+}
+
+// Slice variant: a CTA whose tile range is shorter than one pass over K only needs the n_t k-tiles it streams
+// (k-tile (kb0 + i) % KB for i < n_t); they are staged back to back, so a wide FFN-down input costs a few KB of shared
+// memory per sequence instead of the whole row.  K % 8 == 0.
+__device__ __forceinline__ void stage_plain_slice(__half* xs, const __half* x, int M, int K, int KB, int kb0, int n_t, int Ks, int tid) {
+  const int nv = n_t * 4;  // 16-byte vectors per row: four per k-tile
+  for (int m = 0; m < M; ++m) {
+    for (int v0 = 0; v0 < nv; v0 += 256 * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = v0 + j * 256 + tid;
+        int kb = kb0 + (i >> 2);
+        if (kb >= KB) kb -= KB;
+        const int k = kb * kKT + (i & 3) * 8;
+        const bool ok = i < nv && k + 8 <= K;
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * K + (ok ? k : 0)));
+        v[j] = ok ? t : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = v0 + j * 256 + tid;
+        if (i < nv) *reinterpret_cast<uint4*>(xs + (size_t)m * Ks + i * 8) = v[j];
       }
     }
   }

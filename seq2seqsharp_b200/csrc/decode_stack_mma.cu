@@ -44,7 +44,13 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
   const int max_contrib = (int)(KB / (U / G)) + 2;
   const Epilogue ep = op->ep;
 
-  if (op->xmode == 0) {
+  // a plain input is staged as the slice of k-tiles this CTA streams when that is less than one pass over K
+  const int n_t = u_end - u_begin;
+  const bool slice = op->xmode == 0 && K % 8 == 0 && n_t < KB;
+  const int xstride = slice ? n_t * kKT : Kp;  // elements between staged rows
+  if (slice) {
+    stage_plain_slice(xs, reinterpret_cast<const T*>(op->x), M, K, KB, u_begin % KB, n_t, xstride, tid);
+  } else if (op->xmode == 0) {
     if (K % 8 == 0) stage_plain_vec<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
     else stage_plain<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
   } else if (nvc) {
@@ -68,7 +74,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
   const int lrow = (lane & 7) + ((lane >> 4) << 3);
   const int lunit = (lane >> 3) & 1;
   const bool row_live = g8 < M;                       // B fragment: n = lane / 4 is the sequence
-  const __half* xrow = xs + (size_t)(row_live ? g8 : 0) * Kp + 2 * t4;
+  const __half* xrow = xs + (size_t)(row_live ? g8 : 0) * xstride + 2 * t4;
   float d[2][4];
 #pragma unroll
   for (int cb = 0; cb < 2; ++cb)
@@ -113,8 +119,9 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     for (int kk = 0; kk < 2; ++kk) {
       uint32_t b0 = 0u, b1 = 0u;
       if (row_live) {
-        b0 = *reinterpret_cast<const uint32_t*>(xrow + kb * kKT + kk * 16);
-        b1 = *reinterpret_cast<const uint32_t*>(xrow + kb * kKT + kk * 16 + 8);
+        const int xt = slice ? (u - u_begin) : kb;  // staged k-tile index
+        b0 = *reinterpret_cast<const uint32_t*>(xrow + xt * kKT + kk * 16);
+        b1 = *reinterpret_cast<const uint32_t*>(xrow + xt * kKT + kk * 16 + 8);
       }
       const int k = kk * 16 + lrow;
 #pragma unroll
