@@ -762,7 +762,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
       if (b > g->lin_ws_bytes) g->lin_ws_bytes = b;
     }
   }
-  if (cc.dtype == TSB200_F16 && g->lin_ws_bytes < (24LL << 20)) g->lin_ws_bytes = 24LL << 20;  // split-K partials of the tensor-core GEMM
+  if (cc.dtype == TSB200_F16 && g->lin_ws_bytes < (64LL << 20)) g->lin_ws_bytes = 64LL << 20;  // split-K partials of the tensor-core GEMM
   G_ALLOC(g->lin_ws, g->lin_ws_bytes);
   G_ALLOC(g->err_flag, 64);
   g->attn_ws_bytes = attn_workspace_bytes(MB, cc.H, cc.hd, cc.max_tokens);

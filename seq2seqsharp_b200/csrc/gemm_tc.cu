@@ -112,6 +112,7 @@ struct TcArgs {
   unsigned int* counters;  // one per output tile, zero on entry, self-resetting
   int* error_flag;
   const unsigned char* Wp;  // packed weight tiles
+  int vec_ok;               // pointers and sizes allow the 16-byte epilogue
   Epilogue ep;
 };
 
@@ -152,6 +153,86 @@ __device__ __forceinline__ void tc_finish(const TcArgs& a, int row, int col0, co
         if (a.ep.residual) x += a.ep.residual[o];
         if (a.ep.y32) a.ep.y32[o] = x;
         else reinterpret_cast<__half*>(a.ep.y)[o] = __float2half_rn(x);
+      }
+    }
+  }
+}
+
+// The same epilogue for a full chunk of 32 columns when every pointer is 16-byte aligned and N is a multiple of 32
+// (TcArgs::vec_ok): 16-byte loads of bias and residual, 16-byte stores, i.e. whole 32-byte sectors instead of one
+// 2-byte store per element (scalar stores made the epilogue longer than the mainloop of a 128 x 256 x 4096 tile).
+__device__ __forceinline__ float tc_act(float x, int act) {
+  switch (act) {
+    case TSB200_ACT_RELU: return x < 0.0f ? 0.0f : x;
+    case TSB200_ACT_SILU: return x / (1.0f + expf(-x));
+    case TSB200_ACT_LEAKYRELU: return x < 0.0f ? 0.01f * x : x;
+    case TSB200_ACT_GELU: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    default: return x;
+  }
+}
+__device__ __forceinline__ void tc_finish_fast(const TcArgs& a, int row, int col0, const float* v) {
+  float b[32];
+  if (a.ep.bias) {
+    const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.ep.bias) + col0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 t = bp[q];
+      const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        b[q * 8 + 2 * i] = f.x;
+        b[q * 8 + 2 * i + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) b[j] = 0.0f;
+  }
+  float x[32];
+  int n_out;
+  size_t o;
+  if (!a.ep.glu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = tc_act(v[j] + b[j], a.ep.act);
+    n_out = 32;
+    o = (size_t)row * a.N + col0;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float av = v[2 * j] + b[2 * j];
+      const float gv = v[2 * j + 1] + b[2 * j + 1];
+      if (a.ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
+      x[j] = av * gv;
+    }
+    n_out = 16;
+    o = (size_t)row * (a.N / 2) + (col0 >> 1);
+  }
+  if (a.ep.residual) {
+    const float4* rp = reinterpret_cast<const float4*>(a.ep.residual + o);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (q * 4 < n_out) {
+        const float4 t = rp[q];
+        x[q * 4] += t.x; x[q * 4 + 1] += t.y; x[q * 4 + 2] += t.z; x[q * 4 + 3] += t.w;
+      }
+    }
+  }
+  if (a.ep.y32) {
+    float4* yp = reinterpret_cast<float4*>(a.ep.y32 + o);
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (q * 4 < n_out) yp[q] = make_float4(x[q * 4], x[q * 4 + 1], x[q * 4 + 2], x[q * 4 + 3]);
+  } else {
+    uint4* yp = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.ep.y) + o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (q * 8 < n_out) {
+        uint4 t;
+        __half2* h = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(x[q * 8 + 2 * i], x[q * 8 + 2 * i + 1]);
+        yp[q] = t;
       }
     }
   }
@@ -258,7 +339,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-        tc_finish(a, row, n0 + c, f);
+        if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
+        else tc_finish(a, row, n0 + c, f);
       } else {
         // raw partial sums of this K slice; the last CTA of the tile adds the slices in a fixed order
         float4* dst = reinterpret_cast<float4*>(a.partials + ((size_t)blockIdx.z * a.M + row) * Npad + n0 + c);
@@ -293,7 +375,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
               f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
             }
           }
-          tc_finish(a, row, n0 + c, f);
+          if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
+          else tc_finish(a, row, n0 + c, f);
         }
       }
     }
@@ -303,6 +386,220 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
   if (w == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kBN) : "memory");
+  }
+  if (tid == 0 && s_err) {
+    g_tc_error = 1;
+    if (a.error_flag) *a.error_flag = 1;
+  }
+}
+
+// ---- persistent variant for large M ------------------------------------------------------------------------------------
+// One CTA per SM walks output tiles of 128 rows x 256 columns (a whole packed column tile: the B stage of a 64-k
+// block is two contiguous 16 KB packed tiles, two bulk copies).  Per flop this tile shape needs 0.75x the operand
+// bytes of 128x128.  The fp32 accumulator (256 TMEM columns) is double buffered: the four epilogue warps drain tile
+// i while the MMA thread is already accumulating tile i+1, and the TMA thread runs ahead through a 4-stage ring
+// across tile boundaries.  Tiles are ordered in bands of kBandM row tiles so that the CTAs running at the same
+// time share A and B tiles in L2.
+constexpr int kP_BN = 256;
+constexpr int kP_Stages = 4;
+constexpr int kP_ABytes = kBM * kBK * 2;     // 16 KB
+constexpr int kP_BBytes = kP_BN * kBK * 2;   // 32 KB = two packed tiles
+constexpr int kBandM = 16;
+
+struct TcTile {
+  int m_tile, n_tile;
+};
+__device__ __forceinline__ TcTile tc_tile_of(int t, int m_tiles, int n_tiles) {
+  // bands of kBandM row tiles; inside a band column-major (all rows of a column tile are neighbours in time)
+  const int band_sz = kBandM * n_tiles;
+  const int band = t / band_sz;
+  const int rows_in_band = min(kBandM, m_tiles - band * kBandM);
+  const int r = t - band * band_sz;
+  TcTile o;
+  o.n_tile = r / rows_in_band;
+  o.m_tile = band * kBandM + r % rows_in_band;
+  return o;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap mapA, TcArgs a,
+                                                                           int m_tiles, int n_tiles) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + kP_Stages * kP_ABytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kP_Stages * (kP_ABytes + kP_BBytes));
+  uint64_t* empty = full + kP_Stages;
+  uint64_t* acc_full = empty + kP_Stages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  __shared__ int s_err;
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int k_total = (a.K + kBK - 1) / kBK;
+  const int k_per = (k_total + a.ksplit - 1) / a.ksplit;   // k blocks per work item; items of one tile are neighbours in time
+  const int n_total = m_tiles * n_tiles * a.ksplit;
+  __shared__ int s_last;
+
+  if (tid == 0) {
+    for (int s = 0; s < kP_Stages; ++s) {
+      tc_mbar_init(&full[s], 1);
+      tc_mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc_mbar_init(&acc_full[i], 1);
+      tc_mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    s_err = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (w == 2) {  // all 512 TMEM columns: two accumulators of 256
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (w == 0 && lane == 0) {
+    // ---------------- TMA producer: runs ahead across tiles
+    int it_g = 0;  // k blocks issued so far (ring position)
+    for (int t = blockIdx.x; t < n_total && !s_err; t += gridDim.x) {
+      const TcTile tl = tc_tile_of(t / a.ksplit, m_tiles, n_tiles);
+      const int it_begin = (t % a.ksplit) * k_per, it_end = min(k_total, it_begin + k_per);
+      const unsigned char* wsrc = a.Wp + ((size_t)tl.n_tile * a.KB) * 16384;
+      for (int it = it_begin; it < it_end; ++it, ++it_g) {
+        const int s = it_g % kP_Stages, r = it_g / kP_Stages;
+        if (it_g >= kP_Stages && !tc_mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
+          s_err = 1;
+          break;
+        }
+        const int kb0 = it * 2;
+        const bool two = kb0 + 1 < a.KB;
+        tc_mbar_expect_tx(&full[s], kP_ABytes + (two ? 32768 : 16384));
+        tma_load_2d(sA + s * kP_ABytes, &mapA, it * kBK, tl.m_tile * kBM, &full[s]);
+        tc_bulk_g2s(sB + s * kP_BBytes, wsrc + (size_t)kb0 * 16384, 16384, &full[s]);
+        if (two) tc_bulk_g2s(sB + s * kP_BBytes + 16384, wsrc + (size_t)(kb0 + 1) * 16384, 16384, &full[s]);
+      }
+    }
+  } else if (w == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    // instruction descriptor: D fp32, A/B fp16, A K-major, B MN-major, N = 256, M = 128
+    const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(kP_BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    int it_g = 0, n_done = 0;
+    for (int t = blockIdx.x; t < n_total && !s_err; t += gridDim.x, ++n_done) {
+      const int buf = n_done & 1;
+      if (n_done >= 2 && !tc_mbar_wait(&acc_empty[buf], (unsigned)(((n_done >> 1) - 1) & 1))) {
+        s_err = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + buf * kP_BN;
+      const int it_begin = (t % a.ksplit) * k_per, it_end = min(k_total, it_begin + k_per);
+      for (int it = it_begin; it < it_end; ++it, ++it_g) {
+        const int s = it_g % kP_Stages, r = it_g / kP_Stages;
+        if (!tc_mbar_wait(&full[s], (unsigned)(r & 1))) {
+          s_err = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_base = s_u32(sA + s * kP_ABytes), b_base = s_u32(sB + s * kP_BBytes);
+        const int kk_end = (it * 2 + 1 < a.KB) ? 4 : 2;
+#pragma unroll
+        for (int kk = 0; kk < kBK / 16; ++kk) {
+          if (kk >= kk_end) break;
+          const uint64_t ad = make_desc(a_base + kk * 32, 16, 1024);
+          // B stage = [k tile 2][64-n box 4][32 k][128 B]: boxes 4096 B apart (LBO), 8-k groups 1024 B apart (SBO),
+          // 16 k = 2048 B, the second k tile at 16384 B
+          const uint64_t bd = make_desc(b_base + (kk >> 1) * 16384 + (kk & 1) * 2048, 4096, 1024);
+          umma_f16(tmem_acc, ad, bd, idesc, (it > it_begin || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (s_err) break;
+      umma_commit(&acc_full[buf]);
+    }
+  } else if (w >= 4) {
+    // ---------------- epilogue: warp (w - 4) owns TMEM lanes 32*(w-4) .. +31 = rows of the tile
+    const int q = w - 4;
+    int n_done = 0;
+    for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++n_done) {
+      const int tile = t / a.ksplit, ks = t % a.ksplit;
+      const TcTile tl = tc_tile_of(tile, m_tiles, n_tiles);
+      const int buf = n_done & 1;
+      if (*(volatile int*)&s_err) break;
+      if (!__all_sync(0xffffffffu, tc_mbar_wait(&acc_full[buf], (unsigned)((n_done >> 1) & 1)))) {  // warp-uniform outcome
+        s_err = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = tl.m_tile * kBM + q * 32 + lane;
+      const int n0 = tl.n_tile * kP_BN;
+      const bool live = row < a.M;
+      const size_t Npad = (size_t)n_tiles * kP_BN;
+#pragma unroll 1
+      for (int c = 0; c < kP_BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kP_BN + c), v);
+        if (!live) continue;
+        if (a.ksplit == 1) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
+          else tc_finish(a, row, n0 + c, f);
+        } else {
+          // raw partial sums of this k range; the last item of the tile adds the ranges in a fixed order
+          float4* dst = reinterpret_cast<float4*>(a.partials + ((size_t)ks * a.M + row) * Npad + n0 + c);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                 __uint_as_float(v[4 * j + 3]));
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(&acc_empty[buf])) : "memory");
+      }
+      if (a.ksplit > 1) {
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (w == 4 && lane == 0) {
+          const unsigned int prev = atomicAdd(&a.counters[tile], 1u);
+          s_last = (prev == (unsigned int)(a.ksplit - 1));
+          if (s_last) a.counters[tile] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_last && live) {
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < kP_BN; c += 32) {
+            if (n0 + c >= a.N) break;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = 0.0f;
+            for (int z = 0; z < a.ksplit; ++z) {
+              const float4* src = reinterpret_cast<const float4*>(a.partials + ((size_t)z * a.M + row) * Npad + n0 + c);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 t4 = __ldcg(src + j);
+                f[4 * j] += t4.x; f[4 * j + 1] += t4.y; f[4 * j + 2] += t4.z; f[4 * j + 3] += t4.w;
+              }
+            }
+            if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
+            else tc_finish(a, row, n0 + c, f);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last is rewritten by the next item
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (w == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
   if (tid == 0 && s_err) {
     g_tc_error = 1;
@@ -335,6 +632,8 @@ int init_tc_attrs(int device) {
   if (done[device]) return 1;
   TSB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 kTcStages * (kABytes + kBBytes) + 1024 + 256));
+  TSB_CUDA(cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kP_Stages * (kP_ABytes + kP_BBytes) + 1024 + 256));
   done[device] = true;
   return 1;
 }
@@ -356,9 +655,14 @@ int tc_take_error() {
 // Returns 1 ok, 0 error, 2 not handled (caller falls back to the generic kernel).
 int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count) {
   const int64_t tiles = (int64_t)((N + kBN - 1) / kBN) * ((M + kBM - 1) / kBM);
-  if (tiles >= sm_count) return 0;
+  if (tiles >= 2 * sm_count) return 0;
+  // split-K partials of the persistent kernel (256-column tiles, about three waves of items) or of the 128 x 128 one
+  const int64_t tiles_p = (int64_t)((N + kP_BN - 1) / kP_BN) * ((M + kBM - 1) / kBM);
+  const int64_t ks_p = (3 * sm_count + tiles_p / 2) / tiles_p;
+  const int64_t a = 4096 + kWsCounterBytes + ks_p * M * (int64_t)((N + kP_BN - 1) / kP_BN) * kP_BN * 4;
   const int64_t ks = (2 * sm_count + tiles - 1) / tiles;
-  return 4096 + tiles * 4 + ks * M * (int64_t)((N + kBN - 1) / kBN) * kBN * 4;
+  const int64_t b = 4096 + kWsCounterBytes + ks * M * (int64_t)((N + kBN - 1) / kBN) * kBN * 4;
+  return a > b ? a : b;
 }
 
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
@@ -375,7 +679,7 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
   EncodeTiledFn enc = get_encode();
   if (!enc) return 2;
   TSB_TRY(init_tc_attrs(device));
-  const int KB = (K + 31) / 32, CT = (N + 255) / 256;
+  const int KB = (K + 31) / 32;
   CUtensorMap mapA;
   {
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -390,6 +694,47 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
   TcArgs a{};
   a.M = M; a.N = N; a.K = K; a.KB = KB; a.error_flag = error_flag; a.ep = ep;
   a.Wp = reinterpret_cast<const unsigned char*>(Wp);
+  {
+    const uintptr_t al = (uintptr_t)ep.bias | (uintptr_t)ep.residual | (uintptr_t)ep.y | (uintptr_t)ep.y32;
+    a.vec_ok = (N % 32 == 0) && (al % 16 == 0) ? 1 : 0;
+  }
+  {
+    // large M: persistent 128 x 256 tiles with a double-buffered accumulator
+    static int pers = -1;
+    if (pers < 0) {
+      const char* e = getenv("TSB200_TC_PERSISTENT");  // "0": one 128 x 128 tile per CTA for every M (A/B measurements)
+      pers = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
+    }
+    const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + kP_BN - 1) / kP_BN;
+    const int tiles = m_tiles * n_tiles, k_total = (K + kBK - 1) / kBK;
+    // few tiles (decode-sized M): split K so that about three waves of work items keep every SM streaming weights
+    // (measured slower than the 128 x 128 kernel's split-K at M = 64, so it is only taken when TSB200_TC_PERSISTENT=2)
+    int ks = 1;
+    if (tiles < st->sm_count && ws && pers == 2) {
+      ks = (3 * st->sm_count + tiles / 2) / tiles;
+      if (ks > k_total / 4) ks = k_total / 4;
+      const int64_t cnt = kWsCounterBytes;
+      const int64_t per = (int64_t)M * n_tiles * kP_BN * 4;
+      if (ks > 1 && cnt + ks * per > ws_bytes) ks = (int)((ws_bytes - cnt) / per);
+      if (ks > 1) {
+        const int k_per = (k_total + ks - 1) / ks;
+        ks = (k_total + k_per - 1) / k_per;  // no empty range
+      }
+      if (ks < 1) ks = 1;
+      if (ks > 1) {
+        a.counters = reinterpret_cast<unsigned int*>(ws);
+        a.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + cnt);
+      }
+    }
+    if (pers && tiles * ks >= st->sm_count) {
+      a.ksplit = ks;
+      int g = st->sm_count < tiles * ks ? st->sm_count : tiles * ks;
+      const size_t smem_p = kP_Stages * (kP_ABytes + kP_BBytes) + 1024 + 256;
+      gemm_tc_persistent_kernel<<<g, kTcThreads, smem_p, s>>>(mapA, a, m_tiles, n_tiles);
+      count_launch(device);
+      return check_launch("gemm_tc_persistent");
+    }
+  }
   dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM, 1);
   TSB_CHECK(grid.y <= 65535, "gemm_tc: too many row tiles");
   // few output tiles (decode-sized M): share each tile's K range among several CTAs so that all SMs stream weights
@@ -403,7 +748,7 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
       if (ks > 1) {
         const int k_per = (k_total + ks - 1) / ks;
         ks = (k_total + k_per - 1) / k_per;  // no empty slice
-        const int64_t cnt = ((tiles * 4 + 255) & ~255LL);
+        const int64_t cnt = kWsCounterBytes;
         const int64_t need = cnt + (int64_t)ks * M * grid.x * kBN * 4;
         if (ks > 1 && ws_bytes >= need) {
           a.ksplit = ks;

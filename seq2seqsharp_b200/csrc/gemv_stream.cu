@@ -427,7 +427,7 @@ int64_t stream_workspace_bytes(int dtype, int M, int K, int N, int sm_count) {
   if (g > KB * CT) g = KB * CT;
   const long long per = (KB * CT) / (g > 0 ? g : 1);
   const long long mc = KB / (per > 0 ? per : 1) + 2;
-  return CT * 4 + 768 + CT * mc * M * NT * 4;
+  return kWsCounterBytes + 768 + CT * mc * M * NT * 4;
 }
 
 template <typename T, int M>
@@ -460,7 +460,8 @@ static int launch_stream_t(int device, DeviceState* st, StreamArgs& a, int M, bo
   StreamPlan p;
   if (!plan_stream<T>(st, M, a.K, a.N, &p)) return 2;
   // [counters | 256 spare bytes (the stand-alone entry point keeps its error word there) | partials]
-  const int64_t cnt_bytes = (((int64_t)p.CT * 4 + 255) & ~255LL) + 256;
+  const int64_t cnt_bytes = kWsCounterBytes;
+  TSB_CHECK((int64_t)p.CT * 4 <= kWsCounterBytes - 256, "gemv_stream: too many column tiles (%d)", p.CT);
   const int64_t need = cnt_bytes + (int64_t)p.CT * p.max_contrib * M * NT * 4;
   TSB_CHECK(ws && ws_bytes >= need, "gemv_stream: workspace too small (%lld < %lld)", (long long)ws_bytes, (long long)need);
   a.KB = p.KB;
@@ -563,10 +564,9 @@ int TSB200_LinearPacked(int device, int dtype, void* y, float* y_f32, const void
   cudaStream_t s = pick_stream(st, stream);
   TSB_TRY(init_stream_attrs(device));
   // counters at the head of the workspace must start at zero; the last word of the workspace is the error flag
-  const int64_t z = workspace_bytes < 65536 ? workspace_bytes : 65536;
+  const int64_t z = workspace_bytes < kWsCounterBytes ? workspace_bytes : kWsCounterBytes;
   TSB_CUDA(cudaMemsetAsync(workspace, 0, (size_t)z, s));
-  const int NTc = packed_tile_cols(dtype);
-  int* err = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + ((((int64_t)((N + NTc - 1) / NTc) * 4 + 255) & ~255LL)));
+  int* err = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + kWsCounterBytes - 256);
   if (M <= 4) {
     const int r = launch_gemv_stream(device, st, dtype, Wp, norm_type < 0 ? x : (const void*)x_f32, norm_type < 0 ? 0 : (norm_type == 0 ? 2 : 1),
                                      gamma, norm_type == 0 ? beta : nullptr, eps, M, K, N, ep, err, false, workspace, workspace_bytes - 256, s);

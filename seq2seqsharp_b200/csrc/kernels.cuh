@@ -24,6 +24,11 @@ int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, c
                        const void* beta, float eps, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws,
                        int64_t ws_bytes, cudaStream_t s);
 int64_t stream_workspace_bytes(int dtype, int M, int K, int N, int sm_count);
+// Every linear kernel keeps its (self-resetting, zero between launches) arrival counters in the first kWsCounterBytes
+// of the workspace and its partial sums behind them, so that kernels of different shapes sharing one workspace never
+// find another kernel's partial sums where they expect zeroed counters.  The stand-alone entry point keeps its error
+// word in the last 256 bytes of the counter area.
+constexpr int64_t kWsCounterBytes = 65536;
 
 // ---- persistent decode-step kernel (decode_stack.cu): one launch runs a whole list of operations ---------------
 struct StackOp {

@@ -301,7 +301,7 @@ int64_t linear_workspace_bytes(int M, int K, int N) {
   const int Mb = M > 8 ? 8 : (M < 1 ? 1 : M);
   const int64_t ctiles = (N + 127) / 128;
   const int64_t ctas = 148 * 8 + ctiles * 2;
-  return ctas * Mb * 256 * 4 + ctiles * 4 + 1024;
+  return ctas * Mb * 256 * 4 + kWsCounterBytes + 1024;
 }
 
 template <typename T, int M>
@@ -325,7 +325,7 @@ static int launch_gemv_m(int device, DeviceState* st, const T* x, const T* W, in
                          int64_t ws_bytes, cudaStream_t s, int packedKB) {
   constexpr int NT = 32 * WVec<T>::N;
   GemvPlan p = plan_gemv<T>(st, M, K, N);
-  const int64_t cnt_bytes = ((int64_t)p.ctiles * 4 + 255) & ~255LL;
+  const int64_t cnt_bytes = kWsCounterBytes;
   const int64_t need = cnt_bytes + (int64_t)p.ctiles * p.ksplit * M * NT * 4;
   if (p.ksplit > 1 && (!ws || ws_bytes < need)) {
     // no scratch: fall back to one CTA per column tile over the whole K range (chunked through shared memory

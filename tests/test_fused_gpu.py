@@ -266,7 +266,10 @@ def test_linear_packed_with_fused_norm(cuda, oracle, dtype, tol, norm_type, M, K
 
 
 @pytest.mark.parametrize("M,K,Nn", [(64, 64, 128), (128, 512, 256), (200, 96, 264), (17, 4096, 6144), (512, 768, 2304),
-                                    (130, 1376, 512), (64, 2048, 1000), (300, 160, 96)])
+                                    (130, 1376, 512), (64, 2048, 1000), (300, 160, 96),
+                                    # >= 148 tiles of 128 x 256: the persistent kernel (odd k-tile count; ragged M in one
+                                    # band of 16 row tiles; a second, shorter band)
+                                    (640, 160, 8000), (2000, 96, 2560), (2200, 64, 2304), (1300, 128, 4008)])
 def test_linear_packed_tensor_core_gemm(cuda, oracle, M, K, Nn):
     """M > 16 on fp16 packed weights runs the tcgen05/TMEM GEMM (TMA-fed, accumulator in tensor memory): every epilogue,
     ragged M (rows zero-filled by TMA), K not a multiple of the 64-wide k block, N not a multiple of the tile."""
