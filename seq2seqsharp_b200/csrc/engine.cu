@@ -579,6 +579,7 @@ static int check_err_flag(Gpt* g) {
   int e = 0;
   TSB_CUDA(cudaMemcpy(&e, g->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
   e |= tc_take_error();
+  e |= gs_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count

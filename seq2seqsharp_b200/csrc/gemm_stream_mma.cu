@@ -1,0 +1,413 @@
+// Linear layer for decode batches of 5..64 rows on packed fp16 weights: y[M,N] = epilogue(x[M,K] * W[K,N]).
+//
+// At these row counts the product is still bound by streaming the weights once (HBM), but there are too many rows
+// for FMA pipes and too few output tiles for a tile-per-CTA tensor-core GEMM (its split-K variants spend most of their
+// time in pipeline fill, drain and partial-sum hand-over).  So this kernel keeps the structure of the streaming GEMV:
+//   * persistent CTAs, one per SM, each owning a contiguous, evenly sized range of the packed 16 KB weight tiles
+//     (stream-K over column-tile-major order);
+//   * a producer lane feeds a shared-memory ring: per stage one linear bulk copy of a weight tile (stored as its
+//     128-byte-swizzled shared-memory image) and one TMA tensor copy of the matching activation tile [rows][32 k]
+//     (64-byte swizzle, rows beyond M zero-filled);
+//   * eight consumer warps, 32 columns each: ldmatrix.trans of the weight fragments, ldmatrix of the activation
+//     fragments, mma.sync m16n8k16 with fp32 accumulators for up to 8 row blocks;
+//   * at the end of a CTA's share of a column tile the accumulators go to a scratch slot; the CTA that delivers the
+//     last share adds the slots in fixed order (bitwise reproducible) and applies bias / activation / gate / residual.
+// Every mbarrier wait is bounded; on timeout the error word is raised and the CTA drains and returns.
+//
+// Replaces cublasGemmEx + bias / activation kernels for decode batches (TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-362).
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "kernels.cuh"
+#include "stream_common.cuh"
+
+namespace tsb {
+
+constexpr int kGsXBytes = 4096;                       // activation tile per stage: up to 64 rows x 32 k halves
+constexpr int kGsStageBytes = kTileBytes + kGsXBytes;
+
+// Raised by a kernel whose bounded wait ran out; read and cleared by gs_take_error().
+__device__ int g_gs_error;
+
+struct GsArgs {
+  const unsigned char* Wp;
+  int M, K, N, KB, CT;
+  int stages, max_contrib;
+  float* partials;          // [CT][max_contrib][M][256]
+  unsigned int* counters;   // [CT], zero on entry, self-resetting
+  int* error_flag;
+  Epilogue ep;
+};
+
+__device__ __forceinline__ void gs_tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void gs_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void gs_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void gs_mma_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned gs_atom_add_acq_rel(unsigned* p, unsigned v) {
+  unsigned old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void gs_consumers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ float gs_act(float v, int act) {
+  switch (act) {
+    case TSB200_ACT_RELU: return v < 0.0f ? 0.0f : v;
+    case TSB200_ACT_SILU: return v / (1.0f + expf(-v));
+    case TSB200_ACT_LEAKYRELU: return v < 0.0f ? 0.01f * v : v;
+    case TSB200_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    default: return v;
+  }
+}
+
+template <int NB>  // row blocks of 8: M <= 8 * NB
+__global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(const __grid_constant__ CUtensorMap mapX, GsArgs a) {
+  constexpr int NT = 256;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int S = a.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * kGsStageBytes);
+  uint64_t* empty = full + 16;
+  __shared__ int s_err, s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int M = a.M, N = a.N, KB = a.KB;
+  const long long U = (long long)KB * a.CT, G = gridDim.x;  // the host launches at most U CTAs: no range is empty
+  const int u_begin = (int)(U * blockIdx.x / G), u_end = (int)(U * (blockIdx.x + 1) / G);
+
+  if (tid == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], kConsumerWarps);
+    }
+    s_err = 0;
+    s_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  grid_dep_launch();
+  grid_dep_wait();  // the activation rows come from the previous kernel (the producer reads them through TMA)
+
+  if (w == kConsumerWarps) {
+    if (lane == 0) {
+      const unsigned char* src = a.Wp + (size_t)u_begin * kTileBytes;
+      int s = 0, kb = u_begin % KB;
+      unsigned round = 0;
+      long long issued = 0;
+      for (int u = u_begin; u < u_end; ++u) {
+        if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
+          s_err = 1;
+          break;
+        }
+        if (*(volatile int*)&s_err) break;
+        unsigned char* dst = smem + (size_t)s * kGsStageBytes;
+        mbar_expect_tx(&full[s], kTileBytes + NB * 8 * 64);
+        bulk_g2s(dst, src, kTileBytes, &full[s]);
+        gs_tma_load_2d(dst + kTileBytes, &mapX, kb * kKT, 0, &full[s]);  // x = kb * 32 halves: a 64-byte multiple
+        src += kTileBytes;
+        ++issued;
+        if (++kb == KB) kb = 0;
+        if (++s == S) {
+          s = 0;
+          ++round;
+        }
+      }
+      if (*(volatile int*)&s_err) {
+        const long long first = issued > S ? issued - S : 0;
+        for (long long j = first; j < issued; ++j) mbar_wait(&full[(int)(j % S)], (unsigned)((j / S) & 1));
+        g_gs_error = 1;
+        if (a.error_flag) *a.error_flag = 1;
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumer warps: warp w owns columns [w*32, w*32+32) of every tile
+  const int chunk = w >> 1, hf = w & 1;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int lrow = (lane & 7) + ((lane >> 4) << 3);   // weight fragments: k row inside a 16-k block
+  const int lunit = (lane >> 3) & 1;                  //                   which 8-column unit of a 16-column block
+  const int xr = lane & 7, xc = lane >> 3;            // activation fragments: row inside an 8-row block, 16-byte k chunk
+  float d[2][NB][4];
+#pragma unroll
+  for (int cb = 0; cb < 2; ++cb)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d[cb][nb][e] = 0.0f;
+
+  const int max_contrib = a.max_contrib;
+  const Epilogue ep = a.ep;
+  const __half* bias = reinterpret_cast<const __half*>(ep.bias);
+  int s = 0;
+  unsigned round = 0;
+  bool dead = false;
+  int ct = u_begin / KB, kb = u_begin % KB;
+  for (int u = u_begin; u < u_end; ++u) {
+    if (*(volatile int*)&s_err) dead = true;
+    if (!mbar_wait(&full[s], round & 1u, dead ? 4096u : kSpinLimit)) {
+      s_err = 1;
+      dead = true;
+    }
+    const uint32_t wbase = smem_u32(smem + (size_t)s * kGsStageBytes) + chunk * 4096;
+    const uint32_t xbase = smem_u32(smem + (size_t)s * kGsStageBytes + kTileBytes);
+    // activation fragments of all row blocks: [rows][32 k] with 64-byte rows, 16-byte chunks XOR-ed with (row / 2) & 3
+    uint32_t bf[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int n = nb * 8 + xr;
+      gs_ldmatrix_x4(xbase + n * 64 + ((xc ^ ((n >> 1) & 3)) << 4), bf[nb][0], bf[nb][1], bf[nb][2], bf[nb][3]);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      const int k = kk * 16 + lrow;
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+        const int unit = hf * 4 + cb * 2 + lunit;
+        uint32_t a0, a1, a2, a3;
+        gs_ldmatrix_x4_trans(wbase + k * 128 + ((unit ^ (k & 7)) << 4), a0, a1, a2, a3);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) gs_mma_16816(d[cb][nb], a0, a1, a2, a3, bf[nb][2 * kk], bf[nb][2 * kk + 1]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+    if (++s == S) {
+      s = 0;
+      ++round;
+    }
+    const int cur_ct = ct, cur_kb = kb;
+    if (++kb == KB) {
+      kb = 0;
+      ++ct;
+    }
+    const bool seg_end = (cur_kb == KB - 1) || (u == u_end - 1);
+    if (!seg_end) continue;
+    // ---- end of this CTA's share of column tile cur_ct: accumulators -> scratch slot, last arriver finishes the tile
+    const long long ct_first_u = (long long)cur_ct * KB, ct_last_u = ct_first_u + KB - 1;
+    const int c_first = (int)(((ct_first_u + 1) * G + U - 1) / U - 1);
+    const int c_last = (int)(((ct_last_u + 1) * G + U - 1) / U - 1);
+    const int n_contrib = c_last - c_first + 1;
+    const int slot = blockIdx.x - c_first;
+    float* mine = a.partials + (((size_t)cur_ct * max_contrib + slot) * M) * NT;
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb) {
+      const int col = chunk * 64 + hf * 32 + cb * 16 + g8;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = nb * 8 + 2 * t4 + (e & 1);
+          if (row < M) mine[(size_t)row * NT + col + (e >> 1) * 8] = d[cb][nb][e];
+          d[cb][nb][e] = 0.0f;
+        }
+    }
+    gs_consumers_sync();
+    if (tid == 0) {
+      const unsigned int prev = gs_atom_add_acq_rel(&a.counters[cur_ct], 1u);  // publishes this CTA's slot, acquires the others'
+      const int last = (prev == (unsigned int)(n_contrib - 1));
+      if (last) a.counters[cur_ct] = 0u;
+      s_last = last;
+    }
+    gs_consumers_sync();
+    if (*(volatile int*)&s_last) {
+      const float* all = a.partials + ((size_t)cur_ct * max_contrib * M) * NT;
+      const int No = ep.glu ? N / 2 : N;
+      // work items: (row, group of 4 columns); eight items per thread in flight
+      for (int i0 = 0; i0 < M * 64; i0 += 256 * 8) {
+        float4 acc[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < n_contrib; ++j) {
+          float4 t[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int idx = i0 + q * 256 + tid;
+            const int ic = idx < M * 64 ? idx : 0;
+            t[q] = __ldcg(reinterpret_cast<const float4*>(all + (size_t)j * M * NT) + ic);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            acc[q].x += t[q].x; acc[q].y += t[q].y; acc[q].z += t[q].z; acc[q].w += t[q].w;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int idx = i0 + q * 256 + tid;
+          if (idx >= M * 64) continue;
+          const int row = idx >> 6, c = cur_ct * NT + (idx & 63) * 4;
+          const float v[4] = {acc[q].x, acc[q].y, acc[q].z, acc[q].w};
+          if (!ep.glu) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (c + e < N) {
+                float x = gs_act(v[e] + (bias ? __half2float(bias[c + e]) : 0.0f), ep.act);
+                const size_t o = (size_t)row * N + c + e;
+                if (ep.residual) x += ep.residual[o];
+                if (ep.y32) ep.y32[o] = x;
+                else reinterpret_cast<__half*>(ep.y)[o] = __float2half_rn(x);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+              if (c + e + 1 < N) {
+                float av = v[e] + (bias ? __half2float(bias[c + e]) : 0.0f);
+                const float gv = v[e + 1] + (bias ? __half2float(bias[c + e + 1]) : 0.0f);
+                if (ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
+                float x = av * gv;
+                const size_t o = (size_t)row * No + ((c + e) >> 1);
+                if (ep.residual) x += ep.residual[o];
+                if (ep.y32) ep.y32[o] = x;
+                else reinterpret_cast<__half*>(ep.y)[o] = __float2half_rn(x);
+              }
+            }
+          }
+        }
+      }
+    }
+    gs_consumers_sync();  // s_last is rewritten at the next segment end
+  }
+  if (tid == 0 && *(volatile int*)&s_err) {
+    g_gs_error = 1;
+    if (a.error_flag) *a.error_flag = 1;
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------------
+typedef CUresult (*GsEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static GsEncodeTiledFn gs_get_encode() {
+  static GsEncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<GsEncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+template <int NB>
+static int gs_launch(int device, const CUtensorMap& mapX, const GsArgs& a, int grid, size_t smem, bool pdl, cudaStream_t s) {
+  static bool attr_done[kMaxDevices] = {};
+  if (!attr_done[device]) {
+    TSB_CUDA(cudaFuncSetAttribute(gemm_stream_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    attr_done[device] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  TSB_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_mma_kernel<NB>, mapX, a));
+  count_launch(device);
+  return 1;
+}
+
+// 1 when a kernel of this file gave up waiting since the last call (and clears the mark).
+int gs_take_error() {
+  int e = 0;
+  if (cudaMemcpyFromSymbol(&e, g_gs_error, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (e) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_gs_error, &z, sizeof(int));
+  }
+  return e;
+}
+
+int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count) {
+  const long long KB = (K + kKT - 1) / kKT, CT = (N + 255) / 256;
+  long long g = sm_count;
+  if (g > KB * CT) g = KB * CT;
+  const long long per = (KB * CT) / (g > 0 ? g : 1);
+  const long long mc = KB / (per > 0 ? per : 1) + 2;
+  return kWsCounterBytes + CT * mc * M * 256 * 4 + 256;
+}
+
+// 1 ok, 0 error, 2 shape not handled (caller falls back).
+int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                           int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s) {
+  {
+    static int enabled = -1;
+    if (enabled < 0) {
+      const char* e = getenv("TSB200_GEMM_STREAM");  // "0": decode batches go to the tile-per-CTA tensor-core GEMM (A/B measurements)
+      enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (!enabled) return 2;
+  }
+  if (M < 1 || M > 64 || K % 8 != 0 || ((uintptr_t)x % 16) != 0 || ((uintptr_t)Wp % 16) != 0) return 2;
+  GsEncodeTiledFn enc = gs_get_encode();
+  if (!enc) return 2;
+  const int NB = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  GsArgs a{};
+  a.Wp = reinterpret_cast<const unsigned char*>(Wp);
+  a.M = M; a.K = K; a.N = N;
+  a.KB = (K + kKT - 1) / kKT;
+  a.CT = (N + 255) / 256;
+  const long long U = (long long)a.KB * a.CT;
+  long long g = st->sm_count;
+  if (g > U) g = U;
+  a.max_contrib = (int)(a.KB / (U / g)) + 2;
+  const size_t fixed = 32 * sizeof(uint64_t) + 1024 + 128;
+  int stages = (int)((225 * 1024 - fixed) / kGsStageBytes);
+  if (stages > 16) stages = 16;
+  a.stages = stages;
+  const int64_t need = kWsCounterBytes + (int64_t)a.CT * a.max_contrib * M * 256 * 4;
+  if (!ws || ws_bytes < need) return 2;
+  a.counters = reinterpret_cast<unsigned int*>(ws);
+  a.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
+  a.error_flag = error_flag;
+  a.ep = ep;
+  CUtensorMap mapX;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {32, (cuuint32_t)(NB * 8)};
+    const cuuint32_t el[2] = {1, 1};
+    const CUresult r = enc(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, el,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TSB_CHECK(r == CUDA_SUCCESS, "gemm_stream: cuTensorMapEncodeTiled failed with %d", (int)r);
+  }
+  const size_t smem = fixed + (size_t)stages * kGsStageBytes;
+  switch (NB) {
+    case 1: return gs_launch<1>(device, mapX, a, (int)g, smem, pdl, s);
+    case 2: return gs_launch<2>(device, mapX, a, (int)g, smem, pdl, s);
+    case 4: return gs_launch<4>(device, mapX, a, (int)g, smem, pdl, s);
+    default: return gs_launch<8>(device, mapX, a, (int)g, smem, pdl, s);
+  }
+}
+
+}  // namespace tsb

@@ -26,7 +26,7 @@
 namespace tsb {
 
 constexpr int kBM = 128, kBN = 128, kBK = 64;
-constexpr int kTcStages = 4;
+constexpr int kTcStages = 3;   // 3 x 32 KB: two CTAs per SM, so one CTA's epilogue overlaps the other's mainloop
 constexpr int kTcThreads = 256;
 constexpr int kABytes = kBM * kBK * 2;  // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;  // 16 KB
@@ -238,7 +238,7 @@ __device__ __forceinline__ void tc_finish_fast(const TcArgs& a, int row, int col
   }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, TcArgs a) {
+__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, TcArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // carve: [stages][A 16K][B 16K] (1024-byte aligned for the 128B swizzle atoms), then barriers
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -367,7 +367,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = 0.0f;
-          for (int z = 0; z < a.ksplit; ++z) {
+          // two K slices in flight per round trip, added in slice order (bitwise reproducible)
+          int z = 0;
+          for (; z + 1 < a.ksplit; z += 2) {
+            const float4* s0 = reinterpret_cast<const float4*>(a.partials + ((size_t)z * a.M + row) * Npad + n0 + c);
+            const float4* s1 = reinterpret_cast<const float4*>(a.partials + ((size_t)(z + 1) * a.M + row) * Npad + n0 + c);
+            float4 t0[8], t1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              t0[j] = __ldcg(s0 + j);
+              t1[j] = __ldcg(s1 + j);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[4 * j] += t0[j].x; f[4 * j + 1] += t0[j].y; f[4 * j + 2] += t0[j].z; f[4 * j + 3] += t0[j].w;
+              f[4 * j] += t1[j].x; f[4 * j + 1] += t1[j].y; f[4 * j + 2] += t1[j].z; f[4 * j + 3] += t1[j].w;
+            }
+          }
+          for (; z < a.ksplit; ++z) {
             const float4* src = reinterpret_cast<const float4*>(a.partials + ((size_t)z * a.M + row) * Npad + n0 + c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -743,8 +760,10 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
     const int64_t tiles = (int64_t)grid.x * grid.y;
     const int k_total = (K + kBK - 1) / kBK;
     if (tiles < st->sm_count && k_total >= 8 && ws) {
-      int ks = (int)((2 * st->sm_count + tiles - 1) / tiles);
+      // about 1.5 CTAs per SM (two fit); every extra K slice costs the last arriver another partial to add
+      int ks = (int)((3 * st->sm_count / 2 + tiles - 1) / tiles);
       if (ks > k_total / 4) ks = k_total / 4;
+      if (ks > 6) ks = 6;
       if (ks > 1) {
         const int k_per = (k_total + ks - 1) / ks;
         ks = (k_total + k_per - 1) / k_per;  // no empty slice

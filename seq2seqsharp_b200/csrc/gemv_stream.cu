@@ -539,6 +539,8 @@ int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N) {
   int64_t b = linear_workspace_bytes(M, K, N);
   const int64_t c = dtype == TSB200_F16 && M > 16 ? gemm_tc_workspace_bytes(M, N, 132) : 0;
   if (c > b) b = c;
+  const int64_t d = dtype == TSB200_F16 && M > 4 && M <= 64 ? gemm_stream_mma_workspace_bytes(M, K, N, 132) : 0;
+  if (d > b) b = d;
   return (a > b ? a : b) + 256;
 }
 

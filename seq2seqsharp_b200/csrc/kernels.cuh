@@ -83,6 +83,11 @@ int init_stream_attrs(int device);
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
                    int* error_flag, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count);
+// stream-K mma.sync GEMM for decode batches of up to 64 rows on packed fp16 weights (gemm_stream_mma.cu)
+int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                           int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
+int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count);
+int gs_take_error();
 int init_tc_attrs(int device);
 int tc_take_error();
 int64_t linear_workspace_bytes(int M, int K, int N);

@@ -269,9 +269,12 @@ def test_linear_packed_with_fused_norm(cuda, oracle, dtype, tol, norm_type, M, K
                                     (130, 1376, 512), (64, 2048, 1000), (300, 160, 96),
                                     # >= 148 tiles of 128 x 256: the persistent kernel (odd k-tile count; ragged M in one
                                     # band of 16 row tiles; a second, shorter band)
-                                    (640, 160, 8000), (2000, 96, 2560), (2200, 64, 2304), (1300, 128, 4008)])
+                                    (640, 160, 8000), (2000, 96, 2560), (2200, 64, 2304), (1300, 128, 4008),
+                                    # 5..64 rows: the stream-K mma.sync kernel (1, 2, 4 and 8 row blocks, wide K, ragged N)
+                                    (5, 4096, 4096), (12, 512, 264), (33, 1376, 512), (40, 96, 1002), (64, 11008, 4096)])
 def test_linear_packed_tensor_core_gemm(cuda, oracle, M, K, Nn):
-    """M > 16 on fp16 packed weights runs the tcgen05/TMEM GEMM (TMA-fed, accumulator in tensor memory): every epilogue,
+    """More than 4 rows on fp16 packed weights: up to 64 rows the stream-K mma.sync kernel, above that the tcgen05/TMEM
+    GEMMs (TMA-fed, accumulator in tensor memory): every epilogue,
     ragged M (rows zero-filled by TMA), K not a multiple of the 64-wide k block, N not a multiple of the tile."""
     dtype, tol = torch.float16, 4e-3
     rng = np.random.default_rng(M + K + Nn)
