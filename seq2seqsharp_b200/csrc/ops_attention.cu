@@ -8,6 +8,8 @@
 // RoPE follows TensorSharp/TensorApplyCPU.cs:1148-1178 (same math as TensorSharp.CUDA/DeviceCode/
 // AdvFuncKernels.cs:1245-1279 without fast-math): interleaved pairs (2i, 2i+1), theta_i = base^(-2i/hd) rounded to
 // float, angle = theta_i * position in float, cos/sin evaluated in double and rounded to float.
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace tsb {
@@ -253,6 +255,158 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* out, float* part,
   }
 }
 
+// Decode variant (one query position per sequence) with the cached K/V rows staged through shared memory by
+// cp.async: three stages of kStageTokens tokens are in flight per CTA and several CTAs fit on an SM, so ~150 KB per SM
+// are outstanding instead of the two 16-byte loads per lane of attn_kernel — at large batch the cache read is bound
+// by memory latency x bytes in flight, not by arithmetic.  Same arithmetic and the same merge as attn_kernel.
+constexpr int kStageTokens = 32;
+constexpr int kAttnStages = 3;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kAttnThreads) attn_staged_kernel(T* out, float* part, const T* q, int64_t q_rs, const T* cK,
+                                                                   const T* cV, int H, int Hkv, int hd, int T0_arg, const int* dT0,
+                                                                   int Tmax, int splits, float scale) {
+  constexpr int EPL = Vec16<T>::N;
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int lpt = hd / EPL;              // lanes per token (power of two, <= 32)
+  const int tpw = 32 / lpt;              // tokens per warp pass
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int sub = lane / lpt, li = lane % lpt;
+  const int nwarps = kAttnThreads / 32;
+  const int split = blockIdx.x;
+  const int groups_per_kv = (H / Hkv) / G;
+  const int kvh = blockIdx.y / groups_per_kv;
+  const int h0 = kvh * (H / Hkv) + (blockIdx.y % groups_per_kv) * G;
+  const int row = blockIdx.z;  // sequence
+  const int Tk = min(T0 + 1, Tmax);
+  const int per_split = (Tk + splits - 1) / splits;
+  const int t_beg = split * per_split, t_end = min(Tk, t_beg + per_split);
+  const size_t row_bytes = (size_t)hd * sizeof(T);
+  const size_t stage_bytes = 2 * kStageTokens * row_bytes;   // K rows then V rows
+  const T* Kb = cK + ((int64_t)row * Hkv + kvh) * Tmax * hd;
+  const T* Vb = cV + ((int64_t)row * Hkv + kvh) * Tmax * hd;
+  const int n_tiles = (max(t_end - t_beg, 0) + kStageTokens - 1) / kStageTokens;
+  const int vec_per_row = hd / EPL;                           // 16-byte vectors per row
+  const int vec_per_tile = kStageTokens * vec_per_row;
+
+  auto issue = [&](int tile) {
+    if (tile < n_tiles) {
+      unsigned char* st = attn_smem + (size_t)(tile % kAttnStages) * stage_bytes;
+      const int t0 = t_beg + tile * kStageTokens;
+      for (int v = threadIdx.x; v < vec_per_tile; v += kAttnThreads) {
+        const int tt = v / vec_per_row, c = v % vec_per_row;
+        const int t = min(t0 + tt, t_end - 1);  // the tail re-reads the last token of the range; it is masked below
+        cp_async_16(st + (size_t)tt * row_bytes + c * 16, Kb + (int64_t)t * hd + c * EPL);
+        cp_async_16(st + (size_t)(kStageTokens + tt) * row_bytes + c * 16, Vb + (int64_t)t * hd + c * EPL);
+      }
+    }
+    cp_async_commit();
+  };
+  for (int i = 0; i < kAttnStages - 1; ++i) issue(i);
+
+  float qf[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    Vec16<T> qv;
+    qv.load(q + (int64_t)row * q_rs + (int64_t)(h0 + g) * hd + li * EPL);
+    qv.get(qf[g]);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qf[g][e] *= scale;
+  }
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
+  }
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    issue(tile + kAttnStages - 1);
+    cp_async_wait<kAttnStages - 1>();
+    __syncthreads();
+    const unsigned char* st = attn_smem + (size_t)(tile % kAttnStages) * stage_bytes;
+    const int t0 = t_beg + tile * kStageTokens;
+    for (int tt = w * tpw + sub; tt < kStageTokens; tt += nwarps * tpw) {
+      const bool live = t0 + tt < t_end;  // uniform trip count: kStageTokens is a multiple of nwarps * tpw
+      Vec16<T> kv, vv;
+      kv.load(reinterpret_cast<const T*>(st + (size_t)tt * row_bytes) + li * EPL);
+      vv.load(reinterpret_cast<const T*>(st + (size_t)(kStageTokens + tt) * row_bytes) + li * EPL);
+      float kf[EPL], vf[EPL];
+      kv.get(kf);
+      vv.get(vf);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
+        for (int o = lpt >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (live) {
+          const float mn = fmaxf(m[g], d);
+          const float corr = __expf(m[g] - mn);  // exp(-inf) = 0 on the first token
+          const float p = __expf(d - mn);
+          l[g] = l[g] * corr + p;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+          m[g] = mn;
+        }
+      }
+    }
+    __syncthreads();  // the stage is overwritten by the copy issued in the next iteration
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // merge the nwarps*tpw lane-group states through shared memory (the stage area is free now)
+  float* sm = reinterpret_cast<float*>(attn_smem);  // [nstates][G][hd + 2]
+  const int nstates = nwarps * tpw;
+  const int stt = w * tpw + sub;
+  const int rec = hd + 2;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float* r = sm + ((int64_t)stt * G + g) * rec;
+    if (li == 0) {
+      r[0] = m[g];
+      r[1] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) r[2 + li * EPL + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += kAttnThreads) {
+    const int g = idx / hd, e = idx % hd;
+    float mx = -INFINITY;
+    for (int i = 0; i < nstates; ++i) mx = fmaxf(mx, sm[((int64_t)i * G + g) * rec]);
+    float L = 0.0f, A = 0.0f;
+    for (int i = 0; i < nstates; ++i) {
+      const float* r = sm + ((int64_t)i * G + g) * rec;
+      const float c = (r[0] == -INFINITY) ? 0.0f : __expf(r[0] - mx);
+      L += r[1] * c;
+      A += r[2 + e] * c;
+    }
+    const int h = h0 + g;
+    if (splits == 1) {
+      out[((int64_t)row * H + h) * hd + e] = from_f<T>(L > 0.0f ? A / L : 0.0f);
+    } else {
+      float* pr = part + (((int64_t)row * H + h) * splits + split) * rec;
+      if (e == 0) {
+        pr[0] = mx;
+        pr[1] = L;
+      }
+      pr[2 + e] = A;
+    }
+  }
+}
+
 template <typename T>
 __global__ void attn_combine_kernel(T* out, const float* part, int hd, int splits) {
   pdl_trigger();
@@ -317,6 +471,43 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   TSB_CHECK(smem <= 48 * 1024, "attention: shared memory need %zu exceeds 48 KB", smem);
   dim3 grid(splits, ygroups, B * S);
   const float scale = 1.0f / sqrtf((float)hd);
+  // cached decode at batch: K/V rows staged through shared memory (cp.async), several tiles in flight per CTA
+  static int staged = -1;
+  if (staged < 0) {
+    const char* e = getenv("TSB200_ATTN_STAGED");  // "0": register-only kernel for every case (A/B measurements)
+    staged = (e && e[0] == '0') ? 0 : 1;
+  }
+  const size_t stage_smem = (size_t)kAttnStages * 2 * kStageTokens * hd * sizeof(T);
+  if (staged && S == 1 && kStageTokens % ((kAttnThreads / 32) * tpw) == 0 && B * ygroups * splits >= 2 * st->sm_count) {
+    const size_t sm2 = stage_smem > smem ? stage_smem : smem;
+    if (sm2 <= 96 * 1024) {
+#define TSB_ATTN_S(GG)                                                                                                          \
+  do {                                                                                                                          \
+    static bool attr_done[kMaxDevices] = {};                                                                                    \
+    if (!attr_done[device]) {                                                                                                   \
+      TSB_CUDA(cudaFuncSetAttribute(attn_staged_kernel<T, GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));        \
+      attr_done[device] = true;                                                                                                 \
+    }                                                                                                                           \
+    TSB_CUDA(launch_k(attn_staged_kernel<T, GG>, grid, dim3(kAttnThreads), sm2, s, out, ws, q, q_rs, cK, cV, H, Hkv, hd, T0, dT0, \
+                      Tmax, splits, scale));                                                                                    \
+  } while (0)
+      switch (G) {
+        case 8: TSB_ATTN_S(8); break;
+        case 4: TSB_ATTN_S(4); break;
+        case 2: TSB_ATTN_S(2); break;
+        default: TSB_ATTN_S(1); break;
+      }
+#undef TSB_ATTN_S
+      count_launch(device);
+      TSB_TRY(check_launch("attention_staged"));
+      if (splits > 1) {
+        TSB_CUDA(launch_k(attn_combine_kernel<T>, dim3(B * S * H), dim3(hd < 128 ? 64 : 128), 0, s, out, (const float*)ws, hd, splits));
+        count_launch(device);
+        TSB_TRY(check_launch("attention_combine"));
+      }
+      return 1;
+    }
+  }
 #define TSB_ATTN(GG) TSB_CUDA(launch_k(attn_kernel<T, GG>, grid, dim3(kAttnThreads), smem, s, out, ws, q, q_rs, cK, cV, S, H, Hkv, hd, T0, dT0, Tmax, splits, scale))
   switch (G) {
     case 8: TSB_ATTN(8); break;

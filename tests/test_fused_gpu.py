@@ -113,7 +113,10 @@ def ref_attention(oracle, q, K, V, H, Hkv, T_per_query):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.float16, 3e-3)])
 @pytest.mark.parametrize("B,H,Hkv,hd,T", [(1, 8, 8, 64, 33), (2, 32, 8, 64, 300), (1, 32, 8, 128, 1025), (3, 4, 2, 16, 5),
-                                          (2, 8, 1, 32, 700), (1, 4, 4, 64, 1)])
+                                          (2, 8, 1, 32, 700), (1, 4, 4, 64, 1),
+                                          # enough (sequence, head group, split) CTAs for the cp.async-staged decode kernel:
+                                          # split ranges that are not multiples of the 32-token stage, 1..5 stages per CTA
+                                          (40, 32, 8, 128, 200), (64, 8, 8, 64, 77), (48, 16, 4, 128, 101), (37, 32, 32, 64, 150)])
 def test_rope_append_and_flash_decode(cuda, oracle, dtype, tol, B, H, Hkv, hd, T):
     rng = np.random.default_rng(B * 1000 + T)
     dt = N.F16 if dtype == torch.float16 else N.F32
