@@ -275,6 +275,14 @@ typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOpti
  * attention, out-projection, FFN up, FFN down; then the LM head (5*L + 1).  No counterpart in the reference. */
 TSB200_API int TSB200_GptDebugStackTrace(void* gpt, void* device_buffer);
 
+/* Peer-memory all-reduce for the few KB a decode step exchanges (optional; without it the engine uses NCCL for every
+ * size).  Each rank exports a 64-byte IPC handle of its exchange region (room for messages of up to max_count floats),
+ * the host carries the handles of all ranks to every rank (rank order), and Import maps them.  One process per GPU.
+ * The reference has no counterpart (its devices exchange whole tensors with cuMemcpyPeer inside one process,
+ * TensorSharp.CUDA/KernelOps/CopyOps.cs:47-97). */
+TSB200_API int TSB200_CommPeerExport(void* comm, int64_t max_count, void* handle64);
+TSB200_API int TSB200_CommPeerImport(void* comm, const void* handles, int n_ranks);
+
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);
 /* name = the reference's weight key (IModel.AddWeights/GetWeights, Seq2SeqSharp/Tools/WeightTensor.cs:571-604),

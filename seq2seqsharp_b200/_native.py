@@ -125,6 +125,8 @@ def lib():
         "TSB200_GptFillSynthetic": (i32, [vp, u64, f32, f32]),
         "TSB200_CommGetUniqueId": (i32, [vp]),
         "TSB200_CommInitRank": (i32, [vp, i32, i32, i32, C.POINTER(vp)]),
+        "TSB200_CommPeerExport": (i32, [vp, i64, vp]),
+        "TSB200_CommPeerImport": (i32, [vp, vp, i32]),
         "TSB200_CommDestroy": (i32, [vp]),
         "TSB200_AllReduceSumF32": (i32, [vp, vp, i64, vp]),
         "TSB200_GptSetComm": (i32, [vp, vp]),

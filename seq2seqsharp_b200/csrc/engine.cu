@@ -123,6 +123,7 @@ struct Gpt {
   int tp = 1, tp_rank = 0;     // tensor-parallel degree and rank; c.H / c.Hkv / c.F hold this rank's share
   int fullH = 0, fullHkv = 0, fullF = 0;
   void* comm = nullptr;        // communicator for the two all-reduces per layer (TSB200_GptSetComm)
+  bool tp_peer = true;         // use the peer-memory all-reduce when the communicator has one (TSB200_TP_PEER=0: NCCL only)
   float* ar_buf = nullptr;     // fp32 [rows, d] partial sums handed to the all-reduce
   void *E = nullptr, *PE = nullptr, *nf_g = nullptr, *nf_b = nullptr, *head_w = nullptr, *head_b = nullptr;
   int pe_rows = 0;
@@ -433,6 +434,16 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
   const int d = g->c.d;
   if (g->tp <= 1) return engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
   TSB_CHECK(g->comm, "tensor parallel engine has no communicator (call TSB200_GptSetComm)");
+  if (float* pb = g->tp_peer ? comm_peer_buffer(g->comm, (int64_t)rows * d) : nullptr) {
+    // small messages (decode): the partial goes to this rank's peer buffer, one kernel exchanges flags over NVLink,
+    // reads every rank's partial from its memory and adds the sum to the residual stream
+    TSB_TRY(engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, nullptr, nullptr, pb, TSB200_ACT_NONE, 0)));
+    prof_begin(g);
+    const int ok = comm_peer_reduce(g->comm, g->x, (int64_t)rows * d, g->err_flag, g->st->sm_count, g->s);
+    count_launch(g->c.device);
+    prof_end(g, KC_ALLREDUCE);
+    return ok;
+  }
   TSB_TRY(engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, nullptr, nullptr, g->ar_buf, TSB200_ACT_NONE, 0)));
   prof_begin(g);
   int ok = comm_all_reduce_f32(g->comm, g->ar_buf, (int64_t)rows * d, g->s);
@@ -580,6 +591,7 @@ static int check_err_flag(Gpt* g) {
   TSB_CUDA(cudaMemcpy(&e, g->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
   e |= tc_take_error();
   e |= gs_take_error();
+  if (g->tp > 1) e |= comm_peer_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
@@ -703,6 +715,8 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   {
     const char* e = getenv("TSB200_PDL");  // "0" switches programmatic dependent launch off (A/B measurements)
     g->pdl = !(e && e[0] == '0');
+    e = getenv("TSB200_TP_PEER");
+    g->tp_peer = !(e && e[0] == '0');
     e = getenv("TSB200_STACK");            // "0": one launch per operation instead of the persistent decode-step kernel
     g->use_stack = !(e && e[0] == '0');
   }

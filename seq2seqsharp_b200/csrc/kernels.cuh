@@ -77,6 +77,10 @@ int launch_pack(int device, DeviceState* st, int dst_dtype, void* dst, int src_d
 // NCCL binding (comm.cu)
 int comm_all_reduce_f32(void* comm, float* buf, int64_t count, cudaStream_t s);
 int comm_nranks(void* comm);
+// peer-memory all-reduce for small messages (comm.cu)
+float* comm_peer_buffer(void* comm, int64_t count);
+int comm_peer_reduce(void* comm, float* x, int64_t count, int* error_flag, int sm_count, cudaStream_t s);
+int comm_peer_take_error();
 int comm_rank(void* comm);
 int init_stream_attrs(int device);
 // tcgen05/TMEM GEMM on packed fp16 weights (gemm_tc.cu): 1 ok, 0 error, 2 shape not handled

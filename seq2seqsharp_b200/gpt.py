@@ -205,7 +205,7 @@ class GPT:
         N.call("TSB200_GptCreate", C.byref(c), C.byref(self._h))
         self._keep = None
 
-    def InitComm(self, group=None):
+    def InitComm(self, group=None, peer=True):
         """Creates the NCCL communicator of the tensor-parallel group: rank 0 makes the id, torch.distributed (any
         backend) carries its 128 bytes to the other ranks."""
         import torch.distributed as dist
@@ -216,6 +216,14 @@ class GPT:
         dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         ident = (C.c_ubyte * 128).from_buffer_copy(box[0])
         N.call("TSB200_CommInitRank", ident, self.tp_rank, self.tp_size, self.device_id, C.byref(self._comm))
+        # peer-memory all-reduce for decode-sized messages: exchange the IPC handles of the ranks' regions
+        if peer and self.tp_size <= 8:
+            mine = (C.c_ubyte * 64)()
+            N.call("TSB200_CommPeerExport", self._comm, self.max_batch * self.cfg.d, mine)
+            allh = [None] * self.tp_size
+            dist.all_gather_object(allh, bytes(mine), group=group)
+            blob = (C.c_ubyte * (64 * self.tp_size)).from_buffer_copy(b"".join(allh))
+            N.call("TSB200_CommPeerImport", self._comm, blob, self.tp_size)
         N.call("TSB200_GptSetComm", self._h, self._comm)
 
     def close(self):
