@@ -283,6 +283,16 @@ TSB200_API int TSB200_GptDebugStackTrace(void* gpt, void* device_buffer);
 TSB200_API int TSB200_CommPeerExport(void* comm, int64_t max_count, void* handle64);
 TSB200_API int TSB200_CommPeerImport(void* comm, const void* handles, int n_ranks);
 
+/* Tensor parallelism inside the persistent decode-step kernel (fp16 models, up to 8 ranks, one process per GPU):
+ * the finished column tiles of the row-sharded linears are stored straight into every rank's exchange buffer over
+ * NVLink and counted on every rank, and the next operation's norm prologue adds the ranks' partial sums — no
+ * collective launch at all in a cached step.  Export returns the 64-byte IPC handle of this rank's exchange region,
+ * the host gathers the handles of all ranks (rank order) and hands them to Import.  Optional: without it a tensor-
+ * parallel engine runs one launch per operation and all-reduces through the communicator.  No counterpart in the
+ * reference. */
+TSB200_API int TSB200_GptTpExport(void* gpt, void* handle64);
+TSB200_API int TSB200_GptTpImport(void* gpt, const void* handles, int n_ranks);
+
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);
 /* name = the reference's weight key (IModel.AddWeights/GetWeights, Seq2SeqSharp/Tools/WeightTensor.cs:571-604),

@@ -129,6 +129,8 @@ def lib():
         "TSB200_CommPeerImport": (i32, [vp, vp, i32]),
         "TSB200_CommDestroy": (i32, [vp]),
         "TSB200_AllReduceSumF32": (i32, [vp, vp, i64, vp]),
+        "TSB200_GptTpExport": (i32, [vp, vp]),
+        "TSB200_GptTpImport": (i32, [vp, vp, i32]),
         "TSB200_GptSetComm": (i32, [vp, vp]),
         "TSB200_GptReset": (i32, [vp]),
         "TSB200_GptPrefill": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),

@@ -451,6 +451,11 @@ int launch_decode_stack(int device, DeviceState* st, const StackConfig& c, const
                         int n_ops, void* partials, void* counters, void* attn_part, int* error_flag,
                         long long* trace, bool pdl, cudaStream_t s) {
   if (!error_flag || !c.dT) return 2;
+  if (c.tp_size > 1) {
+    // tensor parallelism inside the kernel exists in the mma.sync variant only
+    if (c.dtype != TSB200_F16 || c.tp_size > kStackMaxRanks || !c.peer[c.tp_rank]) return 2;
+    return launch_decode_stack_mma(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
+  }
   if (c.dtype == TSB200_F16) {
     {
       // consumers of the fp16 weight stream: "mma" (default: eight warps, ldmatrix + mma.sync), "tc" (one warp issuing

@@ -47,6 +47,24 @@ __device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
   asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
   return old;
 }
+// System-scope forms for counters that other GPUs increment over NVLink (tensor parallelism).  Counters are
+// monotonic across launches (epochs), compared wrap-safe.
+__device__ __forceinline__ void red_release_add_sys(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool poll_count_sys(const unsigned* p, unsigned want, unsigned limit, const int* err) {
+  for (unsigned i = 0; i < limit; ++i) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if ((int)(v - want) >= 0) return true;
+    if ((i & 1023u) == 1023u && *(volatile const int*)err) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ float* stack_xch(const StackConfig& c, int dest_rank, int site, int src_rank) {
+  return reinterpret_cast<float*>(c.peer[dest_rank] + kStackXchHeader) +
+         ((size_t)(site * c.tp_size + src_rank) * kStackXchRows) * c.d;
+}
 // Bounded acquire-poll until *p >= target.  Also gives up early when another CTA has raised the error word.
 __device__ __forceinline__ bool poll_count(const unsigned* p, unsigned target, unsigned limit, const int* err) {
   for (unsigned i = 0; i < limit; ++i) {
@@ -368,7 +386,8 @@ template <> struct St4<float> {
 };
 template <typename T>
 __device__ __forceinline__ void stage_norm_vec(T* xs, const float* x, const NormVecConsts<T>& nc, int xmode, float eps, int M, int K,
-                                               int Kp, int tid, float* s_stat) {
+                                               int Kp, int tid, float* s_stat, const float* xsum = nullptr, int n_sum = 0,
+                                               size_t sum_stride = 0, float* x_out = nullptr) {
   const int lane = tid & 31, w = tid >> 5;
   for (int m = 0; m < M; ++m) {
     float4 v[4];
@@ -377,6 +396,31 @@ __device__ __forceinline__ void stage_norm_vec(T* xs, const float* x, const Norm
       const int k = (j * 256 + tid) * 4;
       const float4 t = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * K + (k < K ? k : 0)));
       v[j] = (k < K) ? t : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (xsum) {
+      // tensor parallelism: the row is the old residual plus every rank's partial sum, added in rank order (the same
+      // bits on every rank); the block with index 0 also stores the new residual row
+      for (int r = 0; r < n_sum; ++r) {
+        float4 p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = (j * 256 + tid) * 4;
+          p[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)r * sum_stride + (size_t)m * K + (k < K ? k : 0)));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if ((j * 256 + tid) * 4 < K) {
+            v[j].x += p[j].x; v[j].y += p[j].y; v[j].z += p[j].z; v[j].w += p[j].w;
+          }
+        }
+      }
+      if (x_out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = (j * 256 + tid) * 4;
+          if (k < K) *reinterpret_cast<float4*>(x_out + (size_t)m * K + k) = v[j];
+        }
+      }
     }
     float s1 = 0.0f;
 #pragma unroll

@@ -54,7 +54,10 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     if (K % 8 == 0) stage_plain_vec<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
     else stage_plain<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
   } else if (nvc) {
-    stage_norm_vec<T>(xs, reinterpret_cast<const float*>(op->x), *nvc, op->xmode, op->eps, M, K, Kp, tid, s_stat);
+    const bool summed = op->ssite >= 0;
+    stage_norm_vec<T>(xs, reinterpret_cast<const float*>(op->x), *nvc, op->xmode, op->eps, M, K, Kp, tid, s_stat,
+                      summed ? stack_xch(a.c, a.c.tp_rank, op->ssite, 0) : nullptr, a.c.tp_size, (size_t)kStackXchRows * a.c.d,
+                      (summed && blockIdx.x == 0) ? op->x_out : nullptr);
   } else if (K <= 256 * 16) {
     stage_norm<T, 16>(xs, reinterpret_cast<const float*>(op->x), reinterpret_cast<const T*>(op->gamma),
                       reinterpret_cast<const T*>(op->beta), nullptr, op->xmode, op->eps, M, K, Kp, tid, s_stat);
@@ -88,6 +91,8 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
   // latency would otherwise sit at the very end of the dependency chain.  A missing bias / residual aliases the
   // weights and is switched off by a factor, indices are clamped: every address a thread can form is valid.
   const int ct0 = ct;
+  const bool xchg = op->xsite >= 0;  // row-sharded linear under tensor parallelism: partial sums go to every rank
+  if (xchg && a.c.tp_rank != 0) bias = nullptr;  // the bias is added once, by rank 0
   const float b_on = bias ? 1.0f : 0.0f, r_on = ep.residual ? 1.0f : 0.0f;
   const T* bp = bias ? bias : reinterpret_cast<const T*>(op->Wp);
   const float* rp = ep.residual ? ep.residual : reinterpret_cast<const float*>(op->Wp);
@@ -207,6 +212,11 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
               default: break;
             }
             const size_t o = (size_t)m * N + c;
+            if (xchg) {
+              // this rank's slot of the exchange buffer on every rank (peer stores over NVLink for the others)
+              for (int r = 0; r < a.c.tp_size; ++r) stack_xch(a.c, r, op->xsite, a.c.tp_rank)[o] = v;
+              continue;
+            }
             if (ep.residual) v += (pre && m == 0) ? (sg == 0 ? pre_r[0] : pre_r[1]) : __ldcg(ep.residual + o);
             if (ep.y32) ep.y32[o] = v;
             else reinterpret_cast<T*>(ep.y)[o] = from_f<T>(v);
@@ -232,7 +242,15 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       }
     }
     consumers_sync();  // red is reused by the next segment; the release below publishes the epilogue stores
-    if (finish && tid == 0) red_release_add(&a.done[op_i * kDoneStride], 1u);
+    if (finish && tid == 0) {
+      if (xchg) {
+        // one arrival per finished column tile on every rank's counter of this operation (system scope: the stores
+        // above went to other GPUs' memory)
+        for (int r = 0; r < a.c.tp_size; ++r) red_release_add_sys(reinterpret_cast<unsigned*>(a.c.peer[r]) + op_i, 1u);
+      } else {
+        red_release_add(&a.done[op_i * kDoneStride], 1u);
+      }
+    }
     seg_begin = u + 1;
   }
 }
@@ -294,10 +312,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       }
     }
   }
+  // tensor parallelism: counters that other ranks increment are monotonic; this launch is epoch `epoch`
+  unsigned* xcnt = c.tp_size > 1 ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank]) : nullptr;
+  unsigned* epoch_ptr = c.tp_size > 1 ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank] + kStackXchHeader - 4) : nullptr;
+  const unsigned epoch = epoch_ptr ? *reinterpret_cast<volatile unsigned*>(epoch_ptr) : 0u;
   int s = 0;
   unsigned round = 0;
   bool dead = false;
   unsigned prev_target = 0;
+  bool prev_xchg = false;
   for (int i = 0; i < a.n_ops; ++i) {
     const StackOp* op = a.ops + i;
     LinGeom g{};
@@ -318,7 +341,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       const bool hoist = op->type == 0 && op->xmode != 0 && op->K <= 4096 && op->K % 4 == 0;
       if (hoist) norm_vec_consts<T>(nc, reinterpret_cast<const T*>(op->gamma), reinterpret_cast<const T*>(op->beta), op->K, tid);
       if (i > 0) {
-        if (tid == 0 && !poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : kPollLimit, a.error_flag)) {
+        bool ok = true;
+        if (tid == 0) {
+          if (prev_xchg)  // every rank's finishers arrive here: column tiles x ranks, per launch
+            ok = poll_count_sys(xcnt + (i - 1), (epoch + 1u) * prev_target * (unsigned)c.tp_size, dead ? 64u : kPollLimit, a.error_flag);
+          else
+            ok = poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : kPollLimit, a.error_flag);
+        }
+        if (tid == 0 && !ok) {
           s_err = 1;
           *a.error_flag = 1;
         }
@@ -336,6 +366,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       STRACE(i, 3);
     }
     prev_target = target;
+    prev_xchg = op->type == 0 && op->xsite >= 0;
   }
   // leave: the last CTA out clears the operation counters for the next launch
   if (tid == 0) {
@@ -344,6 +375,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
     const unsigned prev = atomicAdd(&a.done[a.n_ops * kDoneStride], 1u);
     if (prev == gridDim.x - 1) {
       for (int i = 0; i <= a.n_ops; ++i) a.done[i * kDoneStride] = 0u;
+      if (epoch_ptr) *reinterpret_cast<volatile unsigned*>(epoch_ptr) = epoch + 1u;
     }
   }
 }

@@ -124,6 +124,13 @@ struct Gpt {
   int fullH = 0, fullHkv = 0, fullF = 0;
   void* comm = nullptr;        // communicator for the two all-reduces per layer (TSB200_GptSetComm)
   bool tp_peer = true;         // use the peer-memory all-reduce when the communicator has one (TSB200_TP_PEER=0: NCCL only)
+  // exchange region of the persistent decode-step kernel under tensor parallelism (TSB200_GptTpExport / Import)
+  unsigned char* xch_region = nullptr;
+  size_t xch_bytes = 0;
+  unsigned char* xch_peer[kStackMaxRanks] = {};
+  bool xch_open[kStackMaxRanks] = {};
+  bool xch_ready = false;
+  float* x2 = nullptr;         // second residual buffer: a summed residual row is written to the buffer the others do not read
   float* ar_buf = nullptr;     // fp32 [rows, d] partial sums handed to the all-reduce
   void *E = nullptr, *PE = nullptr, *nf_g = nullptr, *nf_b = nullptr, *head_w = nullptr, *head_b = nullptr;
   int pe_rows = 0;
@@ -465,7 +472,9 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
 static int ensure_stack(Gpt* g, int B) {
   const TSB200GptConfig& c = g->c;
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
-  if (!g->use_stack || B > g->stack_max_B || g->tp != 1) return 1;
+  if (!g->use_stack || B > g->stack_max_B) return 1;
+  const bool tp = g->tp > 1;
+  if (tp && !(g->xch_ready && c.dtype == TSB200_F16 && c.d <= 4096 && c.d % 4 == 0 && g->tp_peer)) return 1;  // per-operation launches + all-reduce
   if (g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) return 1;
   const int d = c.d, Hd = c.H * c.hd;
   const int nmode = c.norm_type == 0 ? 2 : 1;
@@ -476,17 +485,54 @@ static int ensure_stack(Gpt* g, int B) {
     o.K = K; o.N = N; o.ep = ep;
     ops.push_back(o);
   };
-  for (int k = 0; k < c.L; ++k) {
-    LayerW& L = g->L[k];
-    lin(nmode, g->x, L.n1_g, L.n1_b, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0));
-    StackOp at{};
-    at.type = 1; at.x = g->qkv; at.cK = L.cK; at.cV = L.cV; at.ep.y = g->attn;
-    ops.push_back(at);
-    lin(0, g->attn, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
-    lin(nmode, g->x, L.n2_g, L.n2_b, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, c.act, g->glu));
-    lin(0, g->ffn, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+  if (!tp) {
+    for (int k = 0; k < c.L; ++k) {
+      LayerW& L = g->L[k];
+      lin(nmode, g->x, L.n1_g, L.n1_b, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0));
+      StackOp at{};
+      at.type = 1; at.x = g->qkv; at.cK = L.cK; at.cV = L.cV; at.ep.y = g->attn;
+      ops.push_back(at);
+      lin(0, g->attn, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+      lin(nmode, g->x, L.n2_g, L.n2_b, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, c.act, g->glu));
+      lin(0, g->ffn, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, g->x, nullptr, g->x, TSB200_ACT_NONE, 0));
+    }
+    lin(nmode, g->x, g->nf_g, g->nf_b, g->head_w, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0));
+    for (auto& o : ops) { o.xsite = -1; o.ssite = -1; o.x_out = nullptr; }
+  } else {
+    // Tensor parallel: QKV and FFN-up are column-sharded (local heads / FFN columns), the out-projection and FFN-down
+    // are row-sharded: their finished column tiles are partial sums that go to every rank's exchange buffer; the next
+    // operation's norm prologue adds them (rank order) to the residual row it reads and CTA 0 stores the new row into
+    // the other residual buffer.  Exchange buffers alternate with the layer parity.
+    if (!g->x2) TSB_TRY(dev_alloc(g, (void**)&g->x2, (int64_t)c.max_batch * d * 4));
+    float* xin = g->x;          // residual rows the next norm prologue reads
+    float* xother = g->x2;
+    int pending = -1;           // exchange site whose sums the next norm prologue must add
+    auto norm_lin = [&](const void* ng, const void* nb, const void* Wp, int N, const Epilogue& ep) {
+      lin(nmode, xin, ng, nb, Wp, d, N, ep);
+      StackOp& o = ops.back();
+      o.xsite = -1; o.ssite = pending; o.x_out = nullptr;
+      if (pending >= 0) {
+        o.x_out = xother;
+        std::swap(xin, xother);
+        pending = -1;
+      }
+    };
+    for (int k = 0; k < c.L; ++k) {
+      LayerW& L = g->L[k];
+      norm_lin(L.n1_g, L.n1_b, L.wqkv, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0));
+      StackOp at{};
+      at.type = 1; at.x = g->qkv; at.cK = L.cK; at.cV = L.cV; at.ep.y = g->attn; at.xsite = -1; at.ssite = -1;
+      ops.push_back(at);
+      lin(0, g->attn, nullptr, nullptr, L.wo, Hd, d, make_ep(L.bo, nullptr, nullptr, g->x2, TSB200_ACT_NONE, 0));
+      ops.back().xsite = (k & 1); ops.back().ssite = -1; ops.back().x_out = nullptr;
+      pending = (k & 1);
+      norm_lin(L.n2_g, L.n2_b, L.w1, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, c.act, g->glu));
+      lin(0, g->ffn, nullptr, nullptr, L.w2, c.F, d, make_ep(L.b2, nullptr, nullptr, g->x2, TSB200_ACT_NONE, 0));
+      ops.back().xsite = 2 + (k & 1); ops.back().ssite = -1; ops.back().x_out = nullptr;
+      pending = 2 + (k & 1);
+    }
+    norm_lin(g->nf_g, g->nf_b, g->head_w, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0));
   }
-  lin(nmode, g->x, g->nf_g, g->nf_b, g->head_w, d, c.V, make_ep(g->head_b, nullptr, nullptr, g->logits, TSB200_ACT_NONE, 0));
   if (!g->stack_partials) {
     StackConfig sc{};
     sc.dtype = c.dtype; sc.M = c.max_batch < g->stack_max_B ? c.max_batch : g->stack_max_B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd;
@@ -530,10 +576,12 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
   }
-  if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->tp == 1 && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
+  if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
     StackConfig sc{};
     sc.dtype = dt; sc.M = B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd; sc.Tmax = c.max_tokens; sc.qkv_rs = g->Nqkv;
     sc.use_rope = c.pe_type == 2; sc.rope_tab = g->rope_tab; sc.dT = dT;
+    sc.tp_rank = g->tp_rank; sc.tp_size = g->tp; sc.d = c.d;
+    for (int r = 0; r < g->tp && r < kStackMaxRanks; ++r) sc.peer[r] = g->tp > 1 ? g->xch_peer[r] : nullptr;
     prof_begin(g);
     const int r = launch_decode_stack(dev, g->st, sc, g->stack_dev, g->stack_host.data(), (int)g->stack_host.size(),
                                       g->stack_partials, g->stack_counters, g->stack_attn, g->err_flag, g->stack_trace, g->pdl, g->s);
@@ -810,6 +858,9 @@ int TSB200_GptDestroy(void* h) {
   for (auto e : g->prof_ev) cudaEventDestroy(e);
   for (auto e : g->step_ev) cudaEventDestroy(e);
   if (g->pin_ids) cudaFreeHost(g->pin_ids);
+  for (int r = 0; r < kStackMaxRanks; ++r)
+    if (g->xch_open[r]) cudaIpcCloseMemHandle(g->xch_peer[r]);
+  if (g->xch_region) cudaFree(g->xch_region);
   for (void* p : g->allocs)
     if (p) cudaFree(p);
   delete g;
@@ -906,6 +957,45 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
   cudaFree(tmp);
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   return ok;
+}
+
+int TSB200_GptTpExport(void* h, void* handle64) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && handle64, "gpt_tp_export: null argument");
+  TSB_CHECK(g->tp > 1 && g->tp <= kStackMaxRanks, "gpt_tp_export: the engine is not tensor parallel (or has more than %d ranks)", kStackMaxRanks);
+  TSB_TRY(use_device(g->c.device, nullptr));
+  if (!g->xch_region) {
+    g->xch_bytes = kStackXchHeader + (size_t)kStackXchSites * g->tp * kStackXchRows * g->c.d * sizeof(float);
+    TSB_CUDA(cudaMalloc((void**)&g->xch_region, g->xch_bytes));
+    TSB_CUDA(cudaMemset(g->xch_region, 0, g->xch_bytes));
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t hd;
+  TSB_CUDA(cudaIpcGetMemHandle(&hd, g->xch_region));
+  std::memcpy(handle64, &hd, sizeof(hd));
+  return 1;
+}
+
+int TSB200_GptTpImport(void* h, const void* handles, int n) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && handles && n == g->tp && g->xch_region, "gpt_tp_import: bad arguments (export first; one 64-byte handle per rank)");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  for (int r = 0; r < n; ++r) {
+    if (r == g->tp_rank) {
+      g->xch_peer[r] = g->xch_region;
+      continue;
+    }
+    cudaIpcMemHandle_t hd;
+    std::memcpy(&hd, (const unsigned char*)handles + (size_t)r * 64, sizeof(hd));
+    void* p = nullptr;
+    TSB_CUDA(cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess));
+    g->xch_peer[r] = (unsigned char*)p;
+    g->xch_open[r] = true;
+  }
+  g->xch_ready = true;
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  g->stack_key = nullptr;  // the program is rebuilt with the exchange
+  return 1;
 }
 
 int TSB200_GptSetComm(void* h, void* comm) {

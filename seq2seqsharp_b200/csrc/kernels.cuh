@@ -46,13 +46,28 @@ struct StackOp {
   // rows [M, H*hd] in T at ep.y
   void* cK;
   void* cV;
+  // tensor parallelism (row-sharded linears): xsite >= 0: the finished column tiles are partial sums over this rank's
+  // share of K; they are stored into every rank's exchange buffer `xsite` (slot = this rank) instead of ep.y32.
+  // ssite >= 0 (norm prologue only): the input row is x + the sum over ranks of exchange buffer `ssite`, and CTA 0
+  // stores that new residual row to x_out (a different buffer than x: other CTAs are still reading x).
+  int xsite, ssite;
+  float* x_out;
 };
+constexpr int kStackMaxRanks = 8;
+constexpr int kStackXchSites = 4;     // exchange buffers: {out-projection, FFN down} x layer parity
+constexpr int kStackXchRows = 8;      // rows per exchange slot
 struct StackConfig {
   int dtype, M;           // M = sequences (1..4; up to 8 on the fp16 tensor-core kernel)
   int H, Hkv, hd, Tmax, qkv_rs, use_rope;
   const float2* rope_tab; // [Tmax, hd/2] cos/sin
   const int* dT;          // device word holding the cache length before this step
+  // tensor parallelism inside the kernel: every rank's exchange region as mapped into this process (own included).
+  // Region: [n_ops arrival counters (monotonic, one per operation)] at 0, [epoch word] at 16 KB - 4,
+  // [kStackXchSites][ranks][kStackXchRows][d] fp32 from 16 KB.
+  int tp_rank, tp_size, d;
+  unsigned char* peer[kStackMaxRanks];
 };
+constexpr size_t kStackXchHeader = 16384;
 // Sizes of the scratch areas launch_decode_stack() needs for a program (host copy of the ops).
 void decode_stack_scratch(const StackConfig& c, const StackOp* ops, int n_ops, int sm_count, int64_t* partial_bytes,
                           int64_t* counter_bytes, int64_t* attn_part_bytes);

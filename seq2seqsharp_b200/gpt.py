@@ -224,6 +224,12 @@ class GPT:
             dist.all_gather_object(allh, bytes(mine), group=group)
             blob = (C.c_ubyte * (64 * self.tp_size)).from_buffer_copy(b"".join(allh))
             N.call("TSB200_CommPeerImport", self._comm, blob, self.tp_size)
+            if self.cfg.dtype == "float16":
+                # exchange region of the persistent decode-step kernel (the collective happens inside that kernel)
+                N.call("TSB200_GptTpExport", self._h, mine)
+                dist.all_gather_object(allh, bytes(mine), group=group)
+                blob = (C.c_ubyte * (64 * self.tp_size)).from_buffer_copy(b"".join(allh))
+                N.call("TSB200_GptTpImport", self._h, blob, self.tp_size)
         N.call("TSB200_GptSetComm", self._h, self._comm)
 
     def close(self):
