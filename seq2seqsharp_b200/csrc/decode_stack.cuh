@@ -400,17 +400,24 @@ __device__ __forceinline__ void stage_norm_vec(T* xs, const float* x, const Norm
     if (xsum) {
       // tensor parallelism: the row is the old residual plus every rank's partial sum, added in rank order (the same
       // bits on every rank); the block with index 0 also stores the new residual row
-      for (int r = 0; r < n_sum; ++r) {
-        float4 p[4];
+      // two ranks' rows in flight per round trip; added in rank order
+      for (int r = 0; r < n_sum; r += 2) {
+        const bool two = r + 1 < n_sum;
+        float4 p[4], q[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int k = (j * 256 + tid) * 4;
-          p[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)r * sum_stride + (size_t)m * K + (k < K ? k : 0)));
+          const size_t o = (size_t)m * K + (k < K ? k : 0);
+          p[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)r * sum_stride + o));
+          q[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)(two ? r + 1 : r) * sum_stride + o));
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if ((j * 256 + tid) * 4 < K) {
             v[j].x += p[j].x; v[j].y += p[j].y; v[j].z += p[j].z; v[j].w += p[j].w;
+            if (two) {
+              v[j].x += q[j].x; v[j].y += q[j].y; v[j].z += q[j].z; v[j].w += q[j].w;
+            }
           }
         }
       }

@@ -1,5 +1,6 @@
-"""Tensor-parallel engine on 2 GPUs (one process per GPU, NCCL all-reduce after the out-projection and after the FFN
-down-projection) against the CPU oracle.  Needs two visible GPUs; skipped otherwise."""
+"""Tensor-parallel engine on 2 GPUs (one process per GPU) against the CPU oracle.  The fp16 config decodes through the
+persistent kernel with the exchange over peer memory inside it, the fp32 config through per-operation launches with the
+peer-memory all-reduce; prefill-sized messages go through NCCL in both.  Needs two visible GPUs; skipped otherwise."""
 import os
 import socket
 
