@@ -211,23 +211,21 @@ template <typename T>
 __device__ __forceinline__ void stage_plain_vec(T* xs, const T* x, int M, int K, int Kp, int tid) {
   constexpr int EPV = 16 / (int)sizeof(T);
   const int nv = K / EPV, nvp = Kp / EPV;  // K % EPV == 0 (checked by the caller); Kp is a multiple of 32
-  const int total = M * nvp;               // rows are flattened: eight vectors per thread in flight whatever M is
-  for (int f0 = 0; f0 < total; f0 += 256 * 8) {
-    uint4 v[8];
+  for (int m = 0; m < M; ++m) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)m * K);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * Kp);
+    for (int v0 = 0; v0 < nvp; v0 += 256 * 8) {
+      uint4 v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int f = f0 + j * 256 + tid;
-      const int m = f / nvp, i = f - m * nvp;
-      const bool ok = f < total && i < nv;
-      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)(ok ? m : 0) * K) + (ok ? i : 0));
-      v[j] = ok ? t : make_uint4(0u, 0u, 0u, 0u);
-    }
+      for (int j = 0; j < 8; ++j) {
+        const int i = v0 + j * 256 + tid;
+        const uint4 t = __ldcg(src + (i < nv ? i : 0));
+        v[j] = (i < nv) ? t : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int f = f0 + j * 256 + tid;
-      if (f < total) {
-        const int m = f / nvp, i = f - m * nvp;
-        reinterpret_cast<uint4*>(xs + (size_t)m * Kp)[i] = v[j];
+      for (int j = 0; j < 8; ++j) {
+        const int i = v0 + j * 256 + tid;
+        if (i < nvp) dst[i] = v[j];
       }
     }
   }
@@ -238,26 +236,23 @@ __device__ __forceinline__ void stage_plain_vec(T* xs, const T* x, int M, int K,
 // memory per sequence instead of the whole row.  K % 8 == 0.
 __device__ __forceinline__ void stage_plain_slice(__half* xs, const __half* x, int M, int K, int KB, int kb0, int n_t, int Ks, int tid) {
   const int nv = n_t * 4;  // 16-byte vectors per row: four per k-tile
-  const int total = M * nv;
-  for (int f0 = 0; f0 < total; f0 += 256 * 8) {
-    uint4 v[8];
+  for (int m = 0; m < M; ++m) {
+    for (int v0 = 0; v0 < nv; v0 += 256 * 4) {
+      uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int f = f0 + j * 256 + tid;
-      const int m = f / nv, i = f - m * nv;
-      int kb = kb0 + (i >> 2);
-      if (kb >= KB) kb -= KB;
-      const int k = kb * kKT + (i & 3) * 8;
-      const bool ok = f < total && k + 8 <= K;
-      const uint4 t = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)(ok ? m : 0) * K + (ok ? k : 0)));
-      v[j] = ok ? t : make_uint4(0u, 0u, 0u, 0u);
-    }
+      for (int j = 0; j < 4; ++j) {
+        const int i = v0 + j * 256 + tid;
+        int kb = kb0 + (i >> 2);
+        if (kb >= KB) kb -= KB;
+        const int k = kb * kKT + (i & 3) * 8;
+        const bool ok = i < nv && k + 8 <= K;
+        const uint4 t = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * K + (ok ? k : 0)));
+        v[j] = ok ? t : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int f = f0 + j * 256 + tid;
-      if (f < total) {
-        const int m = f / nv, i = f - m * nv;
-        *reinterpret_cast<uint4*>(xs + (size_t)m * Ks + i * 8) = v[j];
+      for (int j = 0; j < 4; ++j) {
+        const int i = v0 + j * 256 + tid;
+        if (i < nv) *reinterpret_cast<uint4*>(xs + (size_t)m * Ks + i * 8) = v[j];
       }
     }
   }
@@ -394,122 +389,88 @@ __device__ __forceinline__ void stage_norm_vec(T* xs, const float* x, const Norm
                                                int Kp, int tid, float* s_stat, const float* xsum = nullptr, int n_sum = 0,
                                                size_t sum_stride = 0, float* x_out = nullptr) {
   const int lane = tid & 31, w = tid >> 5;
-  // two rows per pass: their loads share one memory round trip and their statistics one barrier
-  for (int m0 = 0; m0 < M; m0 += 2) {
-    const bool has1 = m0 + 1 < M;
-    const int mr[2] = {m0, has1 ? m0 + 1 : m0};
-    float4 v[2][4];
+  for (int m = 0; m < M; ++m) {
+    float4 v[4];
 #pragma unroll
-    for (int r2 = 0; r2 < 2; ++r2)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k = (j * 256 + tid) * 4;
-        v[r2][j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (k < K && (r2 == 0 || has1)) v[r2][j] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)mr[r2] * K + k));
-      }
+    for (int j = 0; j < 4; ++j) {
+      const int k = (j * 256 + tid) * 4;
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * K + (k < K ? k : 0)));
+      v[j] = (k < K) ? t : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     if (xsum) {
       // tensor parallelism: the row is the old residual plus every rank's partial sum, added in rank order (the same
       // bits on every rank); the block with index 0 also stores the new residual row
-      for (int r = 0; r < n_sum; ++r) {
-        float4 p[2][4];
+      // two ranks' rows in flight per round trip; added in rank order
+      for (int r = 0; r < n_sum; r += 2) {
+        const bool two = r + 1 < n_sum;
+        float4 p[4], q[4];
 #pragma unroll
-        for (int r2 = 0; r2 < 2; ++r2)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int k = (j * 256 + tid) * 4;
-            p[r2][j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (k < K && (r2 == 0 || has1))
-              p[r2][j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)r * sum_stride + (size_t)mr[r2] * K + k));
-          }
-#pragma unroll
-        for (int r2 = 0; r2 < 2; ++r2)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if ((j * 256 + tid) * 4 < K) {
-              v[r2][j].x += p[r2][j].x; v[r2][j].y += p[r2][j].y; v[r2][j].z += p[r2][j].z; v[r2][j].w += p[r2][j].w;
-            }
-          }
-      }
-      if (x_out) {
-#pragma unroll
-        for (int r2 = 0; r2 < 2; ++r2) {
-          if (r2 == 1 && !has1) break;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int k = (j * 256 + tid) * 4;
-            if (k < K) *reinterpret_cast<float4*>(x_out + (size_t)mr[r2] * K + k) = v[r2][j];
-          }
+        for (int j = 0; j < 4; ++j) {
+          const int k = (j * 256 + tid) * 4;
+          const size_t o = (size_t)m * K + (k < K ? k : 0);
+          p[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)r * sum_stride + o));
+          q[j] = __ldcg(reinterpret_cast<const float4*>(xsum + (size_t)(two ? r + 1 : r) * sum_stride + o));
         }
-      }
-    }
-    float s1[2];
-#pragma unroll
-    for (int r2 = 0; r2 < 2; ++r2) {
-      float acc = 0.0f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        acc += (xmode == 2) ? (v[r2][j].x + v[r2][j].y) + (v[r2][j].z + v[r2][j].w)
-                            : (v[r2][j].x * v[r2][j].x + v[r2][j].y * v[r2][j].y) + (v[r2][j].z * v[r2][j].z + v[r2][j].w * v[r2][j].w);
-      s1[r2] = warp_sum(acc);
-    }
-    if (lane == 0) {
-      s_stat[w] = s1[0];
-      s_stat[8 + w] = s1[1];
-    }
-    consumers_sync();
-    float mean[2] = {0.0f, 0.0f}, inv[2];
-#pragma unroll
-    for (int r2 = 0; r2 < 2; ++r2) {
-      float tot = 0.0f;
-#pragma unroll
-      for (int i = 0; i < kConsumerWarps; ++i) tot += s_stat[r2 * 8 + i];
-      if (xmode == 2) mean[r2] = tot / K;
-      else inv[r2] = sqrtf(tot / (float)K + eps);
-    }
-    if (xmode == 2) {
-      float s2[2];
-#pragma unroll
-      for (int r2 = 0; r2 < 2; ++r2) {
-        float acc = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if ((j * 256 + tid) * 4 < K) {
-            const float e0 = v[r2][j].x - mean[r2], e1 = v[r2][j].y - mean[r2], e2 = v[r2][j].z - mean[r2], e3 = v[r2][j].w - mean[r2];
-            acc += (e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3);
+            v[j].x += p[j].x; v[j].y += p[j].y; v[j].z += p[j].z; v[j].w += p[j].w;
+            if (two) {
+              v[j].x += q[j].x; v[j].y += q[j].y; v[j].z += q[j].z; v[j].w += q[j].w;
+            }
           }
         }
-        s2[r2] = warp_sum(acc);
       }
-      if (lane == 0) {
-        s_stat[32 + w] = s2[0];
-        s_stat[40 + w] = s2[1];
-      }
-      consumers_sync();
+      if (x_out) {
 #pragma unroll
-      for (int r2 = 0; r2 < 2; ++r2) {
-        float t2 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kConsumerWarps; ++i) t2 += s_stat[32 + r2 * 8 + i];
-        inv[r2] = sqrtf(eps + t2 / K);
-      }
-    }
-#pragma unroll
-    for (int r2 = 0; r2 < 2; ++r2) {
-      if (r2 == 1 && !has1) break;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k = (j * 256 + tid) * 4;
-        if (k < Kp) {
-          float o[4];
-          const float xv[4] = {v[r2][j].x, v[r2][j].y, v[r2][j].z, v[r2][j].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            o[e] = (k < K) ? to_f<T>(nc.g[j][e]) * ((xv[e] - mean[r2]) / inv[r2]) + nc.beta_on * to_f<T>(nc.b[j][e]) : 0.0f;
-          St4<T>::st(xs + (size_t)mr[r2] * Kp + k, o);
+        for (int j = 0; j < 4; ++j) {
+          const int k = (j * 256 + tid) * 4;
+          if (k < K) *reinterpret_cast<float4*>(x_out + (size_t)m * K + k) = v[j];
         }
       }
     }
-    consumers_sync();  // s_stat is rewritten by the next pair of rows
+    float s1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      s1 += (xmode == 2) ? (v[j].x + v[j].y) + (v[j].z + v[j].w) : (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+    s1 = warp_sum(s1);
+    if (lane == 0) s_stat[(m & 3) * 8 + w] = s1;
+    consumers_sync();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kConsumerWarps; ++i) tot += s_stat[(m & 3) * 8 + i];
+    float mean = 0.0f, inv;
+    if (xmode == 2) {
+      mean = tot / K;
+      float s2 = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if ((j * 256 + tid) * 4 < K) {
+          const float e0 = v[j].x - mean, e1 = v[j].y - mean, e2 = v[j].z - mean, e3 = v[j].w - mean;
+          s2 += (e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3);
+        }
+      }
+      s2 = warp_sum(s2);
+      if (lane == 0) s_stat[32 + (m & 3) * 8 + w] = s2;
+      consumers_sync();
+      float t2 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kConsumerWarps; ++i) t2 += s_stat[32 + (m & 3) * 8 + i];
+      inv = sqrtf(eps + t2 / K);
+    } else {
+      inv = sqrtf(tot / (float)K + eps);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = (j * 256 + tid) * 4;
+      if (k < Kp) {
+        float o[4];
+        const float xv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = (k < K) ? to_f<T>(nc.g[j][e]) * ((xv[e] - mean) / inv) + nc.beta_on * to_f<T>(nc.b[j][e]) : 0.0f;
+        St4<T>::st(xs + (size_t)m * Kp + k, o);
+      }
+    }
   }
 }
 
