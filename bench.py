@@ -289,7 +289,7 @@ def run_b200(args):
         # algorithmic bytes are the weights once plus the KV cache read and the appended rows
         lin_ms, lin_groups = prof["decode_stack"]
         es = 2 if cfg.dtype == "float16" else 4
-        lin_bytes += B * cfg.L * 2 * cfg.kv_heads() * cfg.hd * (T_prof + 1) * es
+        lin_bytes += B * cfg.L * 2 * (cfg.kv_heads() // (world if tp else 1)) * cfg.hd * (T_prof + 1) * es
         dominant = "decode_stack_kernel (persistent: all linears, RoPE, cache append and attention of a decode step)"
     hbm, which = peaks()
     achieved = (lin_bytes * n_prof / 1e9) / (lin_ms / 1e3) if lin_ms > 0 else 0.0

@@ -29,6 +29,7 @@ __device__ __forceinline__ void mm_mma_16816(float* d, uint32_t a0, uint32_t a1,
 }
 
 // ------------------------------------------------------------------------------------------- workers: one linear
+template <bool TP>  // TP: tensor-parallel program (exchange sites); the single-GPU instantiation carries none of that code
 __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op, int op_i, const LinGeom& g, unsigned char* stage_mem,
                                           __half* xs, float* red, uint64_t* full, uint64_t* empty, int& s, unsigned& round,
                                           volatile int* s_err, volatile int* s_last, float* s_stat, bool& dead,
@@ -54,7 +55,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     if (K % 8 == 0) stage_plain_vec<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
     else stage_plain<T>(xs, reinterpret_cast<const T*>(op->x), M, K, Kp, tid);
   } else if (nvc) {
-    const bool summed = op->ssite >= 0;
+    const bool summed = TP && op->ssite >= 0;
     stage_norm_vec<T>(xs, reinterpret_cast<const float*>(op->x), *nvc, op->xmode, op->eps, M, K, Kp, tid, s_stat,
                       summed ? stack_xch(a.c, a.c.tp_rank, op->ssite, 0) : nullptr, a.c.tp_size, (size_t)kStackXchRows * a.c.d,
                       (summed && blockIdx.x == 0) ? op->x_out : nullptr);
@@ -91,7 +92,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
   // latency would otherwise sit at the very end of the dependency chain.  A missing bias / residual aliases the
   // weights and is switched off by a factor, indices are clamped: every address a thread can form is valid.
   const int ct0 = ct;
-  const bool xchg = op->xsite >= 0;  // row-sharded linear under tensor parallelism: partial sums go to every rank
+  const bool xchg = TP && op->xsite >= 0;  // row-sharded linear under tensor parallelism: partial sums go to every rank
   if (xchg && a.c.tp_rank != 0) bias = nullptr;  // the bias is added once, by rank 0
   const float b_on = bias ? 1.0f : 0.0f, r_on = ep.residual ? 1.0f : 0.0f;
   const T* bp = bias ? bias : reinterpret_cast<const T*>(op->Wp);
@@ -256,6 +257,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
 }
 
 // ------------------------------------------------------------------------------------------- the kernel
+template <bool TP>
 __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(StackArgs a) {
   typedef __half T;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -313,9 +315,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
     }
   }
   // tensor parallelism: counters that other ranks increment are monotonic; this launch is epoch `epoch`
-  unsigned* xcnt = c.tp_size > 1 ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank]) : nullptr;
-  unsigned* epoch_ptr = c.tp_size > 1 ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank] + kStackXchHeader - 4) : nullptr;
-  const unsigned epoch = epoch_ptr ? *reinterpret_cast<volatile unsigned*>(epoch_ptr) : 0u;
+  unsigned* xcnt = TP ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank]) : nullptr;
+  unsigned* epoch_ptr = TP ? reinterpret_cast<unsigned*>(c.peer[c.tp_rank] + kStackXchHeader - 4) : nullptr;
+  const unsigned epoch = TP ? *reinterpret_cast<volatile unsigned*>(epoch_ptr) : 0u;
   int s = 0;
   unsigned round = 0;
   bool dead = false;
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       if (i > 0) {
         bool ok = true;
         if (tid == 0) {
-          if (prev_xchg)  // every rank's finishers arrive here: column tiles x ranks, per launch
+          if (TP && prev_xchg)  // every rank's finishers arrive here: column tiles x ranks, per launch
             ok = poll_count_sys(xcnt + (i - 1), (epoch + 1u) * prev_target * (unsigned)c.tp_size, dead ? 64u : kPollLimit, a.error_flag);
           else
             ok = poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : kPollLimit, a.error_flag);
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       }
       STRACE(i, 0);
       if (op->type == 0) {
-        mm_linear(a, op, i, g, stage_mem, xs, red, full, empty, s, round, &s_err, &s_last, s_stat, dead, hoist ? &nc : nullptr);
+        mm_linear<TP>(a, op, i, g, stage_mem, xs, red, full, empty, s, round, &s_err, &s_last, s_stat, dead, hoist ? &nc : nullptr);
       } else if (AG == 4) {
         stack_attention<T, 4>(a, op, i, merge, &s_last, T0, splits, rcs, rsn);
       } else {
@@ -366,7 +368,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
       STRACE(i, 3);
     }
     prev_target = target;
-    prev_xchg = op->type == 0 && op->xsite >= 0;
+    prev_xchg = TP && op->type == 0 && op->xsite >= 0;
   }
   // leave: the last CTA out clears the operation counters for the next launch
   if (tid == 0) {
@@ -375,14 +377,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
     const unsigned prev = atomicAdd(&a.done[a.n_ops * kDoneStride], 1u);
     if (prev == gridDim.x - 1) {
       for (int i = 0; i <= a.n_ops; ++i) a.done[i * kDoneStride] = 0u;
-      if (epoch_ptr) *reinterpret_cast<volatile unsigned*>(epoch_ptr) = epoch + 1u;
+      if (TP) *reinterpret_cast<volatile unsigned*>(epoch_ptr) = epoch + 1u;
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------- host side
 int init_stack_mma_attrs() {
-  TSB_CUDA(cudaFuncSetAttribute(decode_stack_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+  TSB_CUDA(cudaFuncSetAttribute(decode_stack_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+  TSB_CUDA(cudaFuncSetAttribute(decode_stack_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
   return 1;
 }
 
@@ -427,7 +430,8 @@ int launch_decode_stack_mma(int device, DeviceState* st, const StackConfig& c, c
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
-  TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_stack_mma_kernel, a));
+  if (c.tp_size > 1) TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_stack_mma_kernel<true>, a));
+  else TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_stack_mma_kernel<false>, a));
   count_launch(device);
   return 1;
 }
