@@ -407,6 +407,204 @@ __global__ void __launch_bounds__(kAttnThreads) attn_staged_kernel(T* out, float
   }
 }
 
+// Decode attention on the warp-level tensor cores (fp16, head_dim 64 or 128, up to 8 query heads per KV head), for
+// large batches: one CTA = (sequence, KV head, split of the key range), the query heads of the group are the rows of
+// the m16n8k16 A operand (rows beyond the group are zero), so K and V are read once for the whole group and a 16-token
+// slice costs a warp 2*(hd/16) + hd/8 mma instructions instead of ~60 shuffle/FMA instructions per token.
+//   S = Q K^T : A = Q fragments held in registers, B = K rows staged in shared memory (ldmatrix);
+//   online softmax per 16-token slice in fp32 (scores scaled by 1/sqrt(hd) after the product, as the reference does);
+//   O += P V  : A = P rounded to fp16, taken straight from the S accumulator fragments, B = V rows (ldmatrix.trans).
+// K/V rows are staged by cp.async, 64 tokens per stage, three stages in flight; every 16-byte chunk is stored at
+// chunk ^ (row & 7) so that the ldmatrix row reads are bank-conflict free.  Each warp owns 16 tokens of a stage and its
+// own (max, sum, O) state; the four states are merged like the lane-group states of attn_kernel.
+constexpr int kMmaStageTokens = 64;
+constexpr int kMmaStages = 3;
+
+__device__ __forceinline__ void at_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void at_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void at_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads) attn_mma_kernel(__half* out, float* part, const __half* q, int64_t q_rs,
+                                                                const __half* cK, const __half* cV, int H, int Hkv, int T0_arg,
+                                                                const int* dT0, int Tmax, int splits, float scale) {
+  constexpr int RB = HD * 2;            // bytes per row
+  constexpr int CPR = RB / 16;          // 16-byte chunks per row
+  constexpr int KS = HD / 16;           // k steps of Q K^T
+  constexpr int NBO = HD / 8;           // n blocks of O
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int G = H / Hkv;                // query heads per KV head (<= 8)
+  const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+  const int h0 = kvh * G;
+  const int Tk = min(T0 + 1, Tmax);
+  const int per_split = (Tk + splits - 1) / splits;
+  const int t_beg = split * per_split, t_end = min(Tk, t_beg + per_split);
+  const size_t stage_bytes = 2 * (size_t)kMmaStageTokens * RB;
+  const __half* Kb = cK + ((int64_t)row * Hkv + kvh) * Tmax * HD;
+  const __half* Vb = cV + ((int64_t)row * Hkv + kvh) * Tmax * HD;
+  const int n_tiles = (max(t_end - t_beg, 0) + kMmaStageTokens - 1) / kMmaStageTokens;
+
+  auto issue = [&](int tile) {
+    if (tile < n_tiles) {
+      unsigned char* st = attn_smem + (size_t)(tile % kMmaStages) * stage_bytes;
+      const int t0 = t_beg + tile * kMmaStageTokens;
+      for (int v = threadIdx.x; v < kMmaStageTokens * CPR; v += kAttnThreads) {
+        const int tt = v / CPR, c = v % CPR;
+        const int t = min(t0 + tt, t_end - 1);  // the tail re-reads the last token of the range; its scores are masked
+        const int pc = (c ^ (tt & 7)) * 16;
+        cp_async_16(st + (size_t)tt * RB + pc, Kb + (int64_t)t * HD + c * 8);
+        cp_async_16(st + (size_t)(kMmaStageTokens + tt) * RB + pc, Vb + (int64_t)t * HD + c * 8);
+      }
+    }
+    cp_async_commit();
+  };
+  for (int i = 0; i < kMmaStages - 1; ++i) issue(i);
+
+  // Q fragments: row g8 = head h0 + g8 (zero rows beyond the group), a0 = k 2*t4.., a2 = k 8 + 2*t4..
+  uint32_t qa[KS][2];
+  {
+    const bool live = g8 < G;
+    const __half* qp = q + (int64_t)row * q_rs + (int64_t)(h0 + (live ? g8 : 0)) * HD + 2 * t4;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][0] = live ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+      qa[ks][1] = live ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+    }
+  }
+  float m_run = -INFINITY, l_run = 0.0f;   // state of head g8 (this lane's part of the row sum)
+  float o[NBO][4];
+#pragma unroll
+  for (int nb = 0; nb < NBO; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    issue(tile + kMmaStages - 1);
+    cp_async_wait<kMmaStages - 1>();
+    __syncthreads();
+    const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(attn_smem + (size_t)(tile % kMmaStages) * stage_bytes);
+    const uint32_t vbase = kbase + kMmaStageTokens * RB;
+    const int tw = w * 16;                                   // this warp's 16 tokens of the stage
+    const int t_first = t_beg + tile * kMmaStageTokens + tw;
+    if (t_first < t_end) {
+      // ---- S = Q K^T for two 8-token blocks
+      float sc[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nb][e] = 0.0f;
+        const int r = tw + nb * 8 + (lane & 7);
+#pragma unroll
+        for (int kp = 0; kp < KS / 2; ++kp) {
+          uint32_t b0, b1, b2, b3;
+          const int c = kp * 4 + (lane >> 3);
+          at_ldmatrix_x4(kbase + r * RB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+          at_mma(sc[nb], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, b0, b1);
+          at_mma(sc[nb], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, b2, b3);
+        }
+      }
+      // ---- online softmax of row g8 over these 16 tokens (this lane: tokens nb*8 + 2*t4, +1)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int t = t_first + nb * 8 + 2 * t4 + e;
+          sc[nb][e] = (t < t_end) ? sc[nb][e] * scale : -INFINITY;
+          mx = fmaxf(mx, sc[nb][e]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);   // finite: the slice has at least one valid token
+      const float corr = __expf(m_run - m_new);
+      float p[2][2];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[nb][e] = __expf(sc[nb][e] - m_new);
+          l_run = (nb == 0 && e == 0) ? l_run * corr + p[nb][e] : l_run + p[nb][e];
+        }
+      m_run = m_new;
+      // P as the A operand of the second product (rows beyond the group stay zero)
+      __half2 h0p = __floats2half2_rn(p[0][0], p[0][1]), h1p = __floats2half2_rn(p[1][0], p[1][1]);
+      const uint32_t pa0 = *reinterpret_cast<uint32_t*>(&h0p), pa2 = *reinterpret_cast<uint32_t*>(&h1p);
+      // ---- O = O * corr + P V
+      const int vr = tw + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int np = 0; np < NBO / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        const int c = np * 2 + (lane >> 4);
+        at_ldmatrix_x4_trans(vbase + vr * RB + ((c ^ (vr & 7)) << 4), b0, b1, b2, b3);
+        o[2 * np][0] *= corr; o[2 * np][1] *= corr;
+        o[2 * np + 1][0] *= corr; o[2 * np + 1][1] *= corr;
+        at_mma(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+        at_mma(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+      }
+    }
+    __syncthreads();  // the stage is overwritten by the copy issued in the next iteration
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // this lane's part of the row sum -> whole row
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  // merge the four warp states through shared memory: [warp][head][hd + 2]
+  float* sm = reinterpret_cast<float*>(attn_smem);
+  const int rec = HD + 2;
+  if (g8 < G) {
+    float* r = sm + ((int64_t)w * G + g8) * rec;
+    if (t4 == 0) {
+      r[0] = m_run;
+      r[1] = l_run;
+    }
+#pragma unroll
+    for (int nb = 0; nb < NBO; ++nb) {
+      r[2 + nb * 8 + 2 * t4] = o[nb][0];
+      r[2 + nb * 8 + 2 * t4 + 1] = o[nb][1];
+    }
+  }
+  __syncthreads();
+  const int nstates = kAttnThreads / 32;
+  for (int idx = threadIdx.x; idx < G * HD; idx += kAttnThreads) {
+    const int g = idx / HD, e = idx % HD;
+    float mx = -INFINITY;
+    for (int i = 0; i < nstates; ++i) mx = fmaxf(mx, sm[((int64_t)i * G + g) * rec]);
+    float L = 0.0f, A = 0.0f;
+    for (int i = 0; i < nstates; ++i) {
+      const float* r = sm + ((int64_t)i * G + g) * rec;
+      const float c = (r[0] == -INFINITY) ? 0.0f : __expf(r[0] - mx);
+      L += r[1] * c;
+      A += r[2 + e] * c;
+    }
+    const int h = h0 + g;
+    if (splits == 1) {
+      out[((int64_t)row * H + h) * HD + e] = __float2half_rn(L > 0.0f ? A / L : 0.0f);
+    } else {
+      float* pr = part + (((int64_t)row * H + h) * splits + split) * rec;
+      if (e == 0) {
+        pr[0] = mx;
+        pr[1] = L;
+      }
+      pr[2 + e] = A;
+    }
+  }
+}
+
 template <typename T>
 __global__ void attn_combine_kernel(T* out, const float* part, int hd, int splits) {
   pdl_trigger();
@@ -476,6 +674,38 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   if (staged < 0) {
     const char* e = getenv("TSB200_ATTN_STAGED");  // "0": register-only kernel for every case (A/B measurements)
     staged = (e && e[0] == '0') ? 0 : 1;
+  }
+  // fp16, head_dim 64 / 128, up to 8 query heads per KV head: scores and P V on the warp-level tensor cores
+  static int use_mma = -1;
+  if (use_mma < 0) {
+    const char* e = getenv("TSB200_ATTN_MMA");  // "0": keep the shuffle/FMA kernels (A/B measurements)
+    use_mma = (e && e[0] == '0') ? 0 : 1;
+  }
+  if constexpr (sizeof(T) == 2) {
+    if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv && B * Hkv * splits >= 2 * st->sm_count) {
+      const size_t sm3 = (size_t)kMmaStages * 2 * kMmaStageTokens * hd * 2;
+      dim3 g3(splits, Hkv, B);
+      static bool attr_done[kMaxDevices] = {};
+      if (!attr_done[device]) {
+        TSB_CUDA(cudaFuncSetAttribute(attn_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        TSB_CUDA(cudaFuncSetAttribute(attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        attr_done[device] = true;
+      }
+      if (hd == 64)
+        TSB_CUDA(launch_k(attn_mma_kernel<64>, g3, dim3(kAttnThreads), sm3, s, (__half*)out, ws, (const __half*)q, q_rs, (const __half*)cK,
+                          (const __half*)cV, H, Hkv, T0, dT0, Tmax, splits, scale));
+      else
+        TSB_CUDA(launch_k(attn_mma_kernel<128>, g3, dim3(kAttnThreads), sm3, s, (__half*)out, ws, (const __half*)q, q_rs, (const __half*)cK,
+                          (const __half*)cV, H, Hkv, T0, dT0, Tmax, splits, scale));
+      count_launch(device);
+      TSB_TRY(check_launch("attention_mma"));
+      if (splits > 1) {
+        TSB_CUDA(launch_k(attn_combine_kernel<T>, dim3(B * S * H), dim3(hd < 128 ? 64 : 128), 0, s, out, (const float*)ws, hd, splits));
+        count_launch(device);
+        TSB_TRY(check_launch("attention_combine"));
+      }
+      return 1;
+    }
   }
   const size_t stage_smem = (size_t)kAttnStages * 2 * kStageTokens * hd * sizeof(T);
   if (staged && S == 1 && kStageTokens % ((kAttnThreads / 32) * tpw) == 0 && B * ygroups * splits >= 2 * st->sm_count) {
