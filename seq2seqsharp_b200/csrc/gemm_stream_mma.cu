@@ -292,6 +292,206 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
   }
 }
 
+// ---- column-chunk variant for 17..64 rows ------------------------------------------------------------------------------
+// With many rows the stream-K hand-over is expensive: every CTA leaves M x 256 floats per shared column tile and the
+// last arriver adds up to ten such slots alone.  Here a CTA owns ONE 64-column box of the packed tiles (4 KB per k tile,
+// contiguous) over a K range, so a box has few contributors (ksplit, usually 1..4) and a partial is M x 64 floats.
+// Stage = two k tiles of the box (2 x 4 KB bulk copies) + the activation tile [rows][64 k] (TMA tensor copy, 128-byte
+// swizzle).  Four consumer warps own 16 columns each; three CTAs fit on an SM, so one CTA's prologue and epilogue
+// overlap the others' streaming.
+constexpr int kGcThreads = 160;            // 4 consumer warps + producer warp
+constexpr int kGcStages = 4;
+constexpr int kGcStageBytes = 8192 + 8192; // W: 2 k tiles x 4 KB; x: 64 rows x 128 B
+
+struct GcArgs {
+  const unsigned char* Wp;
+  int M, K, N, KB, CT;
+  int ksplit, k2_per;        // K ranges per box; stages (pairs of k tiles) per range
+  float* partials;           // [boxes][ksplit][M][64]
+  unsigned int* counters;    // [boxes], zero on entry, self-resetting
+  int* error_flag;
+  Epilogue ep;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(kGcThreads, 3) gemm_chunk_mma_kernel(const __grid_constant__ CUtensorMap mapX, GcArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGcStages * kGcStageBytes);
+  uint64_t* empty = full + kGcStages;
+  float* red = reinterpret_cast<float*>(smem);  // [M][64] after the main loop (the stages are free then)
+  __shared__ int s_err, s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int M = a.M, N = a.N, KB = a.KB;
+  const int box = blockIdx.x / a.ksplit, ks = blockIdx.x % a.ksplit;   // the K ranges of a box run side by side
+  const int ct = box >> 2, j = box & 3;
+  const int k2_total = (KB + 1) / 2;
+  const int k2_beg = ks * a.k2_per, k2_end = min(k2_total, k2_beg + a.k2_per);
+  const int n_st = max(k2_end - k2_beg, 0);
+
+  if (tid == 0) {
+    for (int i = 0; i < kGcStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 4);
+    }
+    s_err = 0;
+    s_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  grid_dep_launch();
+  grid_dep_wait();  // the activation rows come from the previous kernel
+
+  if (w == 4) {
+    if (lane == 0) {
+      const unsigned char* wsrc = a.Wp + ((size_t)ct * KB) * kTileBytes + (size_t)j * 4096;
+      for (int i = 0; i < n_st; ++i) {
+        const int s = i % kGcStages, r = i / kGcStages;
+        if (i >= kGcStages && !mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
+          s_err = 1;
+          break;
+        }
+        const int kb0 = (k2_beg + i) * 2;
+        const bool two = kb0 + 1 < KB;
+        unsigned char* dst = smem + (size_t)s * kGcStageBytes;
+        mbar_expect_tx(&full[s], (two ? 8192 : 4096) + NB * 8 * 128);
+        bulk_g2s(dst, wsrc + (size_t)kb0 * kTileBytes, 4096, &full[s]);
+        if (two) bulk_g2s(dst + 4096, wsrc + (size_t)(kb0 + 1) * kTileBytes, 4096, &full[s]);
+        gs_tma_load_2d(dst + 8192, &mapX, kb0 * kKT, 0, &full[s]);  // x = kb0 * 32 halves: a 64-byte multiple
+      }
+      if (*(volatile int*)&s_err) {
+        const int first = n_st > kGcStages ? n_st - kGcStages : 0;
+        for (int i = first; i < n_st; ++i) mbar_wait(&full[i % kGcStages], (unsigned)((i / kGcStages) & 1), 1u << 16);
+        g_gs_error = 1;
+        if (a.error_flag) *a.error_flag = 1;
+      }
+    }
+  } else {
+    // ---------------- consumer warps: warp w owns columns [w*16, w*16+16) of the box
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int lrow = (lane & 7) + ((lane >> 4) << 3);
+    const int lunit = (lane >> 3) & 1;
+    const int xr = lane & 7, xc = lane >> 3;
+    float d[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d[nb][e] = 0.0f;
+    bool dead = false;
+    for (int i = 0; i < n_st; ++i) {
+      const int s = i % kGcStages, r = i / kGcStages;
+      if (*(volatile int*)&s_err) dead = true;
+      if (!mbar_wait(&full[s], (unsigned)(r & 1), dead ? 4096u : kSpinLimit)) {
+        s_err = 1;
+        dead = true;
+      }
+      const uint32_t wbase = smem_u32(smem + (size_t)s * kGcStageBytes);
+      const uint32_t xbase = wbase + 8192;
+      const int kk_end = ((k2_beg + i) * 2 + 1 < KB) ? 4 : 2;  // a missing second k tile was not copied
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {            // the two k tiles of the stage
+        if (h2 * 2 >= kk_end) break;
+        // activation fragments of this k tile: rows of 128 B, 16-byte chunks XOR-ed with row & 7
+        uint32_t bf[NB][4];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const int n = nb * 8 + xr;
+          const int c = h2 * 4 + xc;
+          gs_ldmatrix_x4(xbase + n * 128 + ((c ^ (n & 7)) << 4), bf[nb][0], bf[nb][1], bf[nb][2], bf[nb][3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int k = kk * 16 + lrow;
+          const int unit = w * 2 + lunit;
+          uint32_t a0, a1, a2, a3;
+          gs_ldmatrix_x4_trans(wbase + h2 * 4096 + k * 128 + ((unit ^ (k & 7)) << 4), a0, a1, a2, a3);
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) gs_mma_16816(d[nb], a0, a1, a2, a3, bf[nb][2 * kk], bf[nb][2 * kk + 1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    // ---- accumulators -> red[row][64] (the stages are free: every copy has been consumed)
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = nb * 8 + 2 * t4 + (e & 1);
+        if (row < M) red[row * 64 + w * 16 + g8 + (e >> 1) * 8] = d[nb][e];
+      }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    bool finish = a.ksplit == 1;
+    if (a.ksplit > 1) {
+      float* mine = a.partials + ((size_t)blockIdx.x * M) * 64;   // [box][ks] = blockIdx.x
+      for (int idx = tid; idx < M * 16; idx += 128) reinterpret_cast<float4*>(mine)[idx] = reinterpret_cast<const float4*>(red)[idx];
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (tid == 0) {
+        const unsigned int prev = gs_atom_add_acq_rel(&a.counters[box], 1u);
+        const int last = (prev == (unsigned int)(a.ksplit - 1));
+        if (last) a.counters[box] = 0u;
+        s_last = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*(volatile int*)&s_last) {
+        const float4* all = reinterpret_cast<const float4*>(a.partials + ((size_t)box * a.ksplit * M) * 64);
+        for (int idx = tid; idx < M * 16; idx += 128) {
+          float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          for (int z = 0; z < a.ksplit; ++z) {
+            const float4 t = __ldcg(all + (size_t)z * M * 16 + idx);
+            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+          }
+          reinterpret_cast<float4*>(red)[idx] = acc;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finish = true;
+      }
+    }
+    if (finish) {
+      const Epilogue ep = a.ep;
+      const __half* bias = reinterpret_cast<const __half*>(ep.bias);
+      const int No = ep.glu ? N / 2 : N;
+      for (int idx = tid; idx < M * 16; idx += 128) {
+        const int row = idx >> 4, c = ct * 256 + j * 64 + (idx & 15) * 4;
+        const float4 t = reinterpret_cast<const float4*>(red)[idx];
+        const float v[4] = {t.x, t.y, t.z, t.w};
+        if (!ep.glu) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (c + e < N) {
+              float x = gs_act(v[e] + (bias ? __half2float(bias[c + e]) : 0.0f), ep.act);
+              const size_t o = (size_t)row * N + c + e;
+              if (ep.residual) x += ep.residual[o];
+              if (ep.y32) ep.y32[o] = x;
+              else reinterpret_cast<__half*>(ep.y)[o] = __float2half_rn(x);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; e += 2) {
+            if (c + e + 1 < N) {
+              float av = v[e] + (bias ? __half2float(bias[c + e]) : 0.0f);
+              const float gv = v[e + 1] + (bias ? __half2float(bias[c + e + 1]) : 0.0f);
+              if (ep.act == TSB200_ACT_SWIGLU) av = av / (1.0f + expf(-av));
+              float x = av * gv;
+              const size_t o = (size_t)row * No + ((c + e) >> 1);
+              if (ep.residual) x += ep.residual[o];
+              if (ep.y32) ep.y32[o] = x;
+              else reinterpret_cast<__half*>(ep.y)[o] = __float2half_rn(x);
+            }
+          }
+        }
+      }
+    }
+    if (tid == 0 && *(volatile int*)&s_err) {
+      g_gs_error = 1;
+      if (a.error_flag) *a.error_flag = 1;
+    }
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------------
 typedef CUresult (*GsEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -353,7 +553,75 @@ int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count) {
   if (g > KB * CT) g = KB * CT;
   const long long per = (KB * CT) / (g > 0 ? g : 1);
   const long long mc = KB / (per > 0 ? per : 1) + 2;
-  return kWsCounterBytes + CT * mc * M * 256 * 4 + 256;
+  const long long chunk = (long long)((N + 63) / 64) * 8 * M * 64 * 4;  // column-chunk variant: up to 8 K ranges per box
+  const long long stream = CT * mc * M * 256 * 4;
+  return kWsCounterBytes + (chunk > stream ? chunk : stream) + 256;
+}
+
+template <int NB>
+static int gc_launch(int device, const CUtensorMap& mapX, const GcArgs& a, int grid, bool pdl, cudaStream_t s) {
+  static bool attr_done[kMaxDevices] = {};
+  const size_t smem = kGcStages * kGcStageBytes + 1024 + 128;
+  if (!attr_done[device]) {
+    TSB_CUDA(cudaFuncSetAttribute(gemm_chunk_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done[device] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  TSB_CUDA(cudaLaunchKernelEx(&cfg, gemm_chunk_mma_kernel<NB>, mapX, a));
+  count_launch(device);
+  return 1;
+}
+
+// Column-chunk variant (17..64 rows).  1 ok, 0 error, 2 not handled.
+static int launch_gemm_chunk_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                                 int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s) {
+  GsEncodeTiledFn enc = gs_get_encode();
+  if (!enc) return 2;
+  const int NB = M <= 32 ? 4 : 8;
+  GcArgs a{};
+  a.Wp = reinterpret_cast<const unsigned char*>(Wp);
+  a.M = M; a.K = K; a.N = N;
+  a.KB = (K + kKT - 1) / kKT;
+  a.CT = (N + 255) / 256;
+  const int boxes = (N + 63) / 64;                 // boxes that hold real columns (the last column tile may have fewer than 4)
+  const int k2_total = (a.KB + 1) / 2;
+  // about two CTAs per SM in flight (three fit); a K range is at least 8 stages long
+  int ks = (2 * st->sm_count + boxes - 1) / boxes;
+  if (ks > k2_total / 8) ks = k2_total / 8;
+  if (ks < 1) ks = 1;
+  if (ks > 8) ks = 8;
+  a.k2_per = (k2_total + ks - 1) / ks;
+  ks = (k2_total + a.k2_per - 1) / a.k2_per;       // no empty range
+  a.ksplit = ks;
+  const int64_t need = kWsCounterBytes + (int64_t)boxes * ks * M * 64 * 4;
+  if (ks > 1 && (!ws || ws_bytes < need || (int64_t)boxes * 4 > kWsCounterBytes - 256)) return 2;
+  a.counters = reinterpret_cast<unsigned int*>(ws);
+  a.partials = ws ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes) : nullptr;
+  a.error_flag = error_flag;
+  a.ep = ep;
+  CUtensorMap mapX;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)(NB * 8)};
+    const cuuint32_t el[2] = {1, 1};
+    const CUresult r = enc(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, el,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TSB_CHECK(r == CUDA_SUCCESS, "gemm_chunk: cuTensorMapEncodeTiled failed with %d", (int)r);
+  }
+  const int grid = boxes * ks;
+  if (NB == 4) return gc_launch<4>(device, mapX, a, grid, pdl, s);
+  return gc_launch<8>(device, mapX, a, grid, pdl, s);
 }
 
 // 1 ok, 0 error, 2 shape not handled (caller falls back).
@@ -368,6 +636,17 @@ int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const voi
     if (!enabled) return 2;
   }
   if (M < 1 || M > 64 || K % 8 != 0 || ((uintptr_t)x % 16) != 0 || ((uintptr_t)Wp % 16) != 0) return 2;
+  if (M > 16) {
+    static int chunk = -1;
+    if (chunk < 0) {
+      const char* e = getenv("TSB200_GEMM_CHUNK");  // "0": stream-K hand-over for every row count (A/B measurements)
+      chunk = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (chunk) {
+      const int r = launch_gemm_chunk_mma(device, st, x, Wp, M, K, N, ep, error_flag, pdl, ws, ws_bytes, s);
+      if (r != 2) return r;
+    }
+  }
   GsEncodeTiledFn enc = gs_get_encode();
   if (!enc) return 2;
   const int NB = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
