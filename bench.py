@@ -10,7 +10,7 @@ path), timing is the max over ranks.
 Workloads (synthetic seeded weights and prompts of the named shapes; no dataset is involved):
     c5_b1   Llama-7B-class fp16, B=1,  prompt 512, Top-P 0.95     (headline: latency-bound decode)
     c5_b64  same model, B=64
-    c5_b4 / c5_b8  same model, B=4 / B=8 (still one persistent launch per step on the fp16 tensor-core variant)
+    c5_b2 .. c5_b8  same model, B=2, 3, 4, 8 (still one persistent launch per step on the fp16 tensor-core variant)
     c3_b1 / c3_b32  Llama-1B-class fp16, prompt 1024, greedy
     c1      tiny fp32 model, B=1, prompt 32, greedy
 """
@@ -33,6 +33,8 @@ WORKLOADS = {
     #            config name               B   prompt  strategy  topP
     "c5_b1": ("c5_llama7b_fp16", 1, 512, "topp", 0.95),
     "c5_b64": ("c5_llama7b_fp16", 64, 512, "topp", 0.95),
+    "c5_b2": ("c5_llama7b_fp16", 2, 512, "topp", 0.95),
+    "c5_b3": ("c5_llama7b_fp16", 3, 512, "topp", 0.95),
     "c5_b4": ("c5_llama7b_fp16", 4, 512, "topp", 0.95),
     "c5_b8": ("c5_llama7b_fp16", 8, 512, "topp", 0.95),
     "c3_b1": ("c3_llama1b_fp16", 1, 1024, "greedy", 1.0),

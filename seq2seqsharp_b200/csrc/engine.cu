@@ -174,6 +174,12 @@ struct Gpt {
   bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
   // persistent decode-step kernel (decode_stack.cu): the program of operations and its scratch
   bool use_stack = true;
+  // Measured crossover on the 7B-class model: one sequence is fastest in the persistent kernel (3.77 ms per step against
+  // 3.95 / 4.13 with one launch per operation); from two sequences on, one launch per operation with the mma.sync
+  // linears is flat at ~3.95 ms up to 8 sequences while the persistent kernel's dependency chain grows with every row
+  // (4.1 / 4.5 / 5.0 / 6.5 ms at 2 / 3 / 4 / 8).  Tensor-parallel engines keep the persistent kernel (the exchange lives there).
+  int stack_cap = 1;           // largest batch the persistent kernel is used for on one GPU (TSB200_STACK_MAXB)
+  int gemv_rows = 1;           // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS)
   std::vector<StackOp> stack_host;
   StackOp* stack_dev = nullptr;
   int stack_B = 0;
@@ -414,7 +420,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
                          const void* Wp, int K, int N, const Epilogue& ep) {
   const TSB200GptConfig& c = g->c;
   const int dev = c.device, dt = c.dtype;
-  if (rows <= 4) {
+  if (rows <= g->gemv_rows) {
     prof_begin(g);
     const int r = launch_gemv_stream(dev, g->st, dt, Wp, ng ? (const void*)x_resid : x_T, ng ? (c.norm_type == 0 ? 2 : 1) : 0, ng,
                                      c.norm_type == 0 ? nb : nullptr, c.eps, rows, K, N, ep, g->err_flag, g->pdl, g->lin_ws,
@@ -472,6 +478,7 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
 static int ensure_stack(Gpt* g, int B) {
   const TSB200GptConfig& c = g->c;
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
+  if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
   if (!g->use_stack || B > g->stack_max_B) return 1;
   const bool tp = g->tp > 1;
   if (tp && !(g->xch_ready && c.dtype == TSB200_F16 && c.d <= 4096 && c.d % 4 == 0 && g->tp_peer)) return 1;  // per-operation launches + all-reduce
@@ -767,6 +774,10 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
     g->tp_peer = !(e && e[0] == '0');
     e = getenv("TSB200_STACK");            // "0": one launch per operation instead of the persistent decode-step kernel
     g->use_stack = !(e && e[0] == '0');
+    e = getenv("TSB200_STACK_MAXB");       // tuning knobs for the crossover between the three decode paths
+    if (e) g->stack_cap = atoi(e);
+    e = getenv("TSB200_GEMV_MAXROWS");
+    if (e) g->gemv_rows = atoi(e);
   }
   const TSB200GptConfig& cc = g->c;
   const int64_t d = cc.d, F = cc.F, V = cc.V, Hd = (int64_t)cc.H * cc.hd, KVd = (int64_t)cc.Hkv * cc.hd;
