@@ -605,6 +605,171 @@ __global__ void __launch_bounds__(kAttnThreads) attn_mma_kernel(__half* out, flo
   }
 }
 
+// Causal prefill attention on the warp-level tensor cores (fp16, head_dim 64 / 128, 1, 2, 4 or 8 query heads per KV
+// head).  One CTA = (sequence, KV head, tile of 64 / G query positions): its 64 rows are the (query, head) pairs of
+// the tile, 16 per warp, so the K/V rows of the tile's key range are staged once (cp.async, 64 tokens per stage,
+// chunk-XOR swizzle) for all heads of the group and all queries of the tile — the one-CTA-per-query kernel re-read
+// the whole prefix for every query.  Per 16-key slice a warp does S = Q K^T (mma.sync), the causal mask, an online
+// softmax in fp32 for its 16 rows and O += P V (mma.sync); slices beyond the warp's last query are skipped.
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads) attn_prefill_mma_kernel(__half* out, const __half* q, int64_t q_rs, const __half* cK,
+                                                                        const __half* cV, int S, int H, int Hkv, int T0_arg,
+                                                                        const int* dT0, int Tmax, float scale) {
+  constexpr int RB = HD * 2, CPR = RB / 16, KS = HD / 16, NBO = HD / 8;
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int G = H / Hkv;                       // 1, 2, 4 or 8
+  const int QT = 64 / G;                       // query positions per CTA
+  const int q0 = blockIdx.x * QT, kvh = blockIdx.y, b = blockIdx.z;
+  const int h0 = kvh * G;
+  // this lane's two rows: (query, head) pairs r0 and r0 + 8 of the CTA's 64
+  const int rA = w * 16 + g8, rB = rA + 8;
+  const int qiA = rA / G, gA = rA % G, qiB = rB / G, gB = rB % G;
+  const int sA = q0 + qiA, sB = q0 + qiB;      // query positions (may be >= S in the last tile)
+  const bool liveA = sA < S, liveB = sB < S;
+  const int q_last_cta = min(S, q0 + QT) - 1;  // last live query of the tile
+  const int n_keys = min(T0 + q_last_cta + 1, Tmax);
+  const int w_last_q = min(S - 1, q0 + (w * 16 + 15) / G);   // last query of this warp
+  const int w_keys = min(T0 + w_last_q + 1, Tmax);           // keys this warp needs
+  const size_t stage_bytes = 2 * (size_t)kMmaStageTokens * RB;
+  const __half* Kb = cK + ((int64_t)b * Hkv + kvh) * Tmax * HD;
+  const __half* Vb = cV + ((int64_t)b * Hkv + kvh) * Tmax * HD;
+  const int n_tiles = (max(n_keys, 0) + kMmaStageTokens - 1) / kMmaStageTokens;
+
+  auto issue = [&](int tile) {
+    if (tile < n_tiles) {
+      unsigned char* st = attn_smem + (size_t)(tile % kMmaStages) * stage_bytes;
+      const int t0 = tile * kMmaStageTokens;
+      for (int v = threadIdx.x; v < kMmaStageTokens * CPR; v += kAttnThreads) {
+        const int tt = v / CPR, c = v % CPR;
+        const int t = min(t0 + tt, n_keys - 1);
+        const int pc = (c ^ (tt & 7)) * 16;
+        cp_async_16(st + (size_t)tt * RB + pc, Kb + (int64_t)t * HD + c * 8);
+        cp_async_16(st + (size_t)(kMmaStageTokens + tt) * RB + pc, Vb + (int64_t)t * HD + c * 8);
+      }
+    }
+    cp_async_commit();
+  };
+  for (int i = 0; i < kMmaStages - 1; ++i) issue(i);
+
+  // Q fragments of the two rows: a0 / a2 = row A (k 2*t4.., 8 + 2*t4..), a1 / a3 = row B
+  uint32_t qa[KS][4];
+  {
+    const __half* qpA = q + ((int64_t)b * S + (liveA ? sA : 0)) * q_rs + (int64_t)(h0 + gA) * HD + 2 * t4;
+    const __half* qpB = q + ((int64_t)b * S + (liveB ? sB : 0)) * q_rs + (int64_t)(h0 + gB) * HD + 2 * t4;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qa[ks][0] = liveA ? *reinterpret_cast<const uint32_t*>(qpA + ks * 16) : 0u;
+      qa[ks][1] = liveB ? *reinterpret_cast<const uint32_t*>(qpB + ks * 16) : 0u;
+      qa[ks][2] = liveA ? *reinterpret_cast<const uint32_t*>(qpA + ks * 16 + 8) : 0u;
+      qa[ks][3] = liveB ? *reinterpret_cast<const uint32_t*>(qpB + ks * 16 + 8) : 0u;
+    }
+  }
+  const int limA = liveA ? min(T0 + sA + 1, Tmax) : 0, limB = liveB ? min(T0 + sB + 1, Tmax) : 0;  // keys [0, lim) are visible
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+  float o[NBO][4];
+#pragma unroll
+  for (int nb = 0; nb < NBO; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.0f;
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    issue(tile + kMmaStages - 1);
+    cp_async_wait<kMmaStages - 1>();
+    __syncthreads();
+    const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(attn_smem + (size_t)(tile % kMmaStages) * stage_bytes);
+    const uint32_t vbase = kbase + kMmaStageTokens * RB;
+#pragma unroll 1
+    for (int sl = 0; sl < kMmaStageTokens / 16; ++sl) {
+      const int tw = sl * 16;
+      const int t_first = tile * kMmaStageTokens + tw;
+      if (t_first >= w_keys) break;   // causal: nothing further in this stage is visible to this warp (warp-uniform)
+      float sc[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nb][e] = 0.0f;
+        const int r = tw + nb * 8 + (lane & 7);
+#pragma unroll
+        for (int kp = 0; kp < KS / 2; ++kp) {
+          uint32_t b0, b1, b2, b3;
+          const int c = kp * 4 + (lane >> 3);
+          at_ldmatrix_x4(kbase + r * RB + ((c ^ (r & 7)) << 4), b0, b1, b2, b3);
+          at_mma(sc[nb], qa[2 * kp][0], qa[2 * kp][1], qa[2 * kp][2], qa[2 * kp][3], b0, b1);
+          at_mma(sc[nb], qa[2 * kp + 1][0], qa[2 * kp + 1][1], qa[2 * kp + 1][2], qa[2 * kp + 1][3], b2, b3);
+        }
+      }
+      // scale, causal mask, row maxima (row A: elements 0,1; row B: elements 2,3; keys nb*8 + 2*t4 + e)
+      float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int t = t_first + nb * 8 + 2 * t4 + e;
+          sc[nb][e] = (t < limA) ? sc[nb][e] * scale : -INFINITY;
+          sc[nb][2 + e] = (t < limB) ? sc[nb][2 + e] * scale : -INFINITY;
+          mxA = fmaxf(mxA, sc[nb][e]);
+          mxB = fmaxf(mxB, sc[nb][2 + e]);
+        }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      // a row may see none of these 16 keys: keep its state (no exp(-inf - -inf))
+      const float mnA = fmaxf(mA, mxA), mnB = fmaxf(mB, mxB);
+      const float corrA = (mnA == -INFINITY) ? 1.0f : __expf(mA - mnA), corrB = (mnB == -INFINITY) ? 1.0f : __expf(mB - mnB);
+      float p[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[nb][e] = (mnA == -INFINITY) ? 0.0f : __expf(sc[nb][e] - mnA);
+          p[nb][2 + e] = (mnB == -INFINITY) ? 0.0f : __expf(sc[nb][2 + e] - mnB);
+        }
+      lA = lA * corrA + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+      lB = lB * corrB + (p[0][2] + p[0][3]) + (p[1][2] + p[1][3]);
+      mA = mnA;
+      mB = mnB;
+      __half2 hA0 = __floats2half2_rn(p[0][0], p[0][1]), hB0 = __floats2half2_rn(p[0][2], p[0][3]);
+      __half2 hA1 = __floats2half2_rn(p[1][0], p[1][1]), hB1 = __floats2half2_rn(p[1][2], p[1][3]);
+      const uint32_t pa0 = *reinterpret_cast<uint32_t*>(&hA0), pa1 = *reinterpret_cast<uint32_t*>(&hB0);
+      const uint32_t pa2 = *reinterpret_cast<uint32_t*>(&hA1), pa3 = *reinterpret_cast<uint32_t*>(&hB1);
+      const int vr = tw + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int np = 0; np < NBO / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        const int c = np * 2 + (lane >> 4);
+        at_ldmatrix_x4_trans(vbase + vr * RB + ((c ^ (vr & 7)) << 4), b0, b1, b2, b3);
+        o[2 * np][0] *= corrA; o[2 * np][1] *= corrA; o[2 * np][2] *= corrB; o[2 * np][3] *= corrB;
+        o[2 * np + 1][0] *= corrA; o[2 * np + 1][1] *= corrA; o[2 * np + 1][2] *= corrB; o[2 * np + 1][3] *= corrB;
+        at_mma(o[2 * np], pa0, pa1, pa2, pa3, b0, b1);
+        at_mma(o[2 * np + 1], pa0, pa1, pa2, pa3, b2, b3);
+      }
+    }
+    __syncthreads();  // the stage is overwritten by the copy issued in the next iteration
+  }
+  cp_async_wait<0>();
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+  lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+  const float iA = lA > 0.0f ? 1.0f / lA : 0.0f, iB = lB > 0.0f ? 1.0f / lB : 0.0f;
+  if (liveA) {
+    __half* op = out + (((int64_t)b * S + sA) * H + h0 + gA) * HD + 2 * t4;
+#pragma unroll
+    for (int nb = 0; nb < NBO; ++nb) *reinterpret_cast<__half2*>(op + nb * 8) = __floats2half2_rn(o[nb][0] * iA, o[nb][1] * iA);
+  }
+  if (liveB) {
+    __half* op = out + (((int64_t)b * S + sB) * H + h0 + gB) * HD + 2 * t4;
+#pragma unroll
+    for (int nb = 0; nb < NBO; ++nb) *reinterpret_cast<__half2*>(op + nb * 8) = __floats2half2_rn(o[nb][2] * iB, o[nb][3] * iB);
+  }
+}
+
 template <typename T>
 __global__ void attn_combine_kernel(T* out, const float* part, int hd, int splits) {
   pdl_trigger();
@@ -682,6 +847,26 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
     use_mma = (e && e[0] == '0') ? 0 : 1;
   }
   if constexpr (sizeof(T) == 2) {
+    if (use_mma && S >= 16 && (hd == 64 || hd == 128) && (group == 1 || group == 2 || group == 4 || group == 8)) {
+      // causal prefill on the tensor cores: K/V staged once per tile of 64 / group query positions
+      const size_t sm3 = (size_t)kMmaStages * 2 * kMmaStageTokens * hd * 2;
+      const int QT = 64 / group;
+      dim3 g3((S + QT - 1) / QT, Hkv, B);
+      static bool attr_done2[kMaxDevices] = {};
+      if (!attr_done2[device]) {
+        TSB_CUDA(cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        TSB_CUDA(cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        attr_done2[device] = true;
+      }
+      if (hd == 64)
+        TSB_CUDA(launch_k(attn_prefill_mma_kernel<64>, g3, dim3(kAttnThreads), sm3, s, (__half*)out, (const __half*)q, q_rs, (const __half*)cK,
+                          (const __half*)cV, S, H, Hkv, T0, dT0, Tmax, scale));
+      else
+        TSB_CUDA(launch_k(attn_prefill_mma_kernel<128>, g3, dim3(kAttnThreads), sm3, s, (__half*)out, (const __half*)q, q_rs, (const __half*)cK,
+                          (const __half*)cV, S, H, Hkv, T0, dT0, Tmax, scale));
+      count_launch(device);
+      return check_launch("attention_prefill_mma");
+    }
     if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv && B * Hkv * splits >= 2 * st->sm_count) {
       const size_t sm3 = (size_t)kMmaStages * 2 * kMmaStageTokens * hd * 2;
       dim3 g3(splits, Hkv, B);
