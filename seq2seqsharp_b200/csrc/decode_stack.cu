@@ -391,16 +391,6 @@ int stack_fill_args(StackArgs& a, const StackPlan& p, const StackConfig& c, cons
   a.attn_part = reinterpret_cast<float*>(attn_part);
   a.error_flag = error_flag;
   a.trace = trace;
-  {
-    static int l2 = -1;
-    if (l2 < 0) {
-      const char* e = getenv("TSB200_STACK_L2AHEAD");  // tiles (16 KB) per SM requested into L2 ahead of the ring
-      l2 = e ? atoi(e) : 0;  // measured: asking L2 ahead of the ring slows the stream down, so it is off unless set
-      if (l2 < 0) l2 = 0;
-      if (l2 > 256) l2 = 256;
-    }
-    a.l2_ahead = l2;
-  }
   return 1;
 }
 

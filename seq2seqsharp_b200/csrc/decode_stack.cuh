@@ -26,8 +26,6 @@ struct StackArgs {
   float* attn_part;         // [M*H][kMaxStackSplits][hd + 2]
   int* error_flag;
   long long* trace;         // optional [grid][n_ops][8] timestamps (+ [grid][8] cycle counters of the MMA warp)
-  int l2_ahead;             // tiles the producer requests into L2 ahead of the shared-memory ring (0 = off)
-  int debug;                // profiling experiments (results invalid): 1 = skip the MMAs, 2 = skip window + fence too
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -116,13 +114,9 @@ struct TileCursor {
     return true;
   }
 };
-__device__ __forceinline__ void bulk_prefetch_l2(const void* p, unsigned bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// The weight stream of one CTA (one lane): tiles go through the shared-memory ring in program order; a second
-// cursor runs `l2_ahead` tiles in front and asks L2 for them, so that HBM keeps working for this CTA while its ring is
-// full (consumers waiting on the dependency chain); the ring is then refilled from L2 faster than HBM could.
+// The weight stream of one CTA (one lane): tiles go through the shared-memory ring in program order, across the
+// boundaries of the operations, never waiting for activations.  (Requesting tiles into L2 ahead of the ring was
+// measured and does not help: refilling the ring from L2 is no faster than from HBM.)
 template <typename T>
 __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned char* stage_mem, uint64_t* full, uint64_t* empty,
                                                    volatile int* s_err) {
@@ -130,29 +124,9 @@ __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned 
   int s = 0;
   unsigned round = 0;
   long long issued = 0;
-  TileCursor<T> fetch, ahead;
-  int n_ahead = 0;
-  bool more_ahead = true;
+  TileCursor<T> fetch;
   const unsigned char* src;
   while (fetch.next(a, src)) {
-    // the look-ahead cursor never falls behind the fetch cursor
-    while (more_ahead && n_ahead < 1) {
-      const unsigned char* p;
-      more_ahead = ahead.next(a, p);
-      if (more_ahead) ++n_ahead;
-    }
-    if (round > 0 && a.l2_ahead > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u, 1u)) {
-      // the ring is full (the consumers are in a dependency wait): let HBM work for this CTA meanwhile by asking L2
-      // for the tiles that come next, then block
-      while (more_ahead && n_ahead < a.l2_ahead + 1) {
-        const unsigned char* p;
-        more_ahead = ahead.next(a, p);
-        if (more_ahead) {
-          bulk_prefetch_l2(p, kTileBytes);
-          ++n_ahead;
-        }
-      }
-    }
     if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
       *s_err = 1;
       break;
@@ -161,7 +135,6 @@ __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned 
     mbar_expect_tx(&full[s], kTileBytes);
     bulk_g2s(stage_mem + (size_t)s * kTileBytes, src, kTileBytes, &full[s]);
     ++issued;
-    --n_ahead;
     if (++s == S) {
       s = 0;
       ++round;

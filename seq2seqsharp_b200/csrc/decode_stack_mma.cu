@@ -412,14 +412,6 @@ int launch_decode_stack_mma(int device, DeviceState* st, const StackConfig& c, c
     if (cap >= 2 && cap < stages) stages = cap;
   }
   a.stages = stages;
-  {
-    static int dbg = -1;
-    if (dbg < 0) {
-      const char* e = getenv("TSB200_STACK_DEBUG");  // timing experiments only: results may be wrong when non-zero
-      dbg = e ? atoi(e) : 0;
-    }
-    a.debug = dbg;
-  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kStreamThreads);

@@ -122,19 +122,19 @@ __device__ __forceinline__ void tcs_mma_warp(const StackArgs& a, const TcsSmem& 
       }
       MMA_LAP(cyc_full);
       // B-operand window of this tile: rows 0..7 = sequences (zero beyond M), 32 k values, as 8x16-byte core matrices
-      if (!(a.debug & 2)) {
+      {
         const int r = lane & 7, kc = lane >> 3;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (r < M) v = *reinterpret_cast<const uint4*>(xs + (size_t)r * Kp + kb * kKT + kc * 8);
         *reinterpret_cast<uint4*>(sm.win + (size_t)s * kWinBytes + kc * 256 + r * 16) = v;
       }
-      if (!(a.debug & 2)) ts_fence_async_smem();  // the window was written through the generic proxy, the tensor core reads it through the async proxy
+      ts_fence_async_smem();  // the window was written through the generic proxy, the tensor core reads it through the async proxy
       __syncwarp();
       MMA_LAP(cyc_win);
       const bool seg_end = (kb == g.KB - 1) || (u == u_end - 1);
       if (lane == 0) {
         ts_fence_after();
-        if (!dead && !(a.debug & 1)) {
+        if (!dead) {
           const uint32_t a_base = smem_u32(sm.stage_mem + (size_t)s * kTileBytes);
           const uint32_t b_base = smem_u32(sm.win + (size_t)s * kWinBytes);
 #pragma unroll
@@ -459,14 +459,6 @@ int launch_decode_stack_tc(int device, DeviceState* st, const StackConfig& c, co
   StackArgs a;
   const int r = stack_fill_args(a, p, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace);
   if (r != 1) return r;
-  {
-    static int dbg = -1;
-    if (dbg < 0) {
-      const char* e = getenv("TSB200_STACK_DEBUG");  // timing experiments only: results are wrong when non-zero
-      dbg = e ? atoi(e) : 0;
-    }
-    a.debug = dbg;
-  }
   const size_t fixed = p.union_bytes + 40 * sizeof(uint64_t) + 1024 /* alignment slack */ + 128;
   const size_t budget = 225 * 1024;  // the kernel also has ~1 KB of static shared memory
   const size_t per_stage = (size_t)kTileBytes + kWinBytes;

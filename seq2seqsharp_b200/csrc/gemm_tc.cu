@@ -453,9 +453,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int k_total = (a.K + kBK - 1) / kBK;
-  const int k_per = (k_total + a.ksplit - 1) / a.ksplit;   // k blocks per work item; items of one tile are neighbours in time
-  const int n_total = m_tiles * n_tiles * a.ksplit;
-  __shared__ int s_last;
+  const int n_total = m_tiles * n_tiles;
 
   if (tid == 0) {
     for (int s = 0; s < kP_Stages; ++s) {
@@ -482,8 +480,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const
     // ---------------- TMA producer: runs ahead across tiles
     int it_g = 0;  // k blocks issued so far (ring position)
     for (int t = blockIdx.x; t < n_total && !s_err; t += gridDim.x) {
-      const TcTile tl = tc_tile_of(t / a.ksplit, m_tiles, n_tiles);
-      const int it_begin = (t % a.ksplit) * k_per, it_end = min(k_total, it_begin + k_per);
+      const TcTile tl = tc_tile_of(t, m_tiles, n_tiles);
+      const int it_begin = 0, it_end = k_total;
       const unsigned char* wsrc = a.Wp + ((size_t)tl.n_tile * a.KB) * 16384;
       for (int it = it_begin; it < it_end; ++it, ++it_g) {
         const int s = it_g % kP_Stages, r = it_g / kP_Stages;
@@ -512,7 +510,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t tmem_acc = tmem_base + buf * kP_BN;
-      const int it_begin = (t % a.ksplit) * k_per, it_end = min(k_total, it_begin + k_per);
+      const int it_begin = 0, it_end = k_total;
       for (int it = it_begin; it < it_end; ++it, ++it_g) {
         const int s = it_g % kP_Stages, r = it_g / kP_Stages;
         if (!tc_mbar_wait(&full[s], (unsigned)(r & 1))) {
@@ -541,8 +539,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const
     const int q = w - 4;
     int n_done = 0;
     for (int t = blockIdx.x; t < n_total; t += gridDim.x, ++n_done) {
-      const int tile = t / a.ksplit, ks = t % a.ksplit;
-      const TcTile tl = tc_tile_of(tile, m_tiles, n_tiles);
+      const TcTile tl = tc_tile_of(t, m_tiles, n_tiles);
       const int buf = n_done & 1;
       if (*(volatile int*)&s_err) break;
       if (!__all_sync(0xffffffffu, tc_mbar_wait(&acc_full[buf], (unsigned)((n_done >> 1) & 1)))) {  // warp-uniform outcome
@@ -553,62 +550,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_persistent_kernel(const
       const int row = tl.m_tile * kBM + q * 32 + lane;
       const int n0 = tl.n_tile * kP_BN;
       const bool live = row < a.M;
-      const size_t Npad = (size_t)n_tiles * kP_BN;
 #pragma unroll 1
       for (int c = 0; c < kP_BN; c += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kP_BN + c), v);
         if (!live) continue;
-        if (a.ksplit == 1) {
-          float f[32];
+        float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
-          else tc_finish(a, row, n0 + c, f);
-        } else {
-          // raw partial sums of this k range; the last item of the tile adds the ranges in a fixed order
-          float4* dst = reinterpret_cast<float4*>(a.partials + ((size_t)ks * a.M + row) * Npad + n0 + c);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                 __uint_as_float(v[4 * j + 3]));
-        }
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
+        else tc_finish(a, row, n0 + c, f);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(&acc_empty[buf])) : "memory");
-      }
-      if (a.ksplit > 1) {
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-        if (w == 4 && lane == 0) {
-          const unsigned int prev = atomicAdd(&a.counters[tile], 1u);
-          s_last = (prev == (unsigned int)(a.ksplit - 1));
-          if (s_last) a.counters[tile] = 0u;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (s_last && live) {
-          __threadfence();
-#pragma unroll 1
-          for (int c = 0; c < kP_BN; c += 32) {
-            if (n0 + c >= a.N) break;
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = 0.0f;
-            for (int z = 0; z < a.ksplit; ++z) {
-              const float4* src = reinterpret_cast<const float4*>(a.partials + ((size_t)z * a.M + row) * Npad + n0 + c);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 t4 = __ldcg(src + j);
-                f[4 * j] += t4.x; f[4 * j + 1] += t4.y; f[4 * j + 2] += t4.z; f[4 * j + 3] += t4.w;
-              }
-            }
-            if (a.vec_ok && n0 + c + 32 <= a.N) tc_finish_fast(a, row, n0 + c, f);
-            else tc_finish(a, row, n0 + c, f);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last is rewritten by the next item
       }
     }
   }
@@ -673,13 +629,9 @@ int tc_take_error() {
 int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count) {
   const int64_t tiles = (int64_t)((N + kBN - 1) / kBN) * ((M + kBM - 1) / kBM);
   if (tiles >= 2 * sm_count) return 0;
-  // split-K partials of the persistent kernel (256-column tiles, about three waves of items) or of the 128 x 128 one
-  const int64_t tiles_p = (int64_t)((N + kP_BN - 1) / kP_BN) * ((M + kBM - 1) / kBM);
-  const int64_t ks_p = (3 * sm_count + tiles_p / 2) / tiles_p;
-  const int64_t a = 4096 + kWsCounterBytes + ks_p * M * (int64_t)((N + kP_BN - 1) / kP_BN) * kP_BN * 4;
+  // split-K partials of the 128 x 128 kernel
   const int64_t ks = (2 * sm_count + tiles - 1) / tiles;
-  const int64_t b = 4096 + kWsCounterBytes + ks * M * (int64_t)((N + kBN - 1) / kBN) * kBN * 4;
-  return a > b ? a : b;
+  return 4096 + kWsCounterBytes + ks * M * (int64_t)((N + kBN - 1) / kBN) * kBN * 4;
 }
 
 int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
@@ -720,32 +672,13 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
     static int pers = -1;
     if (pers < 0) {
       const char* e = getenv("TSB200_TC_PERSISTENT");  // "0": one 128 x 128 tile per CTA for every M (A/B measurements)
-      pers = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
+      pers = (e && e[0] == '0') ? 0 : 1;
     }
     const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + kP_BN - 1) / kP_BN;
-    const int tiles = m_tiles * n_tiles, k_total = (K + kBK - 1) / kBK;
-    // few tiles (decode-sized M): split K so that about three waves of work items keep every SM streaming weights
-    // (measured slower than the 128 x 128 kernel's split-K at M = 64, so it is only taken when TSB200_TC_PERSISTENT=2)
-    int ks = 1;
-    if (tiles < st->sm_count && ws && pers == 2) {
-      ks = (3 * st->sm_count + tiles / 2) / tiles;
-      if (ks > k_total / 4) ks = k_total / 4;
-      const int64_t cnt = kWsCounterBytes;
-      const int64_t per = (int64_t)M * n_tiles * kP_BN * 4;
-      if (ks > 1 && cnt + ks * per > ws_bytes) ks = (int)((ws_bytes - cnt) / per);
-      if (ks > 1) {
-        const int k_per = (k_total + ks - 1) / ks;
-        ks = (k_total + k_per - 1) / k_per;  // no empty range
-      }
-      if (ks < 1) ks = 1;
-      if (ks > 1) {
-        a.counters = reinterpret_cast<unsigned int*>(ws);
-        a.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + cnt);
-      }
-    }
-    if (pers && tiles * ks >= st->sm_count) {
-      a.ksplit = ks;
-      int g = st->sm_count < tiles * ks ? st->sm_count : tiles * ks;
+    const int tiles = m_tiles * n_tiles;
+    if (pers && tiles >= st->sm_count) {
+      a.ksplit = 1;
+      int g = st->sm_count;
       const size_t smem_p = kP_Stages * (kP_ABytes + kP_BBytes) + 1024 + 256;
       gemm_tc_persistent_kernel<<<g, kTcThreads, smem_p, s>>>(mapA, a, m_tiles, n_tiles);
       count_launch(device);
