@@ -50,6 +50,11 @@ __device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
 __device__ __forceinline__ void red_release_add_sys(unsigned* p, unsigned v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// fence.sys by the caller + this relaxed add form a release pattern; used when one thread per peer signals, so that the
+// fences (each waits for the peer stores to be acknowledged over NVLink) run side by side instead of one after another
+__device__ __forceinline__ void red_relaxed_add_sys(unsigned* p, unsigned v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ bool poll_count_sys(const unsigned* p, unsigned want, unsigned limit, const int* err) {
   for (unsigned i = 0; i < limit; ++i) {
     unsigned v;

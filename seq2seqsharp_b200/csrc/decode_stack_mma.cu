@@ -243,14 +243,16 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       }
     }
     consumers_sync();  // red is reused by the next segment; the release below publishes the epilogue stores
-    if (finish && tid == 0) {
-      if (xchg) {
-        // one arrival per finished column tile on every rank's counter of this operation (system scope: the stores
-        // above went to other GPUs' memory)
-        for (int r = 0; r < a.c.tp_size; ++r) red_release_add_sys(reinterpret_cast<unsigned*>(a.c.peer[r]) + op_i, 1u);
-      } else {
-        red_release_add(&a.done[op_i * kDoneStride], 1u);
+    if (finish && xchg) {
+      // one arrival per finished column tile on every rank's counter of this operation, signalled by one thread per
+      // rank: system-scope fence (the stores above went to other GPUs' memory; the barrier makes the fence cumulative
+      // over the CTA's stores), then a relaxed add on that rank's counter
+      if (tid < a.c.tp_size) {
+        __threadfence_system();
+        red_relaxed_add_sys(reinterpret_cast<unsigned*>(a.c.peer[tid]) + op_i, 1u);
       }
+    } else if (finish && tid == 0) {
+      red_release_add(&a.done[op_i * kDoneStride], 1u);
     }
     seg_begin = u + 1;
   }
