@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(1024) norm_kernel(TH* __restrict__ h, TX* __re
                                                     int64_t h_row_stride) {
   extern __shared__ float row[];
   __shared__ float red[32];
+  pdl_trigger();  // chained launches of a decode step: let the next kernel become resident,
+  pdl_wait();     // and read the rows only after the previous kernel has completed
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     TX* xr = x + (int64_t)r * x_row_stride;
     TH* hr = h + (int64_t)r * h_row_stride;
@@ -110,11 +112,11 @@ int launch_norm_residual(int device, DeviceState* st, int dtype, void* h, float*
   const int g = M < st->sm_count * 8 ? M : st->sm_count * 8;
   const int th = norm_threads(d);
   if (dtype == TSB200_F32)
-    norm_kernel<float, float, true><<<g, th, d * sizeof(float), s>>>((float*)h, x, (const float*)delta, (const float*)gamma,
-                                                                   (const float*)beta, norm_type, eps, M, d, d, d);
+    TSB_CUDA(launch_k(norm_kernel<float, float, true>, dim3(g), dim3(th), d * sizeof(float), s, (float*)h, x, (const float*)delta,
+                      (const float*)gamma, (const float*)beta, norm_type, eps, M, d, (int64_t)d, (int64_t)d));
   else
-    norm_kernel<float, __half, true><<<g, th, d * sizeof(float), s>>>((__half*)h, x, (const __half*)delta, (const __half*)gamma,
-                                                                    (const __half*)beta, norm_type, eps, M, d, d, d);
+    TSB_CUDA(launch_k(norm_kernel<float, __half, true>, dim3(g), dim3(th), d * sizeof(float), s, (__half*)h, x, (const __half*)delta,
+                      (const __half*)gamma, (const __half*)beta, norm_type, eps, M, d, (int64_t)d, (int64_t)d));
   count_launch(device);
   return check_launch("norm_residual");
 }
