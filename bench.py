@@ -331,6 +331,27 @@ def run_b200(args):
         "kernel_classes_ms_per_step": {k: v[0] / n_prof for k, v in prof.items()},
         "host_wall_ms_per_step": 1e3 * t_wall / K,
     }
+    if world == 1 and not tp and S >= 16:
+        # outside the timed region: a request whose prompt head is parked (restore + run the rest) against the full prefill
+        head = S - 32 if S > 64 else S // 2
+        gpt.Reset()
+        gpt.Prefill(prompt[:, :head], opts)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        snap = gpt.CacheSnapshot()
+        torch.cuda.synchronize()
+        snap_ms = 1e3 * (time.perf_counter() - t0)
+        gpt.Reset()
+        t0 = time.perf_counter()
+        gpt.CacheRestore(snap)
+        torch.cuda.synchronize()
+        restore_ms = 1e3 * (time.perf_counter() - t0)
+        gpt.Extend(prompt[:, head:], opts)
+        ext_ms, _ = gpt.LastTiming()
+        line["cache_reuse"] = {"cached_tokens": head, "suffix_tokens": S - head, "snapshot_bytes": snap.nbytes,
+                               "snapshot_ms_wall": snap_ms, "restore_ms_wall": restore_ms, "suffix_ms": ext_ms,
+                               "full_prefill_ms": prefill_ms}
+        snap.close()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cpu_oracle as O
         thr = O.max_threads()

@@ -329,6 +329,21 @@ TSB200_API int TSB200_GptDecode(void* gpt, int n_steps, const TSB200DecodingOpti
 /* logits [B,V] / probs [B,V] (F32, host) of the most recent step */
 TSB200_API int TSB200_GptGetLogits(void* gpt, float* logits, float* probs);
 TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);
+/* Prompt suffix on top of a non-empty cache: ids [B,S] host int32 are the text from position T (the cache length)
+ * on; they are appended to the cache (causal attention over T + S positions) and the next id per sequence is
+ * sampled into out_ids [B].  With S = 1 and the pending id this is Decoder.GPTDecode's cached branch
+ * (Decoder.cs:661-678); with S > 1 it serves a request whose prompt starts with an already cached text. */
+TSB200_API int TSB200_GptExtend(void* gpt, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt,
+                                int32_t* out_ids);
+/* Parking a KV cache between calls (the MemoryCache entries of GPT.cs:236-247 and :312-328, which keep every
+ * layer's K/V tensors under the text they belong to): Snapshot copies rows [0,T) of every layer, the token
+ * history and the pending id into a compact device buffer; Restore writes them into an engine of the same model
+ * (B_new = 0: the parked batch; a snapshot of ONE sequence may serve B_new > 1 slots, e.g. a shared system prompt);
+ * Info returns the sizes and, if tokens != NULL, the [B, T+1] token ids (cached text + pending id). */
+TSB200_API int TSB200_GptCacheSnapshot(void* gpt, void** snapshot);
+TSB200_API int TSB200_GptCacheSnapshotInfo(void* snapshot, int* B, int* T, int64_t* bytes, int32_t* tokens);
+TSB200_API int TSB200_GptCacheRestore(void* gpt, void* snapshot, int B_new);
+TSB200_API int TSB200_GptCacheSnapshotFree(void* snapshot);
 /* device-timed duration (ms, CUDA events on the engine's stream) of the last GptDecode / GptPrefill call and
  * the number of kernel launches it issued (graph replays count their nodes) */
 TSB200_API int TSB200_GptLastTiming(void* gpt, float* ms, int64_t* launches);

@@ -137,6 +137,11 @@ def lib():
         "TSB200_GptDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), i32, vp, C.POINTER(i32)]),
         "TSB200_GptGetLogits": (i32, [vp, vp, vp]),
         "TSB200_GptCacheLength": (i32, [vp, C.POINTER(i32)]),
+        "TSB200_GptExtend": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
+        "TSB200_GptCacheSnapshot": (i32, [vp, C.POINTER(vp)]),
+        "TSB200_GptCacheSnapshotInfo": (i32, [vp, C.POINTER(i32), C.POINTER(i32), C.POINTER(i64), vp]),
+        "TSB200_GptCacheRestore": (i32, [vp, vp, i32]),
+        "TSB200_GptCacheSnapshotFree": (i32, [vp]),
         "TSB200_GptLastTiming": (i32, [vp, C.POINTER(f32), C.POINTER(i64)]),
         "TSB200_GptStream": (i32, [vp, C.POINTER(vp)]),
         "TSB200_GptStepHost": (i32, [vp, vp, C.POINTER(DecodingOptionsC), vp]),

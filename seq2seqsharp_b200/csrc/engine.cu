@@ -1031,14 +1031,21 @@ int TSB200_GptReset(void* h) {
   return 1;
 }
 
-int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
-  Gpt* g = (Gpt*)h;
-  TSB_CHECK(g && ids && opt, "gpt_prefill: null argument");
+}  // extern "C"
+
+// Runs S prompt tokens per sequence through the stack on top of T0 = g->T cached positions (0: a fresh prompt;
+// > 0: the suffix of a prompt whose first T0 tokens are already cached), samples the next id.
+static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids, bool extend) {
   const TSB200GptConfig& c = g->c;
-  TSB_TRY(use_device(c.device, nullptr));
-  TSB_CHECK(g->T == 0, "gpt_prefill: the cache is not empty (call TSB200_GptReset first)");
-  TSB_CHECK(B > 0 && B <= c.max_batch, "gpt_prefill: batch %d exceeds capacity %d", B, c.max_batch);
-  TSB_CHECK(S > 0 && S < c.max_tokens, "OOM: prompt of %d tokens exceeds the KV-cache capacity %d", S, c.max_tokens);
+  const int T0 = g->T;
+  if (extend) {
+    TSB_CHECK(T0 > 0 && g->B > 0, "gpt_extend: nothing is cached (prefill or restore a snapshot first)");
+    TSB_CHECK(B == g->B, "gpt_extend: batch %d differs from the cached batch %d", B, g->B);
+  } else {
+    TSB_CHECK(T0 == 0, "gpt_prefill: the cache is not empty (call TSB200_GptReset first)");
+    TSB_CHECK(B > 0 && B <= c.max_batch, "gpt_prefill: batch %d exceeds capacity %d", B, c.max_batch);
+  }
+  TSB_CHECK(S > 0 && T0 + S < c.max_tokens, "OOM: prompt of %d tokens exceeds the KV-cache capacity %d", T0 + S, c.max_tokens);
   for (int64_t i = 0; i < (int64_t)B * S; ++i) TSB_CHECK(ids[i] >= 0 && ids[i] < c.V, "gpt_prefill: token id %d out of range", ids[i]);
   TSB_TRY(ensure_act(g, (int64_t)B * S));
   void* ids_dev = nullptr;
@@ -1048,31 +1055,48 @@ int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200Dec
   do {
     if (cudaMemcpyAsync(ids_dev, ids, (size_t)B * S * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: id upload failed"); break; }
     // history = the prompt (the reference passes the whole sequence as decodedSequence: Decoder.cs:761)
-    if (cudaMemcpy2DAsync(g->hist, (size_t)c.max_tokens * 4, ids_dev, (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history copy failed"); break; }
-    std::vector<int> lens(B, S);
+    //  an extension overwrites the pending id at position T0: the caller's tokens are the text from there on
+    if (cudaMemcpy2DAsync(g->hist + T0, (size_t)c.max_tokens * 4, ids_dev, (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history copy failed"); break; }
+    std::vector<int> lens(B, T0 + S);
     if (cudaMemcpyAsync(g->hist_len, lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history length upload failed"); break; }
     cudaStreamSynchronize(g->s);
     g->B = B;
-    g->step = 0;
+    if (!extend) g->step = 0;
     if (!(ok = upload_blocked(g, opt))) break;
     if (!(ok = set_state(g, 0))) break;
     const long long l0 = g->st->launches;
     cudaEventRecord(g->ev0, g->s);
-    if (!(ok = enqueue_forward(g, B, S, 0, false, 1))) break;
-    g->T = S;
+    if (!(ok = enqueue_forward(g, B, S, T0, false, 1))) break;
+    g->T = T0 + S;
     if (!(ok = enqueue_sample(g, B, opt, true, false))) break;
     cudaEventRecord(g->ev1, g->s);
     if (cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: %s", cudaGetErrorString(cudaGetLastError())); break; }
     cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1);
     if (!(ok = check_err_flag(g))) break;
     g->last_launches = g->st->launches - l0;
-    g->step = 1;
+    g->step += 1;
     g->probs_valid = (opt->strategy == 1);
     if (out_ids && cudaMemcpy(out_ids, g->out_dev, (size_t)B * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: id download failed"); break; }
   } while (0);
   g->ids_in = nullptr;
   cudaFree(ids_dev);
   return ok;
+}
+
+extern "C" {
+
+int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ids && opt, "gpt_prefill: null argument");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  return run_prompt(g, ids, B, S, opt, out_ids, false);
+}
+
+int TSB200_GptExtend(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ids && opt, "gpt_extend: null argument");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  return run_prompt(g, ids, B, S, opt, out_ids, true);
 }
 
 int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int stop_on_eos, int32_t* out_ids, int* steps_done) {
@@ -1158,6 +1182,119 @@ int TSB200_GptCacheLength(void* h, int* T) {
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && T, "gpt_cache_length: null argument");
   *T = g->T;
+  return 1;
+}
+
+}  // extern "C"
+
+// A parked KV cache: rows [0, T) of every layer's K and V for B sequences, compacted, plus what a later call needs
+// to continue the text (token history, the pending id, the sampling step counter).
+struct GptSnapshot {
+  int device = 0, B = 0, T = 0, L = 0, Hkv = 0, hd = 0, es = 0;
+  uint32_t step = 0;
+  void* kv = nullptr;          // [L][2][B * Hkv][T * hd] elements
+  size_t bytes = 0;
+  std::vector<int> hist;       // [B][T + 1]: the cached tokens and the pending one
+  std::vector<int> pending;    // [B]
+};
+
+extern "C" {
+
+int TSB200_GptCacheSnapshot(void* h, void** snap_out) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && snap_out, "gpt_cache_snapshot: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(g->T > 0 && g->B > 0, "gpt_cache_snapshot: nothing is cached");
+  GptSnapshot* sn = new GptSnapshot();
+  sn->device = c.device; sn->B = g->B; sn->T = g->T; sn->L = c.L; sn->Hkv = c.Hkv; sn->hd = c.hd; sn->es = g->es;
+  sn->step = g->step;
+  const size_t row = (size_t)sn->T * c.hd * g->es, pitch = (size_t)c.max_tokens * c.hd * g->es;
+  const size_t rows = (size_t)sn->B * c.Hkv;
+  sn->bytes = (size_t)c.L * 2 * rows * row;
+  auto fail = [&]() { if (sn->kv) cudaFree(sn->kv); delete sn; return 0; };
+  if (cudaMalloc(&sn->kv, sn->bytes) != cudaSuccess) {
+    cudaGetLastError();
+    set_last_error("OOM: gpt_cache_snapshot could not allocate %zu bytes", sn->bytes);
+    return fail();
+  }
+  for (int k = 0; k < c.L; ++k)
+    for (int w = 0; w < 2; ++w) {
+      unsigned char* dst = (unsigned char*)sn->kv + ((size_t)k * 2 + w) * rows * row;
+      const void* src = w == 0 ? g->L[k].cK : g->L[k].cV;
+      if (cudaMemcpy2DAsync(dst, row, src, pitch, row, rows, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) {
+        set_last_error("gpt_cache_snapshot: cache copy failed");
+        return fail();
+      }
+    }
+  sn->hist.assign((size_t)sn->B * (sn->T + 1), 0);
+  sn->pending.assign(sn->B, 0);
+  if (cudaMemcpy2DAsync(sn->hist.data(), (size_t)(sn->T + 1) * 4, g->hist, (size_t)c.max_tokens * 4, (size_t)(sn->T + 1) * 4, sn->B,
+                        cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
+      cudaMemcpyAsync(sn->pending.data(), g->ids_cur, (size_t)sn->B * 4, cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
+      cudaStreamSynchronize(g->s) != cudaSuccess) {
+    set_last_error("gpt_cache_snapshot: %s", cudaGetErrorString(cudaGetLastError()));
+    return fail();
+  }
+  *snap_out = sn;
+  return 1;
+}
+
+int TSB200_GptCacheSnapshotInfo(void* snap, int* B, int* T, int64_t* bytes, int32_t* tokens) {
+  GptSnapshot* sn = (GptSnapshot*)snap;
+  TSB_CHECK(sn, "gpt_cache_snapshot_info: null snapshot");
+  if (B) *B = sn->B;
+  if (T) *T = sn->T;
+  if (bytes) *bytes = (int64_t)sn->bytes;
+  if (tokens) std::memcpy(tokens, sn->hist.data(), sn->hist.size() * 4);
+  return 1;
+}
+
+int TSB200_GptCacheSnapshotFree(void* snap) {
+  GptSnapshot* sn = (GptSnapshot*)snap;
+  if (!sn) return 1;
+  TSB_TRY(use_device(sn->device, nullptr));
+  if (sn->kv) cudaFree(sn->kv);
+  delete sn;
+  return 1;
+}
+
+int TSB200_GptCacheRestore(void* h, void* snap, int B_new) {
+  Gpt* g = (Gpt*)h;
+  GptSnapshot* sn = (GptSnapshot*)snap;
+  TSB_CHECK(g && sn, "gpt_cache_restore: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(sn->device == c.device && sn->L == c.L && sn->Hkv == c.Hkv && sn->hd == c.hd && sn->es == g->es,
+            "gpt_cache_restore: the snapshot was taken from a different model or device");
+  if (B_new <= 0) B_new = sn->B;
+  TSB_CHECK(B_new == sn->B || sn->B == 1, "gpt_cache_restore: a snapshot of %d sequences cannot serve %d", sn->B, B_new);
+  TSB_CHECK(B_new <= c.max_batch, "gpt_cache_restore: batch %d exceeds capacity %d", B_new, c.max_batch);
+  TSB_CHECK(sn->T < c.max_tokens, "OOM: snapshot of %d tokens exceeds the KV-cache capacity %d", sn->T, c.max_tokens);
+  const size_t row = (size_t)sn->T * c.hd * g->es, pitch = (size_t)c.max_tokens * c.hd * g->es;
+  const size_t rows = (size_t)sn->B * c.Hkv;
+  const int copies = (B_new == sn->B) ? 1 : B_new;  // one sequence parked, many served: the rows go to every slot
+  for (int k = 0; k < c.L; ++k)
+    for (int w = 0; w < 2; ++w) {
+      const unsigned char* src = (const unsigned char*)sn->kv + ((size_t)k * 2 + w) * rows * row;
+      unsigned char* dst = (unsigned char*)(w == 0 ? g->L[k].cK : g->L[k].cV);
+      for (int r = 0; r < copies; ++r)
+        TSB_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * c.Hkv * pitch, pitch, src, row, row, rows, cudaMemcpyDeviceToDevice, g->s));
+    }
+  std::vector<int> lens(B_new, sn->T + 1), pend(B_new);
+  for (int b = 0; b < B_new; ++b) {
+    const int sb = (B_new == sn->B) ? b : 0;
+    pend[b] = sn->pending[sb];
+    TSB_CUDA(cudaMemcpyAsync(g->hist + (size_t)b * c.max_tokens, sn->hist.data() + (size_t)sb * (sn->T + 1), (size_t)(sn->T + 1) * 4,
+                             cudaMemcpyHostToDevice, g->s));
+  }
+  TSB_CUDA(cudaMemcpyAsync(g->hist_len, lens.data(), (size_t)B_new * 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaMemcpyAsync(g->ids_cur, pend.data(), (size_t)B_new * 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));  // lens / pend are on the stack
+  g->B = B_new;
+  g->T = sn->T;
+  g->step = sn->step;
+  g->probs_valid = false;
   return 1;
 }
 

@@ -319,6 +319,30 @@ class GPT:
         rest = self.Decode(n_new - 1, decodingOptions, stop_on_eos=stop_on_eos)
         return np.concatenate([first[:, None], rest], axis=1)
 
+    def Extend(self, tokens, opts: DecodingOptions):
+        """tokens [B, S]: the text from the cache length on (the suffix of a prompt whose head is cached).  Appends
+        them to the cache and returns the next id per sequence."""
+        ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        if ids.ndim != 2:
+            raise ValueError("tokens must be [batch, suffix_len]")
+        B, S = ids.shape
+        out = np.zeros(B, dtype=np.int32)
+        c = self._opts(opts)
+        N.call("TSB200_GptExtend", self._h, ids.ctypes.data_as(C.c_void_p), B, S, C.byref(c),
+               out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def CacheSnapshot(self) -> "KvSnapshot":
+        """Parks the cache (every layer's K/V rows, the token history, the pending id) in a device buffer."""
+        h = C.c_void_p()
+        N.call("TSB200_GptCacheSnapshot", self._h, C.byref(h))
+        return KvSnapshot(h)
+
+    def CacheRestore(self, snap: "KvSnapshot", batch: int = 0):
+        """Writes a parked cache back; `batch` > 1 with a one-sequence snapshot serves every slot from it."""
+        N.call("TSB200_GptCacheRestore", self._h, snap._h, int(batch))
+        self._B = batch if batch > 0 else snap.B
+
     def StepHost(self, last_ids, opts: DecodingOptions):
         """One decode step with host buffers: ids in -> ids out (what the reference does per token)."""
         ids = np.ascontiguousarray(last_ids, dtype=np.int32)
@@ -375,3 +399,116 @@ class GPT:
         b = C.c_int64(0)
         N.call("TSB200_GptStepBytes", self._h, B, T, C.byref(b))
         return b.value
+
+
+class KvSnapshot:
+    """Handle of a parked KV cache (device memory); `tokens` [B, T+1] = cached text + the pending id."""
+
+    def __init__(self, handle):
+        self._h = handle
+        B, T, nbytes = C.c_int(0), C.c_int(0), C.c_int64(0)
+        N.call("TSB200_GptCacheSnapshotInfo", self._h, C.byref(B), C.byref(T), C.byref(nbytes), None)
+        self.B, self.T, self.nbytes = B.value, T.value, nbytes.value
+        self.tokens = np.zeros((self.B, self.T + 1), dtype=np.int32)
+        N.call("TSB200_GptCacheSnapshotInfo", self._h, None, None, None, self.tokens.ctypes.data_as(C.c_void_p))
+
+    def close(self):
+        if self._h is not None:
+            N.call("TSB200_GptCacheSnapshotFree", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class KvCachePool:
+    """The reference parks the K/V tensors of a finished call in MemoryCache.Default under the call's text for ten
+    minutes and picks them up when the next request's text equals that key (GPT.cs:153-173 key, :236-247 lookup,
+    :312-328 store).  Here the key is the token-id text itself (ids 0 = </s> dropped, as GenerateCacheKey drops
+    "</s>"), entries are device snapshots, and a lookup also accepts an entry whose cached tokens are a proper
+    prefix of the request (the longest one wins), so a shared prompt head is computed once."""
+
+    def __init__(self, ttl_seconds: float = 600.0, max_bytes: int = 8 << 30, clock=None):
+        import time
+        self._clock = clock or time.monotonic
+        self.ttl, self.max_bytes = float(ttl_seconds), int(max_bytes)
+        self._entries: Dict[tuple, tuple] = {}  # key -> (snapshot, expiry)
+        self.hits = self.misses = 0
+
+    @staticmethod
+    def key_of(tokens) -> tuple:
+        return tuple(int(t) for t in np.asarray(tokens).reshape(-1) if int(t) != 0)
+
+    def _expire(self):
+        now = self._clock()
+        for k in [k for k, (_, exp) in self._entries.items() if exp <= now]:
+            self._entries.pop(k)[0].close()
+
+    @property
+    def nbytes(self):
+        return sum(sn.nbytes for sn, _ in self._entries.values())
+
+    def __len__(self):
+        self._expire()
+        return len(self._entries)
+
+    def put(self, snap: KvSnapshot):
+        """Stores a one-sequence snapshot under its text; the oldest entries leave when the byte budget is exceeded."""
+        if snap.B != 1:
+            raise ValueError("the pool keeps one sequence per entry")
+        self._expire()
+        key = self.key_of(snap.tokens[0])
+        old = self._entries.pop(key, None)
+        if old:
+            old[0].close()
+        self._entries[key] = (snap, self._clock() + self.ttl)
+        while self.nbytes > self.max_bytes and len(self._entries) > 1:
+            k = min(self._entries, key=lambda k: self._entries[k][1])
+            self._entries.pop(k)[0].close()
+
+    def take(self, prompt) -> Optional[KvSnapshot]:
+        """Removes and returns the entry that covers the longest head of `prompt` (the reference removes a hit from
+        the cache, GPT.cs:245), or None.  An entry qualifies if its T cached tokens equal prompt[:T] and T < len(prompt)."""
+        self._expire()
+        p = [int(t) for t in np.asarray(prompt).reshape(-1)]
+        best = None
+        for k, (sn, _) in self._entries.items():
+            T = sn.T
+            if T < len(p) and [int(t) for t in sn.tokens[0, :T]] == p[:T] and (best is None or T > self._entries[best][0].T):
+                best = k
+        if best is None:
+            self.misses += 1
+            return None
+        self.hits += 1
+        return self._entries.pop(best)[0]
+
+    def clear(self):
+        for sn, _ in self._entries.values():
+            sn.close()
+        self._entries.clear()
+
+
+def generate_with_pool(gpt: "GPT", pool: KvCachePool, prompt, opts: DecodingOptions, stop_on_eos: bool = True):
+    """One request of one sequence through the pool: prompt [S] -> generated ids [n] (n <= MaxTgtSentLength - S),
+    the loop of GPT.RunForwardOnSingleDevice (GPT.cs:212-335) with UseKVCache: a parked cache that covers a head of
+    the prompt is restored and only the rest of the prompt is run; the cache is parked again afterwards."""
+    p = np.asarray(prompt, dtype=np.int32).reshape(-1)
+    n_new = opts.MaxTgtSentLength - len(p)
+    if n_new <= 0:
+        return np.zeros(0, dtype=np.int32)
+    gpt.Reset()
+    snap = pool.take(p)
+    if snap is not None:
+        gpt.CacheRestore(snap)
+        first = gpt.Extend(p[None, snap.T:], opts)
+        snap.close()
+    else:
+        first = gpt.Prefill(p[None, :], opts)
+    out = first[:, None]
+    if n_new > 1 and not (stop_on_eos and int(first[0]) == 0):
+        out = np.concatenate([out, gpt.Decode(n_new - 1, opts, stop_on_eos=stop_on_eos)], axis=1)
+    pool.put(gpt.CacheSnapshot())
+    return out[0]
