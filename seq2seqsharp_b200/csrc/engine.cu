@@ -388,6 +388,8 @@ static int ensure_act(Gpt* g, int64_t rows) {
   if (rows <= g->act_rows) return 1;
   const TSB200GptConfig& c = g->c;
   TSB_CUDA(cudaStreamSynchronize(g->s));
+  // the captured decode step holds the old buffers as kernel arguments
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   auto re = [&](void** p, int64_t bytes) -> int {
     if (*p) {
       for (auto& a : g->allocs) if (a == *p) a = nullptr;

@@ -28,7 +28,7 @@ def test_restored_cache_continues_bit_exactly(cuda, case):
     cfg, w, prompt, opts, max_pos = case_inputs(case)
     B, S = prompt.shape
     n1, n2 = 5, 6
-    gpt = GPT(cfg, max_batch=B, max_tokens=S + n1 + n2 + 4)
+    gpt = GPT(cfg, max_batch=B, max_tokens=opts.MaxTgtSentLength + 2)   # the APE table of the case has max_tokens + 2 rows
     gpt.LoadWeights(w)
     gpt.Reset()
     gpt.Prefill(prompt, opts)
@@ -65,7 +65,7 @@ def test_prompt_suffix_on_cached_head_matches_oracle(cuda, oracle, case, suffix)
     orc.reset()
     orc.step(prompt[:, :k], temp, opts.BlockedTokens)
     lo, po = orc.step(prompt[:, k:], temp, opts.BlockedTokens)
-    gpt = GPT(cfg, max_batch=B, max_tokens=S + 8)
+    gpt = GPT(cfg, max_batch=B, max_tokens=opts.MaxTgtSentLength + 2)
     gpt.LoadWeights(w)
     gpt.Reset()
     gpt.Prefill(prompt[:, :k], opts)
@@ -96,7 +96,7 @@ def test_one_parked_sequence_serves_a_batch(cuda, oracle):
     head = prompt[:1, :10]
     B = 3
     tails = prompt_ids(SEED + 7, B, 5, cfg.V)
-    gpt = GPT(cfg, max_batch=B, max_tokens=32)
+    gpt = GPT(cfg, max_batch=B, max_tokens=opts.MaxTgtSentLength + 2)
     gpt.LoadWeights(w)
     gpt.Reset()
     gpt.Prefill(head, opts)
@@ -123,7 +123,7 @@ def test_pool_round_trip_like_the_reference_cache(cuda):
     import dataclasses
     p1 = prompt[0]
     o1 = dataclasses.replace(opts, MaxTgtSentLength=len(p1) + 6)
-    gpt = GPT(cfg, max_batch=1, max_tokens=len(p1) + 24)
+    gpt = GPT(cfg, max_batch=1, max_tokens=opts.MaxTgtSentLength + 2)
     gpt.LoadWeights(w)
     pool = KvCachePool()
     out1 = generate_with_pool(gpt, pool, p1, o1, stop_on_eos=False)
@@ -177,3 +177,23 @@ def test_errors(cuda):
     other.close()
     snap.close()
     gpt.close()
+
+
+def test_longer_prompt_on_a_used_engine(cuda):
+    """A second request with a longer prompt grows the activation buffers; the captured decode step must follow."""
+    import dataclasses
+    case = CASES[0]
+    cfg, w, prompt, opts, max_pos = case_inputs(case)
+    long_p = prompt[:, :12]
+    short_p = prompt[:, :5]
+    o = dataclasses.replace(opts, MaxTgtSentLength=20)
+    used = GPT(cfg, max_batch=1, max_tokens=opts.MaxTgtSentLength + 2)
+    used.LoadWeights(w)
+    used.RunForwardOnSingleDevice(short_p, o, stop_on_eos=False)
+    got = used.RunForwardOnSingleDevice(long_p, o, stop_on_eos=False)
+    used.close()
+    fresh = GPT(cfg, max_batch=1, max_tokens=opts.MaxTgtSentLength + 2)
+    fresh.LoadWeights(w)
+    want = fresh.RunForwardOnSingleDevice(long_p, o, stop_on_eos=False)
+    fresh.close()
+    np.testing.assert_array_equal(got, want)
