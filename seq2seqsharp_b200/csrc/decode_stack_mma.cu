@@ -114,44 +114,101 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       pre_r[sg] = 0.0f;
     }
   }
-  for (int u = u_begin; u < u_end; ++u) {
+  // Per-lane constants of the tile loop: byte offsets of this lane's four ldmatrix rows inside a stage
+  // (k half kk, 16-column block cb), shared-memory addresses of the ring.
+  uint32_t loff[2][2];
+#pragma unroll
+  for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb) {
+      const int k = kk * 16 + lrow, unit = hf * 4 + cb * 2 + lunit;
+      loff[kk][cb] = (uint32_t)(chunk * 4096 + k * 128 + ((unit ^ (k & 7)) << 4));
+    }
+  const uint32_t stage0 = smem_u32(stage_mem);
+  // kk = 0 and kk = 1 accumulate separately (two independent mma chains per column block), summed at the segment end
+  float d2[2][4];
+#pragma unroll
+  for (int cb = 0; cb < 2; ++cb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d2[cb][e] = 0.0f;
+  // one tile: 4 shared loads of the activation fragments, 4 ldmatrix, 4 mma
+  auto eat = [&](uint32_t sbase, const __half* xp) {
+    uint32_t b00 = 0u, b01 = 0u, b10 = 0u, b11 = 0u;
+    if (row_live) {
+      b00 = *reinterpret_cast<const uint32_t*>(xp);
+      b01 = *reinterpret_cast<const uint32_t*>(xp + 8);
+      b10 = *reinterpret_cast<const uint32_t*>(xp + 16);
+      b11 = *reinterpret_cast<const uint32_t*>(xp + 24);
+    }
+    uint32_t f0[4], f1[4], f2[4], f3[4];
+    mm_ldmatrix_x4_trans(sbase + loff[0][0], f0[0], f0[1], f0[2], f0[3]);
+    mm_ldmatrix_x4_trans(sbase + loff[0][1], f1[0], f1[1], f1[2], f1[3]);
+    mm_ldmatrix_x4_trans(sbase + loff[1][0], f2[0], f2[1], f2[2], f2[3]);
+    mm_ldmatrix_x4_trans(sbase + loff[1][1], f3[0], f3[1], f3[2], f3[3]);
+    mm_mma_16816(d[0], f0[0], f0[1], f0[2], f0[3], b00, b01);
+    mm_mma_16816(d[1], f1[0], f1[1], f1[2], f1[3], b00, b01);
+    mm_mma_16816(d2[0], f2[0], f2[1], f2[2], f2[3], b10, b11);
+    mm_mma_16816(d2[1], f3[0], f3[1], f3[2], f3[3], b10, b11);
+  };
+  int un = u_begin;  // next tile
+  while (un < u_end) {
+    // this CTA's share of column tile ct: n tiles, eaten two at a time (the loop carries no segment logic)
+    const int n = min(u_end - un, KB - kb);
+    const __half* xp = xrow + (size_t)(slice ? (un - u_begin) : kb) * kKT;
     if (*s_err) dead = true;
-    if (!mbar_wait(&full[s], round & 1u, dead ? 4096u : kSpinLimit)) {
-      *s_err = 1;
-      dead = true;
-    }
-    const uint32_t base = smem_u32(stage_mem + (size_t)s * kTileBytes) + chunk * 4096;
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-      uint32_t b0 = 0u, b1 = 0u;
-      if (row_live) {
-        const int xt = slice ? (u - u_begin) : kb;  // staged k-tile index
-        b0 = *reinterpret_cast<const uint32_t*>(xrow + xt * kKT + kk * 16);
-        b1 = *reinterpret_cast<const uint32_t*>(xrow + xt * kKT + kk * 16 + 8);
+    const unsigned lim = dead ? 4096u : kSpinLimit;
+    int i = 0;
+    for (; i + 2 <= n; i += 2) {
+      int s1 = s + 1;
+      unsigned r1 = round;
+      if (s1 == S) {
+        s1 = 0;
+        ++r1;
       }
-      const int k = kk * 16 + lrow;
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
-        const int unit = hf * 4 + cb * 2 + lunit;
-        uint32_t a0, a1, a2, a3;
-        mm_ldmatrix_x4_trans(base + k * 128 + ((unit ^ (k & 7)) << 4), a0, a1, a2, a3);
-        mm_mma_16816(d[cb], a0, a1, a2, a3, b0, b1);
+      if (!mbar_wait(&full[s], round & 1u, lim) || !mbar_wait(&full[s1], r1 & 1u, lim)) {
+        *s_err = 1;
+        dead = true;
+      }
+      eat(stage0 + (uint32_t)s * kTileBytes, xp);
+      eat(stage0 + (uint32_t)s1 * kTileBytes, xp + kKT);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&empty[s]);
+        mbar_arrive(&empty[s1]);
+      }
+      s = s1 + 1;
+      round = r1;
+      if (s == S) {
+        s = 0;
+        ++round;
+      }
+      xp += 2 * kKT;
+    }
+    if (i < n) {
+      if (!mbar_wait(&full[s], round & 1u, lim)) {
+        *s_err = 1;
+        dead = true;
+      }
+      eat(stage0 + (uint32_t)s * kTileBytes, xp);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      if (++s == S) {
+        s = 0;
+        ++round;
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
-    if (++s == S) {
-      s = 0;
-      ++round;
-    }
-    const int cur_ct = ct, cur_kb = kb;
-    if (++kb == KB) {
-      kb = 0;
-      ++ct;
-    }
-    const bool seg_end = (cur_kb == KB - 1) || (u == u_end - 1);
+    const int u = un + n - 1;  // the segment's last tile
+    const int cur_ct = ct;
+    ++ct;
+    kb = 0;
     if (u == u_end - 1) STRACE(op_i, 2);
-    if (!seg_end) continue;
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        d[cb][e] += d2[cb][e];
+        d2[cb][e] = 0.0f;
+      }
     // ---- end of this CTA's share of column tile cur_ct: the accumulator fragments go to red[row][column]
     //      (fragment: d0,d1 = column g8, rows 2*t4, 2*t4+1; d2,d3 = column g8 + 8)
 #pragma unroll
@@ -255,6 +312,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       red_release_add(&a.done[op_i * kDoneStride], 1u);
     }
     seg_begin = u + 1;
+    un = u + 1;
   }
 }
 
