@@ -25,6 +25,8 @@ struct StackArgs {
   unsigned int* done;       // [n_ops + 1][kDoneStride]; the last slot counts CTAs that left the kernel
   float* attn_part;         // [M*H][kMaxStackSplits][hd + 2]
   int* error_flag;
+  int defer;                // when the ring slots of an operation's last tiles go back to the producer: 0 at once, 1 after the
+                            // partial sums are published, 2 after the operation's epilogue (default)
   long long* trace;         // optional [grid][n_ops][8] timestamps (+ [grid][8] cycle counters of the MMA warp)
 };
 

@@ -150,6 +150,19 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     mm_mma_16816(d2[0], f2[0], f2[1], f2[2], f2[3], b10, b11);
     mm_mma_16816(d2[1], f3[0], f3[1], f3[2], f3[3], b10, b11);
   };
+  // Slots of the operation's last tiles (no later tile of this operation needs them) can be held back: handing them
+  // over starts the producer's burst for the next operation, whose traffic delays the round trips of the exchange.
+  const int n_hold = a.defer ? min(S, u_end - u_begin) : 0;
+  const int u_hold = u_end - n_hold;
+  auto release_held = [&]() {
+    if (lane == 0) {
+      int sl = s;
+      for (int k = 0; k < n_hold; ++k) {
+        sl = (sl == 0) ? S - 1 : sl - 1;
+        mbar_arrive(&empty[sl]);
+      }
+    }
+  };
   int un = u_begin;  // next tile
   while (un < u_end) {
     // this CTA's share of column tile ct: n tiles, eaten two at a time (the loop carries no segment logic)
@@ -173,8 +186,8 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       eat(stage0 + (uint32_t)s1 * kTileBytes, xp + kKT);
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&empty[s]);
-        mbar_arrive(&empty[s1]);
+        if (un + i < u_hold) mbar_arrive(&empty[s]);
+        if (un + i + 1 < u_hold) mbar_arrive(&empty[s1]);
       }
       s = s1 + 1;
       round = r1;
@@ -191,7 +204,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       }
       eat(stage0 + (uint32_t)s * kTileBytes, xp);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
+      if (lane == 0 && un + i < u_hold) mbar_arrive(&empty[s]);
       if (++s == S) {
         s = 0;
         ++round;
@@ -242,6 +255,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       }
       consumers_sync();
       if (u == u_end - 1) STRACE(op_i, 6);
+      if (u == u_end - 1 && a.defer == 1) release_held();
       if (*s_last) {
         const float* all = a.partials + ((size_t)cur_ct * max_contrib * M) * NT;
         for (int idx = tid; idx < M * NT; idx += 256) {
@@ -311,6 +325,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     } else if (finish && tid == 0) {
       red_release_add(&a.done[op_i * kDoneStride], 1u);
     }
+    if (u == u_end - 1 && (a.defer == 2 || (a.defer == 1 && whole))) release_held();
     seg_begin = u + 1;
     un = u + 1;
   }
@@ -472,6 +487,14 @@ int launch_decode_stack_mma(int device, DeviceState* st, const StackConfig& c, c
     if (cap >= 2 && cap < stages) stages = cap;
   }
   a.stages = stages;
+  {
+    static int defer = -1;
+    if (defer < 0) {
+      const char* e = getenv("TSB200_STACK_DEFER");  // A/B: 0 hands every slot back at once, 1 after the partial sums are published
+      defer = e ? atoi(e) : 2;
+    }
+    a.defer = defer;
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kStreamThreads);
