@@ -174,11 +174,11 @@ struct Gpt {
   bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
   // persistent decode-step kernel (decode_stack.cu): the program of operations and its scratch
   bool use_stack = true;
-  // Measured crossover on the 7B-class model: one sequence is fastest in the persistent kernel (3.77 ms per step against
-  // 3.95 / 4.13 with one launch per operation); from two sequences on, one launch per operation with the mma.sync
-  // linears is flat at ~3.95 ms up to 8 sequences while the persistent kernel's dependency chain grows with every row
-  // (4.1 / 4.5 / 5.0 / 6.5 ms at 2 / 3 / 4 / 8).  Tensor-parallel engines keep the persistent kernel (the exchange lives there).
-  int stack_cap = 1;           // largest batch the persistent kernel is used for on one GPU (TSB200_STACK_MAXB)
+  // Measured crossover on the 7B-class model (ms per step, persistent kernel against one launch per operation with the
+  // mma.sync linears): 1 sequence 3.41 / 3.95, 2 sequences 3.79 / 3.92, 3 sequences 4.23 / 3.91, 4 sequences 4.62 / 3.96 --
+  // the persistent kernel's dependency chain grows with every row, the per-operation path is flat up to 8 sequences.
+  // Tensor-parallel engines keep the persistent kernel (the exchange lives there).
+  int stack_cap = 2;           // largest batch the persistent kernel is used for on one GPU (TSB200_STACK_MAXB)
   int gemv_rows = 1;           // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS)
   std::vector<StackOp> stack_host;
   StackOp* stack_dev = nullptr;
