@@ -150,7 +150,10 @@ TSB200_API int TSB200_TopPSample(int device, int32_t* out, const float* probs, i
  *   - Limit: rows * V <= 262144 (e.g. 4 rows of a 65536-word vocabulary, 8 rows of 32000).  Larger requests fail with a
  *     message naming the limit; use TSB200_TopPSample with your own workspace for those.
  *   - The first call on each device looks up the scratch block's device address and opts the kernel into its shared
- *     memory size; make that first call before starting any stream capture.
+ *     memory size; make that first call before starting any stream capture.  With CUDA's lazy module loading that
+ *     first call may also be the moment the driver reserves the 5 MiB image of the block, so a host that hands all
+ *     free device memory to its own pool should make one call per device (rows = 0 is enough) BEFORE it does so;
+ *     otherwise the call that is meant never to allocate can itself report out-of-memory.
  *   - All calls on a device share the one scratch block, which keeps whatever the previous call left in it; nothing
  *     in it needs clearing (the kernel writes every word before reading it), but two calls that overlap on the GPU
  *     (different streams, or different host threads) race on it.  Serialise them. */
@@ -191,9 +194,6 @@ TSB200_API int TSB200_PackWeight(int device, int dtype, void* packed, const void
  * kernel (M <= 4 only).  M <= 4 runs the TMA-fed streaming GEMV; larger M the fallback kernels.  Replaces
  * LayerNorm/RMSNorm + Affine + activation/gate/residual of one layer (PositionwiseFeedForward.cs:72-98,
  * MultiHeadAttention.cs:130-137,234-237). */
-/* profiling aid: when set to a device buffer of grid*8 int64, every CTA of the streaming GEMV stamps %globaltimer at
- * start / dependency resolved / x staged / first tile landed / last tile consumed / done.  NULL switches it off. */
-TSB200_API int TSB200_DebugSetGemvTrace(void* device_buffer);
 TSB200_API int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N);
 TSB200_API int TSB200_LinearPacked(int device, int dtype, void* y, float* y_f32, const void* x, const float* x_f32,
                                    const void* gamma, const void* beta, int norm_type, float eps, const void* Wp,
@@ -269,12 +269,6 @@ typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOpti
   uint64_t seq_base;
 } TSB200DecodingOptions;
 
-/* Profiling aid: when `device_buffer` is not NULL the persistent decode-step kernel (batch <= 4) writes four
- * %globaltimer stamps per CTA and operation into it ([SMs][operations][8] int64, followed by [SMs][8] cycle counters of the MMA warp: dependency met, input staged, last
- * weight tile consumed, operation left); NULL switches it off.  The operations of a step are, per layer: QKV,
- * attention, out-projection, FFN up, FFN down; then the LM head (5*L + 1).  No counterpart in the reference. */
-TSB200_API int TSB200_GptDebugStackTrace(void* gpt, void* device_buffer);
-
 /* Peer-memory all-reduce for the few KB a decode step exchanges (optional; without it the engine uses NCCL for every
  * size).  Each rank exports a 64-byte IPC handle of its exchange region (room for messages of up to max_count floats),
  * the host carries the handles of all ranks to every rank (rank order), and Import maps them.  One process per GPU.
@@ -292,6 +286,22 @@ TSB200_API int TSB200_CommPeerImport(void* comm, const void* handles, int n_rank
  * reference. */
 TSB200_API int TSB200_GptTpExport(void* gpt, void* handle64);
 TSB200_API int TSB200_GptTpImport(void* gpt, const void* handles, int n_ranks);
+/* Teardown of peer-mapped memory is collective and has two phases.  Phase 1, on every rank: TSB200_GptTpClose(gpt) and
+ * TSB200_CommPeerClose(comm) wait for the device's work and unmap the OTHER ranks' regions.  Then the ranks meet at a
+ * host-side barrier (any channel).  Phase 2: TSB200_GptDestroy / TSB200_CommDestroy free this rank's own region.
+ * Freeing an exported region while a peer still has it mapped, or while a peer's kernel may still store into it, is
+ * undefined behaviour of CUDA IPC and can fault over NVLink; a rank whose call failed must still take part in the
+ * barrier before it destroys its handles.  No counterpart in the reference (one process owns all devices there). */
+TSB200_API int TSB200_GptTpClose(void* gpt);
+TSB200_API int TSB200_CommPeerClose(void* comm);
+
+/* Every device-side wait of the persistent decode-step kernel is bounded: a CTA that polls a dependency counter more
+ * than `polls` times raises the engine's error word, walks through the rest of its program without waiting and leaves;
+ * the other CTAs see the word and do the same, the call fails with a message, and the engine stays usable (the
+ * sequences of the failed call must be reset or restored).  polls = 0 restores the default (2^21, about a second).
+ * For hosts that want a tighter bound than a second per step, and for tests that make a wait run out without any
+ * fault.  No counterpart in the reference (its kernels never wait on each other). */
+TSB200_API int TSB200_GptSetWaitLimit(void* gpt, int polls);
 
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);

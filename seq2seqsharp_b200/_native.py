@@ -109,7 +109,6 @@ def lib():
         "TSB200_LinearWorkspaceBytes": (i64, [i32, i32, i32]),
         "TSB200_PackedWeightBytes": (i64, [i32, i32, i32]),
         "TSB200_PackWeight": (i32, [i32, i32, vp, vp, i32, i32, i32, vp]),
-        "TSB200_DebugSetGemvTrace": (i32, [vp]),
         "TSB200_LinearPackedWorkspaceBytes": (i64, [i32, i32, i32, i32]),
         "TSB200_LinearPacked": (i32, [i32, i32, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, i32, i32, i32, i32, vp, i64, vp]),
         "TSB200_NormResidual": (i32, [i32, i32, vp, vp, vp, vp, vp, i32, f32, i32, i32, vp]),
@@ -128,11 +127,14 @@ def lib():
         "TSB200_CommPeerExport": (i32, [vp, i64, vp]),
         "TSB200_CommPeerImport": (i32, [vp, vp, i32]),
         "TSB200_CommDestroy": (i32, [vp]),
+        "TSB200_CommPeerClose": (i32, [vp]),
+        "TSB200_GptTpClose": (i32, [vp]),
         "TSB200_AllReduceSumF32": (i32, [vp, vp, i64, vp]),
         "TSB200_GptTpExport": (i32, [vp, vp]),
         "TSB200_GptTpImport": (i32, [vp, vp, i32]),
         "TSB200_GptSetComm": (i32, [vp, vp]),
         "TSB200_GptReset": (i32, [vp]),
+        "TSB200_GptSetWaitLimit": (i32, [vp, i32]),
         "TSB200_GptPrefill": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), i32, vp, C.POINTER(i32)]),
         "TSB200_GptGetLogits": (i32, [vp, vp, vp]),
@@ -147,7 +149,6 @@ def lib():
         "TSB200_GptStepHost": (i32, [vp, vp, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptEnableStepTiming": (i32, [vp, i32]),
         "TSB200_GptGetStepTimes": (i32, [vp, vp, i32, C.POINTER(i32)]),
-        "TSB200_GptDebugStackTrace": (i32, [vp, vp]),
         "TSB200_GptProfileDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), vp, vp, i32]),
         "TSB200_GptStepBytes": (i32, [vp, i32, i32, C.POINTER(i64)]),
         "TSB200_FillSynthetic": (i32, [i32, vp, i32, i64, u64, u64, f32, vp]),

@@ -248,6 +248,26 @@ int TSB200_CommPeerImport(void* comm, const void* handles, int n) {
   return 1;
 }
 
+// First phase of a collective teardown: waits for this device's work, then unmaps the peers' regions.  After EVERY rank
+// has returned from this call (a host-side barrier between the ranks) each rank may free its own region with
+// TSB200_CommDestroy: freeing exported memory while an importer still has it mapped is undefined, and a peer's kernel
+// may still be reading it.
+int TSB200_CommPeerClose(void* comm) {
+  if (!comm) return 1;
+  Comm* c = (Comm*)comm;
+  TSB_TRY(use_device(c->device, nullptr));
+  cudaDeviceSynchronize();
+  c->peers_ready = false;
+  for (int r = 0; r < kMaxPeers; ++r)
+    if (c->peer_open[r]) {
+      cudaIpcCloseMemHandle(c->peer_base[r]);
+      c->peer_open[r] = false;
+      c->peer_base[r] = nullptr;
+    }
+  cudaGetLastError();
+  return 1;
+}
+
 int TSB200_CommDestroy(void* comm) {
   if (!comm) return 1;
   Comm* c = (Comm*)comm;

@@ -71,7 +71,8 @@ __device__ __forceinline__ void stack_linear(const StackArgs& a, const StackOp* 
   constexpr int RPW = kKT / kConsumerWarps;
   for (int u = u_begin; u < u_end; ++u) {
     if (*s_err) dead = true;
-    if (!mbar_wait(&full[s], round & 1u, dead ? 4096u : kSpinLimit)) {
+    // a CTA that gave up walks through the rest of its program without waiting (its results are discarded)
+    if (!dead && !mbar_wait(&full[s], round & 1u, kSpinLimit)) {
       *s_err = 1;
       dead = true;
     }
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_kernel(StackAr
       const bool hoist = op->type == 0 && op->xmode != 0 && op->K <= 256 * 16;
       if (hoist) load_norm_consts<T>(nc, reinterpret_cast<const T*>(op->gamma), reinterpret_cast<const T*>(op->beta), op->K, tid);
       if (i > 0) {
-        if (tid == 0 && !poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : kPollLimit, a.error_flag)) {
+        if (tid == 0 && !poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : a.poll_limit, a.error_flag)) {
           s_err = 1;
           *a.error_flag = 1;
         }
@@ -329,9 +330,9 @@ static StackPlan stack_plan_t(const StackConfig& c, const StackOp* ops, int n_op
     const size_t x = (((size_t)c.M * kt * kKT * sizeof(T)) + 127) & ~(size_t)127;
     if (x > xs) xs = x;
   }
-  // mode 0 (FMA consumers): the eight warps' sums meet in shared memory; 1 (tcgen05): accumulators live in tensor
-  // memory; 2 (mma.sync): every warp owns its columns, one [M][NT] block carries them to the epilogue
-  const size_t red = mode == 1 ? 0 : (size_t)(mode == 2 ? 1 : kConsumerWarps) * c.M * NT * sizeof(float);
+  // mode 0 (FMA consumers): the eight warps' sums meet in shared memory; 2 (mma.sync): every warp owns its columns,
+  // one [M][NT] block carries them to the epilogue
+  const size_t red = (size_t)(mode == 2 ? 1 : kConsumerWarps) * c.M * NT * sizeof(float);
   const int lpt = c.hd / EPL;
   const int tpw = lpt > 0 ? 32 / lpt : 1;
   const int group = c.H / c.Hkv;
@@ -391,11 +392,19 @@ int stack_fill_args(StackArgs& a, const StackPlan& p, const StackConfig& c, cons
   a.attn_part = reinterpret_cast<float*>(attn_part);
   a.error_flag = error_flag;
   a.trace = trace;
+  a.poll_limit = c.poll_limit ? c.poll_limit : kPollLimit;
   return 1;
 }
 
 template <typename T, int M>
 static int stack_launch_m(int device, const StackArgs& a, int grid, size_t smem, bool pdl, cudaStream_t s) {
+  {
+    // the CTAs wait on one another: the whole grid must be resident at once, else the caller launches per operation
+    int per_sm = 0, sms = 0;
+    TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_kernel<T, M>, kStreamThreads, smem));
+    TSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    if ((long long)per_sm * sms < grid) return 2;
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kStreamThreads);
@@ -447,21 +456,10 @@ int launch_decode_stack(int device, DeviceState* st, const StackConfig& c, const
     return launch_decode_stack_mma(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
   }
   if (c.dtype == TSB200_F16) {
-    {
-      // consumers of the fp16 weight stream: "mma" (default: eight warps, ldmatrix + mma.sync), "tc" (one warp issuing
-      // tcgen05.mma, accumulators in tensor memory), "fma" (CUDA cores)
-      static int mode = -1;
-      if (mode < 0) {
-        const char* e = getenv("TSB200_STACK_MODE");
-        mode = (e && !strcmp(e, "tc")) ? 1 : (e && !strcmp(e, "fma")) ? 0 : 2;
-      }
-      int r = 2;
-      if (mode == 1)
-        r = launch_decode_stack_tc(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
-      else if (mode == 2)
-        r = launch_decode_stack_mma(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
-      if (r != 2) return r;
-    }
+    // fp16: eight warps eat the weight stream with ldmatrix + mma.sync; shapes that kernel does not take fall through
+    // to the CUDA-core consumers
+    const int r = launch_decode_stack_mma(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
+    if (r != 2) return r;
     return stack_launch_t<__half>(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
   }
   return stack_launch_t<float>(device, st, c, ops_dev, ops_host, n_ops, partials, counters, attn_part, error_flag, trace, pdl, s);
@@ -477,7 +475,6 @@ int init_stack_attrs(int device) {
   if (done[device]) return 1;
   TSB_TRY((stack_attr_one<float, 1>())); TSB_TRY((stack_attr_one<float, 2>())); TSB_TRY((stack_attr_one<float, 3>())); TSB_TRY((stack_attr_one<float, 4>()));
   TSB_TRY((stack_attr_one<__half, 1>())); TSB_TRY((stack_attr_one<__half, 2>())); TSB_TRY((stack_attr_one<__half, 3>())); TSB_TRY((stack_attr_one<__half, 4>()));
-  TSB_TRY(init_stack_tc_attrs());
   TSB_TRY(init_stack_mma_attrs());
   done[device] = true;
   return 1;

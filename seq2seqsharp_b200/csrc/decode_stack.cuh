@@ -1,5 +1,5 @@
-// Device code shared by the two persistent decode-step kernels (decode_stack.cu: CUDA-core consumers, any dtype;
-// decode_stack_tc.cu: tcgen05 consumers, fp16): the argument block, the global-counter protocol between CTAs, input
+// Device code shared by the persistent decode-step kernels (decode_stack.cu: CUDA-core consumers, any dtype;
+// decode_stack_mma.cu: warp-level tensor-core consumers, fp16): the argument block, the global-counter protocol between CTAs, input
 // staging with the fused norms, and the in-kernel RoPE + cache append + split-K attention.
 #pragma once
 #include "kernels.cuh"
@@ -28,6 +28,7 @@ struct StackArgs {
   int defer;                // when the ring slots of an operation's last tiles go back to the producer: 0 at once, 1 after the
                             // partial sums are published, 2 after the operation's epilogue (default)
   long long* trace;         // optional [grid][n_ops][8] timestamps (+ [grid][8] cycle counters of the MMA warp)
+  unsigned poll_limit;      // acquire-polls of a dependency counter before a CTA gives up (kPollLimit unless the host set one)
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -134,9 +135,14 @@ __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned 
   TileCursor<T> fetch;
   const unsigned char* src;
   while (fetch.next(a, src)) {
-    if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
-      *s_err = 1;
-      break;
+    if (round > 0) {
+      // short waits, so that a CTA whose workers gave up (they stop handing slots back) leaves at once
+      bool got = false;
+      for (unsigned t = 0; t < (kSpinLimit >> 10) && !got && !*s_err; ++t) got = mbar_wait(&empty[s], (round - 1u) & 1u, 1024u);
+      if (!got) {
+        *s_err = 1;
+        break;
+      }
     }
     if (*s_err) break;
     mbar_expect_tx(&full[s], kTileBytes);
@@ -155,10 +161,15 @@ __device__ __forceinline__ void stack_stream_tiles(const StackArgs& a, unsigned 
   }
 }
 
+// Time stamps for kernel development exist only in builds with -DTSB200_TRACE; the shipped kernels carry none.
+#ifdef TSB200_TRACE
 #define STRACE(op_i, slot)                                                                        \
   do {                                                                                            \
     if (a.trace && threadIdx.x == 0) a.trace[((size_t)blockIdx.x * a.n_ops + (op_i)) * 8 + (slot)] = gtimer(); \
   } while (0)
+#else
+#define STRACE(op_i, slot) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------------------------------- x staging (workers)
 // All loads of activations are L2-coherent (__ldcg): they were written by other SMs earlier in this same kernel.
@@ -569,7 +580,9 @@ __device__ __forceinline__ void stack_attention(const StackArgs& a, const StackO
 #pragma unroll
       for (int e = 0; e < EPL; ++e) qf[g][e] *= a.scale;
     }
+#ifdef TSB200_TRACE
     if (qf[0][0] == 12345.678f) STRACE(op_i, 7);  // keeps the stamp below after the q loads
+#endif
     STRACE(op_i, 4);
     float mx[G], l[G], acc[G][EPL];
 #pragma unroll
@@ -616,7 +629,9 @@ __device__ __forceinline__ void stack_attention(const StackArgs& a, const StackO
       }
       attn_update<G, EPL>(qf, kf, vf, mx, l, acc, lpt, live);
     }
+#ifdef TSB200_TRACE
     if (l[0] == 12345.678f) STRACE(op_i, 7);
+#endif
     STRACE(op_i, 5);
     // merge the lane-group states through shared memory, write this split's partial state
     const int st = w * tpw + sub;
@@ -704,15 +719,10 @@ struct StackPlan {
   int64_t partial_bytes, counter_words;
   size_t xs_bytes, union_bytes;
 };
-// mode: 0 FMA consumers, 1 tcgen05 consumers, 2 mma.sync consumers
+// mode: 0 FMA consumers, 2 mma.sync consumers
 StackPlan stack_plan(const StackConfig& c, const StackOp* ops, int n_ops, int grid, int mode);
 int stack_fill_args(StackArgs& a, const StackPlan& p, const StackConfig& c, const StackOp* ops_dev, const StackOp* ops_host, int n_ops,
                     void* partials, void* counters, void* attn_part, int* error_flag, long long* trace);
-// tcgen05 variant (decode_stack_tc.cu), fp16 and up to 8 sequences: 1 ok, 0 error, 2 not applicable
-int launch_decode_stack_tc(int device, DeviceState* st, const StackConfig& c, const StackOp* ops_dev, const StackOp* ops_host,
-                           int n_ops, void* partials, void* counters, void* attn_part, int* error_flag,
-                           long long* trace, bool pdl, cudaStream_t s);
-int init_stack_tc_attrs();
 // mma.sync variant (decode_stack_mma.cu), fp16 and up to 8 sequences
 int launch_decode_stack_mma(int device, DeviceState* st, const StackConfig& c, const StackOp* ops_dev, const StackOp* ops_host,
                             int n_ops, void* partials, void* counters, void* attn_part, int* error_flag,

@@ -1,12 +1,12 @@
 // Persistent decode-step kernel, fp16, warp-level tensor-core consumers (ldmatrix + mma.sync m16n8k16).
 //
-// Same program, protocol and producer as decode_stack_tc.cu (TMA bulk copies of the packed weight tiles, which are
+// Same program, protocol and producer as decode_stack.cu (TMA bulk copies of the packed weight tiles, which are
 // stored as their 128-byte-swizzled shared-memory image, into a stage ring), but the weight stream is eaten by all eight worker warps in parallel: per 16 KB
 // tile a warp owns 32 of the 256 columns, loads them as transposed 8x8 fragments (ldmatrix.trans, conflict-free on
 // the swizzled stage) and multiplies them with the staged activations (up to 8 sequences in the n dimension of the
 // instruction): 4 ldmatrix + 4 mma + 4 shared loads per warp and tile instead of ~110 FMA-pipe instructions, and no
 // cross-warp reduction (a warp sees all 32 k of its columns).  Eight independent warps hide the latencies of the
-// barrier handshakes that serialise the single issuing warp of the tcgen05 variant, so a ring filled during a
+// barrier handshakes (a single-warp tcgen05 consumer was measured slower for that reason), so a ring filled during a
 // dependency wait is drained several times faster than HBM refills it.
 #include <cstdlib>
 
@@ -169,7 +169,8 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
     const int n = min(u_end - un, KB - kb);
     const __half* xp = xrow + (size_t)(slice ? (un - u_begin) : kb) * kKT;
     if (*s_err) dead = true;
-    const unsigned lim = dead ? 4096u : kSpinLimit;
+    // a CTA that gave up walks through the rest of its program without waiting (its results are discarded)
+    const unsigned lim = kSpinLimit;
     int i = 0;
     for (; i + 2 <= n; i += 2) {
       int s1 = s + 1;
@@ -178,7 +179,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
         s1 = 0;
         ++r1;
       }
-      if (!mbar_wait(&full[s], round & 1u, lim) || !mbar_wait(&full[s1], r1 & 1u, lim)) {
+      if (!dead && (!mbar_wait(&full[s], round & 1u, lim) || !mbar_wait(&full[s1], r1 & 1u, lim))) {
         *s_err = 1;
         dead = true;
       }
@@ -198,7 +199,7 @@ __device__ __forceinline__ void mm_linear(const StackArgs& a, const StackOp* op,
       xp += 2 * kKT;
     }
     if (i < n) {
-      if (!mbar_wait(&full[s], round & 1u, lim)) {
+      if (!dead && !mbar_wait(&full[s], round & 1u, lim)) {
         *s_err = 1;
         dead = true;
       }
@@ -421,9 +422,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_stack_mma_kernel(Sta
         bool ok = true;
         if (tid == 0) {
           if (TP && prev_xchg)  // every rank's finishers arrive here: column tiles x ranks, per launch
-            ok = poll_count_sys(xcnt + (i - 1), (epoch + 1u) * prev_target * (unsigned)c.tp_size, dead ? 64u : kPollLimit, a.error_flag);
+            ok = poll_count_sys(xcnt + (i - 1), (epoch + 1u) * prev_target * (unsigned)c.tp_size, dead ? 64u : a.poll_limit, a.error_flag);
           else
-            ok = poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : kPollLimit, a.error_flag);
+            ok = poll_count(&a.done[(i - 1) * kDoneStride], prev_target, dead ? 64u : a.poll_limit, a.error_flag);
         }
         if (tid == 0 && !ok) {
           s_err = 1;
@@ -478,28 +479,22 @@ int launch_decode_stack_mma(int device, DeviceState* st, const StackConfig& c, c
   if (fixed + 3 * (size_t)kTileBytes > budget) return 2;
   int stages = (int)((budget - fixed) / kTileBytes);
   if (stages > 16) stages = 16;
-  {
-    static int cap = -1;
-    if (cap < 0) {
-      const char* e = getenv("TSB200_STACK_STAGES");  // experiment: shallower ring
-      cap = e ? atoi(e) : 0;
-    }
-    if (cap >= 2 && cap < stages) stages = cap;
-  }
   a.stages = stages;
-  {
-    static int defer = -1;
-    if (defer < 0) {
-      const char* e = getenv("TSB200_STACK_DEFER");  // A/B: 0 hands every slot back at once, 1 after the partial sums are published
-      defer = e ? atoi(e) : 2;
-    }
-    a.defer = defer;
-  }
+  a.defer = 2;  // measured best: the ring slots of an operation's last tiles go back after its epilogue
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kStreamThreads);
   cfg.dynamicSmemBytes = fixed + (size_t)stages * kTileBytes;
   cfg.stream = s;
+  {
+    // The CTAs wait on one another, so all of them must be resident at the same time: one per SM with this much shared
+    // memory.  If the device cannot hold the grid (fewer SMs available than it reports, a smaller carve-out), the caller
+    // runs one launch per operation instead.
+    int per_sm = 0;
+    if (c.tp_size > 1) TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_mma_kernel<true>, kStreamThreads, cfg.dynamicSmemBytes));
+    else TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_mma_kernel<false>, kStreamThreads, cfg.dynamicSmemBytes));
+    if ((long long)per_sm * st->sm_count < grid) return 2;
+  }
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;

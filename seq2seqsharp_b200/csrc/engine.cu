@@ -187,7 +187,8 @@ struct Gpt {
   void *stack_partials = nullptr, *stack_counters = nullptr, *stack_attn = nullptr;
   int stack_max_B = 4;
   int64_t stack_counter_bytes = 0;
-  long long* stack_trace = nullptr;  // optional timestamps (TSB200_GptDebugStackTrace)
+  long long* stack_trace = nullptr;  // optional timestamps (TSB200_GptDebugStackTrace, -DTSB200_TRACE builds)
+  unsigned poll_limit = 0;           // 0: default; polls of a dependency counter before a CTA of the persistent kernel gives up
 };
 
 enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_STACK = 8, KC_COUNT = 9 };
@@ -390,6 +391,9 @@ static int ensure_act(Gpt* g, int64_t rows) {
   TSB_CUDA(cudaStreamSynchronize(g->s));
   // the captured decode step holds the old buffers as kernel arguments
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  // ... and so does the program of the persistent decode-step kernel (a new buffer may come back at the old address)
+  g->stack_key = nullptr;
+  g->stack_B = 0;
   auto re = [&](void** p, int64_t bytes) -> int {
     if (*p) {
       for (auto& a : g->allocs) if (a == *p) a = nullptr;
@@ -591,6 +595,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     sc.use_rope = c.pe_type == 2; sc.rope_tab = g->rope_tab; sc.dT = dT;
     sc.tp_rank = g->tp_rank; sc.tp_size = g->tp; sc.d = c.d;
     for (int r = 0; r < g->tp && r < kStackMaxRanks; ++r) sc.peer[r] = g->tp > 1 ? g->xch_peer[r] : nullptr;
+    sc.poll_limit = g->poll_limit;
     prof_begin(g);
     const int r = launch_decode_stack(dev, g->st, sc, g->stack_dev, g->stack_host.data(), (int)g->stack_host.size(),
                                       g->stack_partials, g->stack_counters, g->stack_attn, g->err_flag, g->stack_trace, g->pdl, g->s);
@@ -652,7 +657,8 @@ static int check_err_flag(Gpt* g) {
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
-    TSB_FAIL("a kernel gave up waiting on a shared-memory barrier (internal error); results of this call are invalid");
+    TSB_FAIL("a kernel gave up waiting (a dependency counter or a shared-memory barrier did not arrive within its limit); "
+             "the results of this call and the state of its sequences are invalid: reset or restore the cache before the next call");
   }
   return 1;
 }
@@ -1011,6 +1017,28 @@ int TSB200_GptTpImport(void* h, const void* handles, int n) {
   return 1;
 }
 
+// First phase of a collective teardown of a tensor-parallel engine: waits for this device's work, drops the captured
+// step and the program that hold the peers' addresses, and unmaps the peers' exchange regions.  Every rank calls it, the
+// ranks meet at a host-side barrier, and only then each rank frees its own region (TSB200_GptDestroy).
+int TSB200_GptTpClose(void* h) {
+  Gpt* g = (Gpt*)h;
+  if (!g) return 1;
+  TSB_TRY(use_device(g->c.device, nullptr));
+  cudaDeviceSynchronize();
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  g->stack_key = nullptr;
+  g->stack_B = 0;
+  g->xch_ready = false;
+  for (int r = 0; r < kStackMaxRanks; ++r)
+    if (g->xch_open[r]) {
+      cudaIpcCloseMemHandle(g->xch_peer[r]);
+      g->xch_open[r] = false;
+      g->xch_peer[r] = nullptr;
+    }
+  cudaGetLastError();
+  return 1;
+}
+
 int TSB200_GptSetComm(void* h, void* comm) {
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g, "gpt_set_comm: null engine");
@@ -1231,7 +1259,9 @@ int TSB200_GptCacheSnapshot(void* h, void** snap_out) {
     }
   sn->hist.assign((size_t)sn->B * (sn->T + 1), 0);
   sn->pending.assign(sn->B, 0);
-  if (cudaMemcpy2DAsync(sn->hist.data(), (size_t)(sn->T + 1) * 4, g->hist, (size_t)c.max_tokens * 4, (size_t)(sn->T + 1) * 4, sn->B,
+  // a cache decoded to capacity has no history slot for the pending id (it stays in `pending`)
+  const size_t hist_w = (size_t)(sn->T + 1 <= c.max_tokens ? sn->T + 1 : c.max_tokens) * 4;
+  if (cudaMemcpy2DAsync(sn->hist.data(), (size_t)(sn->T + 1) * 4, g->hist, (size_t)c.max_tokens * 4, hist_w, sn->B,
                         cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
       cudaMemcpyAsync(sn->pending.data(), g->ids_cur, (size_t)sn->B * 4, cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
       cudaStreamSynchronize(g->s) != cudaSuccess) {
@@ -1376,6 +1406,7 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   count_launch(c.device, g->graph_nodes);
   TSB_CUDA(cudaMemcpyAsync(g->pin_ids, g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
   TSB_CUDA(cudaStreamSynchronize(g->s));
+  TSB_TRY(check_err_flag(g));
   for (int b = 0; b < B; ++b) out_ids[b] = g->pin_ids[b];
   g->T += 1;
   g->step += 1;
@@ -1384,11 +1415,21 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   return 1;
 }
 
+#ifdef TSB200_TRACE
 int TSB200_GptDebugStackTrace(void* h, void* device_buffer) {
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g, "gpt_debug_stack_trace: null handle");
   g->stack_trace = reinterpret_cast<long long*>(device_buffer);
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }  // the pointer is a kernel argument of the captured step
+  return 1;
+}
+#endif
+
+int TSB200_GptSetWaitLimit(void* h, int polls) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && polls >= 0, "gpt_set_wait_limit: bad arguments");
+  g->poll_limit = (unsigned)polls;
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }  // the limit is a kernel argument of the captured step
   return 1;
 }
 
@@ -1416,6 +1457,7 @@ int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* o
   cudaError_t e = cudaStreamSynchronize(g->s);
   if (!ok) return 0;
   TSB_CUDA(e);
+  TSB_TRY(check_err_flag(g));
   for (size_t i = 0; i < g->prof_n; ++i) {
     float ms = 0.0f;
     TSB_CUDA(cudaEventElapsedTime(&ms, g->prof_ev[2 * i], g->prof_ev[2 * i + 1]));

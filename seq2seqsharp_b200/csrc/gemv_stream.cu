@@ -27,11 +27,16 @@
 
 namespace tsb {
 
+// Time stamps for kernel development exist only in builds with -DTSB200_TRACE; the shipped kernel carries none.
+#ifdef TSB200_TRACE
 #define TRACE(slot)                                                                     \
   do {                                                                                  \
     if (a.trace && (tid & 31) == 0 && ((tid >> 5) == 0 || (tid >> 5) == kConsumerWarps)) \
       a.trace[(size_t)blockIdx.x * 8 + (slot)] = gtimer();                              \
   } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 struct StreamArgs {
   const void* Wp;        // packed tiles
   const void* x;         // xmode 0: T [M,K]; xmode 1/2: fp32 residual stream [M,K]
@@ -479,8 +484,10 @@ static int launch_stream_t(int device, DeviceState* st, StreamArgs& a, int M, bo
   return 2;
 }
 
-static long long* g_gemv_trace = nullptr;  // set through TSB200_DebugSetGemvTrace (profiling aid)
+#ifdef TSB200_TRACE
+static long long* g_gemv_trace = nullptr;  // set through TSB200_DebugSetGemvTrace
 void set_gemv_trace(long long* p) { g_gemv_trace = p; }
+#endif
 
 // Returns 1 on success, 0 on error, 2 when the shape is not handled by this kernel (caller falls back).
 int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, const void* x, int xmode, const void* gamma,
@@ -491,7 +498,9 @@ int launch_gemv_stream(int device, DeviceState* st, int dtype, const void* Wp, c
   StreamArgs a{};
   a.Wp = Wp; a.x = x; a.gamma = gamma; a.beta = beta; a.xmode = xmode; a.eps = eps; a.K = K; a.N = N;
   a.error_flag = error_flag;
+#ifdef TSB200_TRACE
   a.trace = g_gemv_trace;
+#endif
   a.ep = ep;
   if (dtype == TSB200_F16) return launch_stream_t<__half>(device, st, a, M, pdl, ws, ws_bytes, s);
   return launch_stream_t<float>(device, st, a, M, pdl, ws, ws_bytes, s);
@@ -519,10 +528,12 @@ extern "C" {
 
 int64_t TSB200_PackedWeightBytes(int dtype, int K, int N) { return packed_bytes(dtype, K, N); }
 
+#ifdef TSB200_TRACE
 int TSB200_DebugSetGemvTrace(void* device_buffer) {
   set_gemv_trace(reinterpret_cast<long long*>(device_buffer));
   return 1;
 }
+#endif
 
 int TSB200_PackWeight(int device, int dtype, void* packed, const void* W, int src_dtype, int K, int N, void* stream) {
   DeviceState* st;

@@ -66,6 +66,7 @@ struct StackConfig {
   // [kStackXchSites][ranks][kStackXchRows][d] fp32 from 16 KB.
   int tp_rank, tp_size, d;
   unsigned char* peer[kStackMaxRanks];
+  unsigned poll_limit;    // 0: the kernel's default; else acquire-polls of a dependency counter before a CTA gives up
 };
 constexpr size_t kStackXchHeader = 16384;
 // Sizes of the scratch areas launch_decode_stack() needs for a program (host copy of the ops).

@@ -7,6 +7,7 @@
 //                 whole CTA reduces (value, index) pairs with warp shuffles and the same tie rule).
 //  * Top-P      : device version of the host loop ComputeGraphTensor.TopPSample
 //                 (Seq2SeqSharp/Tools/ComputeGraphTensor.cs:2305-2403); see topp_kernel.
+#include <mutex>
 #include <cstdlib>
 
 #include "kernels.cuh"
@@ -999,8 +1000,10 @@ static __device__ __align__(256) unsigned char g_topp_static_scratch[kStaticTopp
 // Host code must not hand `g_topp_static_scratch` itself to a kernel: on the host that name is only a stand-in for the
 // symbol.  The real device address is looked up once per device, with that device current, and cached here.
 static void* g_topp_static_addr[kMaxDevices] = {};
+static std::mutex g_topp_static_mu;  // two host threads may make the first call on one device at the same time
 
 static int topp_static_setup(int device) {
+  std::lock_guard<std::mutex> lk(g_topp_static_mu);
   if (g_topp_static_addr[device]) return 1;
   void* p = nullptr;
   TSB_CUDA(cudaGetSymbolAddress(&p, g_topp_static_scratch));

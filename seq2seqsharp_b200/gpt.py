@@ -231,8 +231,23 @@ class GPT:
                 blob = (C.c_ubyte * (64 * self.tp_size)).from_buffer_copy(b"".join(allh))
                 N.call("TSB200_GptTpImport", self._h, blob, self.tp_size)
         N.call("TSB200_GptSetComm", self._h, self._comm)
+        self._group, self._peer_mapped = group, bool(peer and self.tp_size <= 8)
 
-    def close(self):
+    def close(self, barrier=None):
+        """Frees the engine.  A tensor-parallel engine whose ranks mapped each other's memory is torn down in two
+        phases: every rank unmaps its peers' regions, the ranks meet at a host barrier (`barrier`, default
+        torch.distributed.barrier on the group given to InitComm), then each rank frees its own region."""
+        if getattr(self, "_peer_mapped", False) and getattr(self, "_h", None) and self._h.value:
+            self._peer_mapped = False
+            N.lib().TSB200_GptTpClose(self._h)
+            if self._comm.value:
+                N.lib().TSB200_CommPeerClose(self._comm)
+            if barrier is None:
+                def barrier():
+                    import torch.distributed as dist
+                    if dist.is_available() and dist.is_initialized():
+                        dist.barrier(group=self._group)
+            barrier()
         if getattr(self, "_h", None) and self._h.value:
             N.lib().TSB200_GptDestroy(self._h)
             self._h = C.c_void_p()
@@ -242,7 +257,7 @@ class GPT:
 
     def __del__(self):
         try:
-            self.close()
+            self.close(barrier=lambda: None)  # a finalizer cannot take part in a collective: call close() explicitly
         except Exception:
             pass
 
@@ -282,6 +297,10 @@ class GPT:
 
     def Reset(self):
         N.call("TSB200_GptReset", self._h)
+
+    def SetWaitLimit(self, polls: int):
+        """Bound of the device-side waits of the persistent decode-step kernel (0 = default, about a second)."""
+        N.call("TSB200_GptSetWaitLimit", self._h, int(polls))
 
     def Prefill(self, tokens, opts: DecodingOptions):
         ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
@@ -371,10 +390,6 @@ class GPT:
         N.call("TSB200_GptProfileDecode", self._h, n_steps, C.byref(c), ms.ctypes.data_as(C.c_void_p),
                groups.ctypes.data_as(C.c_void_p), n)
         return {k: (float(ms[i]), int(groups[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
-
-    def DebugStackTrace(self, device_ptr):
-        """Profiling aid: per-CTA, per-operation timestamps of the persistent decode-step kernel (0 switches it off)."""
-        N.call("TSB200_GptDebugStackTrace", self._h, C.c_void_p(device_ptr or None))
 
     # ---- inspection --------------------------------------------------------------------------------
     def Logits(self, want_probs=True):

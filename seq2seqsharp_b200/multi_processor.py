@@ -66,3 +66,49 @@ class MultiProcessorNetworkWrapper:
         parts = [merged[k] for k in sorted(merged)]     # MergeResults: SortedDictionary by block id (BaseSeq2SeqFramework.cs:860-888)
         n = min(p.shape[1] for p in parts)
         return np.concatenate([p[:, :n] for p in parts], axis=0)
+
+
+class RankLeft(RuntimeError):
+    """Another rank of the job left (or stopped answering) between two steps."""
+
+    def __init__(self, rank, reason):
+        super().__init__("rank %d left the job: %s" % (rank, reason))
+        self.rank, self.reason = rank, reason
+
+
+class StepGuard:
+    """Host-side liveness check between the steps of a multi-rank job whose kernels wait on each other (the
+    tensor-parallel decode step exchanges partial sums inside one kernel per rank).  A rank may leave only between
+    steps, with none of its kernels in flight; the others must learn of it on the host BEFORE their next launch,
+    because a kernel that waits for a peer that will never arrive runs into its poll limit, and a peer that has freed
+    its exchange memory must not be written to.  Each rank announces the step it is about to launch in a key-value
+    store (any `torch.distributed` store), announces when it leaves, and checks the others before every launch.
+
+    The reference has no counterpart: its devices are driven by threads of one process, and a failure of one device
+    ends the whole call (Seq2SeqSharp/Tools/BaseSeq2SeqFramework.cs:905-963)."""
+
+    def __init__(self, store, rank: int, world_size: int, timeout_s: float = 5.0, poll_s: float = 0.01):
+        self.store, self.rank, self.world, self.timeout_s, self.poll_s = store, rank, world_size, timeout_s, poll_s
+
+    def announce(self, step: int):
+        self.store.set("step/%d" % self.rank, str(int(step)))
+
+    def leave(self, reason: str = "left"):
+        self.store.set("left/%d" % self.rank, reason or "left")
+
+    def check(self, step: int):
+        """Returns once every other rank has announced `step` (or a later one); raises RankLeft when one of them has
+        announced that it left, or has not announced the step within the timeout."""
+        import time
+        deadline = time.monotonic() + self.timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while True:
+                if self.store.check(["left/%d" % r]):
+                    raise RankLeft(r, self.store.get("left/%d" % r).decode("utf-8", "replace"))
+                if self.store.check(["step/%d" % r]) and int(self.store.get("step/%d" % r)) >= step:
+                    break
+                if time.monotonic() > deadline:
+                    raise RankLeft(r, "no announcement of step %d within %.1f s" % (step, self.timeout_s))
+                time.sleep(self.poll_s)

@@ -34,14 +34,14 @@ def tol_for(cfg):
     return 1e-3 if cfg.dtype == "float32" else 2e-2
 
 
-def run_pair(oracle, cfg, w, prompt, opts, max_pos, n_check_logits=3):
+def run_pair(oracle, cfg, w, prompt, opts, max_pos, n_check_logits=3, threads=1):
     """Runs oracle and device side by side feeding both the ORACLE's ids (teacher forcing is not possible on the device
     loop, so the device runs free and we compare until the first recorded tie)."""
     B, S = prompt.shape
     n_new = opts.MaxTgtSentLength - S
     gpt = GPT(cfg, max_batch=B, max_tokens=opts.MaxTgtSentLength + 2)
     gpt.LoadWeights(w)
-    orc = oracle.OracleGPT(cfg, w, max_pos=max_pos)
+    orc = oracle.OracleGPT(cfg, w, max_pos=max_pos, threads=threads)
     steps = {}
 
     def record(step, logits, probs, nxt):
@@ -268,9 +268,7 @@ def test_persistent_step_kernel_matches_per_op_launches(cuda, cfg, B, monkeypatc
     np.testing.assert_array_equal(last, b.Prefill(prompt, opts))
     a2.Prefill(prompt, opts)
     # fp16 models run up to 8 sequences on the tensor-core variant, fp32 models up to 4 on the CUDA-core variant
-    import os
-    tensor_rows = 4 if os.environ.get("TSB200_STACK_MODE") == "fma" else 8   # debug switch: CUDA-core consumers for fp16 too
-    expect = 1 if B <= (tensor_rows if cfg.dtype == "float16" else 4) else 0
+    expect = 1 if B <= (8 if cfg.dtype == "float16" else 4) else 0
     assert a.ProfileDecode(1, opts)["decode_stack"][1] == expect and b.ProfileDecode(1, opts)["decode_stack"][1] == 0
     a2.ProfileDecode(1, opts)
     worst = 0.0

@@ -197,3 +197,25 @@ def test_longer_prompt_on_a_used_engine(cuda):
     want = fresh.RunForwardOnSingleDevice(long_p, o, stop_on_eos=False)
     fresh.close()
     np.testing.assert_array_equal(got, want)
+
+
+def test_snapshot_of_a_cache_decoded_to_capacity(cuda):
+    """Decoding may fill the cache to its last position (T == max_tokens); parking it then must work: the history has no
+    slot left for the pending id, which the snapshot keeps separately."""
+    case = CASES[0]
+    cfg, w, prompt, opts, max_pos = case_inputs(case)
+    S, cap = 6, 16
+    gpt = GPT(cfg, max_batch=2, max_tokens=cap)
+    gpt.LoadWeights(w)
+    gpt.Reset()
+    gpt.Prefill(prompt[:, :S], opts)
+    ids = gpt.Decode(cap - S, opts)
+    assert gpt.CacheLength() == cap
+    snap = gpt.CacheSnapshot()
+    assert snap.T == cap
+    np.testing.assert_array_equal(snap.tokens[:, :S], prompt[:, :S])
+    np.testing.assert_array_equal(snap.tokens[:, S + 1:cap], ids[:, :cap - S - 1])
+    with pytest.raises(N.TSB200OutOfMemory):
+        gpt.CacheRestore(snap)       # a full cache cannot take another step, so restoring it is refused as out of memory
+    snap.close()
+    gpt.close()

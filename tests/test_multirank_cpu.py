@@ -170,3 +170,93 @@ def test_tensor_parallel_sharding_rule_sums_to_the_unsharded_layer():
         assert p.exitcode == 0
     for rank, err, scale in res:
         assert err <= 1e-5 * max(1.0, scale), "rank %d: sharded layer differs from the unsharded one by %g" % (rank, err)
+
+
+# ---- a rank that leaves between steps is reported to the others before their next launch ---------------------------------
+def _guard_worker(rank, world, port, mode, q):
+    import datetime
+    import time
+    from seq2seqsharp_b200.multi_processor import RankLeft, StepGuard
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30))
+    guard = StepGuard(store, rank, world, timeout_s=2.0)
+    done = 0
+    try:
+        for step in range(6):
+            if rank == 1 and step == 3:
+                if mode == "announced":
+                    guard.leave("KV-cache capacity exceeded")   # leaves between steps, nothing of it in flight
+                break                                           # mode "silent": just stops announcing
+            guard.announce(step)
+            guard.check(step)     # before the launch of `step`: everybody is still there
+            done += 1             # (the launch itself)
+        q.put((rank, "finished", done, ""))
+    except RankLeft as ex:
+        q.put((rank, "peer_left", done, str(ex)))
+    if rank == 0:
+        time.sleep(1.0)   # the store's server lives in rank 0: keep it up while rank 1 finishes
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("mode", ["announced", "silent"])
+def test_a_rank_that_leaves_between_steps_is_seen_before_the_next_launch(mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_guard_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict((r[0], r[1:]) for r in (q.get(timeout=60) for _ in procs))
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert res[1][0] == "finished" and res[1][1] == 3
+    status, done, msg = res[0]
+    assert status == "peer_left" and done == 3 and "rank 1" in msg     # three steps ran, the fourth was never launched
+    assert ("capacity" in msg) if mode == "announced" else ("no announcement of step 3" in msg)
+
+
+# ---- teardown of peer-mapped memory: nobody frees before everybody has unmapped -------------------------------------------
+def _teardown_worker(rank, world, port, q):
+    import time
+    import types
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import ctypes as C
+        from seq2seqsharp_b200 import gpt as G
+        log = []
+
+        class FakeLib:
+            def __getattr__(self, name):
+                def call(*a):
+                    log.append((name, time.monotonic()))
+                    return 1
+                return call
+        G.N.lib = lambda: FakeLib()
+        g = G.GPT.__new__(G.GPT)
+        g._h, g._comm, g._peer_mapped, g._group = C.c_void_p(1), C.c_void_p(2), True, None
+        if rank == 1:
+            time.sleep(0.5)   # a late rank: the early one must wait for it before freeing
+        g.close()
+        q.put((rank, log))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_tensor_parallel_teardown_is_two_phase():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_teardown_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    for r in (0, 1):
+        assert [n for n, _ in res[r]] == ["TSB200_GptTpClose", "TSB200_CommPeerClose", "TSB200_GptDestroy", "TSB200_CommDestroy"]
+    last_unmap = max(t for r in (0, 1) for n, t in res[r] if n == "TSB200_CommPeerClose")
+    first_free = min(t for r in (0, 1) for n, t in res[r] if n == "TSB200_GptDestroy")
+    assert first_free >= last_unmap      # CLOCK_MONOTONIC is shared by the processes of one host
