@@ -302,6 +302,12 @@ TSB200_API int TSB200_CommPeerClose(void* comm);
  * For hosts that want a tighter bound than a second per step, and for tests that make a wait run out without any
  * fault.  No counterpart in the reference (its kernels never wait on each other). */
 TSB200_API int TSB200_GptSetWaitLimit(void* gpt, int polls);
+/* Host-only check of the weight layout of the owner-partitioned decode-step kernel (fp16 engines, one GPU, up to four
+ * sequences): for a model shape and a number of CTAs it verifies that the CTAs' shares tile every matrix exactly once,
+ * that the re-packer places each block where the kernel's consumer loops read it, and that the streams are contiguous.
+ * Needs no device.  No counterpart in the reference (its cuBLAS calls read row-major weights,
+ * TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-504). */
+TSB200_API int TSB200_OwnerLayoutSelfTest(int L, int d, int H, int Hkv, int hd, int F, int V, int glu, int n_ctas);
 
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);

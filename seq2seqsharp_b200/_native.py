@@ -135,6 +135,7 @@ def lib():
         "TSB200_GptSetComm": (i32, [vp, vp]),
         "TSB200_GptReset": (i32, [vp]),
         "TSB200_GptSetWaitLimit": (i32, [vp, i32]),
+        "TSB200_OwnerLayoutSelfTest": (i32, [i32] * 9),
         "TSB200_GptPrefill": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), i32, vp, C.POINTER(i32)]),
         "TSB200_GptGetLogits": (i32, [vp, vp, vp]),

@@ -18,6 +18,7 @@
 #include <string>
 #include <vector>
 
+#include "decode_owner.cuh"
 #include "kernels.cuh"
 
 namespace tsb {
@@ -189,6 +190,12 @@ struct Gpt {
   int64_t stack_counter_bytes = 0;
   long long* stack_trace = nullptr;  // optional timestamps (TSB200_GptDebugStackTrace, -DTSB200_TRACE builds)
   unsigned poll_limit = 0;           // 0: default; polls of a dependency counter before a CTA of the persistent kernel gives up
+  // owner-partitioned persistent decode step (decode_owner.cu): fp16 engines on one GPU, up to own_cap sequences.  It
+  // keeps a second copy of the layer weights, cut into one contiguous stream per CTA (built on first use).
+  bool use_owner = true;             // TSB200_OWNER=0: keep the stream-K persistent kernel (saves the second weight copy)
+  int own_cap = 0;                   // largest batch it is used for: stack_cap unless TSB200_OWNER_MAXB says otherwise
+  OwnerModel* own = nullptr;
+  int own_B = 0;                     // batch the owner kernel serves for the current program (0: not in use)
 };
 
 enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_STACK = 8, KC_COUNT = 9 };
@@ -485,7 +492,30 @@ static int ensure_stack(Gpt* g, int B) {
   const TSB200GptConfig& c = g->c;
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
   if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
-  if (!g->use_stack || B > g->stack_max_B) return 1;
+  g->own_B = 0;
+  if (!g->use_stack) return 1;
+  if (g->use_owner && g->tp == 1 && B <= (g->own_cap > 0 ? g->own_cap : g->stack_cap) && B <= kOwnMaxRows) {
+    OwnDims D{};
+    D.L = c.L; D.d = c.d; D.H = c.H; D.Hkv = c.Hkv; D.hd = c.hd; D.F = c.F; D.V = c.V; D.glu = g->glu;
+    if (owner_applicable(D, c.dtype, g->st->sm_count)) {
+      if (!g->own) {
+        std::vector<OwnLayerPtrs> lp(c.L);
+        for (int k = 0; k < c.L; ++k) {
+          const LayerW& L = g->L[k];
+          lp[k] = OwnLayerPtrs{L.n1_g, L.n1_b, L.wqkv, L.bqkv, L.wo, L.bo, L.n2_g, L.n2_b, L.w1, L.b1, L.w2, L.b2, L.cK, L.cV};
+        }
+        TSB_TRY(owner_create(c.device, g->st, D, c.norm_type, c.act, c.pe_type == 2, c.eps, c.max_tokens, lp.data(), g->nf_g, g->nf_b,
+                             g->head_w, g->head_b, &g->own));
+      }
+      if (!owner_packed(g->own)) {
+        TSB_TRY(owner_repack(g->own, g->s));
+        TSB_CUDA(cudaStreamSynchronize(g->s));
+      }
+      g->own_B = B;
+      return 1;
+    }
+  }
+  if (B > g->stack_max_B) return 1;
   const bool tp = g->tp > 1;
   if (tp && !(g->xch_ready && c.dtype == TSB200_F16 && c.d <= 4096 && c.d % 4 == 0 && g->tp_peer)) return 1;  // per-operation launches + all-reduce
   if (g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) return 1;
@@ -589,6 +619,14 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
   }
+  if (S == 1 && use_state && g->use_stack && g->own_B == B && owner_packed(g->own)) {
+    prof_begin(g);
+    const int r = owner_launch(g->own, g->st, B, g->x, g->logits, g->rope_tab, dT, g->err_flag, g->poll_limit, g->pdl, g->s);
+    if (r != 2) {
+      prof_end(g, KC_STACK);
+      return r;
+    }
+  }
   if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
     StackConfig sc{};
     sc.dtype = dt; sc.M = B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd; sc.Tmax = c.max_tokens; sc.qkv_rs = g->Nqkv;
@@ -657,6 +695,7 @@ static int check_err_flag(Gpt* g) {
   if (e) {
     cudaMemset(g->err_flag, 0, sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
+    owner_reset_counters(g->own);
     TSB_FAIL("a kernel gave up waiting (a dependency counter or a shared-memory barrier did not arrive within its limit); "
              "the results of this call and the state of its sequences are invalid: reset or restore the cache before the next call");
   }
@@ -786,6 +825,10 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
     if (e) g->stack_cap = atoi(e);
     e = getenv("TSB200_GEMV_MAXROWS");
     if (e) g->gemv_rows = atoi(e);
+    e = getenv("TSB200_OWNER");
+    g->use_owner = !(e && e[0] == '0');
+    e = getenv("TSB200_OWNER_MAXB");
+    if (e) g->own_cap = atoi(e);
   }
   const TSB200GptConfig& cc = g->c;
   const int64_t d = cc.d, F = cc.F, V = cc.V, Hd = (int64_t)cc.H * cc.hd, KVd = (int64_t)cc.Hkv * cc.hd;
@@ -852,7 +895,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   g->topp_ws_bytes = TSB200_TopPWorkspaceBytes(MB, cc.V);
   G_ALLOC(g->topp_ws, g->topp_ws_bytes);
 #undef G_ALLOC
-  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device) || !init_tc_attrs(cc.device) || !init_stack_attrs(cc.device)) return fail();
+  if (!init_linear_attrs(cc.device) || !init_topp_attrs(cc.device) || !init_stream_attrs(cc.device) || !init_tc_attrs(cc.device) || !init_stack_attrs(cc.device) || !init_owner_attrs()) return fail();
   if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) {
     set_last_error("gpt_create: cudaEventCreate failed");
     return fail();
@@ -880,6 +923,7 @@ int TSB200_GptDestroy(void* h) {
   for (int r = 0; r < kStackMaxRanks; ++r)
     if (g->xch_open[r]) cudaIpcCloseMemHandle(g->xch_peer[r]);
   if (g->xch_region) cudaFree(g->xch_region);
+  owner_destroy(g->own);
   for (void* p : g->allocs)
     if (p) cudaFree(p);
   delete g;
@@ -922,6 +966,7 @@ int TSB200_GptSetWeight(void* h, const char* name, const void* data, int dtype, 
   }
   if (tmp) cudaFree(tmp);
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  owner_invalidate(g->own);  // the per-CTA weight streams are rebuilt from the packed matrices on the next decode
   return ok;
 }
 
@@ -975,6 +1020,7 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
   }
   cudaFree(tmp);
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  owner_invalidate(g->own);
   return ok;
 }
 

@@ -77,6 +77,26 @@ int launch_decode_stack(int device, DeviceState* st, const StackConfig& c, const
                         int n_ops, void* partials, void* counters, void* attn_part, int* error_flag,
                         long long* trace, bool pdl, cudaStream_t s);
 int init_stack_attrs(int device);
+// ---- owner-partitioned persistent decode step (decode_owner.cu): fp16, one GPU, up to four sequences ------------------
+struct OwnDims;
+struct OwnerModel;
+struct OwnLayerPtrs {  // the engine's buffers of one layer (weights in the packed tile layout)
+  const void *n1_g, *n1_b, *wqkv, *bqkv, *wo, *bo, *n2_g, *n2_b, *w1, *b1, *w2, *b2;
+  void *cK, *cV;
+};
+int owner_applicable(const OwnDims& D, int dtype, int sm_count);
+int owner_create(int device, DeviceState* st, const OwnDims& D, int norm_type, int act, int use_rope, float eps, int Tmax,
+                 const OwnLayerPtrs* layers, const void* nf_g, const void* nf_b, const void* head_w, const void* head_b,
+                 OwnerModel** out);
+void owner_destroy(OwnerModel* m);
+int owner_repack(OwnerModel* m, cudaStream_t s);
+bool owner_packed(const OwnerModel* m);
+void owner_invalidate(OwnerModel* m);
+int owner_reset_counters(OwnerModel* m);
+long long owner_stream_bytes(const OwnerModel* m);
+int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* logits, const float2* rope_tab, const int* dT,
+                 int* error_flag, unsigned poll_limit, bool pdl, cudaStream_t s);
+int init_owner_attrs();
 int64_t packed_bytes(int dtype, int K, int N);
 // Element offset of (k, c) inside one packed 16 KB tile (k < 32, c < tile columns).  fp32 tiles are plain
 // [32 k][128 columns].  fp16 tiles are stored as the shared-memory image the tensor cores want: four 64-column
