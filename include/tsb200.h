@@ -309,6 +309,13 @@ TSB200_API int TSB200_GptSetWaitLimit(void* gpt, int polls);
  * TensorSharp.CUDA/MatrixMul/CudaMatrixMulMM.cs:305-504). */
 TSB200_API int TSB200_OwnerLayoutSelfTest(int L, int d, int H, int Hkv, int hd, int F, int V, int glu, int n_ctas);
 
+#ifdef TSB200_TRACE
+/* Development builds only (-DTSB200_TRACE): the persistent decode-step kernels stamp %globaltimer per CTA and block of
+ * the program into `device_buffer` (NULL switches it off).  The shipped library exports neither of these. */
+TSB200_API int TSB200_GptDebugStackTrace(void* gpt, void* device_buffer);
+TSB200_API int TSB200_DebugSetGemvTrace(void* device_buffer);
+#endif
+
 TSB200_API int TSB200_GptCreate(const TSB200GptConfig* cfg, void** gpt);
 TSB200_API int TSB200_GptDestroy(void* gpt);
 /* name = the reference's weight key (IModel.AddWeights/GetWeights, Seq2SeqSharp/Tools/WeightTensor.cs:571-604),

@@ -16,7 +16,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-]
+] + os.environ.get("TSB200_NVCC_FLAGS", "").split()   # e.g. -DTSB200_TRACE: kernels stamp %globaltimer for development
 
 
 def _sources():

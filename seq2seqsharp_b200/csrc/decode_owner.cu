@@ -37,7 +37,7 @@ struct OwnArgs {
   float* logits;                  // [M, V]
   long long* X[3];                // residual stream, fixed point [kOwnMaxRows, d]
   long long* QA[2];               // group accumulators of q|k|v [Hkv][kOwnMaxRows][QW], fixed point
-  float* AP;                      // partial softmax states [rows][Hkv][grp][gmax][hd + 2]
+  float* AP;                      // partial softmax states [rows][Hkv][grp][gmax][hd + 4]: max, sum, -, -, value[hd]
   unsigned* cnt;                  // [2L block counters | L*Hkv*2 group counters | exit], kOwnCntStride words apart
   const float2* rope_tab;
   const int* dT;
@@ -48,8 +48,18 @@ struct OwnArgs {
   int stages;
   // shared memory (bytes from the aligned base, after the ring)
   int xstride, ystride, hstride, qstride;    // elements between rows
-  int off_xs, off_red, off_merge, off_ys, off_hs, off_qs, off_gsum, off_bar, gsum_cols;
+  int off_xs, off_red, off_merge, off_ys, off_hs, off_qs, off_gsum, off_qbias, off_qcol, off_bar, gsum_cols;
+  long long* trace;               // -DTSB200_TRACE builds: [grid][2L + 1 blocks][16] %globaltimer stamps
 };
+
+#ifdef TSB200_TRACE
+#define OTRACE(block, slot)                                                                                  \
+  do {                                                                                                       \
+    if (a.trace && threadIdx.x == 0) a.trace[((size_t)blockIdx.x * (2 * a.L + 1) + (block)) * 16 + (slot)] = gtimer(); \
+  } while (0)
+#else
+#define OTRACE(block, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ long long own_fix(float v) { return __float2ll_rn(v * kOwnFix); }
 __device__ __forceinline__ float own_unfix(long long v) { return __ll2float_rn(v) * kOwnUnfix; }
@@ -58,141 +68,341 @@ __device__ __forceinline__ void own_add(long long* p, long long v) {
 }
 __device__ __forceinline__ long long own_ldcg(const long long* p) { return __ldcg(p); }
 __device__ __forceinline__ void own_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ------------------------------------------------------------------------------------------- the weight ring (consumer side)
+// Every warp reads its own 512-byte block of every 4 KB row, in order.  Waiting for tiles and handing them back is
+// decoupled from the loads: before a burst of `cnt` blocks the warp makes sure the tiles that hold them have landed
+// (need), then loads them with plain shared-memory loads whose addresses only advance (ptr / step), and after the
+// matching mma instructions have consumed the registers it hands back every tile it has finished (release).  The loops
+// that carry the loads contain no branches, so the compiler pipelines loads and mma instructions freely.
+__device__ __forceinline__ bool own_wait_full(uint64_t* bar, unsigned par, bool dead) {
+  if (dead) return true;   // a CTA that gave up does not wait any more
+  return mbar_wait(bar, par, kSpinLimit);
+}
+// non-blocking look at a barrier phase
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 struct OwnRing {
-  uint32_t stage0;
-  uint64_t *full, *empty;
-  int S, slot, r;
-  unsigned par;
+  unsigned char* base;         // stage memory
+  const unsigned char* src;    // this CTA's stream in global memory
+  uint64_t* full;              // per stage: the bytes of the tile have landed (one arrival + transaction bytes)
+  uint64_t* empty;             // per stage: all eight warps have finished the tile (eight arrivals)
+  int S, rows;                 // stages, rows of the ring (4 per stage)
+  int n_tiles;                 // tiles of the CTA's stream
+  int pos;                     // ring row of the next block
+  int n;                       // rows consumed so far (this launch)
+  int t_have, t_rel;           // tiles known to have landed / finished by this warp
+  int w_slot, r_slot;
+  int f_next, f_slot;          // the next tile this warp is responsible for refilling (tiles w, w + 8, ...) and its stage
+  unsigned w_par, f_par;
   bool dead;
   volatile int* s_err;
-  // the next block of warp `w`: one 16-byte load per lane; a stage goes back to the producer after its fourth row
-  __device__ __forceinline__ uint4 next(int w, int lane) {
-    if (r == 0 && !dead) {
-      if (!mbar_wait(&full[slot], par, kSpinLimit)) {
-        *s_err = 1;
-        dead = true;
+  volatile int* s_code;        // which ring wait ran out (for the error message)
+#ifdef TSB200_TRACE
+  long long wait_cycles = 0, rel_cycles = 0;
+#endif
+  __device__ __forceinline__ void issue(int slot, int tile) {
+    mbar_expect_tx(&full[slot], kOwnTileBytes);
+    bulk_g2s(base + (size_t)slot * kOwnTileBytes, src + (size_t)tile * kOwnTileBytes, kOwnTileBytes, &full[slot]);
+  }
+  // Hands back every tile this warp has finished (a fire-and-forget arrival).  There is no producer warp: tile t is
+  // refilled (with tile t + S) by warp t % 8 once all eight warps have handed it back.  The warp only LOOKS at the
+  // barrier (no wait): a tile that is not free yet is tried again at the warp's next hand-back, so no warp ever stalls
+  // for a slower one.  `block`: wait (bounded) instead - used at the end of a job, before the warps go into a phase
+  // without hand-backs.
+  __device__ __forceinline__ void refill(int lane, bool block) {
+    if (lane == 0 && !dead) {
+#pragma unroll 1
+      while (f_next < t_rel && f_next + S < n_tiles) {
+        bool free_now = mbar_test(&empty[f_slot], f_par);
+        if (!free_now && block) {
+#pragma unroll 1
+          for (unsigned q = 0; q < (kSpinLimit >> 10) && !free_now && !*s_err; ++q) free_now = mbar_wait(&empty[f_slot], f_par, 1024u);
+          if (!free_now) {
+            *s_err = 1;
+            *s_code = 0x20000 | (f_next & 0xffff);   // a stage was not handed back by all warps
+          }
+        }
+        if (!free_now) break;
+        issue(f_slot, f_next + S);
+        f_next += kConsumerWarps;
+        f_slot += kConsumerWarps;
+#pragma unroll 1
+        while (f_slot >= S) {
+          f_slot -= S;
+          f_par ^= 1u;
+        }
       }
     }
-    uint4 v;
-    const uint32_t addr = stage0 + (uint32_t)slot * kOwnTileBytes + (uint32_t)r * kOwnRowBytes + (uint32_t)w * kOwnBlockBytes + (uint32_t)lane * 16u;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    if (++r == 4) {
-      r = 0;
+  }
+  // makes sure the tiles that hold rows [n, n + cnt) have landed (never beyond the end of the stream).  A warp that
+  // has to wait keeps looking after the stages it is responsible for refilling: the tile it waits for may be one of them.
+  __device__ __forceinline__ void need(int cnt, int lane) {
+    int t_need = (n + cnt + 3) >> 2;
+    if (t_need > n_tiles) t_need = n_tiles;
+#pragma unroll 1
+    while (t_have < t_need) {
+#ifdef TSB200_TRACE
+      const long long c0 = clock64();
+#endif
+      if (!dead && !mbar_test(&full[w_slot], w_par)) {
+        bool ok = false;
+#pragma unroll 1
+        for (unsigned q = 0; q < (kSpinLimit >> 8) && !ok && !*s_err; ++q) {
+          refill(lane, false);
+          ok = mbar_wait(&full[w_slot], w_par, 256u);
+        }
+        if (!ok) {
+          *s_err = 1;
+          *s_code = 0x10000 | (t_have & 0xffff);   // a weight tile did not land
+          dead = true;
+        }
+      }
+#ifdef TSB200_TRACE
+      wait_cycles += clock64() - c0;
+#endif
+      ++t_have;
+      if (++w_slot == S) {
+        w_slot = 0;
+        w_par ^= 1u;
+      }
+    }
+  }
+  __device__ __forceinline__ const uint4* ptr(int w, int lane) const {
+    return reinterpret_cast<const uint4*>(base + (size_t)pos * kOwnRowBytes + w * kOwnBlockBytes + lane * 16);
+  }
+  __device__ __forceinline__ void step() {
+    pos = (pos + 1 == rows) ? 0 : pos + 1;
+    ++n;
+  }
+  __device__ __forceinline__ void release(int w, int lane) {
+    (void)w;
+    const int t_done = n >> 2;
+    if (t_rel < t_done) {
+#ifdef TSB200_TRACE
+      const long long c0 = clock64();
+#endif
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[slot]);
-      if (++slot == S) {
-        slot = 0;
-        par ^= 1u;
+#pragma unroll 1
+      while (t_rel < t_done) {
+        if (lane == 0) mbar_arrive(&empty[r_slot]);
+        ++t_rel;
+        if (++r_slot == S) r_slot = 0;
       }
+      refill(lane, false);
+#ifdef TSB200_TRACE
+      __syncwarp();
+      rel_cycles += clock64() - c0;
+#endif
     }
-    return v;
   }
 };
 
 // ------------------------------------------------------------------------------------------- jobs (consumer side)
 // K-split job: see OwnJob.  `xb` is the B operand (activations, fp16 [rows][xstride]) whose element 0 is the job's first k.
 // emit(column of the job, row, sum) is called once per output by some thread after the eight warps' sums have met.
-template <typename Emit>
-__device__ __forceinline__ void own_job_ksplit(const OwnJob& j, OwnRing& R, const __half* xb, int xstride, int M, float* red, int w,
-                                               int lane, int tid, Emit emit) {
+constexpr int kOwnRedCols = 256;   // columns the eight warps' sums can meet for at a time (16 strips)
+
+// Where the finished sums of a job go.  The job loops are separate (not inlined) functions so that the kernel holds ONE
+// copy of each: inlined at every use the kernel grew to 650 KB of code and ran out of the instruction cache, which
+// slowed every phase of the program by a factor of two to three.
+enum OwnEmitKind { OWN_EMIT_ADD64 = 0, OWN_EMIT_SMEM = 1, OWN_EMIT_LOGITS = 2 };
+struct OwnEmit {
+  int kind;
+  long long* x64;       // ADD64: fixed-point accumulator, element [row * stride + cbase + column]
+  float* f32;           // SMEM: f32[row * stride + column]; LOGITS: f32[row * stride + cbase + column] = sum + bias
+  const __half* bias;
+  int stride, cbase, limit;
+};
+__device__ __forceinline__ void own_emit(const OwnEmit& em, int col, int n, float v) {
+  if (em.kind == OWN_EMIT_ADD64) {
+    own_add(em.x64 + (size_t)n * em.stride + em.cbase + col, own_fix(v));
+  } else if (em.kind == OWN_EMIT_SMEM) {
+    em.f32[(size_t)n * em.stride + col] = v;
+  } else {
+    const int c = em.cbase + col;
+    if (c < em.limit) em.f32[(size_t)n * em.stride + c] = v + __half2float(em.bias[c]);
+  }
+}
+
+// The inner loops are instantiated for every burst width: with the width a compile-time constant they are straight-line
+// code (no guards around the loads and the mma instructions), which is what lets eight warps eat the ring faster than
+// HBM refills it (measured: the same loop with run-time guards ran at a third of the rate).
+template <int WC>
+__device__ __forceinline__ void own_ksplit_pass(float (&acc)[kOwnKChunk][4], OwnRing& R, const __half* xrow, bool row_live, int ksw, int ks,
+                                                int w, int lane) {
+  R.need(WC, lane);
+#pragma unroll 1
+  for (int kk = 0; kk < ksw; ++kk) {
+    const int kst = w * ksw + kk;
+    // every lane loads (dead lanes from a valid address), the values of dead lanes are replaced by zero: no divergent branch
+    const bool blive = row_live && kst < ks;
+    const int kc = kst < ks ? kst : 0;
+    const uint32_t v0 = *reinterpret_cast<const uint32_t*>(xrow + kc * 16), v1 = *reinterpret_cast<const uint32_t*>(xrow + kc * 16 + 8);
+    const uint32_t b0 = blive ? v0 : 0u, b1 = blive ? v1 : 0u;
+    uint4 av[WC];
+#pragma unroll
+    for (int s = 0; s < WC; ++s) {
+      av[s] = *R.ptr(w, lane);
+      R.step();
+    }
+    R.need(WC, lane);   // tiles of the blocks to come: the barrier round trip overlaps the loads above and the mma below
+#pragma unroll
+    for (int s = 0; s < WC; ++s) own_mma(acc[s], av[s].x, av[s].y, av[s].z, av[s].w, b0, b1);
+    R.release(w, lane);
+  }
+}
+
+__device__ __noinline__ void own_job_ksplit(const OwnJob* jp, OwnRing* Rp, const __half* xb, int xstride, int M, float* red,
+                                            const OwnEmit* emp) {
+  const OwnJob& j = *jp;
   if (j.nrows == 0) return;
+  OwnRing R = *Rp;        // the ring state lives in registers while the job runs
+  const OwnEmit em = *emp;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const bool row_live = g8 < M;
   const __half* xrow = xb + (size_t)(row_live ? g8 : 0) * xstride + 2 * t4;
-  for (int c = 0; c < j.nchunks; ++c) {
-    const int left = j.ws - c * kOwnKChunk;
-    const int wc = left < kOwnKChunk ? left : kOwnKChunk;
+  const int ws = j.ws, ksw = j.ksw, ks = j.ks, nchunks = j.nchunks;
+  int held0 = 0, held = 0;   // strips [held0, held0 + held) wait in `red` for the reduction
+  for (int c = 0; c < nchunks; ++c) {
+    const int wc = own_chunk_width(ws, nchunks, c);
     float acc[kOwnKChunk][4];
 #pragma unroll
     for (int s = 0; s < kOwnKChunk; ++s)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[s][e] = 0.0f;
-    for (int kk = 0; kk < j.ksw; ++kk) {
-      const int kst = w * j.ksw + kk;
-      const bool klive = kst < j.ks;
-      uint32_t b0 = 0u, b1 = 0u;
-      if (row_live && klive) {
-        b0 = *reinterpret_cast<const uint32_t*>(xrow + kst * 16);
-        b1 = *reinterpret_cast<const uint32_t*>(xrow + kst * 16 + 8);
-      }
-#pragma unroll
-      for (int s = 0; s < kOwnKChunk; ++s) {
-        if (s < wc) {
-          const uint4 av = R.next(w, lane);
-          own_mma(acc[s], av.x, av.y, av.z, av.w, b0, b1);
-        }
-      }
+    switch (wc) {
+      case 1: own_ksplit_pass<1>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 2: own_ksplit_pass<2>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 3: own_ksplit_pass<3>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 4: own_ksplit_pass<4>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 5: own_ksplit_pass<5>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 6: own_ksplit_pass<6>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      case 7: own_ksplit_pass<7>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
+      default: own_ksplit_pass<8>(acc, R, xrow, row_live, ksw, ks, w, lane); break;
     }
-    // the eight warps' sums meet: red[warp][column of the chunk][row]
+    // this warp's sums of the chunk go to red[warp][column][row]; the warps' sums meet when `red` is full or the job ends
 #pragma unroll
     for (int s = 0; s < kOwnKChunk; ++s) {
       if (s < wc) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int n = 2 * t4 + (e & 1), col = s * 16 + g8 + ((e >> 1) << 3);
-          if (n < M) red[(w * (kOwnKChunk * 16) + col) * M + n] = acc[s][e];
+          const int n = 2 * t4 + (e & 1), col = (held + s) * 16 + g8 + ((e >> 1) << 3);
+          if (n < M) red[(w * kOwnRedCols + col) * M + n] = acc[s][e];
         }
       }
     }
-    consumers_sync();
-    for (int idx = tid; idx < wc * 16 * M; idx += 256) {
-      const int n = idx % M, col = idx / M;
-      float v = 0.0f;
+    held += wc;
+    const bool last = c + 1 == nchunks;
+    if (last || held + own_chunk_width(ws, nchunks, c + 1) > kOwnRedCols / 16) {
+      R.refill(lane, true);   // a warp that waits at the barrier cannot look after its stages: settle them first
+      consumers_sync();
+#pragma unroll 1
+      for (int idx = tid; idx < held * 16 * M; idx += 256) {
+        const int n = idx % M, col = idx / M;
+        float v = 0.0f;
 #pragma unroll
-      for (int ww = 0; ww < kConsumerWarps; ++ww) v += red[(ww * (kOwnKChunk * 16) + col) * M + n];
-      emit(c * kOwnKChunk * 16 + col, n, v);
+        for (int ww = 0; ww < kConsumerWarps; ++ww) v += red[(ww * kOwnRedCols + col) * M + n];
+        own_emit(em, held0 * 16 + col, n, v);
+      }
+      consumers_sync();
+      held0 += held;
+      held = 0;
     }
-    consumers_sync();
   }
+  R.refill(lane, true);
+  *Rp = R;
 }
 
 // strip-split job: a warp holds the complete sums of its strips; emit is called from the accumulator registers.
-template <typename Emit>
-__device__ __forceinline__ void own_job_ssplit(const OwnJob& j, OwnRing& R, const __half* xb, int xstride, int M, int w, int lane,
-                                               Emit emit) {
+template <int SPW>
+__device__ __forceinline__ void own_ssplit_pass(float (&acc)[kOwnMaxSpw][4], OwnRing& R, const __half* xrow, bool row_live, int ks, int w, int lane) {
+  R.need(SPW, lane);
+#pragma unroll 1
+  for (int k = 0; k < ks; ++k) {
+    const uint32_t v0 = *reinterpret_cast<const uint32_t*>(xrow + k * 16), v1 = *reinterpret_cast<const uint32_t*>(xrow + k * 16 + 8);
+    const uint32_t b0 = row_live ? v0 : 0u, b1 = row_live ? v1 : 0u;
+    uint4 av[SPW];
+#pragma unroll
+    for (int s = 0; s < SPW; ++s) {
+      av[s] = *R.ptr(w, lane);
+      R.step();
+    }
+    R.need(SPW, lane);
+#pragma unroll
+    for (int s = 0; s < SPW; ++s) own_mma(acc[s], av[s].x, av[s].y, av[s].z, av[s].w, b0, b1);
+    R.release(w, lane);
+  }
+}
+
+__device__ __noinline__ void own_job_ssplit(const OwnJob* jp, OwnRing* Rp, const __half* xb, int xstride, int M, float* red,
+                                            const OwnEmit* emp) {
+  const OwnJob& j = *jp;
   if (j.nrows == 0) return;
+  OwnRing R = *Rp;
+  const OwnEmit em = *emp;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const bool row_live = g8 < M;
   const __half* xrow = xb + (size_t)(row_live ? g8 : 0) * xstride + 2 * t4;
-  for (int c = 0; c < j.nchunks; ++c) {
+  const int spw = j.spw, ks = j.ks, ws = j.ws, nchunks = j.nchunks;
+  for (int c = 0; c < nchunks; ++c) {
     float acc[kOwnMaxSpw][4];
 #pragma unroll
     for (int s = 0; s < kOwnMaxSpw; ++s)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[s][e] = 0.0f;
-    for (int k = 0; k < j.ks; ++k) {
-      uint32_t b0 = 0u, b1 = 0u;
-      if (row_live) {
-        b0 = *reinterpret_cast<const uint32_t*>(xrow + k * 16);
-        b1 = *reinterpret_cast<const uint32_t*>(xrow + k * 16 + 8);
-      }
-#pragma unroll
-      for (int s = 0; s < kOwnMaxSpw; ++s) {
-        if (s < j.spw) {
-          const uint4 av = R.next(w, lane);
-          own_mma(acc[s], av.x, av.y, av.z, av.w, b0, b1);
-        }
-      }
+    switch (spw) {
+      case 1: own_ssplit_pass<1>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 2: own_ssplit_pass<2>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 3: own_ssplit_pass<3>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 4: own_ssplit_pass<4>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 5: own_ssplit_pass<5>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 6: own_ssplit_pass<6>(acc, R, xrow, row_live, ks, w, lane); break;
+      case 7: own_ssplit_pass<7>(acc, R, xrow, row_live, ks, w, lane); break;
+      default: own_ssplit_pass<8>(acc, R, xrow, row_live, ks, w, lane); break;
     }
+    // the warp's sums go through its own corner of shared memory so that all 32 lanes issue the atomic adds (for one
+    // sequence only 8 lanes hold live sums) and the code stays small
+    float* mine = red + (size_t)w * (kOwnMaxSpw * 16) * M;
+    __syncwarp();
 #pragma unroll
     for (int s = 0; s < kOwnMaxSpw; ++s) {
-      const int strip = c * 8 * j.spw + w * j.spw + s;
-      if (s < j.spw && strip < j.ws) {
+      if (s < spw) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int n = 2 * t4 + (e & 1), col = strip * 16 + g8 + ((e >> 1) << 3);
-          if (n < M) emit(col, n, acc[s][e]);
+          const int n = 2 * t4 + (e & 1), col = s * 16 + g8 + ((e >> 1) << 3);
+          if (n < M) mine[col * M + n] = acc[s][e];
         }
       }
     }
+    __syncwarp();
+    const int strip0 = c * 8 * spw + w * spw;
+    int live = ws - strip0;
+    live = live < 0 ? 0 : (live > spw ? spw : live);
+#pragma unroll 1
+    for (int idx = lane; idx < live * 16 * M; idx += 32) {
+      const int n = idx % M, col = idx / M;
+      own_add(em.x64 + (size_t)n * em.stride + em.cbase + strip0 * 16 + col, own_fix(mine[idx]));
+    }
   }
+  R.refill(lane, true);
+  *Rp = R;
 }
 
 // ------------------------------------------------------------------------------------------- staging with the fused norm
@@ -218,9 +428,10 @@ __device__ __forceinline__ void own_half4(const uint2& raw, float* f) {
 }
 // xs[m][k] = norm(X[m])[k] in fp16; RMSNorm (xmode 1) or LayerNorm (xmode 2), the arithmetic of the stand-alone kernels
 // (fp32 sums, sqrt, divide).  d <= 4096, d % 4 == 0.
-__device__ __forceinline__ void own_stage_norm(__half* xs, int xstride, const long long* X, const OwnNormConsts& nc, int xmode, float eps,
-                                               int M, int d, int tid, float* s_stat) {
+__device__ __noinline__ void own_stage_norm(__half* xs, int xstride, const long long* X, const OwnNormConsts& nc, int xmode, float eps,
+                                            int M, int d, int tid, float* s_stat) {
   const int lane = tid & 31, w = tid >> 5;
+#pragma unroll 1
   for (int m = 0; m < M; ++m) {
     float v[4][4];
 #pragma unroll
@@ -283,10 +494,14 @@ __device__ __forceinline__ void own_stage_norm(__half* xs, int xstride, const lo
 
 // ------------------------------------------------------------------------------------------- waits between CTAs
 // One thread polls (bounded); everybody learns the outcome.  A CTA that gave up keeps going without waiting.
-__device__ __forceinline__ void own_wait(const unsigned* p, unsigned target, const OwnArgs& a, volatile int* s_err, bool& dead, int tid) {
+// `where` tells a failed wait apart in the engine's error message: (block of the program << 4) | 1 block counter,
+// 2 / 3 first / second group counter of an attention block.
+__device__ __noinline__ void own_wait(const unsigned* p, unsigned target, const OwnArgs& a, volatile int* s_err, bool& dead, int tid,
+                                      int where) {
   if (tid == 0) {
     if (!poll_count(p, target, dead ? 1u : a.poll_limit, a.error_flag)) {
       *s_err = 1;
+      if (!dead) atomicCAS(a.error_flag + 1, 0, where);   // the first wait that ran out (a CTA that follows another's failure is `dead`)
       *a.error_flag = 1;
     }
   }
@@ -301,35 +516,69 @@ __device__ __forceinline__ void own_arrive(unsigned* p, int tid) {
 
 // ------------------------------------------------------------------------------------------- attention of one KV-head group
 // CTA `i` of the group takes the cached tokens [t_beg, t_end) of every row and GH query heads at a time; lane groups of
-// hd/8 lanes own one token per iteration (16-byte loads, four tokens in flight), each runs an online softmax, the lane
+// hd/8 lanes own one token per iteration (16-byte loads, two tokens in flight), each runs an online softmax, the lane
 // groups' states are merged through shared memory and written as this CTA's partial state of (row, head).
 // q (rotated, rounded to fp16, unscaled), the new k and the new v of the group come from shared memory (`qs`).
-template <int GH>
-__device__ __forceinline__ void own_attention(const OwnArgs& a, const OwnLayerDev& Lr, int g, int i, int gsz, int T0, const float* qs,
-                                              float* merge, int tid) {
-  constexpr int EPL = 8;
-  const int hd = a.hd, grp = a.grp, Hkv = a.Hkv, Tmax = a.Tmax;
-  const int lpt = hd / EPL, tpw = 32 / lpt;
-  const int lane = tid & 31, w = tid >> 5;
-  const int sub = lane / lpt, li = lane % lpt;
+// The first batch of K/V rows (row 0) does not depend on q: it is fetched BEFORE the group's q|k|v sums are waited for
+// (own_attn_prefetch) so that its HBM latency is off the dependency chain.
+constexpr int kOwnTokensInFlight = 2;   // cached tokens a lane group has in flight (each inlined copy of the update is 7 KB of code)
+struct OwnKvBatch {
+  TileVec<__half> kv[kOwnTokensInFlight], vv[kOwnTokensInFlight];
+};
+struct OwnAttnGeom {
+  int lpt, tpw, sub, li, nstates, t_beg, t_end, t_cached_end;
+  bool has_new;
+};
+__device__ __forceinline__ OwnAttnGeom own_attn_geom(const OwnArgs& a, int i, int gsz, int T0, int lane) {
+  OwnAttnGeom q;
+  q.lpt = a.hd / 8;
+  q.tpw = 32 / q.lpt;
+  q.sub = lane / q.lpt;
+  q.li = lane % q.lpt;
+  q.nstates = kConsumerWarps * q.tpw;
   const int Tk = T0 + 1;
   const int per = (Tk + gsz - 1) / gsz;
-  const int t_beg = min(Tk, i * per), t_end = min(Tk, t_beg + per);
-  const int t_cached_end = min(t_end, T0);
-  const bool has_new = (t_beg <= T0) && (T0 < t_end);
-  const int rec = hd + 2;
-  const int nstates = kConsumerWarps * tpw;
+  q.t_beg = min(Tk, i * per);
+  q.t_end = min(Tk, q.t_beg + per);
+  q.t_cached_end = min(q.t_end, T0);
+  q.has_new = (q.t_beg <= T0) && (T0 < q.t_end);
+  return q;
+}
+__device__ __forceinline__ void own_attn_load(OwnKvBatch& b, const OwnAttnGeom& q, const __half* Kb, const __half* Vb, int tb, int hd) {
+#pragma unroll
+  for (int u = 0; u < kOwnTokensInFlight; ++u) {
+    const int t = tb + u * q.nstates + q.sub;
+    const size_t o = (size_t)(t < q.t_cached_end ? t : q.t_beg) * hd;  // dead lanes re-read a valid row
+    b.kv[u].lds(Kb + o);
+    b.vv[u].lds(Vb + o);
+  }
+}
+__device__ __forceinline__ void own_attn_prefetch(OwnKvBatch& b, const OwnArgs& a, const OwnLayerDev& Lr, const OwnAttnGeom& q, int g, int w) {
+  const size_t head_off = ((size_t)0 * a.Hkv + g) * a.Tmax * a.hd + q.li * 8;
+  const int tb = q.t_beg + w * q.tpw;
+  if (tb < q.t_cached_end) own_attn_load(b, q, Lr.cK + head_off, Lr.cV + head_off, tb, a.hd);
+}
+template <int GH>
+__device__ __noinline__ void own_attention(const OwnArgs& a, const OwnLayerDev& Lr, const OwnAttnGeom& q, OwnKvBatch& first, int g, int i,
+                                           const float* qs, float* merge, int tid, int p) {
+  (void)p;
+  constexpr int EPL = 8;
+  const int hd = a.hd, grp = a.grp, Hkv = a.Hkv, Tmax = a.Tmax;
+  const int lane = tid & 31, w = tid >> 5;
+  const int rec = hd + 4;
+#pragma unroll 1
   for (int m = 0; m < a.M; ++m) {
     const float* qrow = qs + (size_t)m * a.qstride;
-    const size_t head_off = ((size_t)m * Hkv + g) * Tmax * hd + li * EPL;
+    const size_t head_off = ((size_t)m * Hkv + g) * Tmax * hd + q.li * EPL;
     const __half* Kb = Lr.cK + head_off;
     const __half* Vb = Lr.cV + head_off;
+#pragma unroll 1
     for (int h0 = 0; h0 < grp; h0 += GH) {
       float qf[GH][EPL];
 #pragma unroll
       for (int gg = 0; gg < GH; ++gg)
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) qf[gg][e] = qrow[(h0 + gg) * hd + li * EPL + e] * a.scale;
+        for (int e = 0; e < EPL; ++e) qf[gg][e] = qrow[(h0 + gg) * hd + q.li * EPL + e] * a.scale;
       float mx[GH], l[GH], acc[GH][EPL];
 #pragma unroll
       for (int gg = 0; gg < GH; ++gg) {
@@ -338,53 +587,69 @@ __device__ __forceinline__ void own_attention(const OwnArgs& a, const OwnLayerDe
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[gg][e] = 0.0f;
       }
-      for (int tb = t_beg + w * tpw; tb < t_cached_end; tb += 4 * nstates) {
-        TileVec<__half> kv[4], vv[4];
-        bool live[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int t = tb + q * nstates + sub;
-          live[q] = t < t_cached_end;  // all lanes iterate together (full-warp shuffles); dead lanes re-read token t_beg
-          const size_t o = (size_t)(live[q] ? t : t_beg) * hd;
-          kv[q].lds(Kb + o);
-          vv[q].lds(Vb + o);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float kf[EPL], vf[EPL];
-          kv[q].get(kf);
-          vv[q].get(vf);
-          attn_update<GH, EPL>(qf, kf, vf, mx, l, acc, lpt, live[q]);
-        }
+      // One copy of the update code: the loop runs over this lane group's cached tokens (two loads in flight: the token
+      // being used and the next one) and, on warp 0, once more for the token of this step, which comes from shared memory.
+      const int tb0 = q.t_beg + w * q.tpw;
+      const int n_c = q.t_cached_end > tb0 ? (q.t_cached_end - tb0 + q.nstates - 1) / q.nstates : 0;
+      const int n_it = n_c + ((q.has_new && w == 0) ? 1 : 0);
+      TileVec<__half> kc, vc, kn, vn;
+      if (m == 0) {   // fetched ahead of the wait
+        kc = first.kv[0]; vc = first.vv[0]; kn = first.kv[1]; vn = first.vv[1];
+      } else if (n_c > 0) {
+        OwnKvBatch b2;
+        own_attn_load(b2, q, Kb, Vb, tb0, hd);
+        kc = b2.kv[0]; vc = b2.vv[0]; kn = b2.kv[1]; vn = b2.vv[1];
       }
-      if (has_new && w == 0) {  // the token of this step, from shared memory
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
         float kf[EPL], vf[EPL];
+        bool live;
+        if (it < n_c) {
+          kc.get(kf);
+          vc.get(vf);
+          live = tb0 + it * q.nstates + q.sub < q.t_cached_end;
+          kc = kn;
+          vc = vn;
+          if (it + 2 < n_c) {
+            const int t = tb0 + (it + 2) * q.nstates + q.sub;
+            const size_t o = (size_t)(t < q.t_cached_end ? t : q.t_beg) * hd;  // dead lanes re-read a valid row
+            kn.lds(Kb + o);
+            vn.lds(Vb + o);
+          }
+        } else {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          kf[e] = qrow[grp * hd + li * EPL + e];
-          vf[e] = qrow[(grp + 1) * hd + li * EPL + e];
+          for (int e = 0; e < EPL; ++e) {
+            kf[e] = qrow[grp * hd + q.li * EPL + e];
+            vf[e] = qrow[(grp + 1) * hd + q.li * EPL + e];
+          }
+          live = q.sub == 0;
         }
-        attn_update<GH, EPL>(qf, kf, vf, mx, l, acc, lpt, sub == 0);
+        attn_update<GH, EPL>(qf, kf, vf, mx, l, acc, q.lpt, live);
       }
-      const int st = w * tpw + sub;
+      if (m == 0 && h0 == 0) OTRACE(p, 10);
+      const int st = w * q.tpw + q.sub;
+      const int srec = hd + 2;   // records of the shared-memory merge area
 #pragma unroll
       for (int gg = 0; gg < GH; ++gg) {
-        float* r = merge + ((size_t)st * GH + gg) * rec;
-        if (li == 0) {
+        float* r = merge + ((size_t)st * GH + gg) * srec;
+        if (q.li == 0) {
           r[0] = mx[gg];
           r[1] = l[gg];
         }
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) r[2 + li * EPL + e] = acc[gg][e];
+        for (int e = 0; e < EPL; ++e) r[2 + q.li * EPL + e] = acc[gg][e];
       }
       consumers_sync();
+#pragma unroll 1
       for (int idx = tid; idx < GH * hd; idx += 256) {
         const int gg = idx / hd, e = idx % hd;
         float mm = -INFINITY;
-        for (int q = 0; q < nstates; ++q) mm = fmaxf(mm, merge[((size_t)q * GH + gg) * rec]);
+#pragma unroll 1
+        for (int u = 0; u < q.nstates; ++u) mm = fmaxf(mm, merge[((size_t)u * GH + gg) * srec]);
         float Ls = 0.0f, As = 0.0f;
-        for (int q = 0; q < nstates; ++q) {
-          const float* r = merge + ((size_t)q * GH + gg) * rec;
+#pragma unroll 2
+        for (int u = 0; u < q.nstates; ++u) {
+          const float* r = merge + ((size_t)u * GH + gg) * srec;
           const float cc = (r[0] == -INFINITY) ? 0.0f : __expf(r[0] - mm);
           Ls += r[1] * cc;
           As += r[2 + e] * cc;
@@ -394,15 +659,174 @@ __device__ __forceinline__ void own_attention(const OwnArgs& a, const OwnLayerDe
           pr[0] = mm;
           pr[1] = Ls;
         }
-        pr[2 + e] = As;
+        pr[4 + e] = As;
       }
       consumers_sync();  // the merge area is free again
+      if (m == 0 && h0 == 0) OTRACE(p, 11);
     }
   }
 }
 
+// ---- short ranges: when a CTA's share of the cache is at most kOwnShortTokens tokens (contexts of up to about
+// kOwnShortTokens x CTAs per group tokens) the lane-group scheme above spends its time merging 16-32 partial states.
+// Instead the CTA's K and V rows are copied to shared memory with cp.async (row 0 before the group's q|k|v sums are
+// awaited, so the HBM latency is off the dependency chain), scores are computed by 8 lanes per (head, token), one warp
+// per head forms the softmax statistics, and every thread accumulates two output dimensions: three barriers, no merge.
+constexpr int kOwnShortTokens = 48;
+__device__ __forceinline__ void own_cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void own_cp_async_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// copies the cached rows [t_beg, t_cached_end) of (row m, KV head g) to Ks / Vs (rows of hd + 8 halves)
+__device__ __forceinline__ void own_short_stage(const OwnArgs& a, const OwnLayerDev& Lr, const OwnAttnGeom& q, int g, int m, __half* Ks,
+                                                __half* Vs, int tid) {
+  const int hd = a.hd, v8 = hd / 8, n_c = q.t_cached_end - q.t_beg, rs = hd + 8;
+  const size_t base = (((size_t)m * a.Hkv + g) * a.Tmax + q.t_beg) * hd;
+#pragma unroll 1
+  for (int idx = tid; idx < n_c * v8; idx += 256) {
+    const int t = idx / v8, c = idx % v8;
+    own_cp_async16(Ks + (size_t)t * rs + c * 8, Lr.cK + base + (size_t)t * hd + c * 8);
+    own_cp_async16(Vs + (size_t)t * rs + c * 8, Lr.cV + base + (size_t)t * hd + c * 8);
+  }
+}
+__device__ __noinline__ void own_attention_short(const OwnArgs& a, const OwnLayerDev& Lr, const OwnAttnGeom& q, int g, int i, const float* qs,
+                                                 float* region, int tid) {
+  const int hd = a.hd, grp = a.grp, rs = hd + 8, NTP = kOwnShortTokens + 1;
+  __half* Ks = reinterpret_cast<__half*>(region);
+  __half* Vs = Ks + (size_t)NTP * rs;
+  float* Ss = reinterpret_cast<float*>(Vs + (size_t)NTP * rs);   // [grp][NTP] scores, then exp(score - max)
+  float* stat = Ss + (size_t)grp * NTP;                            // [grp][2] max, sum
+  const int lane = tid & 31, w = tid >> 5;
+  const int n_c = q.t_cached_end - q.t_beg;
+  const int n_tot = n_c + (q.has_new ? 1 : 0);
+  const int rec = hd + 4;
+#pragma unroll 1
+  for (int m = 0; m < a.M; ++m) {
+    const float* qrow = qs + (size_t)m * a.qstride;
+    if (m > 0) {
+      consumers_sync();   // the previous row's K/V are no longer read
+      own_short_stage(a, Lr, q, g, m, Ks, Vs, tid);
+    }
+    if (q.has_new) {   // the token of this step joins as the last row
+#pragma unroll 1
+      for (int e = tid; e < hd; e += 256) {
+        Ks[(size_t)n_c * rs + e] = __float2half_rn(qrow[grp * hd + e]);
+        Vs[(size_t)n_c * rs + e] = __float2half_rn(qrow[(grp + 1) * hd + e]);
+      }
+    }
+    own_cp_async_wait();
+    consumers_sync();
+    // scores: eight lanes per (head, token) pair, hd / 8 dimensions each
+    {
+      const int dpl = hd / 8, l8 = tid & 7;
+#pragma unroll 1
+      const int npair = grp * n_tot;
+      for (int p0 = (tid >> 5) * 4; p0 < npair; p0 += 32) {   // warp-uniform trip count: the shuffles below need every lane
+        const int pi = p0 + ((tid >> 3) & 3);
+        const bool pon = pi < npair;
+        const int h = pon ? pi / n_tot : 0, t = pon ? pi % n_tot : 0;
+        const float* qh = qrow + h * hd + l8 * dpl;
+        const __half* kr = Ks + (size_t)t * rs + l8 * dpl;
+        float dsum = 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < dpl; c += 8) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+          const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 kf = __half22float2(h2[u]);
+            dsum += qh[c + 2 * u] * kf.x + qh[c + 2 * u + 1] * kf.y;
+          }
+        }
+        dsum += __shfl_xor_sync(0xffffffffu, dsum, 4);
+        dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+        dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+        if (l8 == 0 && pon) Ss[h * NTP + t] = dsum * a.scale;
+      }
+    }
+    consumers_sync();
+    // softmax statistics: one warp per head
+#pragma unroll 1
+    for (int h = w; h < grp; h += kConsumerWarps) {
+      float mx = -INFINITY;
+      for (int t = lane; t < n_tot; t += 32) mx = fmaxf(mx, Ss[h * NTP + t]);
+      mx = warp_max(mx);
+      float l = 0.0f;
+      for (int t = lane; t < n_tot; t += 32) {
+        const float pv = __expf(Ss[h * NTP + t] - mx);
+        Ss[h * NTP + t] = pv;
+        l += pv;
+      }
+      l = warp_sum(l);
+      if (lane == 0) {
+        stat[2 * h] = mx;
+        stat[2 * h + 1] = l;
+      }
+    }
+    consumers_sync();
+    // values: two output dimensions per thread
+#pragma unroll 1
+    for (int o = 2 * tid; o < grp * hd; o += 512) {
+      const int h = o / hd, e = o % hd;
+      float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 4
+      for (int t = 0; t < n_tot; ++t) {
+        const float pv = Ss[h * NTP + t];
+        const float2 vf = __half22float2(*reinterpret_cast<const __half2*>(Vs + (size_t)t * rs + e));
+        a0 += pv * vf.x;
+        a1 += pv * vf.y;
+      }
+      float* pr = a.AP + ((((size_t)m * a.Hkv + g) * grp + h) * a.gmax + i) * rec;
+      if (e == 0) {
+        pr[0] = n_tot > 0 ? stat[2 * h] : -INFINITY;
+        pr[1] = n_tot > 0 ? stat[2 * h + 1] : 0.0f;
+      }
+      pr[4 + e] = a0;
+      pr[4 + e + 1] = a1;
+    }
+  }
+}
+
+// Combines the group's partial softmax states (records [max, sum, -, -, value[hd]] per split) for four consecutive output
+// elements, taking every `step`-th split from `first` on.  Eight splits are read at a time with 8- and 16-byte loads that
+// do not depend on each other (one memory round trip per batch) and folded into a running (max, sum, value).
+__device__ __forceinline__ void own_merge_splits(const float* base, int rec, int e4, int gsz, int first, int step, float& mm, float& Ls,
+                                                 float (&As)[4]) {
+  mm = -INFINITY;
+  Ls = 0.0f;
+  As[0] = As[1] = As[2] = As[3] = 0.0f;
+#pragma unroll 1
+  for (int s0 = first; s0 < gsz; s0 += 8 * step) {
+    float2 ml[8];
+    float4 av[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int sc = s0 + u * step < gsz ? s0 + u * step : first;   // clamped: every address is valid
+      ml[u] = __ldcg(reinterpret_cast<const float2*>(base + (size_t)sc * rec));
+      av[u] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)sc * rec + 4 + e4));
+    }
+    float bm = mm;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (s0 + u * step < gsz) bm = fmaxf(bm, ml[u].x);
+    const float c0 = (mm == -INFINITY) ? 0.0f : __expf(mm - bm);
+    Ls *= c0;
+    As[0] *= c0; As[1] *= c0; As[2] *= c0; As[3] *= c0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (s0 + u * step < gsz) {
+        const float cc = (ml[u].x == -INFINITY) ? 0.0f : __expf(ml[u].x - bm);
+        Ls += ml[u].y * cc;
+        As[0] += av[u].x * cc; As[1] += av[u].y * cc; As[2] += av[u].z * cc; As[3] += av[u].w * cc;
+      }
+    mm = bm;
+  }
+}
+
 // ------------------------------------------------------------------------------------------- the kernel
-__global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs a) {
+constexpr int kOwnThreads = kConsumerWarps * 32;   // eight consumer warps; the ring is refilled by the consumers themselves
+
+__global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int S = a.stages;
@@ -415,14 +839,38 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
   __half* hs = reinterpret_cast<__half*>(un + a.off_hs);
   float* qs = reinterpret_cast<float*>(un + a.off_qs);
   float* gsum = reinterpret_cast<float*>(un + a.off_gsum);
+  float* s_qbias = reinterpret_cast<float*>(un + a.off_qbias);   // q|k|v biases of the group, this layer
+  int* s_qcol = reinterpret_cast<int*>(un + a.off_qcol);         // group-local q|k|v column -> column of the packed matrix
   uint64_t* full = reinterpret_cast<uint64_t*>(un + a.off_bar);
   uint64_t* empty = full + 16;
-  __shared__ int s_err, s_last;
+  __shared__ int s_err, s_last, s_code;
   __shared__ float s_stat[64];
   __shared__ OwnJob s_jobs[5];
+  __shared__ float2 s_rope[128];   // cos / sin of this step's position (head sizes up to 256)
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  OwnRing R;
+  R.base = stage_mem;
+  R.src = a.wstream + (size_t)a.cta_row0[cta] * kOwnRowBytes;
+  R.full = full;
+  R.empty = empty;
+  R.S = S;
+  R.rows = 4 * S;
+  R.n_tiles = a.cta_tiles[cta];
+  R.pos = 0;
+  R.n = 0;
+  R.t_have = 0;
+  R.t_rel = 0;
+  R.w_slot = 0;
+  R.r_slot = 0;
+  R.w_par = 0u;
+  R.f_next = w;
+  R.f_slot = w % S;
+  R.f_par = (unsigned)((w / S) & 1);
+  R.dead = false;
+  R.s_err = &s_err;
+  R.s_code = &s_code;
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(&full[i], 1);
@@ -430,76 +878,54 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
     }
     s_err = 0;
     s_last = 0;
+    s_code = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // weights never depend on earlier kernels: fill the ring at once
+    for (int i = 0; i < S && i < R.n_tiles; ++i) R.issue(i, i);
   }
   {
     const int words = 5 * (int)(sizeof(OwnJob) / 4);
     const int* src = reinterpret_cast<const int*>(a.jobs + (size_t)cta * 5);
     int* dst = reinterpret_cast<int*>(s_jobs);
-    for (int i = tid; i < words; i += kStreamThreads) dst[i] = src[i];
+    for (int i = tid; i < words; i += kOwnThreads) dst[i] = src[i];
   }
   __syncthreads();
-
-  if (w == kConsumerWarps) {
-    // producer: the CTA's stream is one contiguous range; weights never depend on earlier kernels
-    if (lane == 0) {
-      const unsigned char* src = a.wstream + (size_t)a.cta_row0[cta] * kOwnRowBytes;
-      const int n_tiles = a.cta_tiles[cta];
-      int issued = 0;
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % S;
-        if (t >= S) {
-          const unsigned par = (unsigned)((t / S - 1) & 1);
-          bool got = false;
-          for (unsigned q = 0; q < (kSpinLimit >> 10) && !got && !*(volatile int*)&s_err; ++q) got = mbar_wait(&empty[s], par, 1024u);
-          if (!got) {
-            *(volatile int*)&s_err = 1;
-            break;
-          }
-        }
-        if (*(volatile int*)&s_err) break;
-        mbar_expect_tx(&full[s], kOwnTileBytes);
-        bulk_g2s(stage_mem + (size_t)s * kOwnTileBytes, src + (size_t)t * kOwnTileBytes, kOwnTileBytes, &full[s]);
-        ++issued;
-      }
-      if (*(volatile int*)&s_err) {
-        // await (bounded) every copy that may still be in flight, so nothing lands after the CTA has left
-        const int first = issued > S ? issued - S : 0;
-        for (int q = first; q < issued; ++q) mbar_wait(&full[q % S], (unsigned)((q / S) & 1));
-        *a.error_flag = 1;
-      }
-    }
-    return;
-  }
 
   grid_dep_wait();  // the residual row of this step, the cache length and last step's cache appends are visible
   const int M = a.M, d = a.d, hd = a.hd, grp = a.grp, Hkv = a.Hkv;
   const int T0 = min(__ldcg(a.dT), a.Tmax - 1);
+  if (a.use_rope && tid < a.hd / 2) s_rope[tid] = a.rope_tab[(size_t)T0 * (a.hd / 2) + tid];   // visible after the first barrier below
   const OwnJob& jq = s_jobs[OWN_QKV];
   const int g = jq.group;
   const int gb = own_group_begin(g, G, Hkv), gsz = own_group_begin(g + 1, G, Hkv) - gb, gi = cta - gb;
   const int QW = (grp + 2) * hd;
+  for (int jc = tid; jc < QW; jc += 256) s_qcol[jc] = own_qkv_col(jc, g, grp, hd, a.H, Hkv);   // visible after the first barrier below
   const int c0 = own_split(d, G, cta), c1 = own_split(d, G, cta + 1);   // this CTA's slice of the residual columns
   unsigned* cntP = a.cnt;                                               // [2L] block counters
   unsigned* cntG = a.cnt + (size_t)2 * a.L * kOwnCntStride;             // [L][Hkv][2] group counters
   unsigned* cntExit = cntG + (size_t)a.L * Hkv * 2 * kOwnCntStride;
-  OwnRing R;
-  R.stage0 = smem_u32(stage_mem);
-  R.full = full;
-  R.empty = empty;
-  R.S = S;
-  R.slot = 0;
-  R.r = 0;
-  R.par = 0u;
-  R.dead = false;
-  R.s_err = &s_err;
   bool dead = false;
 
   // duties of a block: add the old residual value and the bias of the block's last linear to the CTA's slice of the
   // next buffer, clear the slice of the buffer after that
-  auto duties = [&](const long long* Xc, long long* Xn, long long* Xz, const __half* bias) {
-    const int wdt = c1 - c0;
-    for (int idx = tid; idx < M * wdt; idx += 256) {
+  // duties of a block: add the old residual value and the bias of the block's last linear to the CTA's slice of the
+  // next buffer, clear the slice of the buffer after that.  Split in three so that the loads overlap other work: the bias
+  // before the block's wait, the old value right after it (the norm staging's loads follow at once), the adds after the staging.
+  const int wdt = c1 - c0;
+  auto duty_bias = [&](const __half* bias) -> long long {
+    return (bias && tid < M * wdt) ? own_fix(__half2float(bias[c0 + tid % wdt])) : 0;
+  };
+  auto duty_load = [&](const long long* Xc) -> long long {
+    return (tid < M * wdt) ? own_ldcg(Xc + (size_t)(tid / wdt) * d + c0 + tid % wdt) : 0;
+  };
+  auto duty_commit = [&](const long long* Xc, long long* Xn, long long* Xz, const __half* bias, long long v0) {
+    if (tid < M * wdt) {
+      const size_t o = (size_t)(tid / wdt) * d + c0 + tid % wdt;
+      own_add(Xn + o, v0);
+      Xz[o] = 0;
+    }
+#pragma unroll 1
+    for (int idx = tid + 256; idx < M * wdt; idx += 256) {   // slices wider than one element per thread (few CTAs)
       const int m = idx / wdt, col = c0 + idx % wdt;
       long long v = own_ldcg(Xc + (size_t)m * d + col);
       if (bias) v += own_fix(__half2float(bias[col]));
@@ -520,35 +946,60 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
       long long* qz = a.QA[(layer + 1) & 1] + (size_t)g * kOwnMaxRows * QW;
       OwnNormConsts nc;
       own_norm_consts(nc, Lr.g1, Lr.b1n, d, tid);
-      if (p > 0) own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid);
+      // constants of the block that can be fetched before its input exists: the q|k|v biases of the group (to shared
+      // memory) and the bias of the CTA's residual slice
+#pragma unroll 1
+      for (int jc = tid; jc < QW; jc += 256) s_qbias[jc] = __half2float(Lr.bqkv[s_qcol[jc]]);
+      const long long dbias = duty_bias(Lr.bo);
+      if (p > 0) own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+      OTRACE(p, 0);
       R.dead = R.dead || dead;
+      const long long dval = duty_load(Xc);
       own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
-      duties(Xc, Xn, Xz, Lr.bo);
+      duty_commit(Xc, Xn, Xz, Lr.bo, dval + dbias);
       {
         // clear this CTA's part of the group accumulator the NEXT layer uses
         const int n = kOwnMaxRows * QW, z0 = own_split(n, gsz, gi), z1 = own_split(n, gsz, gi + 1);
+#pragma unroll 1
         for (int idx = z0 + tid; idx < z1; idx += 256) qz[idx] = 0;
       }
       consumers_sync();
+      OTRACE(p, 1);
       // q|k|v of the group: this CTA's range of K, sums meet in the group accumulator
-      own_job_ssplit(jq, R, xs + jq.kbase, a.xstride, M, w, lane,
-                     [&](int col, int n, float v) { own_add(qa + (size_t)n * QW + col, own_fix(v)); });
+      {
+        const OwnEmit em{OWN_EMIT_ADD64, qa, nullptr, nullptr, QW, 0, 0};
+        own_job_ssplit(&jq, &R, xs + jq.kbase, a.xstride, M, red, &em);
+      }
       unsigned* gc = cntG + ((size_t)(layer * Hkv + g) * 2) * kOwnCntStride;
+      OTRACE(p, 2);
       own_arrive(gc, tid);
-      own_wait(gc, (unsigned)gsz, a, &s_err, dead, tid);
-      // bias, rounding to fp16 (the model's activation type), RoPE
+      // the cached K/V rows do not depend on q: their loads fly while the group's sums are awaited
+      const OwnAttnGeom ag = own_attn_geom(a, gi, gsz, T0, lane);
+      const bool short_range = (T0 + 1 + gsz - 1) / gsz <= kOwnShortTokens && hd % 64 == 0;   // the same for every CTA of the group
+      OwnKvBatch kv0;
+      if (short_range) {
+        __half* Ks = reinterpret_cast<__half*>(merge);
+        own_short_stage(a, Lr, ag, g, 0, Ks, Ks + (size_t)(kOwnShortTokens + 1) * (hd + 8), tid);
+      } else {
+        own_attn_prefetch(kv0, a, Lr, ag, g, w);
+      }
+      own_wait(gc, (unsigned)gsz, a, &s_err, dead, tid, (p << 4) | 2);
+      OTRACE(p, 3);
+      // bias, rounding to fp16 (the model's activation type)
+#pragma unroll 1
       for (int idx = tid; idx < M * QW; idx += 256) {
-        const int m = idx / QW, jcol = idx % QW;
-        float v = own_unfix(own_ldcg(qa + (size_t)m * QW + jcol));
-        v += __half2float(Lr.bqkv[own_qkv_col(jcol, g, grp, hd, a.H, Hkv)]);
-        qs[(size_t)m * a.qstride + jcol] = __half2float(__float2half_rn(v));
+        const int jc = idx < QW ? idx : idx % QW;
+        const float v = own_unfix(own_ldcg(qa + idx)) + s_qbias[jc];
+        qs[idx] = __half2float(__float2half_rn(v));   // rows of qs are QW apart, like the accumulator's
       }
       consumers_sync();
-      if (a.use_rope) {
+      OTRACE(p, 8);
+      if (a.use_rope) {   // cos / sin of this step's position were staged in shared memory at the start of the kernel
         const int npair = (grp + 1) * hd / 2;   // q heads and k
+#pragma unroll 1
         for (int idx = tid; idx < M * npair; idx += 256) {
           const int m = idx / npair, pr = idx % npair;
-          const float2 cs = a.rope_tab[(size_t)T0 * (hd / 2) + pr % (hd / 2)];
+          const float2 cs = s_rope[pr % (hd / 2)];
           float* q2 = qs + (size_t)m * a.qstride + 2 * pr;
           const float x0 = q2[0], x1 = q2[1];
           q2[0] = __half2float(__float2half_rn(x0 * cs.x - x1 * cs.y));
@@ -557,6 +1008,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
         consumers_sync();
       }
       if (gi == 0) {  // the first CTA of the group appends the new k and v rows to the cache
+#pragma unroll 1
         for (int idx = tid; idx < M * hd; idx += 256) {
           const int m = idx / hd, e = idx % hd;
           const size_t o = (((size_t)m * Hkv + g) * a.Tmax + T0) * hd + e;
@@ -564,35 +1016,59 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
           Lr.cV[o] = __float2half_rn(qs[(size_t)m * a.qstride + (grp + 1) * hd + e]);
         }
       }
-      if (grp % 4 == 0) own_attention<4>(a, Lr, g, gi, gsz, T0, qs, merge, tid);
-      else own_attention<1>(a, Lr, g, gi, gsz, T0, qs, merge, tid);
+      OTRACE(p, 9);
+      if (short_range) own_attention_short(a, Lr, ag, g, gi, qs, merge, tid);
+      else if (grp % 4 == 0) own_attention<4>(a, Lr, ag, kv0, g, gi, qs, merge, tid, p);
+      else own_attention<1>(a, Lr, ag, kv0, g, gi, qs, merge, tid, p);
+      OTRACE(p, 4);
       own_arrive(gc + kOwnCntStride, tid);
-      own_wait(gc + kOwnCntStride, (unsigned)gsz, a, &s_err, dead, tid);
-      // merge the group's partial states: attention output of the group's heads, fp16, in shared memory
+      own_wait(gc + kOwnCntStride, (unsigned)gsz, a, &s_err, dead, tid, (p << 4) | 3);
+      OTRACE(p, 5);
+      // merge the group's partial states: attention output of the group's heads, fp16, in shared memory.  A thread owns
+      // four consecutive outputs; the two halves of the CTA take every other split and meet in shared memory.
       {
-        const int rec = hd + 2, per_row = grp * hd;
-        for (int idx = tid; idx < M * per_row; idx += 256) {
-          const int m = idx / per_row, r = idx % per_row, head = r / hd, e = r % hd;
-          const float* base = a.AP + ((((size_t)m * Hkv + g) * grp + head) * a.gmax) * rec;
-          float mm = -INFINITY;
-          for (int s = 0; s < gsz; ++s) mm = fmaxf(mm, __ldcg(base + (size_t)s * rec));
-          float Ls = 0.0f, As = 0.0f;
-          for (int s = 0; s < gsz; ++s) {
-            const float mi = __ldcg(base + (size_t)s * rec);
-            const float cc = (mi == -INFINITY) ? 0.0f : __expf(mi - mm);
-            Ls += __ldcg(base + (size_t)s * rec + 1) * cc;
-            As += __ldcg(base + (size_t)s * rec + 2 + e) * cc;
+        const int rec = hd + 4, nq = grp * hd / 4;
+        const int half = tid >> 7, ql = tid & 127;
+#pragma unroll 1
+        for (int m = 0; m < M; ++m) {
+#pragma unroll 1
+          for (int q0 = 0; q0 < nq; q0 += 128) {
+            const int qd = q0 + ql;
+            const bool on = qd < nq;
+            const int qc = on ? qd : 0;
+            const int head = (qc * 4) / hd, e4 = (qc * 4) % hd;
+            const float* base = a.AP + ((((size_t)m * Hkv + g) * grp + head) * a.gmax) * rec;
+            float mm, Ls, As[4];
+            own_merge_splits(base, rec, e4, gsz, half, 2, mm, Ls, As);
+            float* mine = red + (size_t)ql * 6;
+            if (half == 1) {
+              mine[0] = mm; mine[1] = Ls; mine[2] = As[0]; mine[3] = As[1]; mine[4] = As[2]; mine[5] = As[3];
+            }
+            consumers_sync();
+            if (half == 0 && on) {
+              const float m2 = mine[0];
+              const float bm = fmaxf(mm, m2);
+              const float ca = (mm == -INFINITY) ? 0.0f : __expf(mm - bm), cb = (m2 == -INFINITY) ? 0.0f : __expf(m2 - bm);
+              const float L = Ls * ca + mine[1] * cb;
+              float o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) o[e] = L > 0.0f ? (As[e] * ca + mine[2 + e] * cb) / L : 0.0f;
+              St4<__half>::st(ys + (size_t)m * a.ystride + qc * 4, o);
+            }
+            consumers_sync();
           }
-          ys[(size_t)m * a.ystride + r] = __float2half_rn(Ls > 0.0f ? As / Ls : 0.0f);
         }
       }
       consumers_sync();
+      OTRACE(p, 6);
       // the group's rows of W0, this CTA's range of output columns
       const OwnJob& jo = s_jobs[OWN_W0];
       R.dead = R.dead || dead;
-      own_job_ksplit(jo, R, ys, a.ystride, M, red, w, lane, tid, [&](int col, int n, float v) {
-        own_add(Xn + (size_t)n * d + jo.cbase + col, own_fix(v));
-      });
+      {
+        const OwnEmit em{OWN_EMIT_ADD64, Xn, nullptr, nullptr, d, jo.cbase, 0};
+        own_job_ksplit(&jo, &R, ys, a.ystride, M, red, &em);
+      }
+      OTRACE(p, 7);
       own_arrive(cntP + (size_t)p * kOwnCntStride, tid);
     }
     // =================================================================== FFN block
@@ -603,20 +1079,39 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
       long long* Xz = a.X[(p + 2) % 3];
       OwnNormConsts nc;
       own_norm_consts(nc, Lr.g2, Lr.b2n, d, tid);
-      own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid);
+      const long long dbias = duty_bias(Lr.bdown);
+      own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+      OTRACE(p, 0);
       R.dead = R.dead || dead;
+      const long long dval = duty_load(Xc);
       own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
-      duties(Xc, Xn, Xz, Lr.bdown);
+      duty_commit(Xc, Xn, Xz, Lr.bdown, dval + dbias);
       const OwnJob& ju = s_jobs[OWN_UP];
       const OwnJob& jd = s_jobs[OWN_DOWN];
+#pragma unroll 1
       for (int idx = tid; idx < M * a.hstride; idx += 256) hs[idx] = __float2half_rn(0.0f);
       consumers_sync();
-      own_job_ksplit(ju, R, xs, a.xstride, M, red, w, lane, tid,
-                     [&](int col, int n, float v) { gsum[(size_t)n * a.gsum_cols + col] = v; });
+      OTRACE(p, 1);
+#ifdef TSB200_TRACE
+      const long long wc0 = R.wait_cycles, rc0 = R.rel_cycles, cc0 = clock64();
+#endif
+      {
+        const OwnEmit em{OWN_EMIT_SMEM, nullptr, gsum, nullptr, a.gsum_cols, 0, 0};
+        own_job_ksplit(&ju, &R, xs, a.xstride, M, red, &em);
+      }
+#ifdef TSB200_TRACE
+      if (a.trace && tid == 0) {
+        a.trace[((size_t)blockIdx.x * (2 * a.L + 1) + p) * 16 + 12] = R.wait_cycles - wc0;   // cycles warp 0 waited for tiles
+        a.trace[((size_t)blockIdx.x * (2 * a.L + 1) + p) * 16 + 13] = clock64() - cc0;        // cycles of the whole job
+        a.trace[((size_t)blockIdx.x * (2 * a.L + 1) + p) * 16 + 14] = R.rel_cycles - rc0;   // cycles in release (hand-back + refill)
+      }
+#endif
       consumers_sync();
+      OTRACE(p, 2);
       // bias, activation, gate: this CTA's hidden units, fp16, in shared memory
       if (a.glu) {
         const int nh = ju.ws * 8;
+#pragma unroll 1
         for (int idx = tid; idx < M * nh; idx += 256) {
           const int m = idx / nh, jl = idx % nh;
           float av = gsum[(size_t)m * a.gsum_cols + 2 * jl] + __half2float(Lr.bup[ju.cbase + 2 * jl]);
@@ -626,6 +1121,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
         }
       } else {
         const int nh = ju.ws * 16;
+#pragma unroll 1
         for (int idx = tid; idx < M * nh; idx += 256) {
           const int m = idx / nh, jl = idx % nh;
           float v = gsum[(size_t)m * a.gsum_cols + jl] + __half2float(Lr.bup[ju.cbase + jl]);
@@ -640,8 +1136,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
         }
       }
       consumers_sync();
+      OTRACE(p, 3);
       // the matching rows of W2: all d output columns, sums go straight into the next residual buffer
-      own_job_ssplit(jd, R, hs, a.hstride, M, w, lane, [&](int col, int n, float v) { own_add(Xn + (size_t)n * d + col, own_fix(v)); });
+      {
+        const OwnEmit em{OWN_EMIT_ADD64, Xn, nullptr, nullptr, d, 0, 0};
+        own_job_ssplit(&jd, &R, hs, a.hstride, M, red, &em);
+      }
+      OTRACE(p, 7);
       own_arrive(cntP + (size_t)p * kOwnCntStride, tid);
     }
   }
@@ -652,20 +1153,30 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_owner_kernel(OwnArgs
     OwnNormConsts nc;
     own_norm_consts(nc, a.gF, a.bF, d, tid);
     grid_dep_launch();  // the sampling kernels may become resident while the LM head streams
-    own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid);
+    own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+    OTRACE(p, 0);
     R.dead = R.dead || dead;
     own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
     consumers_sync();
+    OTRACE(p, 1);
     const OwnJob& jh = s_jobs[OWN_HEAD];
-    own_job_ksplit(jh, R, xs, a.xstride, M, red, w, lane, tid, [&](int col, int n, float v) {
-      const int c = jh.cbase + col;
-      if (c < a.V) a.logits[(size_t)n * a.V + c] = v + __half2float(a.head_b[c]);
-    });
+    {
+      const OwnEmit em{OWN_EMIT_LOGITS, nullptr, a.logits, a.head_b, a.V, jh.cbase, a.V};
+      own_job_ksplit(&jh, &R, xs, a.xstride, M, red, &em);
+    }
+    OTRACE(p, 7);
+  }
+  // a CTA that gave up did not wait for its tiles: let the copies in flight land (bounded) before the CTA leaves
+  if (R.dead || dead) {
+    for (int i = 0; i < S; ++i) mbar_wait(&full[i], 0u, 1u << 16), mbar_wait(&full[i], 1u, 1u << 16);
   }
   // leave: the last CTA out clears the counters for the next launch
   consumers_sync();
   if (tid == 0) {
-    if (*(volatile int*)&s_err) *a.error_flag = 1;
+    if (*(volatile int*)&s_err) {
+      if (*(volatile int*)&s_code) atomicCAS(a.error_flag + 1, 0, *(volatile int*)&s_code);
+      *a.error_flag = 1;
+    }
     __threadfence();
     const unsigned prev = atomicAdd(cntExit, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
@@ -864,7 +1375,7 @@ int owner_create(int device, DeviceState* st, const OwnDims& D, int norm_type, i
                   alloc((void**)&m->d_layers, ld.size() * sizeof(OwnLayerDev), false) &&
                   alloc((void**)&m->X, (size_t)3 * kOwnMaxRows * D.d * sizeof(long long), true) &&
                   alloc((void**)&m->QA, (size_t)2 * D.Hkv * kOwnMaxRows * QW * sizeof(long long), true) &&
-                  alloc((void**)&m->AP, (size_t)kOwnMaxRows * D.Hkv * grp * m->gmax * (D.hd + 2) * sizeof(float), true) &&
+                  alloc((void**)&m->AP, (size_t)kOwnMaxRows * D.Hkv * grp * m->gmax * (D.hd + 4) * sizeof(float), true) &&
                   alloc((void**)&m->cnt, m->cnt_bytes, true);
   if (!ok || cudaMemcpy(m->d_row0, m->cta_row0.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice) != cudaSuccess ||
       cudaMemcpy(m->d_tiles, m->cta_tiles.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess ||
@@ -925,7 +1436,7 @@ long long owner_stream_bytes(const OwnerModel* m) { return m ? m->total_rows * (
 // One decode step for M rows whose embedded fp32 rows are in `x`.  Returns 1 ok, 0 error, 2 not applicable (the caller
 // takes another path).
 int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* logits, const float2* rope_tab, const int* dT,
-                 int* error_flag, unsigned poll_limit, bool pdl, cudaStream_t s) {
+                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, cudaStream_t s) {
   if (!m || !m->packed || M < 1 || M > kOwnMaxRows || !error_flag || !dT) return 2;
   const OwnDims& D = m->D;
   const int grp = D.H / D.Hkv, QW = (grp + 2) * D.hd;
@@ -937,6 +1448,7 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   for (int i = 0; i < 2; ++i) a.QA[i] = m->QA + (size_t)i * D.Hkv * kOwnMaxRows * QW;
   a.AP = m->AP; a.cnt = m->cnt; a.rope_tab = rope_tab; a.dT = dT; a.error_flag = error_flag;
   a.poll_limit = poll_limit ? poll_limit : kPollLimit;
+  a.trace = trace;
   a.L = D.L; a.M = M; a.d = D.d; a.H = D.H; a.Hkv = D.Hkv; a.hd = D.hd; a.grp = grp; a.F = D.F; a.V = D.V; a.Tmax = m->Tmax;
   a.glu = D.glu; a.act = m->act; a.xmode = m->norm_type == 0 ? 2 : 1; a.use_rope = m->use_rope; a.gmax = m->gmax;
   a.eps = m->eps; a.scale = 1.0f / sqrtf((float)D.hd);
@@ -945,9 +1457,13 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   auto up = [](size_t v, size_t al) { return (v + al - 1) / al * al; };
   a.xstride = D.d + 8; a.ystride = grp * D.hd + 8; a.hstride = m->hid_max + 8; a.qstride = QW;
   const size_t xs_b = up((size_t)M * a.xstride * 2, 128);
-  const size_t red_b = up((size_t)kConsumerWarps * kOwnKChunk * 16 * M * 4, 128);
+  const size_t red_b = up((size_t)kConsumerWarps * kOwnRedCols * M * 4, 128);
   const int lpt = D.hd / 8, tpw = 32 / lpt, GH = (grp % 4 == 0) ? 4 : 1;
-  const size_t merge_b = up((size_t)kConsumerWarps * tpw * GH * (D.hd + 2) * 4, 128);
+  size_t merge_b = up((size_t)kConsumerWarps * tpw * GH * (D.hd + 2) * 4, 128);
+  {
+    const size_t short_b = up((size_t)2 * (kOwnShortTokens + 1) * (D.hd + 8) * 2 + (size_t)grp * (kOwnShortTokens + 1) * 4 + (size_t)grp * 8, 128);
+    if (short_b > merge_b) merge_b = short_b;
+  }
   size_t off = 0;
   a.off_xs = 0; a.off_red = (int)xs_b; a.off_merge = 0;
   off = xs_b + red_b > merge_b ? xs_b + red_b : merge_b;
@@ -956,9 +1472,11 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   a.off_qs = (int)off; off += up((size_t)M * a.qstride * 4, 128);
   a.gsum_cols = m->up_cols_max;
   a.off_gsum = (int)off; off += up((size_t)M * a.gsum_cols * 4, 128);
+  a.off_qbias = (int)off; off += up((size_t)QW * 4, 128);
+  a.off_qcol = (int)off; off += up((size_t)QW * 4, 128);
   a.off_bar = (int)off; off += 32 * sizeof(uint64_t);
   const size_t fixed = off + 1024 /* alignment slack */ + 128;
-  const size_t budget = 225 * 1024;  // the kernel also has some static shared memory
+  const size_t budget = 224 * 1024;  // the kernel also has about 2 KB of static shared memory
   if (fixed + 4 * (size_t)kOwnTileBytes > budget) return 2;
   int stages = (int)((budget - fixed) / kOwnTileBytes);
   if (stages > 16) stages = 16;
@@ -967,7 +1485,7 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   {
     // the CTAs wait on one another: the whole grid must be resident at once
     int per_sm = 0;
-    TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_owner_kernel, kStreamThreads, smem));
+    TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_owner_kernel, kOwnThreads, smem));
     if ((long long)per_sm * st->sm_count < m->G) return 2;
   }
   {
@@ -977,7 +1495,7 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(m->G);
-  cfg.blockDim = dim3(kStreamThreads);
+  cfg.blockDim = dim3(kOwnThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute at[1];
@@ -1002,8 +1520,10 @@ static int own_selftest_job(const OwnJob& j, std::vector<int>& seen, int ks_tota
   for (int w = 0; w < 8; ++w) {
     int row = 0;
     if (j.mode == OWN_KSPLIT) {
+      int held0 = 0, held = 0;
       for (int c = 0; c < j.nchunks; ++c) {
-        const int left = j.ws - c * kOwnKChunk, wc = left < kOwnKChunk ? left : kOwnKChunk;
+        const int wc = own_chunk_width(j.ws, j.nchunks, c);
+        TSB_CHECK(wc >= 1 && wc <= kOwnKChunk, "owner layout: chunk width %d", wc);
         for (int kk = 0; kk < j.ksw; ++kk) {
           const int kst = w * j.ksw + kk;
           for (int s = 0; s < kOwnKChunk; ++s) {
@@ -1011,12 +1531,18 @@ static int own_selftest_job(const OwnJob& j, std::vector<int>& seen, int ks_tota
             int kstep, strip;
             bool live;
             own_block_coords(j, row, w, kstep, strip, live);
-            TSB_CHECK(kstep == kst && strip == c * kOwnKChunk + s && live == (kst < j.ks),
+            // the consumer files the sums of this block under column strip held0 + held + s of the job
+            TSB_CHECK(kstep == kst && strip == held0 + held + s && live == (kst < j.ks),
                       "owner layout: K-split job kind %d: row %d warp %d holds (k-step %d, strip %d) but the consumer expects (%d, %d)",
-                      j.kind, row, w, kstep, strip, kst, c * kOwnKChunk + s);
+                      j.kind, row, w, kstep, strip, kst, held0 + held + s);
             if (live) seen[(size_t)kstep * j.ws + strip] += 1;
             ++row;
           }
+        }
+        held += wc;
+        if (c + 1 == j.nchunks || held + own_chunk_width(j.ws, j.nchunks, c + 1) > 16) {
+          held0 += held;
+          held = 0;
         }
       }
     } else {
@@ -1109,7 +1635,7 @@ int owner_layout_selftest(const OwnDims& D, int G) {
 }
 
 int init_owner_attrs() {
-  TSB_CUDA(cudaFuncSetAttribute(decode_owner_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+  TSB_CUDA(cudaFuncSetAttribute(decode_owner_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
   return 1;
 }
 

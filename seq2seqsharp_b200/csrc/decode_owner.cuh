@@ -43,7 +43,7 @@ namespace tsb {
 constexpr int kOwnBlockBytes = 512;       // one mma A operand (16 columns x 16 k, fp16)
 constexpr int kOwnRowBytes = 4096;        // eight blocks, one per consumer warp
 constexpr int kOwnTileBytes = 16384;      // four rows: one stage of the ring
-constexpr int kOwnKChunk = 16;            // K-split jobs: strips accumulated per pass (registers: 16 x 4 floats)
+constexpr int kOwnKChunk = 8;             // K-split jobs: at most this many strips are accumulated per pass (8 x 4 registers)
 constexpr int kOwnMaxSpw = 8;             // strip-split jobs: strips per warp per pass
 constexpr int kOwnMaxRows = 4;            // sequences per launch
 constexpr int kOwnFixShift = 28;          // fixed point: value * 2^28 in a signed 64-bit integer
@@ -52,8 +52,9 @@ enum OwnJobKind { OWN_QKV = 0, OWN_W0 = 1, OWN_UP = 2, OWN_DOWN = 3, OWN_HEAD = 
 enum OwnJobMode { OWN_KSPLIT = 0, OWN_SSPLIT = 1 };
 
 // One CTA's share of one linear: `ks` k-steps (of 16) x `ws` strips (of 16 columns) of the matrix.
-//  K-split mode: warp w owns k-steps [w*ksw, (w+1)*ksw) of the job and all strips; strips are taken kOwnKChunk at a
-//    time; rows are ordered (chunk, kk, strip).  The eight warps' sums meet in shared memory after every chunk.
+//  K-split mode: warp w owns k-steps [w*ksw, (w+1)*ksw) of the job and all strips; strips are taken in nchunks passes of
+//    nearly equal width (at most kOwnKChunk); rows are ordered (chunk, kk, strip).  The eight warps' sums meet in shared
+//    memory.
 //  strip-split mode: warp w owns `spw` strips per chunk of 8*spw strips and all k-steps; rows are ordered
 //    (chunk, k-step, j).  A warp holds complete sums of its strips.
 // In both modes the block of warp w in a row sits at byte w * 512 of the row; blocks outside the job are zero.
@@ -71,6 +72,12 @@ struct OwnJob {
 };
 
 __host__ __device__ __forceinline__ int own_ceil(int a, int b) { return (a + b - 1) / b; }
+// K-split jobs take their ws strips in nchunks = ceil(ws / kOwnKChunk) passes of nearly equal width
+__host__ __device__ __forceinline__ int own_chunk_width(int ws, int nchunks, int c) { return ws / nchunks + (c < ws % nchunks ? 1 : 0); }
+__host__ __device__ __forceinline__ int own_chunk_start(int ws, int nchunks, int c) {
+  const int r = ws % nchunks;
+  return c * (ws / nchunks) + (c < r ? c : r);
+}
 
 // Fills mode-dependent fields of a job whose kind / ks / ws / bases are set.
 __host__ __device__ __forceinline__ void own_job_finish(OwnJob& j, int mode) {
@@ -102,11 +109,11 @@ __host__ __device__ __forceinline__ void own_block_coords(const OwnJob& j, int r
     // rows: for chunk c, for kk < ksw, for s < width(c)
     int c = 0, r = row;
     for (;;) {
-      const int wc = (j.ws - c * kOwnKChunk) < kOwnKChunk ? (j.ws - c * kOwnKChunk) : kOwnKChunk;
+      const int wc = own_chunk_width(j.ws, j.nchunks, c);
       if (r < j.ksw * wc) {
         const int kk = r / wc, s = r % wc;
         kstep = w * j.ksw + kk;
-        strip = c * kOwnKChunk + s;
+        strip = own_chunk_start(j.ws, j.nchunks, c) + s;
         break;
       }
       r -= j.ksw * wc;

@@ -621,7 +621,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   }
   if (S == 1 && use_state && g->use_stack && g->own_B == B && owner_packed(g->own)) {
     prof_begin(g);
-    const int r = owner_launch(g->own, g->st, B, g->x, g->logits, g->rope_tab, dT, g->err_flag, g->poll_limit, g->pdl, g->s);
+    const int r = owner_launch(g->own, g->st, B, g->x, g->logits, g->rope_tab, dT, g->err_flag, g->poll_limit, g->pdl, g->stack_trace, g->s);
     if (r != 2) {
       prof_end(g, KC_STACK);
       return r;
@@ -687,17 +687,18 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
 
 // A kernel whose bounded wait ran out raises the device error word; surface it as a failure of the call.
 static int check_err_flag(Gpt* g) {
-  int e = 0;
-  TSB_CUDA(cudaMemcpy(&e, g->err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  int ew[2] = {0, 0};   // [0] raised, [1] which wait of the owner-partitioned kernel ran out first (0: another kernel)
+  TSB_CUDA(cudaMemcpy(ew, g->err_flag, sizeof(ew), cudaMemcpyDeviceToHost));
+  int e = ew[0];
   e |= tc_take_error();
   e |= gs_take_error();
   if (g->tp > 1) e |= comm_peer_take_error();
   if (e) {
-    cudaMemset(g->err_flag, 0, sizeof(int));
+    cudaMemset(g->err_flag, 0, 2 * sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
     owner_reset_counters(g->own);
-    TSB_FAIL("a kernel gave up waiting (a dependency counter or a shared-memory barrier did not arrive within its limit); "
-             "the results of this call and the state of its sequences are invalid: reset or restore the cache before the next call");
+    TSB_FAIL("a kernel gave up waiting (a dependency counter or a shared-memory barrier did not arrive within its limit; wait site 0x%x); "
+             "the results of this call and the state of its sequences are invalid: reset or restore the cache before the next call", ew[1]);
   }
   return 1;
 }

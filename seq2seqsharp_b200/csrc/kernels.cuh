@@ -95,7 +95,7 @@ void owner_invalidate(OwnerModel* m);
 int owner_reset_counters(OwnerModel* m);
 long long owner_stream_bytes(const OwnerModel* m);
 int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* logits, const float2* rope_tab, const int* dT,
-                 int* error_flag, unsigned poll_limit, bool pdl, cudaStream_t s);
+                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, cudaStream_t s);
 int init_owner_attrs();
 int64_t packed_bytes(int dtype, int K, int N);
 // Element offset of (k, c) inside one packed 16 KB tile (k < 32, c < tile columns).  fp32 tiles are plain

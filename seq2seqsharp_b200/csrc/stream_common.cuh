@@ -25,6 +25,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Bounded wait: returns false when the phase did not complete within the poll limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned limit = kSpinLimit) {
   const uint32_t a = smem_u32(bar);
+#pragma unroll 1
   for (unsigned i = 0; i < limit; ++i) {
     unsigned ok;
     asm volatile(
