@@ -48,9 +48,10 @@ _lib = None
 
 
 def declared_symbols():
-    """Every TSB200_* function name declared in include/tsb200.h."""
+    """Every TSB200_* function name declared in include/tsb200.h (without the development-build block)."""
     with open(HEADER_PATH) as fh:
         text = fh.read()
+    text = re.sub(r"#ifdef TSB200_TRACE.*?#endif", "", text, flags=re.S)
     return sorted(set(re.findall(r"TSB200_API\s+[\w\s\*]+?\b(TSB200_\w+)\s*\(", text)))
 
 

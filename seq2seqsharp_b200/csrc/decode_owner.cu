@@ -152,7 +152,7 @@ struct OwnRing {
   // makes sure the tiles that hold rows [n, n + cnt) have landed (never beyond the end of the stream).  A warp that
   // has to wait keeps looking after the stages it is responsible for refilling: the tile it waits for may be one of them.
   __device__ __forceinline__ void need(int cnt, int lane) {
-    int t_need = (n + cnt + 3) >> 2;
+    int t_need = (n + cnt + kOwnTileRows - 1) >> kOwnTileShift;
     if (t_need > n_tiles) t_need = n_tiles;
 #pragma unroll 1
     while (t_have < t_need) {
@@ -191,7 +191,7 @@ struct OwnRing {
   }
   __device__ __forceinline__ void release(int w, int lane) {
     (void)w;
-    const int t_done = n >> 2;
+    const int t_done = n >> kOwnTileShift;
     if (t_rel < t_done) {
 #ifdef TSB200_TRACE
       const long long c0 = clock64();
@@ -731,12 +731,10 @@ __device__ __noinline__ void own_attention_short(const OwnArgs& a, const OwnLaye
 #pragma unroll 1
         for (int c = 0; c < dpl; c += 8) {
           const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+          const float4 qa4 = *reinterpret_cast<const float4*>(qh + c), qb4 = *reinterpret_cast<const float4*>(qh + c + 4);
           const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float2 kf = __half22float2(h2[u]);
-            dsum += qh[c + 2 * u] * kf.x + qh[c + 2 * u + 1] * kf.y;
-          }
+          const float2 k0 = __half22float2(h2[0]), k1 = __half22float2(h2[1]), k2 = __half22float2(h2[2]), k3 = __half22float2(h2[3]);
+          dsum += (qa4.x * k0.x + qa4.y * k0.y) + (qa4.z * k1.x + qa4.w * k1.y) + (qb4.x * k2.x + qb4.y * k2.y) + (qb4.z * k3.x + qb4.w * k3.y);
         }
         dsum += __shfl_xor_sync(0xffffffffu, dsum, 4);
         dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
@@ -856,7 +854,7 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
   R.full = full;
   R.empty = empty;
   R.S = S;
-  R.rows = 4 * S;
+  R.rows = kOwnTileRows * S;
   R.n_tiles = a.cta_tiles[cta];
   R.pos = 0;
   R.n = 0;
@@ -946,6 +944,17 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
       long long* qz = a.QA[(layer + 1) & 1] + (size_t)g * kOwnMaxRows * QW;
       OwnNormConsts nc;
       own_norm_consts(nc, Lr.g1, Lr.b1n, d, tid);
+      // this CTA's share of the cached K/V rows is asked into L2 now: by the time attention reads it, HBM has answered
+      {
+        const OwnAttnGeom pg = own_attn_geom(a, gi, gsz, T0, lane);
+        const int lines = (pg.t_cached_end - pg.t_beg) * hd * 2 / 128;   // 128-byte lines of one row's K (and V) share
+#pragma unroll 1
+        for (int idx = tid; idx < M * lines; idx += 256) {
+          const size_t o = (((size_t)(idx / lines) * Hkv + g) * a.Tmax + pg.t_beg) * hd + (size_t)(idx % lines) * 64;
+          prefetch_l2(Lr.cK + o);
+          prefetch_l2(Lr.cV + o);
+        }
+      }
       // constants of the block that can be fetched before its input exists: the q|k|v biases of the group (to shared
       // memory) and the bias of the CTA's residual slice
 #pragma unroll 1
@@ -1314,10 +1323,10 @@ void owner_plan(OwnerModel* m) {
     m->rows_layer[c] = r;
     j[OWN_HEAD].row0 = r * m->D.L;
     const long long rows = r * m->D.L + j[OWN_HEAD].nrows;
-    const long long tiles = (rows + 3) / 4;
+    const long long tiles = (rows + kOwnTileRows - 1) / kOwnTileRows;
     m->cta_row0[c] = row;
     m->cta_tiles[c] = (int)tiles;
-    row += tiles * 4;
+    row += tiles * kOwnTileRows;
     if (j[OWN_UP].ws * 16 > m->up_cols_max) m->up_cols_max = j[OWN_UP].ws * 16;
     if (j[OWN_DOWN].ks * 16 > m->hid_max) m->hid_max = j[OWN_DOWN].ks * 16;
   }
@@ -1415,7 +1424,7 @@ int owner_repack(OwnerModel* m, cudaStream_t s) {
   // the tail of a CTA's last tile (rows beyond its last job) is read by the ring but never used: clear it once
   for (int c = 0; c < m->G; ++c) {
     const long long rows = m->rows_layer[c] * D.L + m->jobs[(size_t)c * 5 + OWN_HEAD].nrows;
-    const long long pad = (long long)m->cta_tiles[c] * 4 - rows;
+    const long long pad = (long long)m->cta_tiles[c] * kOwnTileRows - rows;
     if (pad > 0) TSB_CUDA(cudaMemsetAsync(m->wstream + (size_t)(m->cta_row0[c] + rows) * kOwnRowBytes, 0, (size_t)pad * kOwnRowBytes, s));
   }
   TSB_TRY(check_launch("owner repack"));
@@ -1477,7 +1486,7 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   a.off_bar = (int)off; off += 32 * sizeof(uint64_t);
   const size_t fixed = off + 1024 /* alignment slack */ + 128;
   const size_t budget = 224 * 1024;  // the kernel also has about 2 KB of static shared memory
-  if (fixed + 4 * (size_t)kOwnTileBytes > budget) return 2;
+  if (fixed + 4 * (size_t)kOwnTileBytes > budget) return 2;   // a burst plus the look-ahead for the next one spans up to four tiles
   int stages = (int)((budget - fixed) / kOwnTileBytes);
   if (stages > 16) stages = 16;
   a.stages = stages;
@@ -1588,8 +1597,9 @@ int owner_layout_selftest(const OwnDims& D, int G) {
     }
     TSB_CHECK(j[OWN_HEAD].row0 == r * D.L, "owner layout: CTA %d: LM-head rows do not follow the layers", c);
     const long long rows = r * D.L + j[OWN_HEAD].nrows;
-    TSB_CHECK((long long)m.cta_tiles[c] * 4 >= rows && (long long)m.cta_tiles[c] * 4 < rows + 4, "owner layout: CTA %d: tile count", c);
-    expect_row += (long long)m.cta_tiles[c] * 4;
+    TSB_CHECK((long long)m.cta_tiles[c] * kOwnTileRows >= rows && (long long)m.cta_tiles[c] * kOwnTileRows < rows + kOwnTileRows,
+              "owner layout: CTA %d: tile count", c);
+    expect_row += (long long)m.cta_tiles[c] * kOwnTileRows;
     for (int q = 0; q < 5; ++q) {
       TSB_TRY(own_selftest_job(j[q], seen, 0));
       TSB_CHECK(j[q].mode == OWN_SSPLIT ? (j[q].spw <= kOwnMaxSpw) : true, "owner layout: strips per warp");

@@ -20,7 +20,7 @@
 // Weight blocks: a block is the A operand of ONE mma.sync m16n8k16 (16 output columns x 16 k, fp16) stored in
 // fragment order: lane l = (g = l / 4, t = l % 4) finds its eight values {W[k0+2t+{0,1}][c0+g], W[..][c0+g+8],
 // W[k0+2t+8+{0,1}][c0+g], W[..][c0+g+8]} in 16 consecutive bytes, so a warp loads a block with one conflict-free
-// 16-byte shared-memory load per lane.  Eight blocks (one per consumer warp) form a 4 KB row; four rows a 16 KB tile
+// 16-byte shared-memory load per lane.  Eight blocks (one per consumer warp) form a 4 KB row; eight rows a 32 KB tile
 // of the TMA ring.  Rows of all jobs of a CTA follow each other without gaps.
 //
 // Replaces, per decode step, the chain LayerNorm/RMSNorm -> Affine(QKV) -> RoPE -> cache concat -> softmax(QK^T)V ->
@@ -42,7 +42,9 @@ namespace tsb {
 
 constexpr int kOwnBlockBytes = 512;       // one mma A operand (16 columns x 16 k, fp16)
 constexpr int kOwnRowBytes = 4096;        // eight blocks, one per consumer warp
-constexpr int kOwnTileBytes = 16384;      // four rows: one stage of the ring
+constexpr int kOwnTileRows = 8;           // rows per stage of the ring (a power of two)
+constexpr int kOwnTileShift = 3;
+constexpr int kOwnTileBytes = kOwnTileRows * kOwnRowBytes;   // 32 KB: half as many barrier hand-shakes per byte as 16 KB
 constexpr int kOwnKChunk = 8;             // K-split jobs: at most this many strips are accumulated per pass (8 x 4 registers)
 constexpr int kOwnMaxSpw = 8;             // strip-split jobs: strips per warp per pass
 constexpr int kOwnMaxRows = 4;            // sequences per launch

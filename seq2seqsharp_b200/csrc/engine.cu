@@ -193,7 +193,10 @@ struct Gpt {
   // owner-partitioned persistent decode step (decode_owner.cu): fp16 engines on one GPU, up to own_cap sequences.  It
   // keeps a second copy of the layer weights, cut into one contiguous stream per CTA (built on first use).
   bool use_owner = true;             // TSB200_OWNER=0: keep the stream-K persistent kernel (saves the second weight copy)
-  int own_cap = 0;                   // largest batch it is used for: stack_cap unless TSB200_OWNER_MAXB says otherwise
+  // Measured on the 7B-class model (same GPU, ms per decode step, kernel only): one sequence 3.10 against 3.20 for the
+  // stream-K persistent kernel; two sequences 3.82 against 3.63 (its staging, merges and emissions are per row); on the
+  // 1B-class model 1.02 against 1.03.  So it serves single sequences; TSB200_OWNER_MAXB raises the limit (tests do).
+  int own_cap = 1;
   OwnerModel* own = nullptr;
   int own_B = 0;                     // batch the owner kernel serves for the current program (0: not in use)
 };
@@ -494,7 +497,7 @@ static int ensure_stack(Gpt* g, int B) {
   if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
   g->own_B = 0;
   if (!g->use_stack) return 1;
-  if (g->use_owner && g->tp == 1 && B <= (g->own_cap > 0 ? g->own_cap : g->stack_cap) && B <= kOwnMaxRows) {
+  if (g->use_owner && g->tp == 1 && B <= g->own_cap && B <= kOwnMaxRows) {
     OwnDims D{};
     D.L = c.L; D.d = c.d; D.H = c.H; D.Hkv = c.Hkv; D.hd = c.hd; D.F = c.F; D.V = c.V; D.glu = g->glu;
     if (owner_applicable(D, c.dtype, g->st->sm_count)) {

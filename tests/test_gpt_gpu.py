@@ -244,13 +244,17 @@ def test_step_host_and_profile_paths_agree_with_graph_decode(cuda):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["owner", "streamk"])
 @pytest.mark.parametrize("B", [1, 3, 4, 7])
 @pytest.mark.parametrize("cfg", ARCHS, ids=[c.name for c in ARCHS])
-def test_persistent_step_kernel_matches_per_op_launches(cuda, cfg, B, monkeypatch):
+def test_persistent_step_kernel_matches_per_op_launches(cuda, cfg, B, kernel, monkeypatch):
     """Small batches decode through ONE persistent kernel per step (all linears, RoPE, cache append and attention of the
     layer stack); TSB200_STACK=0 keeps one launch per operation.  Fed the same ids, both must give the same logits
     (attention splits differ, so not bitwise: the tolerance of the dtype) and leave the same cache length; the
     persistent kernel must also be bitwise reproducible run to run."""
+    if kernel == "streamk" and (cfg.dtype != "float16" or B > 4):
+        pytest.skip("the owner-partitioned kernel only exists for fp16 and up to four rows: nothing to switch off")
+    monkeypatch.setenv("TSB200_OWNER", "1" if kernel == "owner" else "0")   # "0": the stream-K persistent kernel for every batch
     S, n_new = 19, 12
     w = synthetic_weights(cfg, 11, std=0.05 if cfg.d < 512 else 0.03, bias_std=0.02, max_pos=66)
     prompt = prompt_ids(13, B, S, cfg.V)
@@ -258,7 +262,8 @@ def test_persistent_step_kernel_matches_per_op_launches(cuda, cfg, B, monkeypatc
 
     def engine(stack):
         monkeypatch.setenv("TSB200_STACK", "1" if stack else "0")
-        monkeypatch.setenv("TSB200_STACK_MAXB", "8")   # by default only single sequences take the persistent kernel
+        monkeypatch.setenv("TSB200_STACK_MAXB", "8")   # by default only one or two sequences take a persistent kernel
+        monkeypatch.setenv("TSB200_OWNER_MAXB", "4")   # fp16: the owner-partitioned kernel up to four rows, the stream-K one above
         g = GPT(cfg, max_batch=B, max_tokens=64)
         g.LoadWeights(w)
         return g
