@@ -1,0 +1,79 @@
+"""The model file reader against files written in the reference's wire format (tests/model_file_writer.py): every
+storage form (float32, float16 bit patterns, INT8 / INT4 code books), packed and element-by-element arrays, the network
+shape fields, the vocabulary, and the error cases.  No GPU involved."""
+import numpy as np
+import pytest
+
+from seq2seqsharp_b200.gpt import (ActivateFuncEnums as A, GPTConfig, MultiHeadAttentionTypeEnums as M, NormEnums as Nm,
+                                   PositionEmbeddingEnums as P, synthetic_weights)
+from seq2seqsharp_b200.model_file import ModelFileError, position_embedding, read_model
+from tests.model_file_writer import write_model
+
+CFG = GPTConfig(L=2, d=64, H=4, Hkv=2, hd=16, F=96, V=38, norm=Nm.RMSNorm, act=A.SwiGLU, pe=P.RoPE, attn=M.GQA)
+
+
+def saved_weights(cfg):
+    w = synthetic_weights(cfg, 5, std=0.1, bias_std=0.05)
+    return {k: v for k, v in w.items() if k != "PosEmbedding"}
+
+
+@pytest.mark.parametrize("packed", [True, False])
+@pytest.mark.parametrize("vq", ["none", "float16", "int8", "int4"])
+def test_round_trip(tmp_path, vq, packed):
+    path = str(tmp_path / "m.model")
+    expect = write_model(path, CFG, saved_weights(CFG), CFG.V, vq=vq, packed=packed)
+    mf = read_model(path)
+    assert (mf.DecoderLayerDepth, mf.HiddenDim, mf.IntermediateDim, mf.MultiHeadNum, mf.KVGroupNum) == (2, 64, 96, 4, 2)
+    assert len(mf.TgtVocab) == CFG.V and mf.TgtVocab[0] == "</s>" and mf.TgtVocab[5] == "w5"
+    cfg = mf.gpt_config()
+    assert (cfg.L, cfg.d, cfg.H, cfg.hd, cfg.F, cfg.V, cfg.kv_heads()) == (2, 64, 4, 16, 96, 38, 2)
+    assert cfg.norm == Nm.RMSNorm and cfg.act == A.SwiGLU and cfg.pe == P.RoPE and cfg.attn == M.GQA
+    assert cfg.dtype == ("float16" if vq == "float16" else "float32")
+    assert sorted(mf.names()) == sorted(expect)
+    for name, want in expect.items():
+        got = mf.get_weights(name, want_half=(vq == "float16"))
+        np.testing.assert_array_equal(got.astype(np.float32), want, err_msg=name)
+    shaped = mf.weights_for(cfg)
+    assert shaped["GPTDecoder.SelfAttn_1.K"].shape == (64, 32) and shaped["FeedForward_Decoder_0.m_Whd"].shape == (64, 38)
+    assert mf.get_weights("no.such.weight") is None
+
+
+def test_float16_model_refuses_float32_request(tmp_path):
+    path = str(tmp_path / "h.model")
+    write_model(path, CFG, saved_weights(CFG), CFG.V, vq="float16")
+    with pytest.raises(ModelFileError, match="Float16"):
+        read_model(path).get_weights("TgtEmbeddings")          # Model.cs:267-270 throws InvalidCastException here
+
+
+def test_mha_ape_model_and_rebuilt_position_table(tmp_path):
+    cfg = GPTConfig(L=1, d=32, H=2, hd=16, F=64, V=11, norm=Nm.LayerNorm, act=A.ReLU, pe=P.APE, attn=M.MHA)
+    path = str(tmp_path / "a.model")
+    write_model(path, cfg, saved_weights(cfg), cfg.V)
+    mf = read_model(path)
+    got = mf.gpt_config()
+    assert got.pe == P.APE and got.attn == M.MHA and got.kv_heads() == 2 and got.norm == Nm.LayerNorm
+    w = mf.weights_for(got, max_pos=10)
+    pos = w["PosEmbedding"]
+    assert pos.shape == (10, 32)
+    np.testing.assert_allclose(pos[0, :16], 0.0)                   # sin(0)
+    np.testing.assert_allclose(pos[0, 16:], 1.0)                   # cos(0)
+    np.testing.assert_allclose(pos[3, 0], np.sin(3.0), rtol=1e-6)  # the first time scale is 1
+    np.testing.assert_allclose(pos[3, 15], np.sin(3.0 / 10000.0), rtol=1e-4)   # the last one 1/10000
+    np.testing.assert_array_equal(position_embedding(10, 32), pos)
+
+
+def test_errors(tmp_path):
+    path = str(tmp_path / "e.model")
+    write_model(path, CFG, saved_weights(CFG), CFG.V, decoder_type=1)
+    with pytest.raises(ModelFileError, match="GPTDecoder"):
+        read_model(path).gpt_config()
+    write_model(path, CFG, {k: v for k, v in saved_weights(CFG).items() if not k.endswith(".W0")}, CFG.V)
+    mf = read_model(path)
+    with pytest.raises(ModelFileError, match="not in the model file"):
+        mf.weights_for(mf.gpt_config())
+    with open(path, "rb") as fh:
+        data = fh.read()
+    with open(path, "wb") as fh:
+        fh.write(data[:len(data) // 2])
+    with pytest.raises(ModelFileError):
+        read_model(path)
