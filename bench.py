@@ -490,6 +490,7 @@ def run_b200(args):
                     "tflops": prefill_flops(cfg, seqs, S) / 1e12 / (prefill_ms / 1e3) / (1 if tp else world)},
         "kernel_classes_ms_per_step": {k: v[0] / n_prof for k, v in prof.items()},
         "host_wall_ms_per_step": 1e3 * t_wall / K,
+        "decode_path": {0: "one launch per operation", 1: "stream-K persistent kernel", 2: "owner-partitioned persistent kernel"}.get(gpt.DecodePath()),
     }
     if prof["attention"][1] > 0:
         # the KV cache read by the decode attention of one step against the time of its launches
@@ -533,6 +534,22 @@ def run_b200(args):
                                "full_prefill_ms": prefill_ms}
         snap.close()
     gpt.close()
+    if tp and not args.no_secondary:
+        # beside the sharded model: the same GPUs as N independent replicas (the reference's own multi-device form), each
+        # decoding its own sequences; no collective on the data path
+        rep_gpt = GPT(cfg, device_id=local, max_batch=B, max_tokens=max_tokens)
+        rep_gpt.FillSynthetic(SEED, 0.02, 0.0)
+        rep_prompt = prompt_ids(SEED + rank, B, S, cfg.V)
+        rep_opts = make_options(strat, topP, max_tokens, SEED, rank * B)
+        rep_gpt.Prefill(rep_prompt, rep_opts)
+        rep_gpt.Decode(W, rep_opts)
+        barrier()
+        rep_gpt.Decode(K, rep_opts)
+        rep_ms, _ = rep_gpt.LastTiming()
+        rep_ms = max_over_ranks(rep_ms)
+        rep_gpt.close()
+        line["replicas"] = {"value": world * B * K / (rep_ms / 1e3), "unit": "tokens/s", "ms_per_step": rep_ms / K, "scaling": "weak",
+                            "note": "%d independent engines, one per GPU, %d sequence(s) each" % (world, B)}
     if world == 1 and args.workload == "c5_b1" and not args.no_secondary:
         # the other figures the metric names, each on its own engine (outside the headline timed region)
         line["secondary"] = {

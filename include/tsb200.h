@@ -352,6 +352,9 @@ TSB200_API int TSB200_GptDecode(void* gpt, int n_steps, const TSB200DecodingOpti
 /* logits [B,V] / probs [B,V] (F32, host) of the most recent step */
 TSB200_API int TSB200_GptGetLogits(void* gpt, float* logits, float* probs);
 TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);
+/* How the most recent cached decode step was launched (the engine chooses by dtype, batch and parallelism):
+ * 0 one launch per operation, 1 the stream-K persistent kernel, 2 the owner-partitioned persistent kernel. */
+TSB200_API int TSB200_GptDecodePath(void* gpt, int* path);
 /* Prompt suffix on top of a non-empty cache: ids [B,S] host int32 are the text from position T (the cache length)
  * on; they are appended to the cache (causal attention over T + S positions) and the next id per sequence is
  * sampled into out_ids [B].  With S = 1 and the pending id this is Decoder.GPTDecode's cached branch

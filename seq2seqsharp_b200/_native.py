@@ -141,6 +141,7 @@ def lib():
         "TSB200_GptDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), i32, vp, C.POINTER(i32)]),
         "TSB200_GptGetLogits": (i32, [vp, vp, vp]),
         "TSB200_GptCacheLength": (i32, [vp, C.POINTER(i32)]),
+        "TSB200_GptDecodePath": (i32, [vp, C.POINTER(i32)]),
         "TSB200_GptExtend": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptCacheSnapshot": (i32, [vp, C.POINTER(vp)]),
         "TSB200_GptCacheSnapshotInfo": (i32, [vp, C.POINTER(i32), C.POINTER(i32), C.POINTER(i64), vp]),

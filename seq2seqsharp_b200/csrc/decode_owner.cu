@@ -1,14 +1,23 @@
 // Owner-partitioned persistent decode step, fp16, one GPU (see decode_owner.cuh for the partition and the weight layout).
 //
-// One CTA per SM.  Warp 8 (one lane) streams the CTA's private, contiguous weight stream through a ring of 16 KB
-// stages with TMA bulk copies; it never waits for activations.  Warps 0-7 follow the program: per layer an attention
-// block and an FFN block, then the LM head.  A block starts with ONE grid-wide wait (the residual stream of the previous
+// One CTA per SM, eight warps.  The CTA's private, contiguous weight stream runs through a ring of 32 KB stages filled by
+// TMA bulk copies that the warps themselves issue (no producer warp); weights never wait for activations.  The warps
+// follow the program: per layer an attention block and an FFN block, then the LM head.  A block starts with ONE grid-wide wait (the residual stream of the previous
 // block is complete), stages the normed row into shared memory and runs its jobs; results that other CTAs need are
 // added with 64-bit integer atomics (fixed point) into the group accumulator or into the next residual buffer.
 //
 // Residual stream: three buffers X[0..2] of int64 [rows, d], fixed point.  Block p reads X[p % 3], every CTA adds its
 // contributions to X[(p+1) % 3] (one CTA per column slice also adds the old value and the bias), and clears its slice of
 // X[(p+2) % 3].  Readers of a buffer have all arrived at the block's counter before anybody clears or refills it.
+//
+// Tensor parallelism (decode_owner_kernel<true>, one sequence): every rank runs this program on its share of the heads
+// and of the FFN columns.  The sums of a block's last linear (out-projection, FFN down) are partial: the CTAs of a rank
+// add them into a local buffer Y, meet at a local counter, and then every CTA adds ITS slice of Y into the next residual
+// buffer of EVERY rank (64-bit integer atomics over NVLink: the same bits everywhere, whatever the order) and signals
+// the block's counter on every rank; a block starts when its counter shows the arrivals of all CTAs of all ranks.
+// Those counters are never reset (a rank may be a launch ahead): a launch counter kept on the device scales the
+// targets, and it also rotates the roles of the three residual buffers from launch to launch so that the buffer a fast
+// rank adds into first is the one the slower rank's previous launch left cleared.
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -50,6 +59,12 @@ struct OwnArgs {
   int xstride, ystride, hstride, qstride;    // elements between rows
   int off_xs, off_red, off_merge, off_ys, off_hs, off_qs, off_gsum, off_qbias, off_qcol, off_bar, gsum_cols;
   long long* trace;               // -DTSB200_TRACE builds: [grid][2L + 1 blocks][16] %globaltimer stamps
+  // tensor parallelism (decode_owner_kernel<true>)
+  int tp_rank, tp_size;
+  long long* Y[2];                // this rank's partial sums of a block's last linear [kOwnMaxRows, d], fixed point
+  unsigned char* peer[kStackMaxRanks];   // every rank's exchange region as mapped here (own included)
+  long long off_X, off_P;         // bytes from a region's base: residual buffers X[3]; block counters [2L] (never reset)
+  unsigned* epoch;                // launches completed so far (this rank's own word)
 };
 
 #ifdef TSB200_TRACE
@@ -67,6 +82,10 @@ __device__ __forceinline__ void own_add(long long* p, long long v) {
   atomicAdd(reinterpret_cast<unsigned long long*>(p), static_cast<unsigned long long>(v));
 }
 __device__ __forceinline__ long long own_ldcg(const long long* p) { return __ldcg(p); }
+// the same add into another GPU's memory (or this one's) at system scope
+__device__ __forceinline__ void own_add_sys(long long* p, long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ void own_mma(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -496,10 +515,12 @@ __device__ __noinline__ void own_stage_norm(__half* xs, int xstride, const long 
 // One thread polls (bounded); everybody learns the outcome.  A CTA that gave up keeps going without waiting.
 // `where` tells a failed wait apart in the engine's error message: (block of the program << 4) | 1 block counter,
 // 2 / 3 first / second group counter of an attention block.
+// `sys`: the counter is incremented by other GPUs too (system-scope acquire, wrap-safe comparison with a monotonic target).
 __device__ __noinline__ void own_wait(const unsigned* p, unsigned target, const OwnArgs& a, volatile int* s_err, bool& dead, int tid,
-                                      int where) {
+                                      int where, bool sys = false) {
   if (tid == 0) {
-    if (!poll_count(p, target, dead ? 1u : a.poll_limit, a.error_flag)) {
+    const unsigned limit = dead ? 1u : a.poll_limit;
+    if (!(sys ? poll_count_sys(p, target, limit, a.error_flag) : poll_count(p, target, limit, a.error_flag))) {
       *s_err = 1;
       if (!dead) atomicCAS(a.error_flag + 1, 0, where);   // the first wait that ran out (a CTA that follows another's failure is `dead`)
       *a.error_flag = 1;
@@ -824,6 +845,7 @@ __device__ __forceinline__ void own_merge_splits(const float* base, int rec, int
 // ------------------------------------------------------------------------------------------- the kernel
 constexpr int kOwnThreads = kConsumerWarps * 32;   // eight consumer warps; the ring is refilled by the consumers themselves
 
+template <bool TP>
 __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -897,12 +919,25 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
   const int g = jq.group;
   const int gb = own_group_begin(g, G, Hkv), gsz = own_group_begin(g + 1, G, Hkv) - gb, gi = cta - gb;
   const int QW = (grp + 2) * hd;
+  // CTAs of the group that take part in attention: about 32 tokens each, so that short contexts are not cut into
+  // slivers whose partial states cost more to merge than the tokens cost to read
+  int asz = (T0 + 1 + 31) / 32;
+  asz = asz > gsz ? gsz : asz;
+  const bool attn_on = gi < asz;
   for (int jc = tid; jc < QW; jc += 256) s_qcol[jc] = own_qkv_col(jc, g, grp, hd, a.H, Hkv);   // visible after the first barrier below
   const int c0 = own_split(d, G, cta), c1 = own_split(d, G, cta + 1);   // this CTA's slice of the residual columns
-  unsigned* cntP = a.cnt;                                               // [2L] block counters
+  // [2L] block counters: one GPU: local, cleared at the end of the launch; tensor parallel: in the exchange region,
+  // incremented by every rank, never reset (the local [2L] then count this rank's CTAs whose partial sums are in Y)
+  unsigned* cntP = TP ? reinterpret_cast<unsigned*>(a.peer[a.tp_rank] + a.off_P) : a.cnt;
+  unsigned* cntL = a.cnt;
   unsigned* cntG = a.cnt + (size_t)2 * a.L * kOwnCntStride;             // [L][Hkv][2] group counters
   unsigned* cntExit = cntG + (size_t)a.L * Hkv * 2 * kOwnCntStride;
   bool dead = false;
+  const unsigned epoch = TP ? *reinterpret_cast<volatile unsigned*>(a.epoch) : 0u;
+  const unsigned ptarget = TP ? (epoch + 1u) * (unsigned)G * (unsigned)a.tp_size : (unsigned)G;
+  // the residual buffer block 0 reads: a launch leaves X[(xb + 2L + 1) % 3] cleared, which must be the buffer block 0 of
+  // the next launch adds into
+  const int xb = TP ? (int)((epoch % 3u) * (unsigned)((2 * a.L) % 3) % 3u) : 0;
 
   // duties of a block: add the old residual value and the bias of the block's last linear to the CTA's slice of the
   // next buffer, clear the slice of the buffer after that
@@ -916,20 +951,60 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
   auto duty_load = [&](const long long* Xc) -> long long {
     return (tid < M * wdt) ? own_ldcg(Xc + (size_t)(tid / wdt) * d + c0 + tid % wdt) : 0;
   };
-  auto duty_commit = [&](const long long* Xc, long long* Xn, long long* Xz, const __half* bias, long long v0) {
+  // Tensor parallel: the old value goes into this rank's own next buffer, the bias (held by rank 0 only) into the
+  // partial sums that every rank receives; the slice of the partial buffer of the NEXT block is cleared as well.
+  auto duty_commit = [&](const long long* Xc, long long* Xn, long long* Xz, const __half* bias, long long v0, long long vb, int p) {
+    long long* Yc = TP ? a.Y[p & 1] : nullptr;
+    long long* Yz = TP ? a.Y[(p + 1) & 1] : nullptr;
     if (tid < M * wdt) {
       const size_t o = (size_t)(tid / wdt) * d + c0 + tid % wdt;
-      own_add(Xn + o, v0);
+      if (TP) {
+        own_add(Xn + o, v0);
+        if (vb != 0) own_add(Yc + o, vb);
+        Yz[o] = 0;
+      } else {
+        own_add(Xn + o, v0 + vb);
+      }
       Xz[o] = 0;
     }
 #pragma unroll 1
     for (int idx = tid + 256; idx < M * wdt; idx += 256) {   // slices wider than one element per thread (few CTAs)
       const int m = idx / wdt, col = c0 + idx % wdt;
-      long long v = own_ldcg(Xc + (size_t)m * d + col);
-      if (bias) v += own_fix(__half2float(bias[col]));
-      own_add(Xn + (size_t)m * d + col, v);
-      Xz[(size_t)m * d + col] = 0;
+      const size_t o = (size_t)m * d + col;
+      long long v = own_ldcg(Xc + o);
+      const long long b = bias ? own_fix(__half2float(bias[col])) : 0;
+      if (TP) {
+        own_add(Xn + o, v);
+        if (b != 0) own_add(Yc + o, b);
+        Yz[o] = 0;
+      } else {
+        own_add(Xn + o, v + b);
+      }
+      Xz[o] = 0;
     }
+  };
+  // Tensor parallel, end of a block: this CTA's partial sums are in Y; when all CTAs of the rank have said so, the CTA
+  // adds its slice of Y into the next residual buffer of every rank and signals the block's counter there.  The
+  // release of the signalling threads covers the adds of all threads (they met at the barrier before it).
+  auto block_done = [&](int p, int xn) {
+    if (!TP) {
+      own_arrive(cntP + (size_t)p * kOwnCntStride, tid);
+      return;
+    }
+    own_arrive(cntL + (size_t)p * kOwnCntStride, tid);
+    own_wait(cntL + (size_t)p * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 4);
+    const long long* Yc = a.Y[p & 1];
+    const int nv = M * wdt;
+#pragma unroll 1
+    for (int idx = tid; idx < nv * a.tp_size; idx += 256) {
+      const int r = idx / nv, e = idx % nv;
+      const size_t o = (size_t)(e / wdt) * d + c0 + e % wdt;
+      const long long v = own_ldcg(Yc + o);
+      long long* dst = reinterpret_cast<long long*>(a.peer[r] + a.off_X) + (size_t)xn * kOwnMaxRows * d + o;
+      if (v != 0) own_add_sys(dst, v);
+    }
+    consumers_sync();
+    if (tid < a.tp_size) red_release_add_sys(reinterpret_cast<unsigned*>(a.peer[tid] + a.off_P) + (size_t)p * kOwnCntStride, 1u);
   };
 
   for (int layer = 0; layer < a.L; ++layer) {
@@ -937,17 +1012,17 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
     // =================================================================== attention block
     {
       const int p = 2 * layer;
-      const long long* Xc = a.X[p % 3];
-      long long* Xn = a.X[(p + 1) % 3];
-      long long* Xz = a.X[(p + 2) % 3];
+      const long long* Xc = a.X[(xb + p) % 3];
+      long long* Xn = a.X[(xb + p + 1) % 3];
+      long long* Xz = a.X[(xb + p + 2) % 3];
       long long* qa = a.QA[layer & 1] + (size_t)g * kOwnMaxRows * QW;
       long long* qz = a.QA[(layer + 1) & 1] + (size_t)g * kOwnMaxRows * QW;
       OwnNormConsts nc;
       own_norm_consts(nc, Lr.g1, Lr.b1n, d, tid);
       // this CTA's share of the cached K/V rows is asked into L2 now: by the time attention reads it, HBM has answered
       {
-        const OwnAttnGeom pg = own_attn_geom(a, gi, gsz, T0, lane);
-        const int lines = (pg.t_cached_end - pg.t_beg) * hd * 2 / 128;   // 128-byte lines of one row's K (and V) share
+        const OwnAttnGeom pg = own_attn_geom(a, gi, asz, T0, lane);
+        const int lines = attn_on ? (pg.t_cached_end - pg.t_beg) * hd * 2 / 128 : 0;   // 128-byte lines of one row's K (and V) share
 #pragma unroll 1
         for (int idx = tid; idx < M * lines; idx += 256) {
           const size_t o = (((size_t)(idx / lines) * Hkv + g) * a.Tmax + pg.t_beg) * hd + (size_t)(idx % lines) * 64;
@@ -960,12 +1035,12 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
 #pragma unroll 1
       for (int jc = tid; jc < QW; jc += 256) s_qbias[jc] = __half2float(Lr.bqkv[s_qcol[jc]]);
       const long long dbias = duty_bias(Lr.bo);
-      if (p > 0) own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+      if (p > 0) own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, ptarget, a, &s_err, dead, tid, (p << 4) | 1, TP);
       OTRACE(p, 0);
       R.dead = R.dead || dead;
       const long long dval = duty_load(Xc);
       own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
-      duty_commit(Xc, Xn, Xz, Lr.bo, dval + dbias);
+      duty_commit(Xc, Xn, Xz, Lr.bo, dval, dbias, p);
       {
         // clear this CTA's part of the group accumulator the NEXT layer uses
         const int n = kOwnMaxRows * QW, z0 = own_split(n, gsz, gi), z1 = own_split(n, gsz, gi + 1);
@@ -983,10 +1058,12 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
       OTRACE(p, 2);
       own_arrive(gc, tid);
       // the cached K/V rows do not depend on q: their loads fly while the group's sums are awaited
-      const OwnAttnGeom ag = own_attn_geom(a, gi, gsz, T0, lane);
-      const bool short_range = (T0 + 1 + gsz - 1) / gsz <= kOwnShortTokens && hd % 64 == 0;   // the same for every CTA of the group
+      const OwnAttnGeom ag = own_attn_geom(a, gi, asz, T0, lane);
+      const bool short_range = (T0 + 1 + asz - 1) / asz <= kOwnShortTokens && hd % 64 == 0;   // the same for every CTA of the group
       OwnKvBatch kv0;
-      if (short_range) {
+      if (!attn_on) {
+        // more CTAs than the context can feed: this one takes no tokens
+      } else if (short_range) {
         __half* Ks = reinterpret_cast<__half*>(merge);
         own_short_stage(a, Lr, ag, g, 0, Ks, Ks + (size_t)(kOwnShortTokens + 1) * (hd + 8), tid);
       } else {
@@ -1026,7 +1103,8 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
         }
       }
       OTRACE(p, 9);
-      if (short_range) own_attention_short(a, Lr, ag, g, gi, qs, merge, tid);
+      if (!attn_on) {
+      } else if (short_range) own_attention_short(a, Lr, ag, g, gi, qs, merge, tid);
       else if (grp % 4 == 0) own_attention<4>(a, Lr, ag, kv0, g, gi, qs, merge, tid, p);
       else own_attention<1>(a, Lr, ag, kv0, g, gi, qs, merge, tid, p);
       OTRACE(p, 4);
@@ -1048,7 +1126,7 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
             const int head = (qc * 4) / hd, e4 = (qc * 4) % hd;
             const float* base = a.AP + ((((size_t)m * Hkv + g) * grp + head) * a.gmax) * rec;
             float mm, Ls, As[4];
-            own_merge_splits(base, rec, e4, gsz, half, 2, mm, Ls, As);
+            own_merge_splits(base, rec, e4, asz, half, 2, mm, Ls, As);
             float* mine = red + (size_t)ql * 6;
             if (half == 1) {
               mine[0] = mm; mine[1] = Ls; mine[2] = As[0]; mine[3] = As[1]; mine[4] = As[2]; mine[5] = As[3];
@@ -1074,27 +1152,27 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
       const OwnJob& jo = s_jobs[OWN_W0];
       R.dead = R.dead || dead;
       {
-        const OwnEmit em{OWN_EMIT_ADD64, Xn, nullptr, nullptr, d, jo.cbase, 0};
+        const OwnEmit em{OWN_EMIT_ADD64, TP ? a.Y[p & 1] : Xn, nullptr, nullptr, d, jo.cbase, 0};
         own_job_ksplit(&jo, &R, ys, a.ystride, M, red, &em);
       }
       OTRACE(p, 7);
-      own_arrive(cntP + (size_t)p * kOwnCntStride, tid);
+      block_done(p, (xb + p + 1) % 3);
     }
     // =================================================================== FFN block
     {
       const int p = 2 * layer + 1;
-      const long long* Xc = a.X[p % 3];
-      long long* Xn = a.X[(p + 1) % 3];
-      long long* Xz = a.X[(p + 2) % 3];
+      const long long* Xc = a.X[(xb + p) % 3];
+      long long* Xn = a.X[(xb + p + 1) % 3];
+      long long* Xz = a.X[(xb + p + 2) % 3];
       OwnNormConsts nc;
       own_norm_consts(nc, Lr.g2, Lr.b2n, d, tid);
       const long long dbias = duty_bias(Lr.bdown);
-      own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+      own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, ptarget, a, &s_err, dead, tid, (p << 4) | 1, TP);
       OTRACE(p, 0);
       R.dead = R.dead || dead;
       const long long dval = duty_load(Xc);
       own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
-      duty_commit(Xc, Xn, Xz, Lr.bdown, dval + dbias);
+      duty_commit(Xc, Xn, Xz, Lr.bdown, dval, dbias, p);
       const OwnJob& ju = s_jobs[OWN_UP];
       const OwnJob& jd = s_jobs[OWN_DOWN];
 #pragma unroll 1
@@ -1148,21 +1226,21 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
       OTRACE(p, 3);
       // the matching rows of W2: all d output columns, sums go straight into the next residual buffer
       {
-        const OwnEmit em{OWN_EMIT_ADD64, Xn, nullptr, nullptr, d, 0, 0};
+        const OwnEmit em{OWN_EMIT_ADD64, TP ? a.Y[p & 1] : Xn, nullptr, nullptr, d, 0, 0};
         own_job_ssplit(&jd, &R, hs, a.hstride, M, red, &em);
       }
       OTRACE(p, 7);
-      own_arrive(cntP + (size_t)p * kOwnCntStride, tid);
+      block_done(p, (xb + p + 1) % 3);
     }
   }
   // =================================================================== LM head
   {
     const int p = 2 * a.L;
-    const long long* Xc = a.X[p % 3];
+    const long long* Xc = a.X[(xb + p) % 3];
     OwnNormConsts nc;
     own_norm_consts(nc, a.gF, a.bF, d, tid);
     grid_dep_launch();  // the sampling kernels may become resident while the LM head streams
-    own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 1);
+    own_wait(cntP + (size_t)(p - 1) * kOwnCntStride, ptarget, a, &s_err, dead, tid, (p << 4) | 1, TP);
     OTRACE(p, 0);
     R.dead = R.dead || dead;
     own_stage_norm(xs, a.xstride, Xc, nc, a.xmode, a.eps, M, d, tid, s_stat);
@@ -1193,7 +1271,8 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
   consumers_sync();
   if (s_last) {
     const int n = 2 * a.L + a.L * Hkv * 2 + 1;
-    for (int i = tid; i < n; i += 256) a.cnt[(size_t)i * kOwnCntStride] = 0u;
+    for (int i = tid; i < n; i += 256) a.cnt[(size_t)i * kOwnCntStride] = 0u;   // the local counters
+    if (TP && tid == 0) *reinterpret_cast<volatile unsigned*>(a.epoch) = epoch + 1u;
   }
 }
 
@@ -1206,6 +1285,23 @@ __global__ void own_init_kernel(long long* X0, long long* X1, long long* X2, lon
     X0[i] = (i < M * d) ? own_fix(x[i]) : 0;
     X1[i] = 0;
     X2[i] = 0;
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < qa_words; i += gridDim.x * blockDim.x) QA0[i] = 0;
+}
+// Tensor parallel form: other ranks add into this rank's residual buffers, also before this kernel runs (a rank may be
+// a launch ahead), so only the buffer block 0 READS is written here; the rotation of the buffers' roles (see the kernel)
+// makes the one block 0 adds into the buffer the previous launch left cleared.  Y0 and QA0 are local.
+__global__ void own_init_tp_kernel(long long* X, long long* Y0, long long* QA0, const float* x, const unsigned* epoch, int L, int M, int d,
+                                   int qa_words) {
+  pdl_trigger();
+  pdl_wait();
+  const unsigned ep = *epoch;
+  const int xb = (int)((ep % 3u) * (unsigned)((2 * L) % 3) % 3u);
+  long long* X0 = X + (size_t)xb * kOwnMaxRows * d;
+  const int n = kOwnMaxRows * d;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    X0[i] = (i < M * d) ? own_fix(x[i]) : 0;
+    Y0[i] = 0;
   }
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < qa_words; i += gridDim.x * blockDim.x) QA0[i] = 0;
 }
@@ -1278,9 +1374,11 @@ struct OwnerModel {
   long long* X = nullptr;     // 3 buffers
   long long* QA = nullptr;    // 2 buffers
   float* AP = nullptr;
-  unsigned* cnt = nullptr;
+  unsigned* cnt = nullptr;    // local counters, then (one sector further) the launch counter of the tensor-parallel form
   size_t cnt_bytes = 0;
+  long long* Y = nullptr;     // 2 buffers (tensor parallel only)
   bool packed = false;
+  bool tp_failed = false;     // a tensor-parallel step failed: the ranks' counters and buffers no longer agree
 };
 
 int owner_applicable(const OwnDims& D, int dtype, int sm_count) {
@@ -1295,7 +1393,7 @@ int owner_applicable(const OwnDims& D, int dtype, int sm_count) {
 void owner_destroy(OwnerModel* m) {
   if (!m) return;
   cudaSetDevice(m->device);
-  void* ptrs[] = {m->wstream, m->d_row0, m->d_tiles, m->d_jobs, m->d_layers, m->X, m->QA, m->AP, m->cnt};
+  void* ptrs[] = {m->wstream, m->d_row0, m->d_tiles, m->d_jobs, m->d_layers, m->X, m->QA, m->AP, m->cnt, m->Y};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;
@@ -1385,7 +1483,8 @@ int owner_create(int device, DeviceState* st, const OwnDims& D, int norm_type, i
                   alloc((void**)&m->X, (size_t)3 * kOwnMaxRows * D.d * sizeof(long long), true) &&
                   alloc((void**)&m->QA, (size_t)2 * D.Hkv * kOwnMaxRows * QW * sizeof(long long), true) &&
                   alloc((void**)&m->AP, (size_t)kOwnMaxRows * D.Hkv * grp * m->gmax * (D.hd + 4) * sizeof(float), true) &&
-                  alloc((void**)&m->cnt, m->cnt_bytes, true);
+                  alloc((void**)&m->cnt, m->cnt_bytes + kOwnCntStride * sizeof(unsigned), true) &&
+                  alloc((void**)&m->Y, (size_t)2 * kOwnMaxRows * D.d * sizeof(long long), true);
   if (!ok || cudaMemcpy(m->d_row0, m->cta_row0.data(), (size_t)G * sizeof(long long), cudaMemcpyHostToDevice) != cudaSuccess ||
       cudaMemcpy(m->d_tiles, m->cta_tiles.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess ||
       cudaMemcpy(m->d_jobs, m->jobs.data(), m->jobs.size() * sizeof(OwnJob), cudaMemcpyHostToDevice) != cudaSuccess ||
@@ -1437,23 +1536,47 @@ void owner_invalidate(OwnerModel* m) {
   if (m) m->packed = false;
 }
 int owner_reset_counters(OwnerModel* m) {
-  if (m && m->cnt) cudaMemset(m->cnt, 0, m->cnt_bytes);
+  if (m && m->cnt) cudaMemset(m->cnt, 0, m->cnt_bytes);   // not the launch counter behind them
   return 1;
+}
+// Bytes of the part of a tensor-parallel engine's exchange region that this kernel uses: [2L block counters][X[3]].
+static size_t own_xch_counters_bytes(int L) { return ((size_t)2 * L * kOwnCntStride * sizeof(unsigned) + 255) / 256 * 256; }
+long long owner_xch_bytes(const OwnDims& D) {
+  return (long long)(own_xch_counters_bytes(D.L) + (size_t)3 * kOwnMaxRows * D.d * sizeof(long long));
+}
+void owner_tp_failed(OwnerModel* m) {
+  if (m) m->tp_failed = true;
 }
 long long owner_stream_bytes(const OwnerModel* m) { return m ? m->total_rows * (long long)kOwnRowBytes : 0; }
 
 // One decode step for M rows whose embedded fp32 rows are in `x`.  Returns 1 ok, 0 error, 2 not applicable (the caller
 // takes another path).
 int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* logits, const float2* rope_tab, const int* dT,
-                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, cudaStream_t s) {
+                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, const OwnTp* tp, cudaStream_t s) {
   if (!m || !m->packed || M < 1 || M > kOwnMaxRows || !error_flag || !dT) return 2;
+  const bool is_tp = tp && tp->size > 1;
+  if (is_tp) {
+    if (M != 1 || tp->size > kStackMaxRanks) return 2;
+    TSB_CHECK(!m->tp_failed, "an earlier step of this tensor-parallel engine failed: the ranks no longer agree on the state of the "
+                             "exchange; close the job on every rank and build it again");
+  }
   const OwnDims& D = m->D;
   const int grp = D.H / D.Hkv, QW = (grp + 2) * D.hd;
   OwnArgs a{};
   a.wstream = m->wstream; a.cta_row0 = m->d_row0; a.cta_tiles = m->d_tiles; a.jobs = m->d_jobs; a.layers = m->d_layers;
   a.gF = (const __half*)m->nf_g; a.bF = m->norm_type == 0 ? (const __half*)m->nf_b : nullptr; a.head_b = (const __half*)m->head_b;
   a.logits = logits;
-  for (int i = 0; i < 3; ++i) a.X[i] = m->X + (size_t)i * kOwnMaxRows * D.d;
+  long long* Xbase = m->X;
+  if (is_tp) {
+    a.tp_rank = tp->rank; a.tp_size = tp->size;
+    for (int r = 0; r < tp->size; ++r) a.peer[r] = tp->peer[r] + tp->offset;
+    a.off_P = 0;
+    a.off_X = (long long)own_xch_counters_bytes(D.L);
+    a.epoch = m->cnt + m->cnt_bytes / sizeof(unsigned);
+    for (int i = 0; i < 2; ++i) a.Y[i] = m->Y + (size_t)i * kOwnMaxRows * D.d;
+    Xbase = reinterpret_cast<long long*>(a.peer[tp->rank] + a.off_X);
+  }
+  for (int i = 0; i < 3; ++i) a.X[i] = Xbase + (size_t)i * kOwnMaxRows * D.d;
   for (int i = 0; i < 2; ++i) a.QA[i] = m->QA + (size_t)i * D.Hkv * kOwnMaxRows * QW;
   a.AP = m->AP; a.cnt = m->cnt; a.rope_tab = rope_tab; a.dT = dT; a.error_flag = error_flag;
   a.poll_limit = poll_limit ? poll_limit : kPollLimit;
@@ -1494,12 +1617,14 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   {
     // the CTAs wait on one another: the whole grid must be resident at once
     int per_sm = 0;
-    TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_owner_kernel, kOwnThreads, smem));
+    if (is_tp) TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_owner_kernel<true>, kOwnThreads, smem));
+    else TSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_owner_kernel<false>, kOwnThreads, smem));
     if ((long long)per_sm * st->sm_count < m->G) return 2;
   }
   {
     const int qa_words = D.Hkv * kOwnMaxRows * QW;
-    TSB_CUDA(launch_k(own_init_kernel, dim3(16), dim3(256), 0, s, a.X[0], a.X[1], a.X[2], a.QA[0], x, M, D.d, qa_words));
+    if (is_tp) TSB_CUDA(launch_k(own_init_tp_kernel, dim3(16), dim3(256), 0, s, Xbase, a.Y[0], a.QA[0], x, (const unsigned*)a.epoch, D.L, M, D.d, qa_words));
+    else TSB_CUDA(launch_k(own_init_kernel, dim3(16), dim3(256), 0, s, a.X[0], a.X[1], a.X[2], a.QA[0], x, M, D.d, qa_words));
     count_launch(m->device);
   }
   cudaLaunchConfig_t cfg{};
@@ -1512,7 +1637,8 @@ int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* l
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
-  TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_owner_kernel, a));
+  if (is_tp) TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_owner_kernel<true>, a));
+  else TSB_CUDA(cudaLaunchKernelEx(&cfg, decode_owner_kernel<false>, a));
   count_launch(m->device);
   return 1;
 }
@@ -1645,7 +1771,8 @@ int owner_layout_selftest(const OwnDims& D, int G) {
 }
 
 int init_owner_attrs() {
-  TSB_CUDA(cudaFuncSetAttribute(decode_owner_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+  TSB_CUDA(cudaFuncSetAttribute(decode_owner_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+  TSB_CUDA(cudaFuncSetAttribute(decode_owner_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
   return 1;
 }
 

@@ -131,6 +131,8 @@ struct Gpt {
   unsigned char* xch_peer[kStackMaxRanks] = {};
   bool xch_open[kStackMaxRanks] = {};
   bool xch_ready = false;
+  size_t xch_own_off = 0;      // where the owner-partitioned kernel's part of the region starts
+  int last_path = 0;           // how the most recent cached decode step ran: 0 one launch per operation, 1 stream-K persistent kernel, 2 owner-partitioned kernel
   float* x2 = nullptr;         // second residual buffer: a summed residual row is written to the buffer the others do not read
   float* ar_buf = nullptr;     // fp32 [rows, d] partial sums handed to the all-reduce
   void *E = nullptr, *PE = nullptr, *nf_g = nullptr, *nf_b = nullptr, *head_w = nullptr, *head_b = nullptr;
@@ -497,7 +499,9 @@ static int ensure_stack(Gpt* g, int B) {
   if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
   g->own_B = 0;
   if (!g->use_stack) return 1;
-  if (g->use_owner && g->tp == 1 && B <= g->own_cap && B <= kOwnMaxRows) {
+  // tensor-parallel engines: one sequence, and only once the ranks' exchange regions are mapped into each other
+  const bool own_tp_ok = g->tp == 1 || (g->xch_ready && g->tp_peer && B == 1 && g->xch_own_off != 0);
+  if (g->use_owner && own_tp_ok && B <= g->own_cap && B <= kOwnMaxRows) {
     OwnDims D{};
     D.L = c.L; D.d = c.d; D.H = c.H; D.Hkv = c.Hkv; D.hd = c.hd; D.F = c.F; D.V = c.V; D.glu = g->glu;
     if (owner_applicable(D, c.dtype, g->st->sm_count)) {
@@ -624,12 +628,18 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   }
   if (S == 1 && use_state && g->use_stack && g->own_B == B && owner_packed(g->own)) {
     prof_begin(g);
-    const int r = owner_launch(g->own, g->st, B, g->x, g->logits, g->rope_tab, dT, g->err_flag, g->poll_limit, g->pdl, g->stack_trace, g->s);
+    OwnTp otp{};
+    otp.rank = g->tp_rank; otp.size = g->tp; otp.offset = (long long)g->xch_own_off;
+    for (int q = 0; q < g->tp && q < kStackMaxRanks; ++q) otp.peer[q] = g->tp > 1 ? g->xch_peer[q] : nullptr;
+    const int r = owner_launch(g->own, g->st, B, g->x, g->logits, g->rope_tab, dT, g->err_flag, g->poll_limit, g->pdl, g->stack_trace,
+                               g->tp > 1 ? &otp : nullptr, g->s);
     if (r != 2) {
       prof_end(g, KC_STACK);
+      g->last_path = 2;
       return r;
     }
   }
+  if (S == 1 && use_state) g->last_path = 0;
   if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
     StackConfig sc{};
     sc.dtype = dt; sc.M = B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd; sc.Tmax = c.max_tokens; sc.qkv_rs = g->Nqkv;
@@ -642,6 +652,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
                                       g->stack_partials, g->stack_counters, g->stack_attn, g->err_flag, g->stack_trace, g->pdl, g->s);
     if (r != 2) {
       prof_end(g, KC_STACK);
+      g->last_path = 1;
       return r;
     }
   }
@@ -700,6 +711,7 @@ static int check_err_flag(Gpt* g) {
     cudaMemset(g->err_flag, 0, 2 * sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
     owner_reset_counters(g->own);
+    if (g->tp > 1) owner_tp_failed(g->own);
     TSB_FAIL("a kernel gave up waiting (a dependency counter or a shared-memory barrier did not arrive within its limit; wait site 0x%x); "
              "the results of this call and the state of its sequences are invalid: reset or restore the cache before the next call", ew[1]);
   }
@@ -1035,6 +1047,17 @@ int TSB200_GptTpExport(void* h, void* handle64) {
   TSB_TRY(use_device(g->c.device, nullptr));
   if (!g->xch_region) {
     g->xch_bytes = kStackXchHeader + (size_t)kStackXchSites * g->tp * kStackXchRows * g->c.d * sizeof(float);
+    g->xch_bytes = (g->xch_bytes + 255) / 256 * 256;
+    {
+      // the owner-partitioned kernel's residual buffers and block counters follow (every rank computes the same offset)
+      const TSB200GptConfig& c = g->c;
+      OwnDims D{};
+      D.L = c.L; D.d = c.d; D.H = c.H; D.Hkv = c.Hkv; D.hd = c.hd; D.F = c.F; D.V = c.V; D.glu = g->glu;
+      if (owner_applicable(D, c.dtype, g->st->sm_count)) {
+        g->xch_own_off = g->xch_bytes;
+        g->xch_bytes += (size_t)owner_xch_bytes(D);
+      }
+    }
     TSB_CUDA(cudaMalloc((void**)&g->xch_region, g->xch_bytes));
     TSB_CUDA(cudaMemset(g->xch_region, 0, g->xch_bytes));
   }
@@ -1078,6 +1101,7 @@ int TSB200_GptTpClose(void* h) {
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   g->stack_key = nullptr;
   g->stack_B = 0;
+  g->own_B = 0;
   g->xch_ready = false;
   for (int r = 0; r < kStackMaxRanks; ++r)
     if (g->xch_open[r]) {
@@ -1255,6 +1279,13 @@ int TSB200_GptGetLogits(void* h, float* logits, float* probs) {
     }
     TSB_CUDA(cudaMemcpy(probs, g->probs, n * 4, cudaMemcpyDeviceToHost));
   }
+  return 1;
+}
+
+int TSB200_GptDecodePath(void* h, int* path) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && path, "gpt_decode_path: null argument");
+  *path = g->last_path;
   return 1;
 }
 

@@ -94,8 +94,16 @@ bool owner_packed(const OwnerModel* m);
 void owner_invalidate(OwnerModel* m);
 int owner_reset_counters(OwnerModel* m);
 long long owner_stream_bytes(const OwnerModel* m);
+// tensor parallelism: every rank's exchange region as mapped here (own included) and the byte offset of this kernel's part
+struct OwnTp {
+  int rank, size;
+  unsigned char* peer[kStackMaxRanks];
+  long long offset;
+};
+long long owner_xch_bytes(const OwnDims& D);   // size of that part
+void owner_tp_failed(OwnerModel* m);           // after a failed tensor-parallel step: later launches are refused
 int owner_launch(OwnerModel* m, DeviceState* st, int M, const float* x, float* logits, const float2* rope_tab, const int* dT,
-                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, cudaStream_t s);
+                 int* error_flag, unsigned poll_limit, bool pdl, long long* trace, const OwnTp* tp, cudaStream_t s);
 int init_owner_attrs();
 int64_t packed_bytes(int dtype, int K, int N);
 // Element offset of (k, c) inside one packed 16 KB tile (k < 32, c < tile columns).  fp32 tiles are plain

@@ -405,6 +405,12 @@ class GPT:
         N.call("TSB200_GptCacheLength", self._h, C.byref(t))
         return t.value
 
+    def DecodePath(self):
+        """How the most recent cached step ran: 0 per-operation launches, 1 stream-K persistent kernel, 2 owner-partitioned kernel."""
+        t = C.c_int(0)
+        N.call("TSB200_GptDecodePath", self._h, C.byref(t))
+        return t.value
+
     def LastTiming(self):
         ms, n = C.c_float(0), C.c_int64(0)
         N.call("TSB200_GptLastTiming", self._h, C.byref(ms), C.byref(n))
