@@ -351,7 +351,8 @@ TSB200_API int TSB200_GptDecode(void* gpt, int n_steps, const TSB200DecodingOpti
                                 int32_t* out_ids, int* steps_done);
 /* logits [B,V] / probs [B,V] (F32, host) of the most recent step */
 TSB200_API int TSB200_GptGetLogits(void* gpt, float* logits, float* probs);
-TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);
+TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);   /* the longest sequence's when they differ */
+TSB200_API int TSB200_GptCacheLengths(void* gpt, int* lens, int n);   /* per sequence (n entries) */
 /* How the most recent cached decode step was launched (the engine chooses by dtype, batch and parallelism):
  * 0 one launch per operation, 1 the stream-K persistent kernel, 2 the owner-partitioned persistent kernel. */
 TSB200_API int TSB200_GptDecodePath(void* gpt, int* path);
@@ -370,6 +371,29 @@ TSB200_API int TSB200_GptCacheSnapshot(void* gpt, void** snapshot);
 TSB200_API int TSB200_GptCacheSnapshotInfo(void* snapshot, int* B, int* T, int64_t* bytes, int32_t* tokens);
 TSB200_API int TSB200_GptCacheRestore(void* gpt, void* snapshot, int B_new);
 TSB200_API int TSB200_GptCacheSnapshotFree(void* snapshot);
+
+/* ---- sequences with their own lengths ---------------------------------------------------------------------------
+ * The reference pads the prompts of a batch to one length and masks the pads (BuildInTokens.PadSentences +
+ * BuildSelfTriMask, Applications/Decoder.cs:656,687-692).  Here every sequence keeps its own cache length, RoPE / APE
+ * position, append position, Philox step and stop rule, so each one continues exactly as if it had been run alone.
+ * Batches whose sequences differ decode with one launch per operation (the persistent kernels serve equal lengths).
+ *
+ * PrefillRagged: ids [B,S] host int32, prompt b occupies columns [0, lens[b]) (1 <= lens[b] <= S; the rest is padding
+ * with any valid id).  out_ids [B]: the next id of every sequence.
+ * With stop_on_eos, TSB200_GptDecode then stops the sequences one by one: a sequence whose previous id was </s> (0)
+ * keeps emitting 0 and its cache, history and Philox step stand still.
+ * SlotSnapshot / SlotRestore / SlotReset / SlotExtend work on ONE sequence while the others keep their state: park a
+ * finished sequence, put another parked one (or an empty one) in its place, give it the rest of its prompt.  A slot
+ * index equal to the number of sequences adds one.  Snapshots are the handles of TSB200_GptCacheSnapshot (one
+ * sequence); SlotExtend runs S >= 1 prompt tokens on top of what the slot holds and returns the slot's next id;
+ * uniforms of slot b come from the Philox stream (seed, seq_base + b).  Not for tensor-parallel engines. */
+TSB200_API int TSB200_GptPrefillRagged(void* gpt, const int32_t* ids, const int32_t* lens, int B, int S,
+                                       const TSB200DecodingOptions* opt, int32_t* out_ids);
+TSB200_API int TSB200_GptSlotSnapshot(void* gpt, int slot, void** snapshot);
+TSB200_API int TSB200_GptSlotRestore(void* gpt, void* snapshot, int slot);
+TSB200_API int TSB200_GptSlotReset(void* gpt, int slot);
+TSB200_API int TSB200_GptSlotExtend(void* gpt, int slot, const int32_t* ids, int S, const TSB200DecodingOptions* opt,
+                                    int32_t* out_id);
 /* device-timed duration (ms, CUDA events on the engine's stream) of the last GptDecode / GptPrefill call and
  * the number of kernel launches it issued (graph replays count their nodes) */
 TSB200_API int TSB200_GptLastTiming(void* gpt, float* ms, int64_t* launches);

@@ -29,11 +29,11 @@ __global__ void embed_kernel(float* x, const T* E, const T* PE, const int* ids,
                              const int* dT0) {
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     int id = ids[r];
     if (id < 0 || id >= V) id = 0;
     const int s = r % S;
+    const int T0 = state_len(dT0, r / S, T0_arg);
     int pos = (pe_mode == 1) ? s : T0 + s;  // pe_mode 1: the reference peeks APE rows [0, S) (PositionEmbedding.cs:30-33)
     if (pos >= pe_rows) pos = pe_rows - 1;
     const T* e = E + (int64_t)id * d;
@@ -46,25 +46,39 @@ __global__ void embed_kernel(float* x, const T* E, const T* PE, const int* ids,
   }
 }
 
-__global__ void gather_last_kernel(float* xl, const float* x, int B, int S, int d) {
-  for (int b = blockIdx.x; b < B; b += gridDim.x)
-    for (int i = threadIdx.x; i < d; i += blockDim.x) xl[(int64_t)b * d + i] = x[((int64_t)b * S + S - 1) * d + i];
+// last prompt row of every sequence; `lens` (device, or NULL): prompts of different lengths padded to S columns
+__global__ void gather_last_kernel(float* xl, const float* x, int B, int S, int d, const int* lens) {
+  for (int b = blockIdx.x; b < B; b += gridDim.x) {
+    int last = lens ? lens[b] - 1 : S - 1;
+    last = last < 0 ? 0 : (last >= S ? S - 1 : last);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) xl[(int64_t)b * d + i] = x[((int64_t)b * S + last) * d + i];
+  }
 }
 
-// state[0] = cache length T, state[1] = Philox step counter, state[2] = output slot of this call
+// state: the device step state (kernels.cuh).  The per-sequence pointers (ids, history, out) address sequence b0 + b of
+// the engine at index b.  stop_fin (sequences with their own lengths only): a sequence whose previous id was </s> (0)
+// has finished: it keeps emitting 0 and neither its history nor its cache length nor its Philox step advance.
 __global__ void commit_kernel(int* ids_cur, const int* ids_new, int* hist,
                               int* hist_len, int hist_stride, int* out, int B, int* state,
-                              int advance_T) {
+                              int advance_T, int b0, int stop_fin) {
   pdl_trigger();
   pdl_wait();
   const int slot = state[2];
+  const bool ragged = state[kStateRagged] != 0;
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    const int id = ids_new[b];
+    int id = ids_new[b];
+    const bool fin = ragged && stop_fin && ids_cur[b] == 0;
+    if (fin) id = 0;
     ids_cur[b] = id;
+    out[(int64_t)slot * B + b] = id;
+    if (fin) continue;
     const int l = hist_len[b];
     if (l < hist_stride) hist[(int64_t)b * hist_stride + l] = id;
     hist_len[b] = l + 1;
-    out[(int64_t)slot * B + b] = id;
+    if (ragged) {
+      if (advance_T) state[kStateLens + b0 + b] += 1;
+      state[state[kStateStepsAt] + b0 + b] += 1;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -105,11 +119,12 @@ struct Dest {  // where a logical tensor lives inside the engine's buffers
 };
 
 struct GraphKey {
-  int B = -1, strategy = -1, splits = -1, n_blocked = -1;
+  int B = -1, strategy = -1, splits = -1, n_blocked = -1, ragged = -1, stop_fin = -1;
   float topP = 0, temperature = 0, penalty = 0;
   uint64_t seed = 0, seq_base = 0, blocked_hash = 0;
   bool operator==(const GraphKey& o) const {
-    return B == o.B && strategy == o.strategy && splits == o.splits && n_blocked == o.n_blocked && topP == o.topP &&
+    return B == o.B && strategy == o.strategy && splits == o.splits && n_blocked == o.n_blocked && ragged == o.ragged &&
+           stop_fin == o.stop_fin && topP == o.topP &&
            temperature == o.temperature && penalty == o.penalty && seed == o.seed && seq_base == o.seq_base &&
            blocked_hash == o.blocked_hash;
   }
@@ -152,8 +167,15 @@ struct Gpt {
   void *lin_ws = nullptr, *attn_ws = nullptr, *topp_ws = nullptr;
   int64_t lin_ws_bytes = 0, attn_ws_bytes = 0, topp_ws_bytes = 0;
   int n_blocked = 0, blocked_cap = 0;
-  int B = 0, T = 0;
-  uint32_t step = 0;
+  int B = 0, T = 0;            // sequences in the cache; cache length (the longest sequence's when they differ)
+  uint32_t step = 0;           // Philox step of the next sampled token (the largest when they differ)
+  // sequences with their own cache lengths / Philox steps (ragged prompts, refilled slots): host mirrors of the device
+  // arrays.  While all sequences agree, `ragged` is false and the kernels read the scalars.
+  std::vector<int> Ts, steps_v;
+  bool ragged = false;
+  int stop_fin = 0;            // per-sequence stop rule in the captured step (ragged decode with stop_on_eos)
+  int seq0 = 0;                // first sequence the per-sequence buffers address (a single-slot prompt run), else 0
+  const int* gather_lens = nullptr;   // device prompt lengths of a padded prefill (NULL: every prompt fills its S columns)
   bool probs_valid = false;
   // graph
   cudaGraphExec_t gexec = nullptr;
@@ -498,7 +520,7 @@ static int ensure_stack(Gpt* g, int B) {
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
   if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
   g->own_B = 0;
-  if (!g->use_stack) return 1;
+  if (!g->use_stack || g->ragged) return 1;   // sequences of different lengths: one launch per operation
   // tensor-parallel engines: one sequence, and only once the ranks' exchange regions are mapped into each other
   const bool own_tp_ok = g->tp == 1 || (g->xch_ready && g->tp_peer && B == 1 && g->xch_own_off != 0);
   if (g->use_owner && own_tp_ok && B <= g->own_cap && B <= kOwnMaxRows) {
@@ -626,7 +648,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     prof_end(g, KC_EMBED);
     TSB_TRY(check_launch("embed"));
   }
-  if (S == 1 && use_state && g->use_stack && g->own_B == B && owner_packed(g->own)) {
+  if (S == 1 && use_state && g->use_stack && !g->ragged && g->own_B == B && owner_packed(g->own)) {
     prof_begin(g);
     OwnTp otp{};
     otp.rank = g->tp_rank; otp.size = g->tp; otp.offset = (long long)g->xch_own_off;
@@ -640,7 +662,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     }
   }
   if (S == 1 && use_state) g->last_path = 0;
-  if (S == 1 && use_state && g->use_stack && B <= g->stack_max_B && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
+  if (S == 1 && use_state && g->use_stack && !g->ragged && B <= g->stack_max_B && g->stack_dev && g->stack_B == B && g->stack_key == (const void*)g->x) {
     StackConfig sc{};
     sc.dtype = dt; sc.M = B; sc.H = c.H; sc.Hkv = c.Hkv; sc.hd = c.hd; sc.Tmax = c.max_tokens; sc.qkv_rs = g->Nqkv;
     sc.use_rope = c.pe_type == 2; sc.rope_tab = g->rope_tab; sc.dT = dT;
@@ -671,7 +693,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   }
   const float* xlast = g->x;
   if (S > 1) {
-    gather_last_kernel<<<B, 256, 0, g->s>>>(g->xl, g->x, B, S, d);
+    gather_last_kernel<<<B, 256, 0, g->s>>>(g->xl, g->x, B, S, d, g->gather_lens);
     count_launch(dev);
     TSB_TRY(check_launch("gather_last"));
     xlast = g->xl;
@@ -689,11 +711,12 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
   const int use_temp = (sampling && opt->temperature != 1.0f) ? 1 : 0;
   PROF(KC_SAMPLE, launch_softmax_argmax(dev, g->st, g->ids_new, sampling ? g->probs : nullptr, g->logits, B, c.V, opt->temperature, use_temp, g->blocked, g->n_blocked, g->s));
   if (sampling) {
-    PROF(KC_SAMPLE, launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state + 1 : nullptr, g->s));
+    PROF(KC_SAMPLE, launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state : nullptr, g->s));
     PROF(KC_SAMPLE, launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
   }
   prof_begin(g);
-  TSB_CUDA(launch_k(commit_kernel, dim3(1), dim3(256), 0, g->s, g->ids_cur, (const int*)g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0));
+  TSB_CUDA(launch_k(commit_kernel, dim3(1), dim3(256), 0, g->s, g->ids_cur, (const int*)g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0, g->seq0,
+                    advance_T ? g->stop_fin : 0));
   count_launch(dev);
   prof_end(g, KC_COMMIT);
   return check_launch("commit");
@@ -741,10 +764,60 @@ static int upload_blocked(Gpt* g, const TSB200DecodingOptions* opt) {
   return 1;
 }
 
+static int state_words(const Gpt* g) { return kStateLens + 2 * g->c.max_batch; }
+// host mirrors of the per-sequence lengths / steps follow the scalars while the sequences agree
+static void mirror_uniform(Gpt* g) {
+  g->Ts.assign(g->c.max_batch, 0);
+  g->steps_v.assign(g->c.max_batch, 0);
+  for (int b = 0; b < g->B; ++b) {
+    g->Ts[b] = g->T;
+    g->steps_v[b] = (int)g->step;
+  }
+  g->ragged = false;
+}
+// after a per-sequence change: the scalars hold the largest values, `ragged` says whether the sequences differ
+static void refresh_ragged(Gpt* g) {
+  int tmax = 0, smax = 0;
+  bool differ = false;
+  for (int b = 0; b < g->B; ++b) {
+    tmax = g->Ts[b] > tmax ? g->Ts[b] : tmax;
+    smax = g->steps_v[b] > smax ? g->steps_v[b] : smax;
+    differ = differ || g->Ts[b] != g->Ts[0] || g->steps_v[b] != g->steps_v[0];
+  }
+  g->T = tmax;
+  g->step = (uint32_t)smax;
+  if (differ != g->ragged && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  g->ragged = differ;
+}
+static void fill_state(const Gpt* g, int* hst, int out_slot) {
+  const int MB = g->c.max_batch;
+  for (int i = 0; i < state_words(g); ++i) hst[i] = 0;
+  hst[0] = g->T; hst[1] = (int)g->step; hst[2] = out_slot;
+  hst[kStateRagged] = g->ragged ? 1 : 0;
+  hst[kStateStepsAt] = kStateLens + MB;
+  for (int b = 0; b < MB; ++b) {
+    const bool have = b < (int)g->Ts.size();
+    hst[kStateLens + b] = have ? g->Ts[b] : 0;
+    hst[kStateLens + MB + b] = have ? g->steps_v[b] : 0;
+  }
+}
 static int set_state(Gpt* g, int out_slot) {
-  const int hst[3] = {g->T, (int)g->step, out_slot};
-  TSB_CUDA(cudaMemcpyAsync(g->state, hst, sizeof(hst), cudaMemcpyHostToDevice, g->s));
-  TSB_CUDA(cudaStreamSynchronize(g->s));  // hst is on the stack
+  std::vector<int> hst(state_words(g));
+  fill_state(g, hst.data(), out_slot);
+  TSB_CUDA(cudaMemcpyAsync(g->state, hst.data(), hst.size() * sizeof(int), cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));  // hst is pageable
+  return 1;
+}
+// per-sequence lengths and steps as the device left them (a decode whose sequences advance on their own)
+static int read_state(Gpt* g) {
+  std::vector<int> hst(state_words(g));
+  TSB_CUDA(cudaMemcpy(hst.data(), g->state, hst.size() * sizeof(int), cudaMemcpyDeviceToHost));
+  const int MB = g->c.max_batch;
+  for (int b = 0; b < g->B; ++b) {
+    g->Ts[b] = hst[kStateLens + b];
+    g->steps_v[b] = hst[kStateLens + MB + b];
+  }
+  refresh_ragged(g);
   return 1;
 }
 
@@ -761,6 +834,7 @@ static int ensure_graph(Gpt* g, const TSB200DecodingOptions* opt, int n_steps) {
   key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
   key.topP = opt->topP; key.temperature = opt->temperature; key.penalty = opt->repeatPenalty;
   key.seed = opt->seed; key.seq_base = opt->seq_base;
+  key.ragged = g->ragged ? 1 : 0; key.stop_fin = g->stop_fin;
   if (g->gexec && g->gkey == key) return 1;
   if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   cudaGraph_t graph = nullptr;
@@ -889,7 +963,8 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   G_ALLOC(g->ids_new, (int64_t)MB * 4);
   G_ALLOC(g->hist, (int64_t)MB * cc.max_tokens * 4);
   G_ALLOC(g->hist_len, (int64_t)MB * 4);
-  G_ALLOC(g->state, 64);
+  G_ALLOC(g->state, (int64_t)(kStateLens + 2 * cc.max_batch) * 4 + 64);
+  mirror_uniform(g);
   G_ALLOC(g->out_dev, (int64_t)MB * (cc.max_tokens + 1) * 4);
   G_ALLOC(g->blocked, 1024);
   g->blocked_cap = 256;
@@ -1131,6 +1206,8 @@ int TSB200_GptReset(void* h) {
   g->T = 0;
   g->step = 0;
   g->probs_valid = false;
+  if (g->ragged && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+  mirror_uniform(g);
   TSB_CUDA(cudaMemsetAsync(g->hist_len, 0, (size_t)g->c.max_batch * 4, g->s));
   return 1;
 }
@@ -1139,18 +1216,26 @@ int TSB200_GptReset(void* h) {
 
 // Runs S prompt tokens per sequence through the stack on top of T0 = g->T cached positions (0: a fresh prompt;
 // > 0: the suffix of a prompt whose first T0 tokens are already cached), samples the next id.
-static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids, bool extend) {
+// `plen` (prefill only, or NULL): the prompts' own lengths; shorter prompts are padded to S columns (the pad ids are
+// ignored: every sequence continues from its own last token, as if it had been run alone).
+static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids, bool extend,
+                      const int32_t* plen = nullptr) {
   const TSB200GptConfig& c = g->c;
   const int T0 = g->T;
   if (extend) {
     TSB_CHECK(T0 > 0 && g->B > 0, "gpt_extend: nothing is cached (prefill or restore a snapshot first)");
     TSB_CHECK(B == g->B, "gpt_extend: batch %d differs from the cached batch %d", B, g->B);
+    TSB_CHECK(!g->ragged, "gpt_extend: the sequences have different lengths; extend them one by one (TSB200_GptSlotExtend)");
   } else {
     TSB_CHECK(T0 == 0, "gpt_prefill: the cache is not empty (call TSB200_GptReset first)");
     TSB_CHECK(B > 0 && B <= c.max_batch, "gpt_prefill: batch %d exceeds capacity %d", B, c.max_batch);
   }
   TSB_CHECK(S > 0 && T0 + S < c.max_tokens, "OOM: prompt of %d tokens exceeds the KV-cache capacity %d", T0 + S, c.max_tokens);
   for (int64_t i = 0; i < (int64_t)B * S; ++i) TSB_CHECK(ids[i] >= 0 && ids[i] < c.V, "gpt_prefill: token id %d out of range", ids[i]);
+  if (plen) {
+    TSB_CHECK(g->tp == 1, "gpt_prefill: prompts of different lengths are not served by tensor-parallel engines");
+    for (int b = 0; b < B; ++b) TSB_CHECK(plen[b] >= 1 && plen[b] <= S, "gpt_prefill: prompt length %d of sequence %d is outside [1, %d]", plen[b], b, S);
+  }
   TSB_TRY(ensure_act(g, (int64_t)B * S));
   void* ids_dev = nullptr;
   TSB_CUDA(cudaMalloc(&ids_dev, (size_t)B * S * 4));
@@ -1162,16 +1247,28 @@ static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200Deco
     //  an extension overwrites the pending id at position T0: the caller's tokens are the text from there on
     if (cudaMemcpy2DAsync(g->hist + T0, (size_t)c.max_tokens * 4, ids_dev, (size_t)S * 4, (size_t)S * 4, B, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history copy failed"); break; }
     std::vector<int> lens(B, T0 + S);
+    if (plen)
+      for (int b = 0; b < B; ++b) lens[b] = plen[b];
     if (cudaMemcpyAsync(g->hist_len, lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: history length upload failed"); break; }
     cudaStreamSynchronize(g->s);
     g->B = B;
     if (!extend) g->step = 0;
+    mirror_uniform(g);
+    if (plen) {   // the device state already holds the lengths the prompts END with: the last-row gather reads them
+      for (int b = 0; b < B; ++b) g->Ts[b] = plen[b];
+      refresh_ragged(g);
+      g->T = T0;  // the forward pass below still starts from an empty cache
+    }
     if (!(ok = upload_blocked(g, opt))) break;
     if (!(ok = set_state(g, 0))) break;
     const long long l0 = g->st->launches;
     cudaEventRecord(g->ev0, g->s);
-    if (!(ok = enqueue_forward(g, B, S, T0, false, 1))) break;
+    g->gather_lens = plen ? g->state + kStateLens : nullptr;
+    ok = enqueue_forward(g, B, S, T0, false, 1);
+    g->gather_lens = nullptr;
+    if (!ok) break;
     g->T = T0 + S;
+    if (plen) refresh_ragged(g);   // T = the longest prompt
     if (!(ok = enqueue_sample(g, B, opt, true, false))) break;
     cudaEventRecord(g->ev1, g->s);
     if (cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: %s", cudaGetErrorString(cudaGetLastError())); break; }
@@ -1179,6 +1276,10 @@ static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200Deco
     if (!(ok = check_err_flag(g))) break;
     g->last_launches = g->st->launches - l0;
     g->step += 1;
+    for (int b = 0; b < B; ++b) {
+      g->steps_v[b] += 1;
+      if (!plen) g->Ts[b] = g->T;
+    }
     g->probs_valid = (opt->strategy == 1);
     if (out_ids && cudaMemcpy(out_ids, g->out_dev, (size_t)B * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = 0; set_last_error("gpt_prefill: id download failed"); break; }
   } while (0);
@@ -1194,6 +1295,14 @@ int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200Dec
   TSB_CHECK(g && ids && opt, "gpt_prefill: null argument");
   TSB_TRY(use_device(g->c.device, nullptr));
   return run_prompt(g, ids, B, S, opt, out_ids, false);
+}
+
+int TSB200_GptPrefillRagged(void* h, const int32_t* ids, const int32_t* lens, int B, int S, const TSB200DecodingOptions* opt,
+                            int32_t* out_ids) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ids && lens && opt, "gpt_prefill_ragged: null argument");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  return run_prompt(g, ids, B, S, opt, out_ids, false, lens);
 }
 
 int TSB200_GptExtend(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
@@ -1216,6 +1325,7 @@ int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int
   if (n_steps == 0) return 1;
   const int B = g->B;
   TSB_TRY(upload_blocked(g, opt));
+  g->stop_fin = (g->ragged && stop_on_eos) ? 1 : 0;   // sequences with their own lengths stop one by one
   TSB_TRY(set_state(g, 0));
   TSB_TRY(ensure_graph(g, opt, n_steps));
   std::vector<int> last(B);
@@ -1252,8 +1362,16 @@ int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int
   TSB_CUDA(cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1));
   TSB_TRY(check_err_flag(g));
   g->last_launches = g->graph_nodes * done;
-  g->T += done;
-  g->step += (uint32_t)done;
+  if (g->ragged) {
+    TSB_TRY(read_state(g));   // finished sequences did not advance
+  } else {
+    g->T += done;
+    g->step += (uint32_t)done;
+    for (int b = 0; b < B; ++b) {
+      g->Ts[b] = g->T;
+      g->steps_v[b] = (int)g->step;
+    }
+  }
   g->probs_valid = (opt->strategy == 1);
   if (steps_done) *steps_done = done;
   if (out_ids) {
@@ -1296,6 +1414,13 @@ int TSB200_GptCacheLength(void* h, int* T) {
   return 1;
 }
 
+int TSB200_GptCacheLengths(void* h, int* lens, int n) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && lens && n >= 0, "gpt_cache_lengths: bad arguments");
+  for (int b = 0; b < n; ++b) lens[b] = b < g->B ? g->Ts[b] : 0;
+  return 1;
+}
+
 }  // extern "C"
 
 // A parked KV cache: rows [0, T) of every layer's K and V for B sequences, compacted, plus what a later call needs
@@ -1317,6 +1442,7 @@ int TSB200_GptCacheSnapshot(void* h, void** snap_out) {
   const TSB200GptConfig& c = g->c;
   TSB_TRY(use_device(c.device, nullptr));
   TSB_CHECK(g->T > 0 && g->B > 0, "gpt_cache_snapshot: nothing is cached");
+  TSB_CHECK(!g->ragged, "gpt_cache_snapshot: the sequences have different lengths; park them one by one (TSB200_GptSlotSnapshot)");
   GptSnapshot* sn = new GptSnapshot();
   sn->device = c.device; sn->B = g->B; sn->T = g->T; sn->L = c.L; sn->Hkv = c.Hkv; sn->hd = c.hd; sn->es = g->es;
   sn->step = g->step;
@@ -1404,9 +1530,183 @@ int TSB200_GptCacheRestore(void* h, void* snap, int B_new) {
   TSB_CUDA(cudaMemcpyAsync(g->hist_len, lens.data(), (size_t)B_new * 4, cudaMemcpyHostToDevice, g->s));
   TSB_CUDA(cudaMemcpyAsync(g->ids_cur, pend.data(), (size_t)B_new * 4, cudaMemcpyHostToDevice, g->s));
   TSB_CUDA(cudaStreamSynchronize(g->s));  // lens / pend are on the stack
+  if (g->ragged && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   g->B = B_new;
   g->T = sn->T;
   g->step = sn->step;
+  mirror_uniform(g);
+  g->probs_valid = false;
+  return 1;
+}
+
+// ---- one sequence of the batch at a time: park it, replace it, give it more prompt, while the others keep their state
+int TSB200_GptSlotSnapshot(void* h, int slot, void** snap_out) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && snap_out, "gpt_slot_snapshot: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(slot >= 0 && slot < g->B && g->Ts[slot] > 0, "gpt_slot_snapshot: sequence %d holds nothing", slot);
+  GptSnapshot* sn = new GptSnapshot();
+  sn->device = c.device; sn->B = 1; sn->T = g->Ts[slot]; sn->L = c.L; sn->Hkv = c.Hkv; sn->hd = c.hd; sn->es = g->es;
+  sn->step = (uint32_t)g->steps_v[slot];
+  const size_t row = (size_t)sn->T * c.hd * g->es, pitch = (size_t)c.max_tokens * c.hd * g->es;
+  const size_t rows = (size_t)c.Hkv;
+  sn->bytes = (size_t)c.L * 2 * rows * row;
+  auto fail = [&]() { if (sn->kv) cudaFree(sn->kv); delete sn; return 0; };
+  if (cudaMalloc(&sn->kv, sn->bytes) != cudaSuccess) {
+    cudaGetLastError();
+    set_last_error("OOM: gpt_slot_snapshot could not allocate %zu bytes", sn->bytes);
+    return fail();
+  }
+  for (int k = 0; k < c.L; ++k)
+    for (int w = 0; w < 2; ++w) {
+      unsigned char* dst = (unsigned char*)sn->kv + ((size_t)k * 2 + w) * rows * row;
+      const unsigned char* src = (const unsigned char*)(w == 0 ? g->L[k].cK : g->L[k].cV) + (size_t)slot * c.Hkv * pitch;
+      if (cudaMemcpy2DAsync(dst, row, src, pitch, row, rows, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess) {
+        set_last_error("gpt_slot_snapshot: cache copy failed");
+        return fail();
+      }
+    }
+  sn->hist.assign((size_t)sn->T + 1, 0);
+  sn->pending.assign(1, 0);
+  const size_t hist_w = (size_t)(sn->T + 1 <= c.max_tokens ? sn->T + 1 : c.max_tokens) * 4;
+  if (cudaMemcpyAsync(sn->hist.data(), g->hist + (size_t)slot * c.max_tokens, hist_w, cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
+      cudaMemcpyAsync(sn->pending.data(), g->ids_cur + slot, 4, cudaMemcpyDeviceToHost, g->s) != cudaSuccess ||
+      cudaStreamSynchronize(g->s) != cudaSuccess) {
+    set_last_error("gpt_slot_snapshot: %s", cudaGetErrorString(cudaGetLastError()));
+    return fail();
+  }
+  *snap_out = sn;
+  return 1;
+}
+
+// slot == the number of sequences: the batch grows by one
+static int slot_claim(Gpt* g, int slot, const char* who) {
+  TSB_CHECK(g->tp == 1, "%s: tensor-parallel engines serve one set of sequences of equal length", who);
+  TSB_CHECK(slot >= 0 && slot <= g->B && slot < g->c.max_batch, "%s: sequence index %d out of range (%d in use, capacity %d)", who, slot, g->B,
+            g->c.max_batch);
+  if (slot == g->B) {
+    if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+    g->B += 1;
+    g->Ts[slot] = 0;
+    g->steps_v[slot] = 0;
+  }
+  return 1;
+}
+
+int TSB200_GptSlotReset(void* h, int slot) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_slot_reset: null engine");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  TSB_TRY(slot_claim(g, slot, "gpt_slot_reset"));
+  g->Ts[slot] = 0;
+  g->steps_v[slot] = 0;
+  TSB_CUDA(cudaMemsetAsync(g->hist_len + slot, 0, 4, g->s));
+  refresh_ragged(g);
+  g->probs_valid = false;
+  return 1;
+}
+
+int TSB200_GptSlotRestore(void* h, void* snap, int slot) {
+  Gpt* g = (Gpt*)h;
+  GptSnapshot* sn = (GptSnapshot*)snap;
+  TSB_CHECK(g && sn, "gpt_slot_restore: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(sn->device == c.device && sn->L == c.L && sn->Hkv == c.Hkv && sn->hd == c.hd && sn->es == g->es,
+            "gpt_slot_restore: the snapshot was taken from a different model or device");
+  TSB_CHECK(sn->B == 1, "gpt_slot_restore: the snapshot holds %d sequences; a slot takes one", sn->B);
+  TSB_CHECK(sn->T < c.max_tokens, "OOM: snapshot of %d tokens exceeds the KV-cache capacity %d", sn->T, c.max_tokens);
+  TSB_TRY(slot_claim(g, slot, "gpt_slot_restore"));
+  const size_t row = (size_t)sn->T * c.hd * g->es, pitch = (size_t)c.max_tokens * c.hd * g->es;
+  const size_t rows = (size_t)c.Hkv;
+  for (int k = 0; k < c.L; ++k)
+    for (int w = 0; w < 2; ++w) {
+      const unsigned char* src = (const unsigned char*)sn->kv + ((size_t)k * 2 + w) * rows * row;
+      unsigned char* dst = (unsigned char*)(w == 0 ? g->L[k].cK : g->L[k].cV) + (size_t)slot * c.Hkv * pitch;
+      TSB_CUDA(cudaMemcpy2DAsync(dst, pitch, src, row, row, rows, cudaMemcpyDeviceToDevice, g->s));
+    }
+  const int len = sn->T + 1;
+  TSB_CUDA(cudaMemcpyAsync(g->hist + (size_t)slot * c.max_tokens, sn->hist.data(), (size_t)len * 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaMemcpyAsync(g->hist_len + slot, &len, 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaMemcpyAsync(g->ids_cur + slot, sn->pending.data(), 4, cudaMemcpyHostToDevice, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));  // `len` is on the stack
+  g->Ts[slot] = sn->T;
+  g->steps_v[slot] = (int)sn->step;
+  refresh_ragged(g);
+  g->probs_valid = false;
+  return 1;
+}
+
+// S prompt tokens for ONE sequence on top of what it has cached (nothing after TSB200_GptSlotReset), then its next id.
+// The run addresses the sequence's rows of every per-sequence buffer; the other sequences are not touched.
+int TSB200_GptSlotExtend(void* h, int slot, const int32_t* ids, int S, const TSB200DecodingOptions* opt, int32_t* out_id) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && ids && opt, "gpt_slot_extend: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_TRY(slot_claim(g, slot, "gpt_slot_extend"));
+  const int T0 = g->Ts[slot];
+  TSB_CHECK(S > 0 && T0 + S < c.max_tokens, "OOM: prompt of %d tokens exceeds the KV-cache capacity %d", T0 + S, c.max_tokens);
+  for (int i = 0; i < S; ++i) TSB_CHECK(ids[i] >= 0 && ids[i] < c.V, "gpt_slot_extend: token id %d out of range", ids[i]);
+  TSB_TRY(ensure_act(g, (int64_t)S));
+  void* ids_dev = nullptr;
+  TSB_CUDA(cudaMalloc(&ids_dev, (size_t)S * 4));
+  // the view of one sequence: every per-sequence pointer moves to the sequence's rows
+  struct View {
+    Gpt* g; int slot; std::vector<std::pair<void*, void*>> kv; int *hist, *hist_len, *ids_cur; uint32_t step;
+    View(Gpt* g_, int slot_) : g(g_), slot(slot_), hist(g_->hist), hist_len(g_->hist_len), ids_cur(g_->ids_cur), step(g_->step) {
+      const size_t pitch = (size_t)g->c.max_tokens * g->c.hd * g->es * g->c.Hkv;
+      for (LayerW& L : g->L) {
+        kv.push_back({L.cK, L.cV});
+        L.cK = (char*)L.cK + (size_t)slot * pitch;
+        L.cV = (char*)L.cV + (size_t)slot * pitch;
+      }
+      g->hist += (size_t)slot * g->c.max_tokens;
+      g->hist_len += slot;
+      g->ids_cur += slot;
+      g->seq0 = slot;
+      g->step = (uint32_t)g->steps_v[slot];
+    }
+    ~View() {
+      for (size_t k = 0; k < kv.size(); ++k) { g->L[k].cK = kv[k].first; g->L[k].cV = kv[k].second; }
+      g->hist = hist; g->hist_len = hist_len; g->ids_cur = ids_cur; g->seq0 = 0; g->step = step;
+      g->ids_in = nullptr;
+    }
+  };
+  int ok = 1;
+  {
+    // the device state is set for the whole batch first (the commit kernel counts the sequence's step there)
+    if (!upload_blocked(g, opt) || !set_state(g, 0)) { cudaFree(ids_dev); return 0; }
+    View view(g, slot);
+    g->ids_in = (int*)ids_dev;
+    TSB200DecodingOptions o2 = *opt;
+    o2.seq_base += (uint64_t)slot;
+    const int len = T0 + S;
+    do {
+      if (cudaMemcpyAsync(ids_dev, ids, (size_t)S * 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess ||
+          cudaMemcpyAsync(g->hist + T0, ids_dev, (size_t)S * 4, cudaMemcpyDeviceToDevice, g->s) != cudaSuccess ||
+          cudaMemcpyAsync(g->hist_len, &len, 4, cudaMemcpyHostToDevice, g->s) != cudaSuccess ||
+          cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_slot_extend: upload failed"); break; }
+      const long long l0 = g->st->launches;
+      cudaEventRecord(g->ev0, g->s);
+      if (!(ok = enqueue_forward(g, 1, S, T0, false, 1))) break;
+      if (!(ok = enqueue_sample(g, 1, &o2, false, false))) break;
+      // the sequence's logits also go to its own row of the logits buffer
+      if (slot != 0) cudaMemcpyAsync(g->logits + (size_t)slot * c.V, g->logits, (size_t)c.V * 4, cudaMemcpyDeviceToDevice, g->s);
+      cudaEventRecord(g->ev1, g->s);
+      if (cudaStreamSynchronize(g->s) != cudaSuccess) { ok = 0; set_last_error("gpt_slot_extend: %s", cudaGetErrorString(cudaGetLastError())); break; }
+      cudaEventElapsedTime(&g->last_ms, g->ev0, g->ev1);
+      if (!(ok = check_err_flag(g))) break;
+      g->last_launches = g->st->launches - l0;
+      if (out_id && cudaMemcpy(out_id, g->out_dev, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = 0; set_last_error("gpt_slot_extend: id download failed"); break; }
+    } while (0);
+  }
+  cudaFree(ids_dev);
+  if (!ok) return 0;
+  g->Ts[slot] = T0 + S;
+  g->steps_v[slot] += 1;
+  refresh_ragged(g);
   g->probs_valid = false;
   return 1;
 }
@@ -1470,19 +1770,20 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   TSB_CHECK(g->T > 0 && g->B > 0, "gpt_step_host: prefill first");
   TSB_CHECK(g->T + 1 <= c.max_tokens, "OOM: KV-cache capacity %d exceeded", c.max_tokens);
   const int B = g->B;
-  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)c.max_batch * 4 + 64, cudaHostAllocDefault));
+  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)(c.max_batch + state_words(g)) * 4 + 64, cudaHostAllocDefault));
   TSB_TRY(upload_blocked(g, opt));
+  g->stop_fin = 0;
   if (!g->gexec) TSB_TRY(set_state(g, 0));
   TSB_TRY(ensure_graph(g, opt, 1));
   for (int b = 0; b < B; ++b) {
     TSB_CHECK(last_ids[b] >= 0 && last_ids[b] < c.V, "gpt_step_host: token id %d out of range", last_ids[b]);
     g->pin_ids[b] = last_ids[b];
   }
-  const int hst[3] = {g->T, (int)g->step, 0};
-  int* pin_state = g->pin_ids + c.max_batch;  // second half of the pinned block
-  pin_state[0] = hst[0]; pin_state[1] = hst[1]; pin_state[2] = hst[2];
+  int* pin_state = g->pin_ids + c.max_batch;  // second part of the pinned block
+  fill_state(g, pin_state, 0);
   TSB_CUDA(cudaMemcpyAsync(g->ids_cur, g->pin_ids, (size_t)B * 4, cudaMemcpyHostToDevice, g->s));
-  TSB_CUDA(cudaMemcpyAsync(g->state, pin_state, 12, cudaMemcpyHostToDevice, g->s));
+  // the scalars and the mode flags always; the per-sequence arrays only when the sequences differ
+  TSB_CUDA(cudaMemcpyAsync(g->state, pin_state, (size_t)(g->ragged ? state_words(g) : kStateLens) * 4, cudaMemcpyHostToDevice, g->s));
   TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
   count_launch(c.device, g->graph_nodes);
   TSB_CUDA(cudaMemcpyAsync(g->pin_ids, g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
@@ -1491,6 +1792,10 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   for (int b = 0; b < B; ++b) out_ids[b] = g->pin_ids[b];
   g->T += 1;
   g->step += 1;
+  for (int b = 0; b < B; ++b) {
+    g->Ts[b] += 1;
+    g->steps_v[b] += 1;
+  }
   g->probs_valid = (opt->strategy == 1);
   g->last_launches = g->graph_nodes;
   return 1;

@@ -53,6 +53,21 @@ struct StackOp {
   int xsite, ssite;
   float* x_out;
 };
+// Device step state of the GPT engine (ints), read by the kernels of a captured decode step:
+//   [0] cache length (all sequences), [1] Philox step (all sequences), [2] output slot of this call,
+//   [3] 1 when the sequences have their own lengths / steps, [4] where the per-sequence steps start,
+//   [kStateLens + b] cache length of sequence b, [state[4] + b] its Philox step.
+constexpr int kStateRagged = 3, kStateStepsAt = 4, kStateLens = 8;
+#ifdef __CUDACC__
+__device__ __forceinline__ int state_len(const int* st, int b, int fallback) {
+  if (!st) return fallback;
+  return st[kStateRagged] ? st[kStateLens + b] : st[0];
+}
+__device__ __forceinline__ int state_step(const int* st, int b, int fallback) {
+  if (!st) return fallback;
+  return st[kStateRagged] ? st[st[kStateStepsAt] + b] : st[1];
+}
+#endif
 constexpr int kStackMaxRanks = 8;
 constexpr int kStackXchSites = 4;     // exchange buffers: {out-projection, FFN down} x layer parity
 constexpr int kStackXchRows = 8;      // rows per exchange slot

@@ -58,7 +58,6 @@ __global__ void rope_append_kernel(T* q, const T* k, const T* v, int64_t q_rs,
                                    const float2* tab) {
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;  // the engine keeps the cache length on the device so one CUDA graph serves every step
   const int hp = hd / 2;
   const int64_t per_row = (int64_t)(H + 2 * Hkv) * hp;
   const int64_t n = (int64_t)B * S * per_row;
@@ -66,6 +65,7 @@ __global__ void rope_append_kernel(T* q, const T* k, const T* v, int64_t q_rs,
     const int64_t row = p / per_row;  // b*S + s
     int rem = (int)(p % per_row);
     const int b = (int)(row / S), s = (int)(row % S);
+    const int T0 = state_len(dT0, b, T0_arg);  // the engine keeps the cache lengths on the device so one CUDA graph serves every step
     const int pos = T0 + s;
     if (pos >= Tmax) continue;  // capacity is checked on the host; never write past the cache
     const int head = rem / hp, i = rem % hp;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(T* out, float* part,
   constexpr int EPL = Vec16<T>::N;
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int T0 = state_len(dT0, (int)blockIdx.z / S, T0_arg);
   const int lpt = hd / EPL;              // lanes per token (power of two, <= 32)
   const int tpw = 32 / lpt;              // tokens per warp iteration
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_staged_kernel(T* out, float
   extern __shared__ __align__(16) unsigned char attn_smem[];
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int T0 = state_len(dT0, (int)blockIdx.z, T0_arg);
   const int lpt = hd / EPL;              // lanes per token (power of two, <= 32)
   const int tpw = 32 / lpt;              // tokens per warp pass
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_mma_kernel(__half* out, flo
   extern __shared__ __align__(128) unsigned char attn_smem[];
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int T0 = state_len(dT0, (int)blockIdx.z, T0_arg);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int G = H / Hkv;                // query heads per KV head (<= 8)
@@ -619,7 +619,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_prefill_mma_kernel(__half* 
   extern __shared__ __align__(128) unsigned char attn_smem[];
   pdl_trigger();
   pdl_wait();
-  const int T0 = dT0 ? *dT0 : T0_arg;
+  const int T0 = state_len(dT0, (int)blockIdx.z, T0_arg);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int G = H / Hkv;                       // 1, 2, 4 or 8

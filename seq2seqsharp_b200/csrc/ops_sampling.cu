@@ -156,12 +156,12 @@ __host__ __device__ inline float philox_uniform(uint64_t seed, uint64_t seq, uin
   philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
   return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
 }
-__global__ void philox_kernel(float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step_arg, const int* dstep) {
+// dstate: the engine's device step state (kernels.cuh), or NULL: then every row uses step_arg
+__global__ void philox_kernel(float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step_arg, const int* dstate) {
   pdl_trigger();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t step = dstep ? (uint32_t)*dstep : step_arg;
-  if (i < n) u[i] = philox_uniform(seed, seq_first + (uint64_t)i, step);
+  if (i < n) u[i] = philox_uniform(seed, seq_first + (uint64_t)i, (uint32_t)state_step(dstate, i, (int)step_arg));
 }
 
 // ------------------------------------------------------------------------------------------------ Top-P

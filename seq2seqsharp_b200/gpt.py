@@ -314,6 +314,51 @@ class GPT:
         self._B = B
         return out
 
+    def PrefillRagged(self, prompts, opts: DecodingOptions):
+        """Prompts of different lengths in one prefill (the reference pads them: BuildInTokens.PadSentences +
+        BuildSelfTriMask, Decoder.cs:656,687-692).  `prompts`: a list of id lists.  Every sequence keeps its own cache
+        length and continues as if it had been run alone.  Returns the next id of every sequence."""
+        lens = np.array([len(p) for p in prompts], dtype=np.int32)
+        B, S = len(prompts), int(lens.max())
+        ids = np.zeros((B, S), dtype=np.int32)
+        for b, p in enumerate(prompts):
+            ids[b, :len(p)] = np.asarray(p, dtype=np.int32)
+        out = np.zeros(B, dtype=np.int32)
+        c = self._opts(opts)
+        N.call("TSB200_GptPrefillRagged", self._h, ids.ctypes.data_as(C.c_void_p), lens.ctypes.data_as(C.c_void_p), B, S, C.byref(c),
+               out.ctypes.data_as(C.c_void_p))
+        self._B = B
+        return out
+
+    def CacheLengths(self):
+        lens = np.zeros(self._B, dtype=np.int32)
+        N.call("TSB200_GptCacheLengths", self._h, lens.ctypes.data_as(C.c_void_p), self._B)
+        return lens
+
+    # ---- one sequence of the batch at a time (the others keep their state)
+    def SlotSnapshot(self, slot: int) -> "KvSnapshot":
+        h = C.c_void_p()
+        N.call("TSB200_GptSlotSnapshot", self._h, int(slot), C.byref(h))
+        return KvSnapshot(h)
+
+    def SlotRestore(self, snap: "KvSnapshot", slot: int):
+        N.call("TSB200_GptSlotRestore", self._h, snap._h, int(slot))
+        self._B = max(self._B, slot + 1)
+
+    def SlotReset(self, slot: int):
+        N.call("TSB200_GptSlotReset", self._h, int(slot))
+        self._B = max(self._B, slot + 1)
+
+    def SlotExtend(self, slot: int, tokens, opts: DecodingOptions) -> int:
+        """Runs `tokens` (one sequence's prompt, or the rest of it) on top of what the slot holds; returns its next id."""
+        ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(-1))
+        out = np.zeros(1, dtype=np.int32)
+        c = self._opts(opts)
+        N.call("TSB200_GptSlotExtend", self._h, int(slot), ids.ctypes.data_as(C.c_void_p), int(ids.size), C.byref(c),
+               out.ctypes.data_as(C.c_void_p))
+        self._B = max(self._B, slot + 1)
+        return int(out[0])
+
     def Decode(self, n_steps: int, opts: DecodingOptions, stop_on_eos: bool = False):
         out = np.zeros((self._B, n_steps), dtype=np.int32)
         done = C.c_int(0)
