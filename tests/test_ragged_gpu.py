@@ -25,7 +25,8 @@ CFGS = [
 ]
 LENS = [19, 7, 12, 1]
 N_NEW = 10
-MAX_POS = 64
+MAX_TOK = 64
+MAX_POS = MAX_TOK + 2   # rows of the position table the engine expects for this capacity
 
 
 def _prompts(cfg, seed=21):
@@ -33,7 +34,7 @@ def _prompts(cfg, seed=21):
     return [list(map(int, full[b, :n])) for b, n in enumerate(LENS)]
 
 
-def _opts(strat, n_total=MAX_POS):
+def _opts(strat, n_total=MAX_TOK):
     return DecodingOptions(MaxTgtSentLength=n_total, DecodingStrategy=strat, TopP=0.9, RepeatPenalty=2.0, BlockedTokens=[0], Seed=5)
 
 
@@ -54,7 +55,7 @@ def test_ragged_prefill_and_decode_match_oracle_sequence_by_sequence(cuda, oracl
     prompts = _prompts(cfg)
     opts = _opts(strat)
     B = len(prompts)
-    gpt = GPT(cfg, max_batch=B, max_tokens=MAX_POS)
+    gpt = GPT(cfg, max_batch=B, max_tokens=MAX_TOK)
     gpt.LoadWeights(w)
     ids = np.zeros((B, N_NEW), dtype=np.int32)
     logits = []
@@ -102,7 +103,7 @@ def test_slot_is_parked_refilled_and_restored_while_the_others_run_on(cuda, orac
     n_a, n_b, n_c = 4, 5, 3
 
     def fresh():
-        g = GPT(cfg, max_batch=B, max_tokens=MAX_POS)
+        g = GPT(cfg, max_batch=B, max_tokens=MAX_TOK)
         g.LoadWeights(w)
         return g
 
@@ -119,8 +120,15 @@ def test_slot_is_parked_refilled_and_restored_while_the_others_run_on(cuda, orac
     assert snap.B == 1 and snap.T == LENS[1] + n_a - 1
     new_prompt = list(map(int, prompt_ids(77, 1, 11, cfg.V)[0]))
     g.SlotReset(1)
-    g.SlotExtend(1, new_prompt[:6], opts)          # the head of the prompt (its sampled id is discarded by the next piece)
-    first_new = g.SlotExtend(1, new_prompt[6:], opts)
+    # RoPE models take the prompt in two pieces (the id sampled after the head is discarded by the next piece).  With the
+    # reference's absolute position table a cached call adds rows [0, S) to its S new tokens whatever is cached
+    # (PositionEmbedding.cs:30-33, Decoder.cs:674-677), so there a two-piece prompt is a different computation.
+    pieces = 2 if cfg.pe == P.RoPE else 1
+    if pieces == 2:
+        g.SlotExtend(1, new_prompt[:6], opts)
+        first_new = g.SlotExtend(1, new_prompt[6:], opts)
+    else:
+        first_new = g.SlotExtend(1, new_prompt, opts)
     lens = g.CacheLengths()
     assert lens[1] == len(new_prompt) and lens[0] == LENS[0] + n_a - 1 and lens[2] == LENS[2] + n_a - 1
     logits_new = [g.Logits()]
@@ -130,9 +138,9 @@ def test_slot_is_parked_refilled_and_restored_while_the_others_run_on(cuda, orac
         logits_new.append(g.Logits())
     # the others never noticed
     np.testing.assert_array_equal(ids_b[[0, 2]], r_ids[[0, 2], n_a:n_a + n_b])
-    # the newcomer behaves like the oracle on that prompt alone.  Its Philox stream is (seed, seq_base + 1); the head
-    # piece consumed step 0, so the full prompt's first id is drawn at step 1: compare from the oracle's distribution
-    # with the device's own rule instead of the oracle's ids
+    # the newcomer behaves like the oracle on that prompt alone.  Its Philox stream is (seed, seq_base + 1); a head
+    # piece consumes step 0, so the full prompt's first id is then drawn at step 1: compare from the oracle's
+    # distribution with the device's own rule instead of the oracle's ids
     o, o_ids, steps = _oracle_alone(oracle, cfg, w, new_prompt, opts, 1, n_b + 1)
     tol = tol_for(cfg)
     assert rel_err(logits_new[0][0][1], steps[0][0][0]) <= tol
@@ -140,7 +148,7 @@ def test_slot_is_parked_refilled_and_restored_while_the_others_run_on(cuda, orac
     new_ids = [first_new] + [int(x) for x in ids_b[1]]
     for i, nid in enumerate(new_ids):
         pd = logits_new[i][1][1:2]
-        u = np.array([oracle.philox_uniform(opts.Seed, opts.SeqBase + 1, i + 1)], dtype=np.float32)
+        u = np.array([oracle.philox_uniform(opts.Seed, opts.SeqBase + 1, i + pieces - 1)], dtype=np.float32)
         want = oracle.topp(pd, opts.TopP, opts.RepeatPenalty, [hist], u)
         assert nid == int(want[0]), "newcomer step %d" % i
         hist.append(nid)
@@ -163,8 +171,8 @@ def test_sequences_stop_one_by_one(cuda):
     hb.reshape(-1)[0] = 50.0
     w["FeedForward_Decoder_0.m_Bd"] = hb
     prompts = _prompts(cfg)
-    opts = DecodingOptions(MaxTgtSentLength=MAX_POS, DecodingStrategy=DS.GreedySearch)
-    g = GPT(cfg, max_batch=len(prompts), max_tokens=MAX_POS)
+    opts = DecodingOptions(MaxTgtSentLength=MAX_TOK, DecodingStrategy=DS.GreedySearch)
+    g = GPT(cfg, max_batch=len(prompts), max_tokens=MAX_TOK)
     g.LoadWeights(w)
     first = g.PrefillRagged(prompts, opts)
     np.testing.assert_array_equal(first, 0)
