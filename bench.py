@@ -461,6 +461,8 @@ def run_b200(args):
             tj = json.load(fh)
         # dram bytes per algorithmic byte measured by ncu on the same kernel, scaled to one launch of this workload
         ratio = tj.get("dram_bytes_per_algorithmic_byte", 0)
+        if gpt.DecodePath() == 2:
+            ratio = tj.get("owner_kernel", {}).get("dram_bytes_per_algorithmic_byte", ratio)
         if prof["decode_stack"][1] == 0:
             ratio = tj.get("per_linear_kernel", {}).get("dram_bytes_per_algorithmic_byte", ratio)
         traffic = ratio * lin_bytes / max(1, lin_groups // n_prof) or None

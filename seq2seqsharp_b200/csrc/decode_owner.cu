@@ -993,6 +993,7 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
     }
     own_arrive(cntL + (size_t)p * kOwnCntStride, tid);
     own_wait(cntL + (size_t)p * kOwnCntStride, (unsigned)G, a, &s_err, dead, tid, (p << 4) | 4);
+    OTRACE(p, 15);
     const long long* Yc = a.Y[p & 1];
     const int nv = M * wdt;
 #pragma unroll 1
@@ -1005,6 +1006,7 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
     }
     consumers_sync();
     if (tid < a.tp_size) red_release_add_sys(reinterpret_cast<unsigned*>(a.peer[tid] + a.off_P) + (size_t)p * kOwnCntStride, 1u);
+    OTRACE(p, 11);
   };
 
   for (int layer = 0; layer < a.L; ++layer) {
