@@ -729,6 +729,7 @@ static int check_err_flag(Gpt* g) {
   int e = ew[0];
   e |= tc_take_error();
   e |= gs_take_error();
+  e |= stc_take_error();
   if (g->tp > 1) e |= comm_peer_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, 2 * sizeof(int));

@@ -552,6 +552,8 @@ int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N) {
   if (c > b) b = c;
   const int64_t d = dtype == TSB200_F16 && M > 4 && M <= 64 ? gemm_stream_mma_workspace_bytes(M, K, N, 132) : 0;
   if (d > b) b = d;
+  const int64_t e = dtype == TSB200_F16 && M > 16 && M <= 64 ? gemm_stream_tc_workspace_bytes(M, K, N, 160) : 0;
+  if (e > b) b = e;
   return (a > b ? a : b) + 256;
 }
 

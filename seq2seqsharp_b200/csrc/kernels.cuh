@@ -147,6 +147,11 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
                    int* error_flag, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count);
 // stream-K mma.sync GEMM for decode batches of up to 64 rows on packed fp16 weights (gemm_stream_mma.cu)
+// tcgen05 streaming GEMM for 17..64 rows (gemm_stream_tc.cu): the weights are the 128-row operand, the activation rows N
+int launch_gemm_stream_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
+                          int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
+int64_t gemm_stream_tc_workspace_bytes(int M, int K, int N, int sm_count);
+int stc_take_error();
 int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
                            int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count);

@@ -358,6 +358,11 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
   if (M == 0) return 1;
   const int vec = dtype == TSB200_F16 ? 8 : 4;
   const int packedKB = packed ? (K + 31) / 32 : 0;
+  if (packed && dtype == TSB200_F16 && M > 16 && M <= 64) {
+    // 17..64 rows: the weights stream once through tcgen05 with the activation rows as the N dimension
+    const int r = launch_gemm_stream_tc(device, st, x, W, M, K, N, ep, nullptr, true, ws, ws_bytes, s);
+    if (r != 2) return r;
+  }
   if (packed && dtype == TSB200_F16 && M > 1 && M <= 64) {
     // decode batches: weights streamed once through a ring, mma.sync consumers (measured: for 33..64 rows and wide
     // outputs the split-K tcgen05 kernel below is faster, its partial sums being a smaller share of the traffic)
