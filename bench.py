@@ -592,6 +592,8 @@ def main():
                          "scaling); 'replicas' = batch-sharded independent sequences (weak scaling); 'auto' = tp for the "
                          "7B-class workloads (c5_*), replicas otherwise")
     args = ap.parse_args()
+    # stdout carries the ONE JSON line: whatever NCCL has to say (its version banner, INFO lines) goes to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     if args.impl == "reference":
         run_reference(args)
     else:
