@@ -353,6 +353,11 @@ TSB200_API int TSB200_GptDecode(void* gpt, int n_steps, const TSB200DecodingOpti
 TSB200_API int TSB200_GptGetLogits(void* gpt, float* logits, float* probs);
 TSB200_API int TSB200_GptCacheLength(void* gpt, int* T);   /* the longest sequence's when they differ */
 TSB200_API int TSB200_GptCacheLengths(void* gpt, int* lens, int n);   /* per sequence (n entries) */
+/* Every device buffer of the engine (weights, caches, activations, scratch) lies between two 256-byte guard regions with a
+ * known pattern.  Returns 0 (message names the buffer) if any guard byte has changed, i.e. if some kernel wrote outside a
+ * buffer since the engine was created.  Synchronises the engine's stream; meant for tests and for debugging a new model
+ * shape, not for the token loop. */
+TSB200_API int TSB200_GptCheckGuards(void* gpt);
 /* How the most recent cached decode step was launched (the engine chooses by dtype, batch and parallelism):
  * 0 one launch per operation, 1 the stream-K persistent kernel, 2 the owner-partitioned persistent kernel. */
 TSB200_API int TSB200_GptDecodePath(void* gpt, int* path);

@@ -142,6 +142,7 @@ def lib():
         "TSB200_GptGetLogits": (i32, [vp, vp, vp]),
         "TSB200_GptCacheLength": (i32, [vp, C.POINTER(i32)]),
         "TSB200_GptDecodePath": (i32, [vp, C.POINTER(i32)]),
+        "TSB200_GptCheckGuards": (i32, [vp]),
         "TSB200_GptCacheLengths": (i32, [vp, vp, i32]),
         "TSB200_GptPrefillRagged": (i32, [vp, vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptSlotSnapshot": (i32, [vp, i32, C.POINTER(vp)]),

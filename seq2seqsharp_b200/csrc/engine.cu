@@ -184,7 +184,10 @@ struct Gpt {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = 0.0f;
   long long last_launches = 0;
-  std::vector<void*> allocs;
+  // every device buffer of the engine sits between two guard regions of kGuardBytes filled with kGuardByte; a kernel that
+  // writes past either end of a buffer changes them, and TSB200_GptCheckGuards finds out
+  struct Alloc { void* user; void* base; size_t bytes; };
+  std::vector<Alloc> allocs;
   // instrumentation (TSB200_GptProfileDecode): events around every launch group, by kernel class
   bool prof = false;
   std::vector<cudaEvent_t> prof_ev;
@@ -251,16 +254,31 @@ static void prof_end(Gpt* g, int cls) {
     if (!_ok) return 0;          \
   } while (0)
 
+constexpr size_t kGuardBytes = 256;
+constexpr int kGuardByte = 0xC5;
 static int dev_alloc(Gpt* g, void** p, int64_t bytes, bool zero = true) {
   if (bytes <= 0) bytes = 256;
-  cudaError_t e = cudaMalloc(p, (size_t)bytes);
+  void* base = nullptr;
+  cudaError_t e = cudaMalloc(&base, (size_t)bytes + 2 * kGuardBytes);
   if (e != cudaSuccess) {
     cudaGetLastError();
     TSB_FAIL("OOM: cudaMalloc of %lld bytes failed: %s", (long long)bytes, cudaGetErrorString(e));
   }
+  *p = (char*)base + kGuardBytes;   // still 256-byte aligned
+  TSB_CUDA(cudaMemsetAsync(base, kGuardByte, kGuardBytes, g->s));
+  TSB_CUDA(cudaMemsetAsync((char*)*p + bytes, kGuardByte, kGuardBytes, g->s));
   if (zero) TSB_CUDA(cudaMemsetAsync(*p, 0, (size_t)bytes, g->s));
-  g->allocs.push_back(*p);
+  g->allocs.push_back(Gpt::Alloc{*p, base, (size_t)bytes});
   return 1;
+}
+static int dev_free(Gpt* g, void* user) {
+  for (auto& a : g->allocs)
+    if (a.user == user && a.base) {
+      TSB_CUDA(cudaFree(a.base));
+      a.base = a.user = nullptr;
+      return 1;
+    }
+  TSB_FAIL("engine: freeing a buffer the engine did not allocate");
 }
 
 static int fill_const(Gpt* g, void* p, int64_t n, float v) {
@@ -430,8 +448,7 @@ static int ensure_act(Gpt* g, int64_t rows) {
   g->stack_B = 0;
   auto re = [&](void** p, int64_t bytes) -> int {
     if (*p) {
-      for (auto& a : g->allocs) if (a == *p) a = nullptr;
-      TSB_CUDA(cudaFree(*p));
+      TSB_TRY(dev_free(g, *p));
       *p = nullptr;
     }
     return dev_alloc(g, p, bytes, false);
@@ -1016,8 +1033,8 @@ int TSB200_GptDestroy(void* h) {
     if (g->xch_open[r]) cudaIpcCloseMemHandle(g->xch_peer[r]);
   if (g->xch_region) cudaFree(g->xch_region);
   owner_destroy(g->own);
-  for (void* p : g->allocs)
-    if (p) cudaFree(p);
+  for (auto& a : g->allocs)
+    if (a.base) cudaFree(a.base);
   delete g;
   return 1;
 }
@@ -1397,6 +1414,26 @@ int TSB200_GptGetLogits(void* h, float* logits, float* probs) {
       TSB_CUDA(cudaStreamSynchronize(g->s));
     }
     TSB_CUDA(cudaMemcpy(probs, g->probs, n * 4, cudaMemcpyDeviceToHost));
+  }
+  return 1;
+}
+
+int TSB200_GptCheckGuards(void* h) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_check_guards: null engine");
+  TSB_TRY(use_device(g->c.device, nullptr));
+  TSB_CUDA(cudaStreamSynchronize(g->s));
+  unsigned char host[2 * kGuardBytes];
+  int idx = 0;
+  for (const auto& a : g->allocs) {
+    ++idx;
+    if (!a.base) continue;
+    TSB_CUDA(cudaMemcpy(host, a.base, kGuardBytes, cudaMemcpyDeviceToHost));
+    TSB_CUDA(cudaMemcpy(host + kGuardBytes, (const char*)a.user + a.bytes, kGuardBytes, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < 2 * kGuardBytes; ++i)
+      TSB_CHECK(host[i] == (unsigned char)kGuardByte,
+                "gpt_check_guards: buffer %d of the engine (%zu bytes) was written out of bounds: guard byte %zu %s it is 0x%02x", idx, a.bytes,
+                i % kGuardBytes, i < kGuardBytes ? "before" : "after", host[i]);
   }
   return 1;
 }

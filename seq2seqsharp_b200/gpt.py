@@ -450,6 +450,10 @@ class GPT:
         N.call("TSB200_GptCacheLength", self._h, C.byref(t))
         return t.value
 
+    def CheckGuards(self):
+        """Raises if any kernel wrote outside one of the engine's device buffers (guard regions around every buffer)."""
+        N.call("TSB200_GptCheckGuards", self._h)
+
     def DecodePath(self):
         """How the most recent cached step ran: 0 per-operation launches, 1 stream-K persistent kernel, 2 owner-partitioned kernel."""
         t = C.c_int(0)
