@@ -412,8 +412,8 @@ def run_b200(args):
     # ---- timed region: K graph-replayed decode steps, ids fed back on the device, inputs resident in HBM
     gpt.EnableStepTiming(True)
     sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
+    sampler.start()   # before the barrier: spawning the sampler takes milliseconds, and under tensor parallelism a rank that
+    barrier()         # starts late makes the others wait inside their first step
     l0 = launches()
     t_wall0 = time.perf_counter()
     ids = gpt.Decode(K, opts)
