@@ -103,51 +103,6 @@ __global__ void __launch_bounds__(1024) softmax_argmax_kernel(int* out_ids, floa
   pdl_wait();
   const int r = blockIdx.x;
   const float* z = logits + (int64_t)r * V;
-  if (V <= 32 * 1024 && blockDim.x == 1024) {
-    // The row fits in the CTA's registers (32 values per thread): one pass over memory with all loads in flight and one
-    // exponential per element.  Elements are assigned to threads and summed in the same order as in the general path
-    // below, so both produce the same bits.
-    float v[32];
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const int i = threadIdx.x + k * 1024;
-      float x = i < V ? z[i] : -INFINITY;
-      if (use_temp) x = x / inv_temp_div;
-      v[k] = x;
-    }
-    float mx = -INFINITY;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) mx = fmaxf(mx, v[k]);
-    mx = block_max(mx, red);
-    float s = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const int i = threadIdx.x + k * 1024;
-      v[k] = expf(v[k] - mx);
-      if (i < V) s += v[k];
-    }
-    s = block_sum(s, red);
-    ValIdx best;
-    best.v = -INFINITY;
-    best.i = 0x7fffffff;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-      const int i = threadIdx.x + k * 1024;
-      if (i < V) {
-        float p = v[k] / s;
-        for (int j = 0; j < n_blocked; ++j)
-          if (blocked[j] == i) p += -1.0f;
-        if (probs) probs[(int64_t)r * V + i] = p;
-        ValIdx c;
-        c.v = p;
-        c.i = i;
-        best = better(best, c);
-      }
-    }
-    best = block_argmax(best, redi);
-    if (threadIdx.x == 0 && out_ids) out_ids[r] = best.i == 0x7fffffff ? 0 : best.i;
-    return;
-  }
   float mx = -INFINITY;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     float v = z[i];

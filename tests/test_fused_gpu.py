@@ -275,9 +275,9 @@ def test_linear_packed_with_fused_norm(cuda, oracle, dtype, tol, norm_type, M, K
                                     (640, 160, 8000), (2000, 96, 2560), (2200, 64, 2304), (1300, 128, 4008),
                                     # 5..64 rows: the stream-K mma.sync kernel (1, 2, 4 and 8 row blocks, wide K, ragged N)
                                     (5, 4096, 4096), (12, 512, 264), (33, 1376, 512), (40, 96, 1002), (64, 11008, 4096),
-                                    # 17..64 rows, K a multiple of 128: the tcgen05 streaming kernel (whole column tiles and halves as
-                                    # groups, ragged N, few k tiles)
-                                    (64, 4096, 22016), (48, 128, 300), (20, 4096, 4096), (17, 256, 2304)])
+                                    # 17..64 rows: the tcgen05 streaming kernel takes K >= 4096 with at least 16 M weights (whole column
+                                    # tiles and halves as groups, ragged N and M); the small ones stay with the mma.sync kernels
+                                    (64, 4096, 22016), (48, 128, 300), (20, 4096, 4096), (17, 256, 2304), (33, 4096, 5000)])
 def test_linear_packed_tensor_core_gemm(cuda, oracle, M, K, Nn):
     """More than 4 rows on fp16 packed weights: up to 16 rows the stream-K mma.sync kernel, 17..64 rows the tcgen05 streaming
     kernel (weights as the 128-row operand; shapes it does not take fall to the mma.sync kernels), above that the tcgen05/TMEM
