@@ -133,6 +133,7 @@ struct OwnRing {
   volatile int* s_code;        // which ring wait ran out (for the error message)
 #ifdef TSB200_TRACE
   long long wait_cycles = 0, rel_cycles = 0;
+  long long job_cycles[4] = {0, 0, 0, 0};   // K-split job: passes, wait before the reduction, reduction + emission, final refill
 #endif
   __device__ __forceinline__ void issue(int slot, int tile) {
     mbar_expect_tx(&full[slot], kOwnTileBytes);
@@ -298,6 +299,10 @@ __device__ __noinline__ void own_job_ksplit(const OwnJob* jp, OwnRing* Rp, const
   const __half* xrow = xb + (size_t)(row_live ? g8 : 0) * xstride + 2 * t4;
   const int ws = j.ws, ksw = j.ksw, ks = j.ks, nchunks = j.nchunks;
   int held0 = 0, held = 0;   // strips [held0, held0 + held) wait in `red` for the reduction
+#ifdef TSB200_TRACE
+  long long tc0 = clock64();
+  R.job_cycles[0] = R.job_cycles[1] = R.job_cycles[2] = R.job_cycles[3] = 0;
+#endif
   for (int c = 0; c < nchunks; ++c) {
     const int wc = own_chunk_width(ws, nchunks, c);
     float acc[kOwnKChunk][4];
@@ -329,8 +334,14 @@ __device__ __noinline__ void own_job_ksplit(const OwnJob* jp, OwnRing* Rp, const
     held += wc;
     const bool last = c + 1 == nchunks;
     if (last || held + own_chunk_width(ws, nchunks, c + 1) > kOwnRedCols / 16) {
+#ifdef TSB200_TRACE
+      { const long long t = clock64(); R.job_cycles[0] += t - tc0; tc0 = t; }
+#endif
       R.refill(lane, true);   // a warp that waits at the barrier cannot look after its stages: settle them first
       consumers_sync();
+#ifdef TSB200_TRACE
+      { const long long t = clock64(); R.job_cycles[1] += t - tc0; tc0 = t; }
+#endif
 #pragma unroll 1
       for (int idx = tid; idx < held * 16 * M; idx += 256) {
         const int n = idx % M, col = idx / M;
@@ -342,9 +353,15 @@ __device__ __noinline__ void own_job_ksplit(const OwnJob* jp, OwnRing* Rp, const
       consumers_sync();
       held0 += held;
       held = 0;
+#ifdef TSB200_TRACE
+      { const long long t = clock64(); R.job_cycles[2] += t - tc0; tc0 = t; }
+#endif
     }
   }
   R.refill(lane, true);
+#ifdef TSB200_TRACE
+  R.job_cycles[3] += clock64() - tc0;
+#endif
   *Rp = R;
 }
 
@@ -1153,10 +1170,32 @@ __global__ void __launch_bounds__(kOwnThreads, 1) decode_owner_kernel(OwnArgs a)
       // the group's rows of W0, this CTA's range of output columns
       const OwnJob& jo = s_jobs[OWN_W0];
       R.dead = R.dead || dead;
+#ifdef TSB200_TRACE
+      const long long w0_wait0 = R.wait_cycles, w0_rel0 = R.rel_cycles;
+      if (a.trace && tid == 0) {
+        // how many of the tiles the job is about to read have landed already
+        int landed = 0, sl = R.w_slot;
+        unsigned par = R.w_par;
+        for (int i = 0; i < S && R.t_have + i < R.n_tiles; ++i) {
+          if (!mbar_test(&full[sl], par)) break;
+          ++landed;
+          if (++sl == S) { sl = 0; par ^= 1u; }
+        }
+        a.trace[((size_t)blockIdx.x * (2 * a.L + 1) + p) * 16 + 15] = landed * 1000 + S * 10 + (R.t_have - (R.n >> kOwnTileShift));
+      }
+#endif
       {
         const OwnEmit em{OWN_EMIT_ADD64, TP ? a.Y[p & 1] : Xn, nullptr, nullptr, d, jo.cbase, 0};
         own_job_ksplit(&jo, &R, ys, a.ystride, M, red, &em);
       }
+#ifdef TSB200_TRACE
+      if (a.trace && tid == 0) {
+        long long* tr = a.trace + ((size_t)blockIdx.x * (2 * a.L + 1) + p) * 16;
+        tr[12] = R.job_cycles[0];            // cycles in the passes of the W0 job (warp 0)
+        tr[13] = R.wait_cycles - w0_wait0;   // of which waiting for tiles
+        tr[14] = R.rel_cycles - w0_rel0;     // and in hand-back + refill
+      }
+#endif
       OTRACE(p, 7);
       block_done(p, (xb + p + 1) % 3);
     }
