@@ -147,6 +147,8 @@ struct Gpt {
   bool xch_open[kStackMaxRanks] = {};
   bool xch_ready = false;
   size_t xch_own_off = 0;      // where the owner-partitioned kernel's part of the region starts
+  bool lin_syms_used = false;  // a kernel that reports errors through its own symbol ran since the last check
+  bool graph_lin_syms = false; // ... and the captured decode step contains such kernels (every replay sets the flag above)
   int last_path = 0;           // how the most recent cached decode step ran: 0 one launch per operation, 1 stream-K persistent kernel, 2 owner-partitioned kernel
   float* x2 = nullptr;         // second residual buffer: a summed residual row is written to the buffer the others do not read
   float* ar_buf = nullptr;     // fp32 [rows, d] partial sums handed to the all-reduce
@@ -492,6 +494,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
                                        c.norm_type, c.eps, rows, K, g->s));
     x_T = h_tmp;
   }
+  g->lin_syms_used = true;   // these kernels report a wait that ran out through their own error symbols
   PROF(KC_LINEAR, launch_linear(dev, g->st, dt, x_T, Wp, rows, K, N, ep, g->lin_ws, g->lin_ws_bytes, g->s, true));
   return 1;
 }
@@ -740,13 +743,23 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
 }
 
 // A kernel whose bounded wait ran out raises the device error word; surface it as a failure of the call.
-static int check_err_flag(Gpt* g) {
+// `pre`: the two words of the device error flag if the caller has already brought them to the host (in stream order, after
+// the step).  The kernels behind launch_linear keep their own error symbols; those are only read when such a kernel ran.
+static int check_err_flag(Gpt* g, const int* pre = nullptr) {
   int ew[2] = {0, 0};   // [0] raised, [1] which wait of the owner-partitioned kernel ran out first (0: another kernel)
-  TSB_CUDA(cudaMemcpy(ew, g->err_flag, sizeof(ew), cudaMemcpyDeviceToHost));
+  if (pre) {
+    ew[0] = pre[0];
+    ew[1] = pre[1];
+  } else {
+    TSB_CUDA(cudaMemcpy(ew, g->err_flag, sizeof(ew), cudaMemcpyDeviceToHost));
+  }
   int e = ew[0];
-  e |= tc_take_error();
-  e |= gs_take_error();
-  e |= stc_take_error();
+  if (g->lin_syms_used) {
+    e |= tc_take_error();
+    e |= gs_take_error();
+    e |= stc_take_error();
+    g->lin_syms_used = false;
+  }
   if (g->tp > 1) e |= comm_peer_take_error();
   if (e) {
     cudaMemset(g->err_flag, 0, 2 * sizeof(int));
@@ -859,9 +872,13 @@ static int ensure_graph(Gpt* g, const TSB200DecodingOptions* opt, int n_steps) {
   const long long l0 = g->st->launches;
   const bool prof = g->prof;
   g->prof = false;
+  const bool syms_before = g->lin_syms_used;
+  g->lin_syms_used = false;
   TSB_CUDA(cudaStreamBeginCapture(g->s, cudaStreamCaptureModeThreadLocal));
   int ok = enqueue_forward(g, B, 1, g->T, true, key.splits) && enqueue_sample(g, B, opt, true, true);
   cudaError_t e = cudaStreamEndCapture(g->s, &graph);
+  g->graph_lin_syms = g->lin_syms_used;
+  g->lin_syms_used = syms_before;
   g->prof = prof;
   if (!ok || e != cudaSuccess) {
     if (graph) cudaGraphDestroy(graph);
@@ -1360,6 +1377,7 @@ int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int
   if (g->step_timing) TSB_CUDA(cudaEventRecord(g->step_ev[0], g->s));
   for (int i = 0; i < n_steps; ++i) {
     TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
+    g->lin_syms_used = g->lin_syms_used || g->graph_lin_syms;
     count_launch(c.device, g->graph_nodes);
     ++done;
     if (g->step_timing) {
@@ -1808,7 +1826,7 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   TSB_CHECK(g->T > 0 && g->B > 0, "gpt_step_host: prefill first");
   TSB_CHECK(g->T + 1 <= c.max_tokens, "OOM: KV-cache capacity %d exceeded", c.max_tokens);
   const int B = g->B;
-  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)(c.max_batch + state_words(g)) * 4 + 64, cudaHostAllocDefault));
+  if (!g->pin_ids) TSB_CUDA(cudaHostAlloc((void**)&g->pin_ids, (size_t)(c.max_batch + state_words(g)) * 4 + 64 + 16, cudaHostAllocDefault));
   TSB_TRY(upload_blocked(g, opt));
   g->stop_fin = 0;
   if (!g->gexec) TSB_TRY(set_state(g, 0));
@@ -1823,10 +1841,13 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   // the scalars and the mode flags always; the per-sequence arrays only when the sequences differ
   TSB_CUDA(cudaMemcpyAsync(g->state, pin_state, (size_t)(g->ragged ? state_words(g) : kStateLens) * 4, cudaMemcpyHostToDevice, g->s));
   TSB_CUDA(cudaGraphLaunch(g->gexec, g->s));
+  g->lin_syms_used = g->lin_syms_used || g->graph_lin_syms;
   count_launch(c.device, g->graph_nodes);
   TSB_CUDA(cudaMemcpyAsync(g->pin_ids, g->ids_cur, (size_t)B * 4, cudaMemcpyDeviceToHost, g->s));
+  int* pin_err = pin_state + state_words(g) + 4;   // the error words travel back with the ids: one synchronisation per step
+  TSB_CUDA(cudaMemcpyAsync(pin_err, g->err_flag, 8, cudaMemcpyDeviceToHost, g->s));
   TSB_CUDA(cudaStreamSynchronize(g->s));
-  TSB_TRY(check_err_flag(g));
+  TSB_TRY(check_err_flag(g, pin_err));
   for (int b = 0; b < B; ++b) out_ids[b] = g->pin_ids[b];
   g->T += 1;
   g->step += 1;
