@@ -396,7 +396,10 @@ TSB200_API int TSB200_GptPrefillRagged(void* gpt, const int32_t* ids, const int3
                                        const TSB200DecodingOptions* opt, int32_t* out_ids);
 TSB200_API int TSB200_GptSlotSnapshot(void* gpt, int slot, void** snapshot);
 TSB200_API int TSB200_GptSlotRestore(void* gpt, void* snapshot, int slot);
-TSB200_API int TSB200_GptSlotReset(void* gpt, int slot);
+TSB200_API int TSB200_GptSlotReset(void* gpt, int slot);   /* empties the slot; its pending id becomes </s> */
+/* on != 0: the per-sequence state (and with it the per-sequence stop rule of TSB200_GptDecode with stop_on_eos) stays in
+ * use even while all sequences happen to have the same length - what a scheduler that refills slots wants. */
+TSB200_API int TSB200_GptSetPerSequenceState(void* gpt, int on);
 TSB200_API int TSB200_GptSlotExtend(void* gpt, int slot, const int32_t* ids, int S, const TSB200DecodingOptions* opt,
                                     int32_t* out_id);
 /* device-timed duration (ms, CUDA events on the engine's stream) of the last GptDecode / GptPrefill call and

@@ -148,6 +148,7 @@ def lib():
         "TSB200_GptSlotSnapshot": (i32, [vp, i32, C.POINTER(vp)]),
         "TSB200_GptSlotRestore": (i32, [vp, vp, i32]),
         "TSB200_GptSlotReset": (i32, [vp, i32]),
+        "TSB200_GptSetPerSequenceState": (i32, [vp, i32]),
         "TSB200_GptSlotExtend": (i32, [vp, i32, vp, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptExtend": (i32, [vp, vp, i32, i32, C.POINTER(DecodingOptionsC), vp]),
         "TSB200_GptCacheSnapshot": (i32, [vp, C.POINTER(vp)]),

@@ -175,6 +175,7 @@ struct Gpt {
   // arrays.  While all sequences agree, `ragged` is false and the kernels read the scalars.
   std::vector<int> Ts, steps_v;
   bool ragged = false;
+  bool force_per_seq = false;  // keep the per-sequence state in use even while the sequences agree (TSB200_GptSetPerSequenceState)
   int stop_fin = 0;            // per-sequence stop rule in the captured step (ragged decode with stop_on_eos)
   int seq0 = 0;                // first sequence the per-sequence buffers address (a single-slot prompt run), else 0
   const int* gather_lens = nullptr;   // device prompt lengths of a padded prefill (NULL: every prompt fills its S columns)
@@ -804,7 +805,7 @@ static void mirror_uniform(Gpt* g) {
     g->Ts[b] = g->T;
     g->steps_v[b] = (int)g->step;
   }
-  g->ragged = false;
+  g->ragged = g->force_per_seq;
 }
 // after a per-sequence change: the scalars hold the largest values, `ragged` says whether the sequences differ
 static void refresh_ragged(Gpt* g) {
@@ -817,6 +818,7 @@ static void refresh_ragged(Gpt* g) {
   }
   g->T = tmax;
   g->step = (uint32_t)smax;
+  differ = differ || g->force_per_seq;
   if (differ != g->ragged && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
   g->ragged = differ;
 }
@@ -1658,8 +1660,19 @@ int TSB200_GptSlotReset(void* h, int slot) {
   g->Ts[slot] = 0;
   g->steps_v[slot] = 0;
   TSB_CUDA(cudaMemsetAsync(g->hist_len + slot, 0, 4, g->s));
+  TSB_CUDA(cudaMemsetAsync(g->ids_cur + slot, 0, 4, g->s));   // pending id </s>: with stop_on_eos an empty slot stands still
   refresh_ragged(g);
   g->probs_valid = false;
+  return 1;
+}
+
+int TSB200_GptSetPerSequenceState(void* h, int on) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g, "gpt_set_per_sequence_state: null engine");
+  TSB_CHECK(g->tp == 1 || !on, "gpt_set_per_sequence_state: tensor-parallel engines serve sequences of equal length");
+  g->force_per_seq = on != 0;
+  if (g->Ts.empty()) mirror_uniform(g);
+  refresh_ragged(g);
   return 1;
 }
 

@@ -297,6 +297,7 @@ class GPT:
 
     def Reset(self):
         N.call("TSB200_GptReset", self._h)
+        self._B = 0
 
     def SetWaitLimit(self, polls: int):
         """Bound of the device-side waits of the persistent decode-step kernel (0 = default, about a second)."""
@@ -330,6 +331,10 @@ class GPT:
         self._B = B
         return out
 
+    def Batch(self) -> int:
+        """Sequences the engine currently holds."""
+        return self._B
+
     def CacheLengths(self):
         lens = np.zeros(self._B, dtype=np.int32)
         N.call("TSB200_GptCacheLengths", self._h, lens.ctypes.data_as(C.c_void_p), self._B)
@@ -348,6 +353,10 @@ class GPT:
     def SlotReset(self, slot: int):
         N.call("TSB200_GptSlotReset", self._h, int(slot))
         self._B = max(self._B, slot + 1)
+
+    def SetPerSequenceState(self, on: bool = True):
+        """Keeps the per-sequence lengths / stop rule in use even while the sequences agree (slot schedulers)."""
+        N.call("TSB200_GptSetPerSequenceState", self._h, 1 if on else 0)
 
     def SlotExtend(self, slot: int, tokens, opts: DecodingOptions) -> int:
         """Runs `tokens` (one sequence's prompt, or the rest of it) on top of what the slot holds; returns its next id."""
