@@ -256,6 +256,11 @@ typedef struct TSB200GptConfig {
    * results of the out-projection and of the down-projection over the ranks of the communicator given to
    * TSB200_GptSetComm (one all-reduce each per layer).  tp_size <= 1 = off */
   int32_t tp_rank, tp_size;
+  /* mixture of experts (Networks/GPTDecoder.cs:114-123, Layers/MoEFeedForward.cs): n_experts > 1 makes layers 2, 3, ... use
+   * a router + n_experts feed-forward experts of width 4 d (weights GPTDecoder.MoEFFN_k.{layerNorm.m_alpha, layerNorm.m_beta,
+   * m_Router [d,E], m_RouterBias [1,E], m_Whd1 [E*d,4d], m_Whd2 [E*4d,d]}), experts_per_token of them per token.
+   * Decoded with one launch per operation; not tensor-parallel.  0 or 1 = off */
+  int32_t n_experts, experts_per_token;
 } TSB200GptConfig;
 
 typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOptions.cs:16-39 */

@@ -16,7 +16,7 @@ _LIB = os.path.join(_HERE, "liboracle.so")
 class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("L", "d", "H", "Hkv", "hd", "F", "V", "norm_type", "act", "pe_type",
                                           "attn_type")] + [("eps", C.c_float), ("rope_base", C.c_float)] + \
-               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_pos", "faithful_cache", "threads")]
+               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_pos", "faithful_cache", "threads", "n_experts", "experts_per_token")]
 
 
 _lib = None
@@ -100,6 +100,19 @@ def rope(x, seq_len, row_offset, base=500000.0):
     return out
 
 
+def topk(x, k):
+    """TensorApplyCPU.TopK (TensorSharp/TensorApplyCPU.cs:1121-1146): values and indices of the k largest entries of every
+    row, descending; a value equal to the current k-th replaces it."""
+    x = _c32(x)
+    rows, cols = x.shape
+    val = np.empty((rows, k), dtype=np.float32)
+    idx = np.empty((rows, k), dtype=np.int32)
+    L = lib()
+    L.orc_topk.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int32), C.POINTER(C.c_float), C.c_int, C.c_int, C.c_int]
+    L.orc_topk(_f(val), _i(idx), _f(x), rows, cols, k)
+    return val, idx
+
+
 def argmax(p):
     p = _c32(p)
     cols = p.shape[-1]
@@ -175,6 +188,7 @@ class OracleGPT:
         c.eps, c.rope_base = cfg.eps, cfg.rope_base
         c.ape_decode_pos0 = 1 if cfg.ape_decode_pos0 else 0
         c.max_pos, c.faithful_cache, c.threads = max_pos, 1 if faithful_cache else 0, threads
+        c.n_experts, c.experts_per_token = getattr(cfg, "expertNum", 1), getattr(cfg, "expertsPerTokenFactor", 1)
         self.cfg = cfg
         self._h = lib().orc_create(C.byref(c))
         for name, w in weights.items():

@@ -39,6 +39,8 @@ struct OrcConfig {
   int32_t max_pos;          // rows of the APE table
   int32_t faithful_cache;   // 1 = grow the cache by allocate+copy each step and keep GQA K/V expanded to H heads, as the reference does
   int32_t threads;          // 1 = as the reference's managed SGEMM; >1 = std::thread workers over output columns / heads
+  int32_t n_experts;        // > 1: layers 2.. use MoEFeedForward instead of PositionwiseFeedForward (Networks/GPTDecoder.cs:114-123)
+  int32_t experts_per_token;
 };
 
 }  // extern "C"
@@ -58,6 +60,8 @@ struct Layer {
   // cache, reference layout: K [B*Hc, hd, T], V [B*Hc, T, hd]  (MultiHeadAttention.cs:173-193)
   vecf K, Vc;
   int Tcap = 0;
+  // MoEFeedForward (Layers/MoEFeedForward.cs:31-52): its own LayerNorm, experts [E, d, 4d] and [E, 4d, d] without bias, router [d, E] + bias
+  vecf moe_g, moe_b, moe_w1, moe_w2, router_w, router_b;
 };
 
 struct Model {
@@ -457,6 +461,76 @@ void ffn_block(Model* m, Layer& L, vecf& x, int M) {
   for (size_t i = 0; i < x.size(); ++i) x[i] = o[i] + x[i];
 }
 
+// TensorApplyCPU.TopK / replace_smaller (TensorSharp/TensorApplyCPU.cs:1097-1146): k best values of a row in descending
+// order; a value equal to the current k-th one replaces it (the later index wins at the boundary), equal values further
+// up keep their order.
+void topk_row(float* val, int* idx, const float* in, int cols, int k) {
+  for (int i = 0; i < k; ++i) {
+    val[i] = -1.70141e+38f;
+    idx[i] = -1;
+  }
+  for (int i = 0; i < cols; ++i) {
+    const float data = in[i];
+    if (data < val[k - 1]) continue;
+    int j = k - 2;
+    for (; j >= 0; --j) {
+      if (data > val[j]) {
+        val[j + 1] = val[j];
+        idx[j + 1] = idx[j];
+      } else {
+        break;
+      }
+    }
+    val[j + 1] = data;
+    idx[j + 1] = i;
+  }
+}
+
+// MoEFeedForward.Process at inference (Layers/MoEFeedForward.cs:72-160): LayerNorm, router affine, the constant
+// -65000 "mask" (its dropout is the identity outside training) added to every router logit - in fp32 that rounds the
+// logits to multiples of 2^-7, which is part of the reference's behaviour -, softmax, TopK; then expert by expert (ascending)
+// the tokens routed to it: x W1_e, activation, W2_e (no biases), times the token's router probability of that expert,
+// accumulated per token in that order (IndexUpdate with accumulate on a zero tensor), and the residual add.
+void moe_block(Model* m, Layer& L, vecf& x, int M) {
+  const OrcConfig& c = m->c;
+  const int d = c.d, E = c.n_experts, k = c.experts_per_token, Fh = 4 * d;
+  vecf h((size_t)M * d);
+  layernorm(h.data(), x.data(), L.moe_g.data(), L.moe_b.empty() ? nullptr : L.moe_b.data(), c.eps, M, d);
+  Linear router;
+  router.W = L.router_w;
+  router.b = L.router_b;
+  router.in = d;
+  router.out = E;
+  vecf r;
+  affine(r, h, router, M, 1);
+  for (auto& v : r) v = v + (-65000.0f);
+  vecf p((size_t)M * E);
+  softmax(p.data(), r.data(), M, E);
+  std::vector<int> top((size_t)M * k);
+  vecf topv((size_t)M * k);
+  for (int i = 0; i < M; ++i) topk_row(&topv[(size_t)i * k], &top[(size_t)i * k], &p[(size_t)i * E], E, k);
+  vecf res((size_t)M * d, 0.0f);
+  for (int e = 0; e < E; ++e) {
+    std::vector<int> rows;
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < k; ++j)
+        if (top[(size_t)i * k + j] == e) rows.push_back(i);
+    if (rows.empty()) continue;
+    const int n = (int)rows.size();
+    vecf xe((size_t)n * d), a((size_t)n * Fh, 0.0f), o((size_t)n * d, 0.0f);
+    for (int q = 0; q < n; ++q) std::memcpy(&xe[(size_t)q * d], &h[(size_t)rows[q] * d], sizeof(float) * d);
+    gemm_axpy(a.data(), xe.data(), &L.moe_w1[(size_t)e * d * Fh], n, d, Fh, 1.0f, c.threads);
+    if (c.act == 0 || c.act == 1 || c.act == 2)   // RunActivateFunction has branches for ReLU, SiLU and LeakyReLU only (:162-178)
+      for (auto& v : a) v = act_fn(c.act, v);
+    gemm_axpy(o.data(), a.data(), &L.moe_w2[(size_t)e * Fh * d], n, Fh, d, 1.0f, c.threads);
+    for (int q = 0; q < n; ++q) {
+      const float score = p[(size_t)rows[q] * E + e];
+      for (int i = 0; i < d; ++i) res[(size_t)rows[q] * d + i] += o[(size_t)q * d + i] * score;
+    }
+  }
+  for (size_t i = 0; i < x.size(); ++i) x[i] = x[i] + res[i];
+}
+
 // Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).
 inline void philox4x32_10(uint32_t ctr[4], const uint32_t key_in[2]) {
   uint32_t k0 = key_in[0], k1 = key_in[1];
@@ -508,6 +582,19 @@ int orc_set_weight(void* h, const char* name_c, const float* data, int rows, int
     const bool first = name.find(".layerNormQ.") != std::string::npos;
     if (ends_with(name, "m_alpha")) return assign(first ? L.n1_g : L.n2_g);
     if (ends_with(name, "m_beta")) return assign(first ? L.n1_b : L.n2_b);
+    return 0;
+  }
+  if (name.compare(0, 18, "GPTDecoder.MoEFFN_") == 0) {
+    const std::string rest = name.substr(18);
+    const int k = std::atoi(rest.c_str());
+    if (k < 0 || k >= (int)m->layers.size()) return 0;
+    Layer& L = m->layers[k];
+    if (ends_with(name, ".layerNorm.m_alpha")) return assign(L.moe_g);
+    if (ends_with(name, ".layerNorm.m_beta")) return assign(L.moe_b);
+    if (ends_with(name, ".m_Whd1")) return assign(L.moe_w1);
+    if (ends_with(name, ".m_Whd2")) return assign(L.moe_w2);
+    if (ends_with(name, ".m_RouterBias")) return assign(L.router_b);
+    if (ends_with(name, ".m_Router")) return assign(L.router_w);
     return 0;
   }
   size_t dot = name.rfind('.');
@@ -573,7 +660,8 @@ int orc_step(void* h, const int* ids, int B, int S, float temperature, const int
   }
   for (int k = 0; k < c.L; ++k) {  // GPTDecoder.Decode (Networks/GPTDecoder.cs:153-191)
     attention_block(m, m->layers[k], x, B, S, T0);
-    ffn_block(m, m->layers[k], x, M);
+    if (c.n_experts > 1 && k > 1) moe_block(m, m->layers[k], x, M);   // GPTDecoder.cs:116
+    else ffn_block(m, m->layers[k], x, M);
   }
   m->T = T0 + S;
   vecf last((size_t)B * d), hn((size_t)B * d);
@@ -599,6 +687,9 @@ void orc_rmsnorm(float* out, const float* in, const float* g, const float* b, fl
 void orc_softmax(float* out, const float* in, int rows, int cols) { softmax(out, in, rows, cols); }
 void orc_rope(float* out, const float* in, int rows, int cols, int seqLen, int rowOffset, double base) { rope(out, in, rows, cols, seqLen, rowOffset, base); }
 void orc_argmax(int* out, const float* p, int rows, int cols) { argmax_rows(out, p, rows, cols); }
+void orc_topk(float* val, int* idx, const float* in, int rows, int cols, int k) {
+  for (int r = 0; r < rows; ++r) topk_row(val + (long)r * k, idx + (long)r * k, in + (long)r * cols, cols, k);
+}
 // C = beta*src + alpha*A*B, row-major (CpuBasicOps.Addmm, TensorSharp/Cpu/CpuBasicOps.cs:49-114)
 void orc_addmm(float* C, float beta, const float* src, float alpha, const float* A, const float* Bm, int M, int K, int N) {
   for (long i = 0; i < (long)M * N; ++i) C[i] = (beta == 0.0f) ? 0.0f : (beta == 1.0f ? src[i] : beta * src[i]);

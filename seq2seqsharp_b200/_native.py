@@ -35,7 +35,8 @@ class GptConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("L", "d", "H", "Hkv", "hd", "F", "V", "norm_type", "act", "pe_type",
                                           "attn_type", "dtype")] + \
                [("eps", C.c_float), ("rope_base", C.c_float)] + \
-               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_batch", "max_tokens", "device", "tp_rank", "tp_size")]
+               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_batch", "max_tokens", "device", "tp_rank", "tp_size", "n_experts",
+                                         "experts_per_token")]
 
 
 class DecodingOptionsC(C.Structure):

@@ -104,6 +104,10 @@ struct LayerW {
   void *n1_g = nullptr, *n1_b = nullptr, *wqkv = nullptr, *bqkv = nullptr, *wo = nullptr, *bo = nullptr;
   void *n2_g = nullptr, *n2_b = nullptr, *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr;
   void *cK = nullptr, *cV = nullptr;
+  // mixture-of-experts layers (Layers/MoEFeedForward.cs): the layer's LayerNorm, router [d, E] + bias, experts [E, d, 4d] and
+  // [E, 4d, d], row-major in the model type.  n2_g / n2_b / w1 / w2 are unused there.
+  bool moe = false;
+  void *moe_g = nullptr, *moe_b = nullptr, *router_w = nullptr, *router_b = nullptr, *moe_w1 = nullptr, *moe_w2 = nullptr;
 };
 
 struct Dest {  // where a logical tensor lives inside the engine's buffers
@@ -162,6 +166,8 @@ struct Gpt {
   void *h = nullptr, *qkv = nullptr, *attn = nullptr, *ffn = nullptr;
   float* xl = nullptr;
   void* hl = nullptr;
+  int* moe_picks = nullptr;      // [rows, experts_per_token] experts chosen by the router, ascending per token
+  float* moe_scores = nullptr;   // their router probabilities
   float *logits = nullptr, *probs = nullptr, *u = nullptr;
   int *ids_in = nullptr, *ids_cur = nullptr, *ids_new = nullptr, *hist = nullptr, *hist_len = nullptr, *blocked = nullptr;
   int* state = nullptr;
@@ -378,7 +384,17 @@ static int resolve_local(Gpt* g, const std::string& name, Dest* out) {
       if (field == "V") return setp(L.wqkv, d, KVd, Hd + KVd, 1);
       if (field == "Vb") return set(off(L.bqkv, Hd + KVd), 1, KVd, Nq, 1);
     }
+  } else if (unit == "MoEFFN") {
+    TSB_CHECK(L.moe, "'%s': layer %d is not a mixture-of-experts layer", name.c_str(), k);
+    const int64_t E = c.n_experts, Fh = 4 * d;
+    if (field == "layerNorm.m_alpha") return set(L.moe_g, 1, d, d, 1);
+    if (field == "layerNorm.m_beta") return set(L.moe_b, 1, d, d, 1);
+    if (field == "m_Router") return set(L.router_w, d, E, E, 1);
+    if (field == "m_RouterBias") return set(L.router_b, 1, E, E, 1);
+    if (field == "m_Whd1") return set(L.moe_w1, E * d, Fh, Fh, 1);      // [E, d, 4d] handed over as [E * d, 4d]
+    if (field == "m_Whd2") return set(L.moe_w2, E * Fh, d, d, 1);
   } else if (unit == "PosFFN") {
+    TSB_CHECK(!L.moe, "'%s': layer %d is a mixture-of-experts layer", name.c_str(), k);
     if (field == "layerNorm2.m_alpha") return set(L.n2_g, 1, d, d, 1);
     if (field == "layerNorm2.m_beta") return set(L.n2_b, 1, d, d, 1);
     const int64_t w1c = g->glu ? 2 * F : F, cs = g->glu ? 2 : 1;
@@ -427,6 +443,14 @@ static std::vector<std::string> weight_names(const Gpt* g, bool biases, bool nor
     }
     add(matrices, a + "W0");
     add(biases, a + "b0");
+    if (g->L[k].moe) {
+      const std::string m = "GPTDecoder.MoEFFN_" + std::to_string(k) + ".";
+      add(norms, m + "layerNorm.m_alpha");
+      add(norms, m + "layerNorm.m_beta");
+      add(matrices, m + "m_Whd1"); add(matrices, m + "m_Whd2");
+      add(matrices, m + "m_Router"); add(biases, m + "m_RouterBias");
+      continue;
+    }
     add(norms, f + "layerNorm2.m_alpha");
     if (c.norm_type == 0) add(norms, f + "layerNorm2.m_beta");
     add(matrices, f + "feedForwardLayer1.m_Whd"); add(biases, f + "feedForwardLayer1.m_Bd");
@@ -461,7 +485,16 @@ static int ensure_act(Gpt* g, int64_t rows) {
   TSB_TRY(re(&g->h, rows * c.d * g->es));
   TSB_TRY(re(&g->qkv, rows * g->Nqkv * g->es));
   TSB_TRY(re(&g->attn, rows * Hd * g->es));
-  TSB_TRY(re(&g->ffn, rows * c.F * g->es));
+  {
+    // FFN hidden rows; mixture-of-experts layers keep experts_per_token hidden rows of 4 d per token there
+    int64_t ffn_elems = rows * c.F;
+    if (c.n_experts > 1 && rows * c.experts_per_token * 4 * c.d > ffn_elems) ffn_elems = rows * c.experts_per_token * 4 * c.d;
+    TSB_TRY(re(&g->ffn, ffn_elems * g->es));
+    if (c.n_experts > 1) {
+      TSB_TRY(re((void**)&g->moe_picks, rows * c.experts_per_token * 4));
+      TSB_TRY(re((void**)&g->moe_scores, rows * c.experts_per_token * 4));
+    }
+  }
   if (g->tp > 1) TSB_TRY(re((void**)&g->ar_buf, rows * c.d * 4));
   g->act_rows = rows;
   return 1;
@@ -542,6 +575,7 @@ static int ensure_stack(Gpt* g, int B) {
   if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
   g->own_B = 0;
   if (!g->use_stack || g->ragged) return 1;   // sequences of different lengths: one launch per operation
+  if (g->c.n_experts > 1) return 1;           // mixture-of-experts layers exist only as separate launches
   // tensor-parallel engines: one sequence, and only once the ranks' exchange regions are mapped into each other
   const bool own_tp_ok = g->tp == 1 || (g->xch_ready && g->tp_peer && B == 1 && g->xch_own_off != 0);
   if (g->use_owner && own_tp_ok && B <= g->own_cap && B <= kOwnMaxRows) {
@@ -709,6 +743,13 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
     PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
     TSB_TRY(row_parallel_linear(g, rows, g->attn, L.wo, Hd, L.bo));
+    if (L.moe) {
+      // MoEFeedForward.Process: the layer's own LayerNorm (whatever the model's norm type), router, experts, residual add
+      PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.moe_g, L.moe_b, 0, c.eps, rows, d, g->s));
+      PROF(KC_LINEAR, launch_moe_ffn(dev, g->st, dt, g->x, g->h, L.router_w, L.router_b, L.moe_w1, L.moe_w2, g->ffn, g->moe_picks, g->moe_scores,
+                                     rows, d, c.n_experts, c.experts_per_token, act, g->s));
+      continue;
+    }
     TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n2_g, L.n2_b, g->h, L.w1, d, g->glu ? 2 * c.F : c.F, make_ep(L.b1, nullptr, g->ffn, nullptr, act, g->glu)));
     TSB_TRY(row_parallel_linear(g, rows, g->ffn, L.w2, c.F, L.b2));
   }
@@ -924,6 +965,11 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
               "gpt_create: tensor parallel degree %d must divide the query heads (%d), KV heads (%d) and FFN width (%d)", tp, c.H, hkv, c.F);
   }
   TSB_CHECK(c.max_batch > 0 && c.max_batch <= 1024 && c.max_tokens > 0, "gpt_create: bad cache capacity");
+  if (c.n_experts > 1) {
+    TSB_CHECK(tp == 1, "gpt_create: mixture-of-experts models are not served tensor-parallel");
+    TSB_CHECK(c.experts_per_token >= 1 && c.experts_per_token <= c.n_experts && c.experts_per_token <= 8 && c.n_experts <= 256,
+              "gpt_create: %d experts with %d per token is not supported", c.n_experts, c.experts_per_token);
+  }
   DeviceState* st;
   TSB_TRY(use_device(c.device, &st));
   Gpt* g = new Gpt();
@@ -936,6 +982,10 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   if (g->c.Hkv <= 0 || g->c.H % g->c.Hkv != 0) {
     delete g;
     TSB_FAIL("gpt_create: H must be divisible by Hkv");
+  }
+  if (g->c.n_experts <= 1) {
+    g->c.n_experts = 1;
+    g->c.experts_per_token = 1;
   }
   g->st = st;
   g->s = st->stream;
@@ -979,8 +1029,17 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
     G_ALLOC(L.n1_g, d * es); G_ALLOC(L.n1_b, d * es); G_ALLOC(L.n2_g, d * es); G_ALLOC(L.n2_b, d * es);
     G_ALLOC(L.wqkv, packed_bytes(cc.dtype, (int)d, g->Nqkv)); G_ALLOC(L.bqkv, (int64_t)g->Nqkv * es);
     G_ALLOC(L.wo, packed_bytes(cc.dtype, (int)Hd, (int)d)); G_ALLOC(L.bo, d * es);
-    G_ALLOC(L.w1, packed_bytes(cc.dtype, (int)d, (int)(F * (g->glu ? 2 : 1)))); G_ALLOC(L.b1, F * es * (g->glu ? 2 : 1));
-    G_ALLOC(L.w2, packed_bytes(cc.dtype, (int)F, (int)d)); G_ALLOC(L.b2, d * es);
+    L.moe = cc.n_experts > 1 && k > 1;   // Networks/GPTDecoder.cs:116
+    if (L.moe) {
+      const int64_t E = cc.n_experts, Fh = 4 * d;
+      G_ALLOC(L.moe_g, d * es); G_ALLOC(L.moe_b, d * es);
+      G_ALLOC(L.router_w, d * E * es); G_ALLOC(L.router_b, E * es);
+      G_ALLOC(L.moe_w1, E * d * Fh * es); G_ALLOC(L.moe_w2, E * Fh * d * es);
+      if (!fill_const(g, L.moe_g, d, 1.0f)) return fail();
+    } else {
+      G_ALLOC(L.w1, packed_bytes(cc.dtype, (int)d, (int)(F * (g->glu ? 2 : 1)))); G_ALLOC(L.b1, F * es * (g->glu ? 2 : 1));
+      G_ALLOC(L.w2, packed_bytes(cc.dtype, (int)F, (int)d)); G_ALLOC(L.b2, d * es);
+    }
     G_ALLOC(L.cK, cache_elems * es); G_ALLOC(L.cV, cache_elems * es);
     if (!fill_const(g, L.n1_g, d, 1.0f) || !fill_const(g, L.n2_g, d, 1.0f)) return fail();
   }
@@ -1135,7 +1194,7 @@ int TSB200_GptFillSynthetic(void* h, uint64_t seed, float std, float bias_std) {
     ok = resolve(g, n, &dst, 0, &nparts);
     if (!ok) break;
     const bool is_bias = ends_with(n, "m_Bd") || ends_with(n, "QKVb") || ends_with(n, ".Qb") || ends_with(n, ".Kb") ||
-                         ends_with(n, ".Vb") || ends_with(n, ".b0");
+                         ends_with(n, ".Vb") || ends_with(n, ".b0") || ends_with(n, "m_RouterBias");
     // the FULL logical tensor is generated (every rank produces the same values) and this rank's block is kept
     ok = launch_synthetic(g->c.device, g->st, tmp, g->c.dtype, dst.full_rows * dst.full_cols, seed, fnv1a64(n.c_str()),
                           is_bias ? bias_std : std, g->s);

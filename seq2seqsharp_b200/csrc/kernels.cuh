@@ -147,6 +147,10 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
                    int* error_flag, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_tc_workspace_bytes(int M, int N, int sm_count);
 // stream-K mma.sync GEMM for decode batches of up to 64 rows on packed fp16 weights (gemm_stream_mma.cu)
+// mixture-of-experts feed-forward (ops_moe.cu): x32 += sum over the token's experts of score * W2_e act(W1_e h)
+int launch_moe_ffn(int device, DeviceState* st, int dtype, float* x32, const void* h, const void* router_w, const void* router_b,
+                   const void* W1, const void* W2, void* hidden, int* picks, float* scores, int rows, int d, int E, int k, int act,
+                   cudaStream_t s);
 // tcgen05 streaming GEMM for 17..64 rows (gemm_stream_tc.cu): the weights are the 128-row operand, the activation rows N
 int launch_gemm_stream_tc(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
                           int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);

@@ -79,6 +79,11 @@ class GPTConfig:
     rope_base: float = 500000.0     # TensorSharp/TensorApplyCPU.cs:1162
     ape_decode_pos0: bool = True    # Decoder.cs:674-677 adds APE row 0 in cached decode
     name: str = ""
+    expertNum: int = 1              # > 1: layers 2.. use MoEFeedForward (Networks/GPTDecoder.cs:114-123), experts [d, 4d] and [4d, d]
+    expertsPerTokenFactor: int = 1  # experts per token (TopK of the router's softmax, Layers/MoEFeedForward.cs:84)
+
+    def is_moe_layer(self, k: int) -> bool:
+        return self.expertNum > 1 and k > 1
 
     def kv_heads(self):
         return self.Hkv if (self.attn == MultiHeadAttentionTypeEnums.GQA and self.Hkv) else self.H
@@ -105,6 +110,14 @@ class GPTConfig:
                 s[a + "K"], s[a + "Kb"] = (d, KVd), (1, KVd)
                 s[a + "V"], s[a + "Vb"] = (d, KVd), (1, KVd)
             s[a + "W0"], s[a + "b0"] = (Hd, d), (1, d)
+            if self.is_moe_layer(k):
+                # MoEFeedForward (Layers/MoEFeedForward.cs:31-52): always LayerNorm; experts without bias; 3-D tensors are
+                # handed over as [E * rows, cols]
+                m, E = "GPTDecoder.MoEFFN_%d." % k, self.expertNum
+                s[m + "layerNorm.m_alpha"], s[m + "layerNorm.m_beta"] = (1, d), (1, d)
+                s[m + "m_Whd1"], s[m + "m_Whd2"] = (E * d, 4 * d), (E * 4 * d, d)
+                s[m + "m_Router"], s[m + "m_RouterBias"] = (d, E), (1, E)
+                continue
             s[f + "layerNorm2.m_alpha"] = (1, d)
             if self.norm == NormEnums.LayerNorm:
                 s[f + "layerNorm2.m_beta"] = (1, d)
@@ -124,7 +137,7 @@ class GPTConfig:
 
 
 def is_bias(name: str) -> bool:
-    return name.endswith(("m_Bd", "QKVb", ".Qb", ".Kb", ".Vb", ".b0"))
+    return name.endswith(("m_Bd", "QKVb", ".Qb", ".Kb", ".Vb", ".b0", "m_RouterBias"))
 
 
 def is_norm(name: str) -> bool:
@@ -200,6 +213,7 @@ class GPT:
         c.ape_decode_pos0 = 1 if cfg.ape_decode_pos0 else 0
         c.max_batch, c.max_tokens, c.device = max_batch, max_tokens, device_id
         c.tp_rank, c.tp_size = tp_rank, tp_size
+        c.n_experts, c.experts_per_token = cfg.expertNum, cfg.expertsPerTokenFactor
         self.tp_rank, self.tp_size = tp_rank, tp_size
         self._h = C.c_void_p()
         N.call("TSB200_GptCreate", C.byref(c), C.byref(self._h))

@@ -199,3 +199,37 @@ def test_oracle_against_committed_goldens(oracle):
                 np.testing.assert_array_equal(v, g[key], err_msg=key)
             else:
                 np.testing.assert_allclose(v, g[key], rtol=0, atol=1e-6 * max(1.0, float(np.abs(g[key]).max())), err_msg=key)
+
+
+def test_topk_follows_the_reference_loop(oracle):
+    """TensorApplyCPU.TopK / replace_smaller (TensorSharp/TensorApplyCPU.cs:1097-1146), restated literally in Python, on
+    random rows and on rows full of ties (the router of a mixture-of-experts layer produces many: its logits are rounded
+    to multiples of 2^-7)."""
+    def ref(row, k):
+        val, idx = [-1.70141e+38] * k, [-1] * k
+        for i, data in enumerate(row):
+            if data < val[k - 1]:
+                continue
+            placed = False
+            for j in range(k - 2, -1, -1):
+                if data > val[j]:
+                    val[j + 1], idx[j + 1] = val[j], idx[j]
+                else:
+                    val[j + 1], idx[j + 1] = data, i
+                    placed = True
+                    break
+            if not placed:
+                val[0], idx[0] = data, i
+        return val, idx
+
+    rng = np.random.default_rng(3)
+    for cols, k in ((8, 1), (8, 2), (5, 5), (64, 4), (3, 1)):
+        x = rng.standard_normal((40, cols)).astype(np.float32)
+        x[10:30] = np.round(x[10:30] * 2) / 2          # ties
+        x[30:] = 0.125                                  # all equal
+        val, idx = oracle.topk(x, k)
+        for r in range(x.shape[0]):
+            v, i = ref([float(t) for t in x[r]], k)
+            assert list(idx[r]) == i and [float(t) for t in val[r]] == v, (cols, k, r)
+    # k = 1: the LAST of equal maxima wins (data < array[0] is the only early exit)
+    assert oracle.topk(np.array([[1.0, 3.0, 3.0, 2.0]], dtype=np.float32), 1)[1][0, 0] == 2
