@@ -29,6 +29,7 @@ from .gpt import (ActivateFuncEnums, GPTConfig, MultiHeadAttentionTypeEnums, Nor
 F_WEIGHTS, F_DEC_EMB, F_ENC_EMB, F_DEC_DEPTH, F_ENC_DEPTH, F_DEC_TYPE, F_ENC_TYPE, F_HIDDEN, F_INTER = 1, 2, 3, 4, 5, 6, 7, 8, 9
 F_SEG, F_HEADS, F_SRC_VOCAB, F_TGT_VOCAB, F_CLS_VOCABS = 10, 11, 12, 13, 14
 F_EXPERTS, F_ACT, F_VQTYPE, F_VQ, F_CODEBOOK, F_HALF, F_PE, F_NORM, F_MHA_TYPE, F_KV_GROUPS = 21, 23, 24, 25, 26, 27, 28, 29, 30, 31
+F_EXPERTS_PER_TOKEN = 22
 VQ_NONE, VQ_INT4, VQ_INT8, VQ_FLOAT16 = 0, 16, 256, 65536          # Seq2SeqSharp/Utils/ModeEnums.cs:41-47
 DECODER_GPT = 2                                                    # DecoderTypeEnums.GPTDecoder
 
@@ -128,6 +129,7 @@ class ModelFile:
     IntermediateDim: int = 0
     MultiHeadNum: int = 0
     ExpertNum: int = 0
+    ExpertsPerTokenFactor: int = 0
     ActivateFunc: int = 0
     VQType: int = 0
     PEType: int = 0
@@ -171,8 +173,6 @@ class ModelFile:
         """The GPTDecoder this file describes, in the engine's terms (GPT.cs:112-134 builds the network from these fields)."""
         if self.DecoderType != DECODER_GPT:
             raise ModelFileError("DecoderType %d is not GPTDecoder: only the GPT decode path runs on this backend" % self.DecoderType)
-        if self.ExpertNum > 1:
-            raise ModelFileError("mixture-of-experts feed-forward layers are outside this backend's scope")
         if self.MultiHeadNum <= 0 or self.HiddenDim % self.MultiHeadNum:
             raise ModelFileError("HiddenDim %d is not divisible by MultiHeadNum %d" % (self.HiddenDim, self.MultiHeadNum))
         if self.TgtVocab is None:
@@ -184,7 +184,8 @@ class ModelFile:
         return GPTConfig(L=self.DecoderLayerDepth, d=self.HiddenDim, H=self.MultiHeadNum, hd=self.HiddenDim // self.MultiHeadNum,
                          F=self.IntermediateDim, V=len(self.TgtVocab), Hkv=self.KVGroupNum if gqa else 0,
                          norm=NormEnums(self.NormType), act=ActivateFuncEnums(self.ActivateFunc), pe=pe,
-                         attn=MultiHeadAttentionTypeEnums.GQA if gqa else MultiHeadAttentionTypeEnums.MHA, dtype=dtype, name="model_file")
+                         attn=MultiHeadAttentionTypeEnums.GQA if gqa else MultiHeadAttentionTypeEnums.MHA, dtype=dtype, name="model_file",
+                         expertNum=max(1, self.ExpertNum), expertsPerTokenFactor=max(1, self.ExpertsPerTokenFactor))
 
     def weights_for(self, cfg: GPTConfig, max_pos: int = 0) -> Dict[str, np.ndarray]:
         """Every tensor the engine asks for, shaped [rows, cols], in the file's own precision (float16 arrays for a
@@ -239,7 +240,7 @@ def parse_model(data) -> ModelFile:
     m = ModelFile()
     scalars = {F_DEC_EMB: "DecoderEmbeddingDim", F_ENC_EMB: "EncoderEmbeddingDim", F_DEC_DEPTH: "DecoderLayerDepth",
                F_ENC_DEPTH: "EncoderLayerDepth", F_DEC_TYPE: "DecoderType", F_ENC_TYPE: "EncoderType", F_HIDDEN: "HiddenDim",
-               F_INTER: "IntermediateDim", F_HEADS: "MultiHeadNum", F_EXPERTS: "ExpertNum", F_ACT: "ActivateFunc", F_VQTYPE: "VQType",
+               F_INTER: "IntermediateDim", F_HEADS: "MultiHeadNum", F_EXPERTS: "ExpertNum", F_EXPERTS_PER_TOKEN: "ExpertsPerTokenFactor", F_ACT: "ActivateFunc", F_VQTYPE: "VQType",
                F_PE: "PEType", F_NORM: "NormType", F_MHA_TYPE: "MultiHeadAttentionType", F_KV_GROUPS: "KVGroupNum"}
     for fno, wt, v in _fields(buf):
         if fno in scalars and wt == 0:

@@ -89,7 +89,8 @@ def write_model(path, cfg, weights, vocab_size, vq="none", packed=True, decoder_
             out += _entry(25, name, _ld(2, by.tobytes()))
             out += _entry(26, name, _scalars(2, book, "f64", packed))
             expect[name] = book[idx].astype(np.float32)
-    for fno, v in ((2, cfg.d), (3, cfg.d), (4, cfg.L), (5, 0), (6, decoder_type), (8, cfg.d), (9, cfg.F), (11, cfg.H), (23, int(cfg.act)),
+    for fno, v in ((2, cfg.d), (3, cfg.d), (4, cfg.L), (5, 0), (6, decoder_type), (8, cfg.d), (9, cfg.F), (11, cfg.H),
+                   (21, cfg.expertNum if cfg.expertNum > 1 else 0), (22, cfg.expertsPerTokenFactor if cfg.expertNum > 1 else 0), (23, int(cfg.act)),
                    (24, vqtype), (28, pe), (29, int(cfg.norm)), (30, int(cfg.attn)), (31, cfg.kv_heads() if int(cfg.attn) == 1 else 0)):
         if v:   # protobuf-net leaves default (zero) values out
             out += _key(fno, 0) + _varint(v)

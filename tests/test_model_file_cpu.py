@@ -77,3 +77,21 @@ def test_errors(tmp_path):
         fh.write(data[:len(data) // 2])
     with pytest.raises(ModelFileError):
         read_model(path)
+
+
+def test_mixture_of_experts_model(tmp_path):
+    """ExpertNum / ExpertsPerTokenFactor (fields 21, 22) and the tensors of MoEFeedForward (router, experts, its LayerNorm)."""
+    cfg = GPTConfig(L=4, d=32, H=2, hd=16, F=64, V=38, norm=Nm.LayerNorm, act=A.SiLU, pe=P.RoPE, attn=M.MHA, expertNum=3, expertsPerTokenFactor=2)
+    w = saved_weights(cfg)
+    assert "GPTDecoder.MoEFFN_2.m_Whd1" in w and "GPTDecoder.PosFFN_1.feedForwardLayer1.m_Whd" in w and "GPTDecoder.PosFFN_3.feedForwardLayer1.m_Whd" not in w
+    path = str(tmp_path / "moe.model")
+    expect = write_model(path, cfg, w, cfg.V, vq="none")
+    mf = read_model(path)
+    assert (mf.ExpertNum, mf.ExpertsPerTokenFactor) == (3, 2)
+    got_cfg = mf.gpt_config()
+    assert (got_cfg.expertNum, got_cfg.expertsPerTokenFactor) == (3, 2) and got_cfg.is_moe_layer(2) and not got_cfg.is_moe_layer(1)
+    shaped = mf.weights_for(got_cfg)
+    assert shaped["GPTDecoder.MoEFFN_3.m_Whd1"].shape == (3 * 32, 128) and shaped["GPTDecoder.MoEFFN_3.m_Whd2"].shape == (3 * 128, 32)
+    assert shaped["GPTDecoder.MoEFFN_2.m_Router"].shape == (32, 3) and shaped["GPTDecoder.MoEFFN_2.m_RouterBias"].shape == (1, 3)
+    for name, want in expect.items():
+        np.testing.assert_array_equal(mf.get_weights(name).astype(np.float32), want, err_msg=name)
