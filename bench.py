@@ -11,7 +11,7 @@ Workloads (synthetic seeded weights and prompts of the named shapes; no dataset 
     c5_b1   Llama-7B-class fp16, B=1,  prompt 512, Top-P 0.95     (headline: latency-bound decode)
     c5_b64  same model, B=64
     c5_b2 .. c5_b8  same model, B=2, 3, 4, 8 (still one persistent launch per step on the fp16 tensor-core variant)
-    c3_b1 / c3_b32  Llama-1B-class fp16, prompt 1024, greedy
+    c3_b1 / c3_b2 / c3_b4 / c3_b8 / c3_b32  Llama-1B-class fp16, prompt 1024, greedy
     c4_b4   the same 1B-class model, B=4, 16384-token prompts, greedy (long-context KV-cache stress)
     c1      tiny fp32 model, B=1, prompt 32, greedy
 
@@ -45,6 +45,9 @@ WORKLOADS = {
     "c5_b4": ("c5_llama7b_fp16", 4, 512, "topp", 0.95),
     "c5_b8": ("c5_llama7b_fp16", 8, 512, "topp", 0.95),
     "c3_b1": ("c3_llama1b_fp16", 1, 1024, "greedy", 1.0),
+    "c3_b2": ("c3_llama1b_fp16", 2, 1024, "greedy", 1.0),
+    "c3_b4": ("c3_llama1b_fp16", 4, 1024, "greedy", 1.0),
+    "c3_b8": ("c3_llama1b_fp16", 8, 1024, "greedy", 1.0),
     "c3_b32": ("c3_llama1b_fp16", 32, 1024, "greedy", 1.0),
     "c4_b4": ("c4_llama1b_longctx_fp16", 4, 16384, "greedy", 1.0),
     "c2_b8": ("c2_gpt2small_fp16", 8, 128, "topp", 0.9),

@@ -215,7 +215,8 @@ struct Gpt {
   // mma.sync linears): 1 sequence 3.41 / 3.95, 2 sequences 3.79 / 3.92, 3 sequences 4.23 / 3.91, 4 sequences 4.62 / 3.96 --
   // the persistent kernel's dependency chain grows with every row, the per-operation path is flat up to 8 sequences.
   // Tensor-parallel engines keep the persistent kernel (the exchange lives there).
-  int stack_cap = 2;           // largest batch the persistent kernel is used for on one GPU (TSB200_STACK_MAXB)
+  int stack_cap = -1;          // largest batch the persistent kernels are used for on one GPU (TSB200_STACK_MAXB); -1: fp16 one
+                               // sequence (from two on, one launch per operation on the tensor-core linears is faster), fp32 two
   int gemv_rows = 1;           // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS)
   std::vector<StackOp> stack_host;
   StackOp* stack_dev = nullptr;
@@ -572,7 +573,8 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
 static int ensure_stack(Gpt* g, int B) {
   const TSB200GptConfig& c = g->c;
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
-  if (g->tp == 1 && g->stack_cap > 0 && g->stack_cap < g->stack_max_B) g->stack_max_B = g->stack_cap;
+  const int cap = g->stack_cap >= 0 ? g->stack_cap : (c.dtype == TSB200_F16 ? 1 : 2);
+  if (g->tp == 1 && cap > 0 && cap < g->stack_max_B) g->stack_max_B = cap;
   g->own_B = 0;
   if (!g->use_stack || g->ragged) return 1;   // sequences of different lengths: one launch per operation
   if (g->c.n_experts > 1) return 1;           // mixture-of-experts layers exist only as separate launches

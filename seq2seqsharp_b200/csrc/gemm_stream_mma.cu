@@ -34,6 +34,7 @@ struct GsArgs {
   const unsigned char* Wp;
   int M, K, N, KB, CT;
   int stages, max_contrib;
+  int prefetch;             // 1: the first ring-full of weight tiles is requested before the wait on the previous kernel
   float* partials;          // [CT][max_contrib][M][256]
   unsigned int* counters;   // [CT], zero on entry, self-resetting
   int* error_flag;
@@ -104,7 +105,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
   }
   __syncthreads();
   grid_dep_launch();
-  grid_dep_wait();  // the activation rows come from the previous kernel (the producer reads them through TMA)
 
   if (w == kConsumerWarps) {
     if (lane == 0) {
@@ -112,6 +112,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
       int s = 0, kb = u_begin % KB;
       unsigned round = 0;
       long long issued = 0;
+      // The weights do not depend on the previous kernel: the first ring-full of tiles is requested before the wait on it,
+      // so the stream starts while that kernel's last CTAs still reduce and store (and while a norm kernel in between runs).
+      const int n_pre = a.prefetch ? min(S, u_end - u_begin) : 0;
+      for (int i = 0; i < n_pre; ++i) {
+        mbar_expect_tx(&full[i], kTileBytes + NB * 8 * 64);
+        bulk_g2s(smem + (size_t)i * kGsStageBytes, src + (size_t)i * kTileBytes, kTileBytes, &full[i]);
+      }
+      grid_dep_wait();  // the activation rows come from the previous kernel (read through TMA)
       for (int u = u_begin; u < u_end; ++u) {
         if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
           s_err = 1;
@@ -119,8 +127,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
         }
         if (*(volatile int*)&s_err) break;
         unsigned char* dst = smem + (size_t)s * kGsStageBytes;
-        mbar_expect_tx(&full[s], kTileBytes + NB * 8 * 64);
-        bulk_g2s(dst, src, kTileBytes, &full[s]);
+        if (u - u_begin >= n_pre) {
+          mbar_expect_tx(&full[s], kTileBytes + NB * 8 * 64);
+          bulk_g2s(dst, src, kTileBytes, &full[s]);
+        }
         gs_tma_load_2d(dst + kTileBytes, &mapX, kb * kKT, 0, &full[s]);  // x = kb * 32 halves: a 64-byte multiple
         src += kTileBytes;
         ++issued;
@@ -131,6 +141,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
         }
       }
       if (*(volatile int*)&s_err) {
+        // stages whose weight tile was requested ahead still lack their activation tile: request it (any k block), so
+        // that every copy into this CTA's shared memory has landed before the CTA returns
+        for (long long j = issued; j < n_pre; ++j) {
+          gs_tma_load_2d(smem + (size_t)j * kGsStageBytes + kTileBytes, &mapX, 0, 0, &full[(int)j]);
+          ++issued;
+        }
         const long long first = issued > S ? issued - S : 0;
         for (long long j = first; j < issued; ++j) mbar_wait(&full[(int)(j % S)], (unsigned)((j / S) & 1));
         g_gs_error = 1;
@@ -139,6 +155,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
     }
     return;
   }
+  grid_dep_wait();  // consumers touch the scratch slots, counters and the residual rows of earlier kernels
 
   // ---------------- consumer warps: warp w owns columns [w*32, w*32+32) of every tile
   const int chunk = w >> 1, hf = w & 1;
@@ -231,30 +248,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
     if (*(volatile int*)&s_last) {
       const float* all = a.partials + ((size_t)cur_ct * max_contrib * M) * NT;
       const int No = ep.glu ? N / 2 : N;
-      // work items: (row, group of 4 columns); eight items per thread in flight
-      for (int i0 = 0; i0 < M * 64; i0 += 256 * 8) {
-        float4 acc[8];
+      // work items: (row, group of 4 columns); per item up to eight slots are read at once and added in slot order
+      for (int idx = tid; idx < M * 64; idx += 256) {
+        {
+          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          const float4* src = reinterpret_cast<const float4*>(all) + idx;
+          const size_t slot_stride = (size_t)M * NT / 4;
+          for (int j0 = 0; j0 < n_contrib; j0 += 8) {
+            float4 t[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int j = 0; j < n_contrib; ++j) {
-          float4 t[8];
+            for (int q = 0; q < 8; ++q)
+              t[q] = j0 + q < n_contrib ? __ldcg(src + (size_t)(j0 + q) * slot_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int idx = i0 + q * 256 + tid;
-            const int ic = idx < M * 64 ? idx : 0;
-            t[q] = __ldcg(reinterpret_cast<const float4*>(all + (size_t)j * M * NT) + ic);
+            for (int q = 0; q < 8; ++q)
+              if (j0 + q < n_contrib) {
+                sum.x += t[q].x; sum.y += t[q].y; sum.z += t[q].z; sum.w += t[q].w;
+              }
           }
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            acc[q].x += t[q].x; acc[q].y += t[q].y; acc[q].z += t[q].z; acc[q].w += t[q].w;
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int idx = i0 + q * 256 + tid;
-          if (idx >= M * 64) continue;
           const int row = idx >> 6, c = cur_ct * NT + (idx & 63) * 4;
-          const float v[4] = {acc[q].x, acc[q].y, acc[q].z, acc[q].w};
+          const float v[4] = {sum.x, sum.y, sum.z, sum.w};
           if (!ep.glu) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -307,6 +319,7 @@ struct GcArgs {
   const unsigned char* Wp;
   int M, K, N, KB, CT;
   int ksplit, k2_per;        // K ranges per box; stages (pairs of k tiles) per range
+  int prefetch;              // 1: the first ring-full of weight tiles is requested before the wait on the previous kernel
   float* partials;           // [boxes][ksplit][M][64]
   unsigned int* counters;    // [boxes], zero on entry, self-resetting
   int* error_flag;
@@ -341,28 +354,41 @@ __global__ void __launch_bounds__(kGcThreads, 3) gemm_chunk_mma_kernel(const __g
   }
   __syncthreads();
   grid_dep_launch();
-  grid_dep_wait();  // the activation rows come from the previous kernel
+  if (!(w == 4 && lane == 0)) grid_dep_wait();  // scratch slots, counters and residual rows belong to earlier kernels too
 
   if (w == 4) {
     if (lane == 0) {
       const unsigned char* wsrc = a.Wp + ((size_t)ct * KB) * kTileBytes + (size_t)j * 4096;
-      for (int i = 0; i < n_st; ++i) {
-        const int s = i % kGcStages, r = i / kGcStages;
-        if (i >= kGcStages && !mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
-          s_err = 1;
-          break;
-        }
+      auto put_w = [&](int i) {
+        const int s = i % kGcStages;
         const int kb0 = (k2_beg + i) * 2;
         const bool two = kb0 + 1 < KB;
         unsigned char* dst = smem + (size_t)s * kGcStageBytes;
         mbar_expect_tx(&full[s], (two ? 8192 : 4096) + NB * 8 * 128);
         bulk_g2s(dst, wsrc + (size_t)kb0 * kTileBytes, 4096, &full[s]);
         if (two) bulk_g2s(dst + 4096, wsrc + (size_t)(kb0 + 1) * kTileBytes, 4096, &full[s]);
-        gs_tma_load_2d(dst + 8192, &mapX, kb0 * kKT, 0, &full[s]);  // x = kb0 * 32 halves: a 64-byte multiple
+      };
+      // the weights do not depend on the previous kernel: the first ring-full is requested before the wait on it
+      const int n_pre = a.prefetch ? min(kGcStages, n_st) : 0;
+      for (int i = 0; i < n_pre; ++i) put_w(i);
+      grid_dep_wait();  // the activation rows come from the previous kernel
+      int done = 0;
+      for (int i = 0; i < n_st; ++i) {
+        const int s = i % kGcStages, r = i / kGcStages;
+        if (i >= kGcStages && !mbar_wait(&empty[s], (unsigned)((r - 1) & 1))) {
+          s_err = 1;
+          break;
+        }
+        if (i >= n_pre) put_w(i);
+        gs_tma_load_2d(smem + (size_t)s * kGcStageBytes + 8192, &mapX, (k2_beg + i) * 2 * kKT, 0, &full[s]);  // x = kb0 * 32 halves: a 64-byte multiple
+        done = i + 1;
       }
       if (*(volatile int*)&s_err) {
-        const int first = n_st > kGcStages ? n_st - kGcStages : 0;
-        for (int i = first; i < n_st; ++i) mbar_wait(&full[i % kGcStages], (unsigned)((i / kGcStages) & 1), 1u << 16);
+        // stages requested ahead get their activation tile too, so that every copy into this CTA has landed on return
+        for (int i = done; i < n_pre; ++i) gs_tma_load_2d(smem + (size_t)(i % kGcStages) * kGcStageBytes + 8192, &mapX, 0, 0, &full[i % kGcStages]);
+        if (done < n_pre) done = n_pre;
+        const int first = done > kGcStages ? done - kGcStages : 0;
+        for (int i = first; i < done; ++i) mbar_wait(&full[i % kGcStages], (unsigned)((i / kGcStages) & 1), 1u << 16);
         g_gs_error = 1;
         if (a.error_flag) *a.error_flag = 1;
       }
@@ -558,6 +584,15 @@ int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count) {
   return kWsCounterBytes + (chunk > stream ? chunk : stream) + 256;
 }
 
+static int gs_prefetch_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TSB200_GEMM_PREFETCH");  // "0": weights are requested only after the previous kernel has ended (A/B measurements)
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on;
+}
+
 template <int NB>
 static int gc_launch(int device, const CUtensorMap& mapX, const GcArgs& a, int grid, bool pdl, cudaStream_t s) {
   static bool attr_done[kMaxDevices] = {};
@@ -602,6 +637,7 @@ static int launch_gemm_chunk_mma(int device, DeviceState* st, const void* x, con
   a.k2_per = (k2_total + ks - 1) / ks;
   ks = (k2_total + a.k2_per - 1) / a.k2_per;       // no empty range
   a.ksplit = ks;
+  a.prefetch = gs_prefetch_enabled();
   const int64_t need = kWsCounterBytes + (int64_t)boxes * ks * M * 64 * 4;
   if (ks > 1 && (!ws || ws_bytes < need || (int64_t)boxes * 4 > kWsCounterBytes - 256)) return 2;
   a.counters = reinterpret_cast<unsigned int*>(ws);
@@ -663,6 +699,7 @@ int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const voi
   int stages = (int)((225 * 1024 - fixed) / kGsStageBytes);
   if (stages > 16) stages = 16;
   a.stages = stages;
+  a.prefetch = gs_prefetch_enabled();
   const int64_t need = kWsCounterBytes + (int64_t)a.CT * a.max_contrib * M * 256 * 4;
   if (!ws || ws_bytes < need) return 2;
   a.counters = reinterpret_cast<unsigned int*>(ws);

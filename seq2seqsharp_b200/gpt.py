@@ -48,6 +48,7 @@ class MultiHeadAttentionTypeEnums(IntEnum):
 
 @dataclass
 class DecodingOptions:
+    MaxSrcSentLength: int = 128     # lines of an input file are cut to this many tokens less two (Applications/DecodingOptions.cs:18)
     MaxTgtSentLength: int = 256
     RepeatPenalty: float = 2.0
     BeamSearchSize: int = 1
