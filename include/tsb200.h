@@ -415,6 +415,19 @@ TSB200_API int TSB200_GptLastTiming(void* gpt, float* ms, int64_t* launches);
  * TensorUtils.CreateTokensEmbeddings; ids read back, Decoder.cs:769-782): B*4 bytes each way. */
 TSB200_API int TSB200_GptStepHost(void* gpt, const int32_t* last_ids, const TSB200DecodingOptions* opt,
                                   int32_t* out_ids);
+/* Beam search (DecodingOptions.BeamSearchSize > 1; GPT.cs:236-304, Decoder.cs:447-517, Utils/BeamSearch.cs:36-46).  The
+ * reference re-runs every hypothesis from its first token at every step (no KV cache with beams); here every hypothesis is
+ * a sequence of the engine with its own cache rows, the host keeps the scores and decides which hypotheses survive:
+ *   TSB200_GptBeamCandidates  the K best next ids of every sequence after the latest forward, found as the reference finds
+ *                             them (K rounds of first-arg-max and zero-fill on softmax(logits) with -1 on blocked ids), with
+ *                             their probabilities and natural logarithms; host arrays [sequences][K];
+ *   TSB200_GptBeamCopy        sequence src[i] over sequence dst[i] (cache rows, history, pending id, length): the children
+ *                             of a hypothesis beyond the first take the places of dropped hypotheses; dst[i] == number of
+ *                             sequences adds a sequence (used once, after the prefill, to open the beams);
+ *   TSB200_GptStepHost        then feeds the chosen id of every hypothesis and runs the next step. */
+TSB200_API int TSB200_GptBeamCandidates(void* gpt, int K, const TSB200DecodingOptions* opt, int32_t* ids, float* probs,
+                                        float* log_probs);
+TSB200_API int TSB200_GptBeamCopy(void* gpt, const int32_t* src, const int32_t* dst, int n);
 /* per-step device durations of the last TSB200_GptDecode call (CUDA events between graph launches) */
 TSB200_API int TSB200_GptEnableStepTiming(void* gpt, int enable);
 TSB200_API int TSB200_GptGetStepTimes(void* gpt, float* ms, int n, int* n_out);

@@ -159,6 +159,8 @@ def lib():
         "TSB200_GptLastTiming": (i32, [vp, C.POINTER(f32), C.POINTER(i64)]),
         "TSB200_GptStream": (i32, [vp, C.POINTER(vp)]),
         "TSB200_GptStepHost": (i32, [vp, vp, C.POINTER(DecodingOptionsC), vp]),
+        "TSB200_GptBeamCandidates": (i32, [vp, i32, C.POINTER(DecodingOptionsC), vp, vp, vp]),
+        "TSB200_GptBeamCopy": (i32, [vp, vp, vp, i32]),
         "TSB200_GptEnableStepTiming": (i32, [vp, i32]),
         "TSB200_GptGetStepTimes": (i32, [vp, vp, i32, C.POINTER(i32)]),
         "TSB200_GptProfileDecode": (i32, [vp, i32, C.POINTER(DecodingOptionsC), vp, vp, i32]),

@@ -166,6 +166,12 @@ struct Gpt {
   void *h = nullptr, *qkv = nullptr, *attn = nullptr, *ffn = nullptr;
   float* xl = nullptr;
   void* hl = nullptr;
+  // beam search: candidate scratch [max_batch][kMaxBeam] (ids, probabilities, log probabilities), the table of the layers'
+  // cache pointers and the (source, destination) pairs of a sequence copy
+  int* beam_ids = nullptr;
+  float* beam_p = nullptr;
+  void** beam_layers = nullptr;   // [2 * L]: K cache, V cache of layer 0, 1, ...
+  int* beam_pairs = nullptr;      // [2 * max_batch]
   int* moe_picks = nullptr;      // [rows, experts_per_token] experts chosen by the router, ascending per token
   float* moe_scores = nullptr;   // their router probabilities
   float *logits = nullptr, *probs = nullptr, *u = nullptr;
@@ -217,7 +223,8 @@ struct Gpt {
   // Tensor-parallel engines keep the persistent kernel (the exchange lives there).
   int stack_cap = -1;          // largest batch the persistent kernels are used for on one GPU (TSB200_STACK_MAXB); -1: fp16 one
                                // sequence (from two on, one launch per operation on the tensor-core linears is faster), fp32 two
-  int gemv_rows = 1;           // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS)
+  int gemv_rows = -1;          // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS);
+                               // -1: fp16 none (the tensor-core streaming kernel is faster from one row on), fp32 four
   std::vector<StackOp> stack_host;
   StackOp* stack_dev = nullptr;
   int stack_B = 0;
@@ -266,6 +273,28 @@ static void prof_end(Gpt* g, int cls) {
 
 constexpr size_t kGuardBytes = 256;
 constexpr int kGuardByte = 0xC5;
+constexpr int kMaxBeam = 32;
+
+// Copies whole sequences inside the engine: for every pair (src, dst) the first T cache rows of every (layer, K or V, KV
+// head), the token history and the pending id.  grid = (pairs, 2 * L * Hkv); sources and destinations are disjoint.
+__global__ void __launch_bounds__(256) seq_copy_kernel(void* const* layers, const int* pairs, int Hkv, int64_t seq_bytes, int64_t head_pitch,
+                                                       int64_t head_bytes, int* hist, int* hist_len, int* ids_cur, int hist_stride) {
+  const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+  const int lw = blockIdx.y / Hkv, kvh = blockIdx.y % Hkv;
+  unsigned char* base = reinterpret_cast<unsigned char*>(layers[lw]);
+  const uint4* from = reinterpret_cast<const uint4*>(base + (size_t)src * seq_bytes + (size_t)kvh * head_pitch);
+  uint4* to = reinterpret_cast<uint4*>(base + (size_t)dst * seq_bytes + (size_t)kvh * head_pitch);
+  for (int64_t i = threadIdx.x; i < head_bytes / 16; i += blockDim.x) to[i] = from[i];
+  if (blockIdx.y == 0) {
+    const int n = hist_len[src];
+    for (int i = threadIdx.x; i < n && i < hist_stride; i += blockDim.x) hist[(size_t)dst * hist_stride + i] = hist[(size_t)src * hist_stride + i];
+    if (threadIdx.x == 0) {
+      hist_len[dst] = n;
+      ids_cur[dst] = ids_cur[src];
+    }
+  }
+}
+
 static int dev_alloc(Gpt* g, void** p, int64_t bytes, bool zero = true) {
   if (bytes <= 0) bytes = 256;
   void* base = nullptr;
@@ -514,7 +543,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
                          const void* Wp, int K, int N, const Epilogue& ep) {
   const TSB200GptConfig& c = g->c;
   const int dev = c.device, dt = c.dtype;
-  if (rows <= g->gemv_rows) {
+  if (rows <= (g->gemv_rows >= 0 ? g->gemv_rows : (dt == TSB200_F16 ? 0 : 4))) {
     prof_begin(g);
     const int r = launch_gemv_stream(dev, g->st, dt, Wp, ng ? (const void*)x_resid : x_T, ng ? (c.norm_type == 0 ? 2 : 1) : 0, ng,
                                      c.norm_type == 0 ? nb : nullptr, c.eps, rows, K, N, ep, g->err_flag, g->pdl, g->lin_ws,
@@ -1931,6 +1960,83 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   }
   g->probs_valid = (opt->strategy == 1);
   g->last_launches = g->graph_nodes;
+  return 1;
+}
+
+// The K most probable next ids of every sequence after the latest forward (prefill, extend or step), taken as the
+// reference takes them in beam search: softmax of the logits, -1 on blocked ids, then K rounds of (first arg-max, zero it)
+// (Decoder.cs:447-517 / the same loop in GPTDecode).  ids, probs, log_probs: host arrays [sequences][K].
+int TSB200_GptBeamCandidates(void* h, int K, const TSB200DecodingOptions* opt, int32_t* ids, float* probs, float* log_probs) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && opt && ids && probs && log_probs, "gpt_beam_candidates: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(g->B > 0 && g->T > 0, "gpt_beam_candidates: nothing has run yet");
+  TSB_CHECK(K >= 1 && K <= kMaxBeam && K <= c.V, "gpt_beam_candidates: %d candidates asked, at most %d", K, kMaxBeam < c.V ? kMaxBeam : c.V);
+  if (!g->beam_ids) {
+    TSB_TRY(dev_alloc(g, (void**)&g->beam_ids, (int64_t)c.max_batch * kMaxBeam * 4));
+    TSB_TRY(dev_alloc(g, (void**)&g->beam_p, (int64_t)c.max_batch * kMaxBeam * 8));
+  }
+  TSB_TRY(upload_blocked(g, opt));
+  const int B = g->B;
+  float* logp = g->beam_p + (size_t)c.max_batch * kMaxBeam;
+  TSB_TRY(launch_softmax_argmax(c.device, g->st, nullptr, g->probs, g->logits, B, c.V, 1.0f, 0, g->blocked, g->n_blocked, g->s));
+  TSB_TRY(launch_beam_topk(c.device, g->st, g->beam_ids, g->beam_p, logp, g->probs, B, c.V, K, g->s));
+  g->probs_valid = false;   // the chosen entries of the probabilities are zero now
+  TSB_CUDA(cudaMemcpyAsync(ids, g->beam_ids, (size_t)B * K * 4, cudaMemcpyDeviceToHost, g->s));
+  TSB_CUDA(cudaMemcpyAsync(probs, g->beam_p, (size_t)B * K * 4, cudaMemcpyDeviceToHost, g->s));
+  TSB_CUDA(cudaMemcpyAsync(log_probs, logp, (size_t)B * K * 4, cudaMemcpyDeviceToHost, g->s));
+  TSB_CUDA(cudaStreamSynchronize(g->s));
+  return 1;
+}
+
+// Sequence src[i] is copied over sequence dst[i] (cache rows, history, pending id, length and step), i < n.  A destination
+// equal to the number of sequences adds one (destinations in ascending order then).  No destination may also be a source:
+// a surviving hypothesis keeps its place, the copies fill the places of the ones that were dropped.
+int TSB200_GptBeamCopy(void* h, const int32_t* src, const int32_t* dst, int n) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && (n == 0 || (src && dst)), "gpt_beam_copy: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(n >= 0 && n <= c.max_batch, "gpt_beam_copy: %d copies for %d sequences", n, c.max_batch);
+  if (n == 0) return 1;
+  if (g->Ts.empty()) mirror_uniform(g);
+  for (int i = 0; i < n; ++i) {
+    TSB_CHECK(src[i] >= 0 && src[i] < g->B, "gpt_beam_copy: source %d is not a sequence in use (%d)", src[i], g->B);
+    for (int j = 0; j < n; ++j) TSB_CHECK(dst[j] != src[i], "gpt_beam_copy: sequence %d is both a source and a destination", src[i]);
+    for (int j = 0; j < i; ++j) TSB_CHECK(dst[j] != dst[i], "gpt_beam_copy: destination %d named twice", dst[i]);
+  }
+  if (!g->beam_layers) {
+    TSB_TRY(dev_alloc(g, (void**)&g->beam_layers, (int64_t)2 * c.L * sizeof(void*)));
+    TSB_TRY(dev_alloc(g, (void**)&g->beam_pairs, (int64_t)2 * c.max_batch * 4));
+    std::vector<void*> lp((size_t)2 * c.L);
+    for (int k = 0; k < c.L; ++k) {
+      lp[2 * k] = g->L[k].cK;
+      lp[2 * k + 1] = g->L[k].cV;
+    }
+    TSB_CUDA(cudaMemcpy(g->beam_layers, lp.data(), lp.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  }
+  std::vector<int> pairs((size_t)2 * n);
+  int Tmax = 0;
+  for (int i = 0; i < n; ++i) {
+    TSB_TRY(slot_claim(g, dst[i], "gpt_beam_copy"));
+    pairs[2 * i] = src[i];
+    pairs[2 * i + 1] = dst[i];
+    g->Ts[dst[i]] = g->Ts[src[i]];
+    g->steps_v[dst[i]] = g->steps_v[src[i]];
+    Tmax = g->Ts[src[i]] > Tmax ? g->Ts[src[i]] : Tmax;
+  }
+  TSB_CUDA(cudaMemcpyAsync(g->beam_pairs, pairs.data(), pairs.size() * 4, cudaMemcpyHostToDevice, g->s));
+  const int64_t head_pitch = (int64_t)c.max_tokens * c.hd * g->es;
+  const int64_t head_bytes = (((int64_t)Tmax * c.hd * g->es) + 15) / 16 * 16;   // rows of 16-byte multiples (hd * es is one)
+  if (Tmax > 0)
+    seq_copy_kernel<<<dim3(n, 2 * c.L * c.Hkv), 256, 0, g->s>>>(g->beam_layers, g->beam_pairs, c.Hkv, head_pitch * c.Hkv, head_pitch, head_bytes,
+                                                                  g->hist, g->hist_len, g->ids_cur, c.max_tokens);
+  count_launch(c.device);
+  TSB_TRY(check_launch("seq_copy"));
+  TSB_CUDA(cudaStreamSynchronize(g->s));   // `pairs` is pageable
+  refresh_ragged(g);
+  g->probs_valid = false;
   return 1;
 }
 

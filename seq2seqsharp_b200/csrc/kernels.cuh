@@ -174,6 +174,8 @@ int launch_rope_append(int device, DeviceState* st, int dtype, void* q, const vo
                        int Tmax, int use_rope, double base, const float2* tab, cudaStream_t s);
 int launch_softmax_argmax(int device, DeviceState* st, int* out_ids, float* probs, const float* logits, int B, int V,
                           float temperature, int use_temp, const int* blocked_dev, int n_blocked, cudaStream_t s);
+int launch_beam_topk(int device, DeviceState* st, int* out_ids, float* out_p, float* out_logp, float* probs, int rows, int V, int K,
+                     cudaStream_t s);
 int launch_topp(int device, DeviceState* st, int* out, const float* probs, int rows, int V, float topP, float repeatPenalty,
                 const int* history, const int* history_len, int history_stride, const float* u, void* ws, cudaStream_t s);
 int launch_philox(int device, float* u, int n, uint64_t seed, uint64_t seq_first, uint32_t step, const int* dstep,

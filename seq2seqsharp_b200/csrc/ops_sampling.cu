@@ -885,6 +885,46 @@ int launch_philox(int device, float* u, int n, uint64_t seed, uint64_t seq_first
   return check_launch("philox");
 }
 
+// ------------------------------------------------------------------------------------------------ beam candidates
+// The reference takes the K candidates of a hypothesis by K rounds of (ArgMax, Gather, Log, ScatterFill 0) on the
+// probabilities (Decoder.cs:459-517 `while (beamSearchSize > 0)`): the same here, one CTA per row, the rounds inside the
+// kernel.  probs is changed as the reference changes it (the chosen entries end as 0).  Ties go to the lower index.
+__global__ void __launch_bounds__(1024) beam_topk_kernel(int* __restrict__ out_ids, float* __restrict__ out_p, float* __restrict__ out_logp,
+                                                         float* __restrict__ probs, int V, int K) {
+  __shared__ ValIdx red[32];
+  pdl_trigger();
+  pdl_wait();
+  float* p = probs + (size_t)blockIdx.x * V;
+  for (int k = 0; k < K; ++k) {
+    ValIdx best;
+    best.v = -INFINITY;
+    best.i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      ValIdx c;
+      c.v = p[i];
+      c.i = i;
+      best = better(best, c);
+    }
+    best = block_argmax(best, red);
+    if (threadIdx.x == 0) {
+      out_ids[(size_t)blockIdx.x * K + k] = best.i;
+      out_p[(size_t)blockIdx.x * K + k] = best.v;
+      out_logp[(size_t)blockIdx.x * K + k] = logf(best.v);
+      if (best.i < V) p[best.i] = 0.0f;
+    }
+    __syncthreads();   // the zero is in place (same CTA, global memory) before the next round reads the row
+  }
+}
+
+int launch_beam_topk(int device, DeviceState* st, int* out_ids, float* out_p, float* out_logp, float* probs, int rows, int V, int K,
+                     cudaStream_t s) {
+  (void)st;
+  if (rows == 0 || K == 0) return 1;
+  TSB_CUDA(launch_k(beam_topk_kernel, dim3(rows), dim3(V >= 8192 ? 1024 : 256), 0, s, out_ids, out_p, out_logp, probs, V, K));
+  count_launch(device);
+  return check_launch("beam_topk");
+}
+
 }  // namespace tsb
 
 using namespace tsb;

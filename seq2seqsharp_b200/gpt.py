@@ -391,10 +391,18 @@ class GPT:
                out.ctypes.data_as(C.c_void_p), C.byref(done))
         return out[:, :done.value]
 
+    def BeamSearch(self, tokens, decodingOptions: DecodingOptions):
+        """tokens [B, promptLen] -> `beam.BeamResult`: the BeamSearchSize hypotheses of every prompt in the reference's beam
+        order, each held as a sequence of this engine with its own cache (needs max_batch >= B * BeamSearchSize)."""
+        from .beam import beam_search
+        return beam_search(self, tokens, decodingOptions)
+
     def RunForwardOnSingleDevice(self, tokens, decodingOptions: DecodingOptions, stop_on_eos: bool = True):
         """tokens [B, promptLen] -> generated ids [B, n] with n <= MaxTgtSentLength - promptLen: the loop
         `for (i = promptLen; i < MaxTgtSentLength; i++)` with the all-sequences-ended-with-EOS stop rule
         (GPT.cs:249-304).  Raises TSB200OutOfMemory where the reference returns NetworkResultStatus.OOM."""
+        if decodingOptions.BeamSearchSize > 1:
+            raise ValueError("RunForwardOnSingleDevice returns one hypothesis per prompt; BeamSearch() serves BeamSearchSize > 1")
         ids = np.asarray(tokens, dtype=np.int32)
         B, S = ids.shape
         n_new = decodingOptions.MaxTgtSentLength - S
@@ -438,6 +446,29 @@ class GPT:
         c = self._opts(opts)
         N.call("TSB200_GptStepHost", self._h, ids.ctypes.data_as(C.c_void_p), C.byref(c), out.ctypes.data_as(C.c_void_p))
         return out
+
+    def BeamCandidates(self, K: int, opts: DecodingOptions):
+        """The K best next ids of every sequence after the latest forward, as the reference's beam loop finds them:
+        (ids [sequences, K], probabilities, natural logarithms)."""
+        B = self._B
+        ids = np.zeros((B, K), dtype=np.int32)
+        p = np.zeros((B, K), dtype=np.float32)
+        lp = np.zeros((B, K), dtype=np.float32)
+        c = self._opts(opts)
+        N.call("TSB200_GptBeamCandidates", self._h, int(K), C.byref(c), ids.ctypes.data_as(C.c_void_p), p.ctypes.data_as(C.c_void_p),
+               lp.ctypes.data_as(C.c_void_p))
+        return ids, p, lp
+
+    def BeamCopy(self, src, dst):
+        """Sequence src[i] over sequence dst[i]; a destination equal to the number of sequences adds one."""
+        src = np.ascontiguousarray(src, dtype=np.int32)
+        dst = np.ascontiguousarray(dst, dtype=np.int32)
+        if src.size != dst.size:
+            raise ValueError("BeamCopy: as many sources as destinations")
+        if src.size == 0:
+            return
+        N.call("TSB200_GptBeamCopy", self._h, src.ctypes.data_as(C.c_void_p), dst.ctypes.data_as(C.c_void_p), int(src.size))
+        self._B = max(self._B, int(dst.max()) + 1)
 
     def EnableStepTiming(self, on=True):
         N.call("TSB200_GptEnableStepTiming", self._h, 1 if on else 0)

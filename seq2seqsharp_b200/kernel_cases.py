@@ -4,6 +4,7 @@
     python -m seq2seqsharp_b200.kernel_cases decode [--workload c3_b1] [--steps 2]      (whole decode steps, small model)
     python -m seq2seqsharp_b200.kernel_cases topp   [--rows 8] [--V 32000]
     python -m seq2seqsharp_b200.kernel_cases attention [--B 4] [--H 32] [--Hkv 8] [--hd 64] [--T 16384]
+    python -m seq2seqsharp_b200.kernel_cases beam   [--workload c3_b1] [--B 1] [--beams 4] [--prompt 1024] [--steps 32]
 
 Each case prints its own CUDA-event timing and the algorithmic bytes it moves, so a capture and a plain run can be
 compared.  Device buffers are torch tensors; every kernel is reached through the C ABI.
@@ -126,6 +127,36 @@ def case_decode(a):
     gpt.close()
 
 
+def case_beam(a):
+    """Beam search on a benchmark configuration: wall time per step (a forward of one token per hypothesis, the candidate
+    kernel, the host's selection and the cache copies of that step)."""
+    import time
+    from .beam import beam_search
+    from .configs import CONFIGS, SEED
+    from .gpt import DecodingOptions, DecodingStrategyEnums, GPT
+    from .synthetic import prompt_ids
+    sys.path.insert(0, ".")
+    from bench import WORKLOADS
+    name, _, S, _, _ = WORKLOADS[a.workload]
+    cfg = CONFIGS[name]
+    S = min(S, a.prompt)
+    B, K = a.B, a.beams
+    gpt = GPT(cfg, max_batch=B * K, max_tokens=S + a.steps + 16)
+    gpt.FillSynthetic(SEED, 0.02, 0.0)
+    opts = DecodingOptions(MaxTgtSentLength=S + a.steps, BlockedTokens=[0], BeamSearchSize=K,
+                           DecodingStrategy=DecodingStrategyEnums.GreedySearch)
+    prompts = prompt_ids(SEED, B, S, cfg.V)
+    beam_search(gpt, prompts, DecodingOptions(MaxTgtSentLength=S + 3, BlockedTokens=[0], BeamSearchSize=K))   # warm-up: graphs, scratch
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = beam_search(gpt, prompts, opts)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    print("beam search %s: %d prompts of %d tokens x %d beams, %d steps in %.1f ms (prefill included): %.3f ms/step wall, %d sequence copies" % (
+        a.workload, B, S, K, res.steps, dt * 1e3, dt * 1e3 / max(1, res.steps), res.copies))
+    gpt.close()
+
+
 def case_topp(a):
     from .ops import Ops
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -161,7 +192,7 @@ def case_attention(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemv", "gemv_packed", "decode", "topp", "attention"])
+    ap.add_argument("case", choices=["gemv", "gemv_packed", "decode", "topp", "attention", "beam"])
     ap.add_argument("--norm", type=int, default=0)
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--K", type=int, default=4096)
@@ -181,11 +212,12 @@ def main():
     ap.add_argument("--Hkv", type=int, default=8)
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--T", type=int, default=16384)
+    ap.add_argument("--beams", type=int, default=4)
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("kernel_cases needs a GPU (no CPU fallback)")
     torch.cuda.set_device(0)
-    {"gemv": case_gemv, "gemv_packed": case_gemv_packed, "decode": case_decode, "topp": case_topp, "attention": case_attention}[a.case](a)
+    {"gemv": case_gemv, "gemv_packed": case_gemv_packed, "decode": case_decode, "topp": case_topp, "attention": case_attention, "beam": case_beam}[a.case](a)
 
 
 if __name__ == "__main__":

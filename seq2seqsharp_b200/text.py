@@ -287,9 +287,37 @@ class GptTextRunner:
             out.append(g)
         return out
 
+    def _run_beams(self, token_lists: List[List[str]], prompts: List[List[int]]) -> List[List[List[str]]]:
+        """BeamSearchSize > 1: output[beam][sequence], beams in the reference's order.  Lines of one length share a search
+        while the engine has sequences for all their hypotheses; otherwise the lines are searched one after the other."""
+        from .beam import beam_search
+        K = int(self.opts.BeamSearchSize)
+        out = [[None] * len(prompts) for _ in range(K)]
+        groups: Dict[int, List[int]] = {}
+        for i, p in enumerate(prompts):
+            groups.setdefault(len(p), []).append(i)
+        per_call = max(1, int(getattr(self.gpt, "max_batch", K)) // K)
+        for idxs in groups.values():
+            for at in range(0, len(idxs), per_call):
+                part = idxs[at:at + per_call]
+                res = beam_search(self.gpt, np.asarray([prompts[i] for i in part], dtype=np.int32), self.opts)
+                for k in range(K):
+                    for j, i in enumerate(part):
+                        gen = res.ids[k][j] if k < len(res.ids) else []
+                        out[k][i] = list(token_lists[i]) + self.vocab.ConvertIdsToString(list(gen))
+                        self.stats.new_tokens += len(gen)
+        for beam in out:
+            RemoveDuplicatedEOS(beam)
+        self.stats.lines += len(token_lists)
+        self.stats.prompt_tokens += sum(len(p) for p in prompts)
+        return out
+
     def run_batch(self, token_lists: List[List[str]]) -> List[List[List[str]]]:
-        """token lists (with <s>) -> output[beam = 0][sequence] = prompt words + generated words."""
+        """token lists (with <s>) -> output[beam][sequence] = prompt words + generated words (one beam unless
+        BeamSearchSize > 1)."""
         prompts = self.vocab.GetWordIndex(token_lists)
+        if int(getattr(self.opts, "BeamSearchSize", 1)) > 1:
+            return self._run_beams(token_lists, prompts)
         gen = self._generate(prompts)
         words = self.vocab.ConvertIdsToString([list(g) for g in gen]) if gen else []
         combined = [list(t) + list(w) for t, w in zip(token_lists, words)]

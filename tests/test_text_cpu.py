@@ -170,3 +170,27 @@ def test_runner_respects_max_target_length(tmp_path):
     # a prompt that already fills the limit gets nothing
     out = GptTextRunner(eng, vocab, DecodingOptions(MaxTgtSentLength=2)).run_batch([["<s>", "w8"]])[0]
     assert out == [["<s>", "w8"]]
+
+
+def test_runner_writes_all_beams_of_a_line(tmp_path):
+    from tests.test_beam_cpu import _FakeEngine, _TableModel
+    vocab = Vocab(["w%d" % i for i in range(5, 23)] + ["x"])          # 24 entries
+    model = _TableModel(V=24, seed=5, eos_boost=0.5)
+    eng = _FakeEngine(model, max_batch=4)                              # room for two lines of two beams
+    opts = DecodingOptions(MaxSrcSentLength=16, MaxTgtSentLength=9, BeamSearchSize=2)
+    src = tmp_path / "in.txt"
+    src.write_text("w5 w6\nw7 w8\nw9\n", encoding="utf-8")
+    run = GptTextRunner(eng, vocab, opts)
+    lines = run.Test(str(src), None, batch_size=3)
+    assert len(lines) == 3
+    from seq2seqsharp_b200.beam import beam_search
+    for text, line in zip(["w5 w6", "w7 w8", "w9"], lines):
+        beams = line.split("\t")
+        assert len(beams) == 2
+        words = ["<s>"] + text.split(" ")
+        alone = beam_search(_FakeEngine(model, max_batch=2), [vocab.GetWordIndex([words])[0]], opts)
+        for k, beam in enumerate(beams):
+            want = words + vocab.ConvertIdsToString(alone.ids[k][0])
+            if "</s>" in want:
+                want = want[: want.index("</s>") + 1]
+            assert beam.split(" ") == want
