@@ -261,6 +261,12 @@ typedef struct TSB200GptConfig {
    * m_Router [d,E], m_RouterBias [1,E], m_Whd1 [E*d,4d], m_Whd2 [E*4d,d]}), experts_per_token of them per token.
    * Decoded with one launch per operation; not tensor-parallel.  0 or 1 = off */
   int32_t n_experts, experts_per_token;
+  /* encoder-decoder models (Networks/TransformerDecoder.cs:73-120): cross_attn != 0 gives every layer a second attention
+   * block between self-attention and feed-forward that reads the encoder's output (weights <prefix>.EncAttn_k.{layerNormQ.*,
+   * Q, Qb, K, Kb, V, Vb, W0, b0}, Layers/MultiHeadAttention.cs:434-527); max_src_tokens = capacity of its K/V rows per
+   * sequence.  The encoder output arrives through TSB200_GptSetEncoderOutput.  One launch per operation; not tensor-parallel.
+   * The layer names may then start with "Decoder." instead of "GPTDecoder.". */
+  int32_t cross_attn, max_src_tokens;
 } TSB200GptConfig;
 
 typedef struct TSB200DecodingOptions { /* Seq2SeqSharp/Applications/DecodingOptions.cs:16-39 */
@@ -425,6 +431,13 @@ TSB200_API int TSB200_GptStepHost(void* gpt, const int32_t* last_ids, const TSB2
  *                             of a hypothesis beyond the first take the places of dropped hypotheses; dst[i] == number of
  *                             sequences adds a sequence (used once, after the prefill, to open the beams);
  *   TSB200_GptStepHost        then feeds the chosen id of every hypothesis and runs the next step. */
+/* Encoder output for the cross-attention blocks (cross_attn engines): enc [B, S_src, d] float32 or float16 (host, or
+ * device with on_device != 0), src_lens[B] (host; NULL: all S_src) the unpadded source lengths - keys beyond them are not
+ * attended, as under the reference's source/target mask (Decoder.cs:283, BuildSrcTgtMask).  Computes every layer's K and V
+ * rows once (the reference caches them after the first step, MultiHeadAttention.cs:462-488).  replicas > 1 serves sequence
+ * b + k * B (k < replicas) from source b: the hypotheses of a beam search.  Call after TSB200_GptReset, before the prefill. */
+TSB200_API int TSB200_GptSetEncoderOutput(void* gpt, const void* enc, int dtype, int on_device, const int32_t* src_lens, int B,
+                                          int S_src, int replicas);
 TSB200_API int TSB200_GptBeamCandidates(void* gpt, int K, const TSB200DecodingOptions* opt, int32_t* ids, float* probs,
                                         float* log_probs);
 TSB200_API int TSB200_GptBeamCopy(void* gpt, const int32_t* src, const int32_t* dst, int n);

@@ -36,7 +36,7 @@ class GptConfig(C.Structure):
                                           "attn_type", "dtype")] + \
                [("eps", C.c_float), ("rope_base", C.c_float)] + \
                [(n, C.c_int32) for n in ("ape_decode_pos0", "max_batch", "max_tokens", "device", "tp_rank", "tp_size", "n_experts",
-                                         "experts_per_token")]
+                                         "experts_per_token", "cross_attn", "max_src_tokens")]
 
 
 class DecodingOptionsC(C.Structure):
@@ -159,6 +159,7 @@ def lib():
         "TSB200_GptLastTiming": (i32, [vp, C.POINTER(f32), C.POINTER(i64)]),
         "TSB200_GptStream": (i32, [vp, C.POINTER(vp)]),
         "TSB200_GptStepHost": (i32, [vp, vp, C.POINTER(DecodingOptionsC), vp]),
+        "TSB200_GptSetEncoderOutput": (i32, [vp, vp, i32, i32, vp, i32, i32, i32]),
         "TSB200_GptBeamCandidates": (i32, [vp, i32, C.POINTER(DecodingOptionsC), vp, vp, vp]),
         "TSB200_GptBeamCopy": (i32, [vp, vp, vp, i32]),
         "TSB200_GptEnableStepTiming": (i32, [vp, i32]),

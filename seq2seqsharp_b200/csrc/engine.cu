@@ -108,6 +108,10 @@ struct LayerW {
   // [E, 4d, d], row-major in the model type.  n2_g / n2_b / w1 / w2 are unused there.
   bool moe = false;
   void *moe_g = nullptr, *moe_b = nullptr, *router_w = nullptr, *router_b = nullptr, *moe_w1 = nullptr, *moe_w2 = nullptr;
+  // cross-attention of encoder-decoder models (Layers/MultiHeadAttention.cs:434-527): norm of the query side, Q / K / V / out
+  // projections (packed like the other matrices) and the K / V rows of the encoder output [max_batch, H, max_src_tokens, hd]
+  void *nx_g = nullptr, *nx_b = nullptr, *xq = nullptr, *xqb = nullptr, *xk = nullptr, *xkb = nullptr, *xv = nullptr, *xvb = nullptr;
+  void *xo = nullptr, *xob = nullptr, *xK = nullptr, *xV = nullptr;
 };
 
 struct Dest {  // where a logical tensor lives inside the engine's buffers
@@ -168,6 +172,8 @@ struct Gpt {
   void* hl = nullptr;
   // beam search: candidate scratch [max_batch][kMaxBeam] (ids, probabilities, log probabilities), the table of the layers'
   // cache pointers and the (source, destination) pairs of a sequence copy
+  int* cross_state = nullptr;     // lengths of the encoder outputs in the layout of the step state (flag at [3], lengths from [8])
+  int cross_T = 0;                // longest encoder output of the current call (0: none set)
   int* beam_ids = nullptr;
   float* beam_p = nullptr;
   void** beam_layers = nullptr;   // [2 * L]: K cache, V cache of layer 0, 1, ...
@@ -389,8 +395,11 @@ static int resolve_local(Gpt* g, const std::string& name, Dest* out) {
   if (name == "GPTDecoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
   if (name == "FeedForward_Decoder_0.m_Whd") return setp(g->head_w, d, V, 0, 1);
   if (name == "FeedForward_Decoder_0.m_Bd") return set(g->head_b, 1, V, V, 1);
-  TSB_CHECK(starts_with(name, "GPTDecoder."), "unknown weight name '%s'", name.c_str());
-  const std::string rest = name.substr(11);
+  const bool dec_prefix = c.cross_attn && starts_with(name, "Decoder.");   // TransformerDecoder's own prefix
+  if (dec_prefix && name == "Decoder.layerNorm.m_alpha") return set(g->nf_g, 1, d, d, 1);
+  if (dec_prefix && name == "Decoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
+  TSB_CHECK(starts_with(name, "GPTDecoder.") || dec_prefix, "unknown weight name '%s'", name.c_str());
+  const std::string rest = name.substr(dec_prefix ? 8 : 11);
   const size_t us = rest.find('_'), dot = rest.find('.');
   TSB_CHECK(us != std::string::npos && dot != std::string::npos && us < dot, "unknown weight name '%s'", name.c_str());
   const int k = std::atoi(rest.substr(us + 1, dot - us - 1).c_str());
@@ -414,6 +423,18 @@ static int resolve_local(Gpt* g, const std::string& name, Dest* out) {
       if (field == "V") return setp(L.wqkv, d, KVd, Hd + KVd, 1);
       if (field == "Vb") return set(off(L.bqkv, Hd + KVd), 1, KVd, Nq, 1);
     }
+  } else if (unit == "EncAttn") {
+    TSB_CHECK(c.cross_attn, "'%s': the model has no cross-attention blocks", name.c_str());
+    if (field == "layerNormQ.m_alpha") return set(L.nx_g, 1, d, d, 1);
+    if (field == "layerNormQ.m_beta") return set(L.nx_b, 1, d, d, 1);
+    if (field == "Q") return setp(L.xq, d, Hd, 0, 1);
+    if (field == "Qb") return set(L.xqb, 1, Hd, Hd, 1);
+    if (field == "K") return setp(L.xk, d, Hd, 0, 1);
+    if (field == "Kb") return set(L.xkb, 1, Hd, Hd, 1);
+    if (field == "V") return setp(L.xv, d, Hd, 0, 1);
+    if (field == "Vb") return set(L.xvb, 1, Hd, Hd, 1);
+    if (field == "W0") return setp(L.xo, Hd, d, 0, 1);
+    if (field == "b0") return set(L.xob, 1, d, d, 1);
   } else if (unit == "MoEFFN") {
     TSB_CHECK(L.moe, "'%s': layer %d is not a mixture-of-experts layer", name.c_str(), k);
     const int64_t E = c.n_experts, Fh = 4 * d;
@@ -607,6 +628,7 @@ static int ensure_stack(Gpt* g, int B) {
   g->own_B = 0;
   if (!g->use_stack || g->ragged) return 1;   // sequences of different lengths: one launch per operation
   if (g->c.n_experts > 1) return 1;           // mixture-of-experts layers exist only as separate launches
+  if (g->c.cross_attn) return 1;              // so do the cross-attention blocks
   // tensor-parallel engines: one sequence, and only once the ranks' exchange regions are mapped into each other
   const bool own_tp_ok = g->tp == 1 || (g->xch_ready && g->tp_peer && B == 1 && g->xch_own_off != 0);
   if (g->use_owner && own_tp_ok && B <= g->own_cap && B <= kOwnMaxRows) {
@@ -774,6 +796,16 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
     PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
     TSB_TRY(row_parallel_linear(g, rows, g->attn, L.wo, Hd, L.bo));
+    if (c.cross_attn) {
+      // x += W0 (softmax(Q K^T / sqrt(hd)) V) + b0 with Q from the normed stream, K / V the encoder rows prepared by
+      // TSB200_GptSetEncoderOutput; every new position sees all source positions of its sequence
+      TSB_CHECK(g->cross_T > 0, "decoder step before TSB200_GptSetEncoderOutput");
+      TSB_CHECK(S == 1, "cross-attention engines take one new token per sequence and call (got %d)", S);
+      TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.nx_g, L.nx_b, g->h, L.xq, d, (int)Hd, make_ep(L.xqb, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
+      PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, g->qkv, Hd, L.xK, L.xV, B, 1, c.H, c.H, c.hd, g->cross_T - 1, g->cross_state,
+                                          c.max_src_tokens, attn_pick_splits(g->st, B, c.H, c.H, g->cross_T), g->attn_ws, g->attn_ws_bytes, g->s));
+      TSB_TRY(row_parallel_linear(g, rows, g->attn, L.xo, Hd, L.xob));
+    }
     if (L.moe) {
       // MoEFeedForward.Process: the layer's own LayerNorm (whatever the model's norm type), router, experts, residual add
       PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, g->h, g->x, nullptr, L.moe_g, L.moe_b, 0, c.eps, rows, d, g->s));
@@ -1072,6 +1104,16 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
       G_ALLOC(L.w2, packed_bytes(cc.dtype, (int)F, (int)d)); G_ALLOC(L.b2, d * es);
     }
     G_ALLOC(L.cK, cache_elems * es); G_ALLOC(L.cV, cache_elems * es);
+    if (cc.cross_attn) {
+      G_ALLOC(L.nx_g, d * es); G_ALLOC(L.nx_b, d * es);
+      G_ALLOC(L.xq, packed_bytes(cc.dtype, (int)d, (int)Hd)); G_ALLOC(L.xqb, Hd * es);
+      G_ALLOC(L.xk, packed_bytes(cc.dtype, (int)d, (int)Hd)); G_ALLOC(L.xkb, Hd * es);
+      G_ALLOC(L.xv, packed_bytes(cc.dtype, (int)d, (int)Hd)); G_ALLOC(L.xvb, Hd * es);
+      G_ALLOC(L.xo, packed_bytes(cc.dtype, (int)Hd, (int)d)); G_ALLOC(L.xob, d * es);
+      const int64_t xe = (int64_t)cc.max_batch * cc.H * cc.max_src_tokens * cc.hd;
+      G_ALLOC(L.xK, xe * es); G_ALLOC(L.xV, xe * es);
+      if (!fill_const(g, L.nx_g, d, 1.0f)) return fail();
+    }
     if (!fill_const(g, L.n1_g, d, 1.0f) || !fill_const(g, L.n2_g, d, 1.0f)) return fail();
   }
   if (!fill_const(g, g->nf_g, d, 1.0f)) return fail();
@@ -1091,6 +1133,7 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
   G_ALLOC(g->hist, (int64_t)MB * cc.max_tokens * 4);
   G_ALLOC(g->hist_len, (int64_t)MB * 4);
   G_ALLOC(g->state, (int64_t)(kStateLens + 2 * cc.max_batch) * 4 + 64);
+  if (cc.cross_attn) G_ALLOC(g->cross_state, (int64_t)(kStateLens + 2 * cc.max_batch) * 4 + 64);
   mirror_uniform(g);
   G_ALLOC(g->out_dev, (int64_t)MB * (cc.max_tokens + 1) * 4);
   G_ALLOC(g->blocked, 1024);

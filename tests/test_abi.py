@@ -69,6 +69,6 @@ def test_workspace_queries_need_no_gpu(native):
 
 def test_config_struct_layout_matches_header():
     # field order/size of the ctypes mirrors = the C structs (all 4-byte fields, no padding until the pointers)
-    assert C.sizeof(N.GptConfig) == 22 * 4
+    assert C.sizeof(N.GptConfig) == 24 * 4
     assert C.sizeof(N.Tensor) == 8 + 4 + 4 + 32 + 32
     assert N.DecodingOptionsC.blocked.offset == 16 and N.DecodingOptionsC.seed.offset == 32
