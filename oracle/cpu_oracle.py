@@ -16,7 +16,8 @@ _LIB = os.path.join(_HERE, "liboracle.so")
 class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("L", "d", "H", "Hkv", "hd", "F", "V", "norm_type", "act", "pe_type",
                                           "attn_type")] + [("eps", C.c_float), ("rope_base", C.c_float)] + \
-               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_pos", "faithful_cache", "threads", "n_experts", "experts_per_token")]
+               [(n, C.c_int32) for n in ("ape_decode_pos0", "max_pos", "faithful_cache", "threads", "n_experts", "experts_per_token",
+                                         "cross_attn")]
 
 
 _lib = None
@@ -41,6 +42,8 @@ def lib():
         L.orc_reset.argtypes = [vp]
         L.orc_cache_len.restype = C.c_int
         L.orc_cache_len.argtypes = [vp]
+        L.orc_set_encoder_output.restype = C.c_int
+        L.orc_set_encoder_output.argtypes = [vp, fp, ip, C.c_int, C.c_int]
         L.orc_step.restype = C.c_int
         L.orc_step.argtypes = [vp, ip, C.c_int, C.c_int, C.c_float, ip, C.c_int, fp, fp, fp]
         L.orc_layernorm.argtypes = [fp, fp, fp, fp, C.c_float, C.c_int, C.c_int]
@@ -189,6 +192,7 @@ class OracleGPT:
         c.ape_decode_pos0 = 1 if cfg.ape_decode_pos0 else 0
         c.max_pos, c.faithful_cache, c.threads = max_pos, 1 if faithful_cache else 0, threads
         c.n_experts, c.experts_per_token = getattr(cfg, "expertNum", 1), getattr(cfg, "expertsPerTokenFactor", 1)
+        c.cross_attn = 1 if getattr(cfg, "cross_attn", False) else 0
         self.cfg = cfg
         self._h = lib().orc_create(C.byref(c))
         for name, w in weights.items():
@@ -204,6 +208,14 @@ class OracleGPT:
 
     def reset(self):
         lib().orc_reset(self._h)
+
+    def set_encoder_output(self, enc, src_lens=None):
+        """enc [B, S_src, d]: what the encoder handed to TransformerDecoder.Decode; src_lens: unpadded source lengths."""
+        enc = _c32(enc)
+        B, Ts = enc.shape[0], enc.shape[1]
+        lens = None if src_lens is None else np.ascontiguousarray(src_lens, dtype=np.int32)
+        if not lib().orc_set_encoder_output(self._h, _f(enc), _i(lens) if lens is not None else None, B, Ts):
+            raise RuntimeError("oracle: the model has no cross-attention blocks or the shapes are wrong")
 
     def cache_len(self):
         return int(lib().orc_cache_len(self._h))

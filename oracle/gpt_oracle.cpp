@@ -41,6 +41,7 @@ struct OrcConfig {
   int32_t threads;          // 1 = as the reference's managed SGEMM; >1 = std::thread workers over output columns / heads
   int32_t n_experts;        // > 1: layers 2.. use MoEFeedForward instead of PositionwiseFeedForward (Networks/GPTDecoder.cs:114-123)
   int32_t experts_per_token;
+  int32_t cross_attn;       // 1: TransformerDecoder layers (self-attention, attention over the encoder output, feed-forward: Networks/TransformerDecoder.cs:137-160)
 };
 
 }  // extern "C"
@@ -62,6 +63,10 @@ struct Layer {
   int Tcap = 0;
   // MoEFeedForward (Layers/MoEFeedForward.cs:31-52): its own LayerNorm, experts [E, d, 4d] and [E, 4d, d] without bias, router [d, E] + bias
   vecf moe_g, moe_b, moe_w1, moe_w2, router_w, router_b;
+  // attention over the encoder output (MultiHeadAttention.Perform with three inputs, Layers/MultiHeadAttention.cs:434-527):
+  // its own norm of the query side, Q / K / V / W0, and the projected encoder rows Ks [B*H, hd, Ts], Vs [B*H, Ts, hd]
+  vecf nx_g, nx_b, xKs, xVs;
+  Linear xq, xk, xv, xo;
 };
 
 struct Model {
@@ -71,6 +76,8 @@ struct Model {
   std::vector<Layer> layers;
   int B = 0, T = 0;  // cache batch and length
   int Hc = 0;        // heads held in the cache (H when faithful, Hkv otherwise)
+  int xB = 0, xTs = 0;        // encoder output: sequences and (padded) source length
+  std::vector<int> src_lens;  // unpadded source lengths
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -314,6 +321,11 @@ Linear* find_linear(Model* m, const std::string& name, bool bias) {
     if (field == "K" || field == "Kb") return &L.k;
     if (field == "V" || field == "Vb") return &L.v;
     if (field == "W0" || field == "b0") return &L.o;
+  } else if (unit.compare(0, 7, "EncAttn") == 0) {
+    if (field == "Q" || field == "Qb") return &L.xq;
+    if (field == "K" || field == "Kb") return &L.xk;
+    if (field == "V" || field == "Vb") return &L.xv;
+    if (field == "W0" || field == "b0") return &L.xo;
   } else if (unit.compare(0, 6, "PosFFN") == 0) {
     if (field.compare(0, 17, "feedForwardLayer1") == 0) return &L.w1;
     if (field.compare(0, 17, "feedForwardLayer2") == 0) return &L.w2;
@@ -443,6 +455,35 @@ void attention_block(Model* m, Layer& L, vecf& x, int B, int S, int T0) {
   vecf o;
   affine(o, merged, L.o, M, c.threads);
   for (size_t i = 0; i < x.size(); ++i) x[i] = o[i] + x[i];  // graph.Add(finalAttResults, inputQ)
+}
+
+// MultiHeadAttention.Perform(inputQ, inputK, inputV, keyMask, ...) (Layers/MultiHeadAttention.cs:434-527) with the projected
+// encoder rows taken from the cache the first step leaves (:462-488).  Mask: BuildSrcTgtMask (TensorApplyCPU.cs:1069-1096)
+// adds -30000 to source positions beyond a sequence's unpadded length; the reference builds it only for batches of more than
+// one sequence (Decoder.cs:283) - with one sequence there is no padding, so the rule below covers both.
+void cross_attention_block(Model* m, Layer& L, vecf& x, int B, int S) {
+  const OrcConfig& c = m->c;
+  const int d = c.d, H = c.H, hd = c.hd, M = B * S, Ts = m->xTs;
+  vecf h((size_t)M * d);
+  norm_apply(m, h.data(), x.data(), L.nx_g, L.nx_b, M);
+  vecf yq;
+  affine(yq, h, L.xq, M, c.threads);
+  const float scale = 1.0f / (float)std::sqrt((double)hd);
+  vecf merged((size_t)M * d);
+  parallel_for(B * H, c.threads, [&](int bh) {
+    const int b = bh / H, hh = bh % H;
+    vecf q((size_t)S * hd), sc((size_t)S * Ts, 0.0f), ctx((size_t)S * hd, 0.0f);
+    for (int s = 0; s < S; ++s) std::memcpy(&q[(size_t)s * hd], &yq[((size_t)b * S + s) * d + hh * hd], sizeof(float) * hd);
+    gemm_axpy(sc.data(), q.data(), &L.xKs[(size_t)bh * hd * Ts], S, hd, Ts, scale, 1, hd, Ts, Ts);
+    for (int s = 0; s < S; ++s)
+      for (int t = 0; t < Ts; ++t) sc[(size_t)s * Ts + t] += (t < m->src_lens[b] ? 0.0f : -30000.0f);
+    softmax(sc.data(), sc.data(), S, Ts);
+    gemm_axpy(ctx.data(), sc.data(), &L.xVs[(size_t)bh * Ts * hd], S, Ts, hd, 1.0f, 1, Ts, hd, hd);
+    for (int s = 0; s < S; ++s) std::memcpy(&merged[((size_t)b * S + s) * d + hh * hd], &ctx[(size_t)s * hd], sizeof(float) * hd);
+  });
+  vecf o;
+  affine(o, merged, L.xo, M, c.threads);
+  for (size_t i = 0; i < x.size(); ++i) x[i] = o[i] + x[i];
 }
 
 // PositionwiseFeedForward.Process (Layers/PositionwiseFeedForward.cs:72-98)
@@ -580,6 +621,11 @@ int orc_set_weight(void* h, const char* name_c, const float* data, int rows, int
     if (k < 0 || k >= (int)m->layers.size()) return 0;
     Layer& L = m->layers[k];
     const bool first = name.find(".layerNormQ.") != std::string::npos;
+    if (rest.compare(0, 7, "EncAttn") == 0) {
+      if (ends_with(name, "m_alpha")) return assign(L.nx_g);
+      if (ends_with(name, "m_beta")) return assign(L.nx_b);
+      return 0;
+    }
     if (ends_with(name, "m_alpha")) return assign(first ? L.n1_g : L.n2_g);
     if (ends_with(name, "m_beta")) return assign(first ? L.n1_b : L.n2_b);
     return 0;
@@ -632,6 +678,35 @@ void orc_reset(void* h) {
 
 int orc_cache_len(void* h) { return ((Model*)h)->T; }
 
+// The encoder's output [B, Ts, d] and the unpadded source lengths: every layer's K = Affine(enc, K, Kb) and V likewise,
+// laid out as the reference caches them (Ks [B*H, hd, Ts], Vs [B*H, Ts, hd]; MultiHeadAttention.cs:466-485).
+int orc_set_encoder_output(void* h, const float* enc, const int* src_lens, int B, int Ts) {
+  Model* m = (Model*)h;
+  const OrcConfig& c = m->c;
+  if (!c.cross_attn || B < 1 || Ts < 1) return 0;
+  const int d = c.d, H = c.H, hd = c.hd;
+  m->xB = B;
+  m->xTs = Ts;
+  m->src_lens.assign(B, Ts);
+  if (src_lens) m->src_lens.assign(src_lens, src_lens + B);
+  vecf e(enc, enc + (size_t)B * Ts * d);
+  for (auto& L : m->layers) {
+    vecf yk, yv;
+    affine(yk, e, L.xk, B * Ts, c.threads);
+    affine(yv, e, L.xv, B * Ts, c.threads);
+    L.xKs.assign((size_t)B * H * hd * Ts, 0.0f);
+    L.xVs.assign((size_t)B * H * Ts * hd, 0.0f);
+    for (int b = 0; b < B; ++b)
+      for (int t = 0; t < Ts; ++t)
+        for (int hh = 0; hh < H; ++hh) {
+          const float* kr = &yk[((size_t)b * Ts + t) * d + hh * hd];
+          for (int i = 0; i < hd; ++i) L.xKs[(((size_t)b * H + hh) * hd + i) * Ts + t] = kr[i];
+          std::memcpy(&L.xVs[(((size_t)b * H + hh) * Ts + t) * hd], &yv[((size_t)b * Ts + t) * d + hh * hd], sizeof(float) * hd);
+        }
+  }
+  return 1;
+}
+
 // One forward step — Decoder.GPTDecode (Seq2SeqSharp/Applications/Decoder.cs:648-794) up to the
 // probabilities.  ids is [B, S] row-major (prefill: the whole prompt with an empty cache; decode:
 // S = 1, the last token).  logits/probs are [B, V]; `blocked` ids get probs += -1 (Decoder.cs:744-752).
@@ -660,6 +735,10 @@ int orc_step(void* h, const int* ids, int B, int S, float temperature, const int
   }
   for (int k = 0; k < c.L; ++k) {  // GPTDecoder.Decode (Networks/GPTDecoder.cs:153-191)
     attention_block(m, m->layers[k], x, B, S, T0);
+    if (c.cross_attn) {   // TransformerDecoder.Decode (Networks/TransformerDecoder.cs:150-158)
+      if (m->xB != B || m->xTs <= 0) return 0;
+      cross_attention_block(m, m->layers[k], x, B, S);
+    }
     if (c.n_experts > 1 && k > 1) moe_block(m, m->layers[k], x, M);   // GPTDecoder.cs:116
     else ffn_block(m, m->layers[k], x, M);
   }

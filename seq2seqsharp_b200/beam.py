@@ -211,6 +211,11 @@ def beam_search(gpt, prompts, opts, trace: bool = False) -> BeamResult:
     if int(opts.DecodingStrategy) != 0:
         raise ValueError("beam search runs with DecodingStrategy GreedySearch")
     B, S = prompts.shape
+    cfg = getattr(gpt, "cfg", None)
+    if K > 1 and cfg is not None and int(cfg.pe) == 1 and cfg.ape_decode_pos0:
+        # with a KV cache the reference adds position row 0 to every new token (Decoder.cs:674-677); with beams it has no cache,
+        # re-runs whole texts and so adds each token's own row: an engine that mimics the cached quirk would not match it
+        raise ValueError("beam search on a model with learned/sinusoid position rows needs an engine built with ape_decode_pos0=False")
     if B * K > gpt.max_batch:
         raise ValueError("beam search over %d prompts with %d beams needs max_batch >= %d" % (B, K, B * K))
     res = BeamResult(ids=[], scores=[])

@@ -494,6 +494,15 @@ static std::vector<std::string> weight_names(const Gpt* g, bool biases, bool nor
     }
     add(matrices, a + "W0");
     add(biases, a + "b0");
+    if (c.cross_attn) {
+      const std::string e = "GPTDecoder.EncAttn_" + std::to_string(k) + ".";
+      add(norms, e + "layerNormQ.m_alpha");
+      if (c.norm_type == 0) add(norms, e + "layerNormQ.m_beta");
+      add(matrices, e + "Q"); add(biases, e + "Qb");
+      add(matrices, e + "K"); add(biases, e + "Kb");
+      add(matrices, e + "V"); add(biases, e + "Vb");
+      add(matrices, e + "W0"); add(biases, e + "b0");
+    }
     if (g->L[k].moe) {
       const std::string m = "GPTDecoder.MoEFFN_" + std::to_string(k) + ".";
       add(norms, m + "layerNorm.m_alpha");
@@ -1028,6 +1037,8 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
               "gpt_create: tensor parallel degree %d must divide the query heads (%d), KV heads (%d) and FFN width (%d)", tp, c.H, hkv, c.F);
   }
   TSB_CHECK(c.max_batch > 0 && c.max_batch <= 1024 && c.max_tokens > 0, "gpt_create: bad cache capacity");
+  TSB_CHECK(!c.cross_attn || (c.max_src_tokens > 0 && c.tp_size <= 1 && c.attn_type == 0),
+            "gpt_create: cross-attention engines need max_src_tokens > 0, one GPU and the MultiHeadAttention self-attention of TransformerDecoder");
   if (c.n_experts > 1) {
     TSB_CHECK(tp == 1, "gpt_create: mixture-of-experts models are not served tensor-parallel");
     TSB_CHECK(c.experts_per_token >= 1 && c.experts_per_token <= c.n_experts && c.experts_per_token <= 8 && c.n_experts <= 256,
@@ -2003,6 +2014,74 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
   }
   g->probs_valid = (opt->strategy == 1);
   g->last_launches = g->graph_nodes;
+  return 1;
+}
+
+// K and V rows of the encoder output for every layer's cross-attention block (see the header).
+int TSB200_GptSetEncoderOutput(void* h, const void* enc, int dtype, int on_device, const int32_t* src_lens, int B, int S_src, int replicas) {
+  Gpt* g = (Gpt*)h;
+  TSB_CHECK(g && enc, "gpt_set_encoder_output: null argument");
+  const TSB200GptConfig& c = g->c;
+  TSB_TRY(use_device(c.device, nullptr));
+  TSB_CHECK(c.cross_attn, "gpt_set_encoder_output: the model has no cross-attention blocks");
+  TSB_CHECK(dtype == TSB200_F32 || dtype == TSB200_F16, "gpt_set_encoder_output: unsupported dtype %d", dtype);
+  if (replicas < 1) replicas = 1;
+  TSB_CHECK(B >= 1 && (int64_t)B * replicas <= c.max_batch, "gpt_set_encoder_output: %d sources x %d exceed max_batch %d", B, replicas, c.max_batch);
+  TSB_CHECK(S_src >= 1 && S_src <= c.max_src_tokens, "OOM: encoder output of %d positions exceeds max_src_tokens %d", S_src, c.max_src_tokens);
+  const int64_t rows = (int64_t)B * S_src, d = c.d, Hd = (int64_t)c.H * c.hd;
+  std::vector<int> st((size_t)kStateLens + 2 * c.max_batch, 0);
+  st[0] = S_src - 1;
+  st[kStateRagged] = 1;
+  st[kStateStepsAt] = kStateLens + c.max_batch;
+  for (int r = 0; r < replicas; ++r)
+    for (int b = 0; b < B; ++b) {
+      const int len = src_lens ? src_lens[b] : S_src;
+      TSB_CHECK(len >= 1 && len <= S_src, "gpt_set_encoder_output: source length %d of sequence %d outside 1..%d", len, b, S_src);
+      st[(size_t)kStateLens + r * B + b] = len - 1;   // the attention kernels read "length before the newest key"
+    }
+  TSB_TRY(ensure_act(g, rows));
+  if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }   // the split count of the captured step follows S_src
+  const int64_t bytes = rows * d * (dtype == TSB200_F16 ? 2 : 4);
+  const void* src = enc;
+  void* tmp = nullptr;
+  if (!on_device) {
+    cudaError_t e = cudaMalloc(&tmp, (size_t)bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      TSB_FAIL("OOM: staging buffer of %lld bytes: %s", (long long)bytes, cudaGetErrorString(e));
+    }
+    if (cudaMemcpyAsync(tmp, enc, (size_t)bytes, cudaMemcpyHostToDevice, g->s) != cudaSuccess) {
+      cudaFree(tmp);
+      TSB_FAIL("gpt_set_encoder_output: host to device copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    src = tmp;
+  }
+  auto body = [&]() -> int {
+    TSB_CUDA(cudaMemcpyAsync(g->cross_state, st.data(), st.size() * 4, cudaMemcpyHostToDevice, g->s));
+    Dest dst;
+    dst.base = g->h; dst.rows = rows; dst.cols = d; dst.row_stride = d; dst.col_stride = 1; dst.full_rows = rows; dst.full_cols = d;
+    TSB_TRY(copy_into(g, dst, src, dtype));   // encoder rows in the model's type
+    const int64_t seq_elems = (int64_t)c.H * c.max_src_tokens * c.hd;
+    for (int k = 0; k < c.L; ++k) {
+      LayerW& L = g->L[k];
+      // K = enc Wk + bk, V = enc Wv + bv (the encoder output is not normed here: MultiHeadAttention.cs:453-456)
+      TSB_TRY(engine_linear(g, (int)rows, g->h, nullptr, nullptr, nullptr, nullptr, L.xk, (int)d, (int)Hd, make_ep(L.xkb, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
+      TSB_TRY(engine_linear(g, (int)rows, g->h, nullptr, nullptr, nullptr, nullptr, L.xv, (int)d, (int)Hd, make_ep(L.xvb, nullptr, g->attn, nullptr, TSB200_ACT_NONE, 0)));
+      for (int r = 0; r < replicas; ++r) {
+        void* dK = (char*)L.xK + (size_t)r * B * seq_elems * g->es;
+        void* dV = (char*)L.xV + (size_t)r * B * seq_elems * g->es;
+        // no rotation, no query rows: the rows go to positions 0 .. S_src - 1 of the head-major layout the attention kernels read
+        TSB_TRY(launch_rope_append(c.device, g->st, c.dtype, nullptr, g->qkv, g->attn, Hd, Hd, dK, dV, B, S_src, 0, c.H, c.hd, 0, nullptr,
+                                   c.max_src_tokens, 0, (double)c.rope_base, nullptr, g->s));
+      }
+    }
+    TSB_CUDA(cudaStreamSynchronize(g->s));   // `st` and the staging buffer go away
+    return 1;
+  };
+  const int ok = body();
+  if (tmp) cudaFree(tmp);
+  if (!ok) return 0;
+  g->cross_T = S_src;
   return 1;
 }
 

@@ -82,6 +82,8 @@ class GPTConfig:
     name: str = ""
     expertNum: int = 1              # > 1: layers 2.. use MoEFeedForward (Networks/GPTDecoder.cs:114-123), experts [d, 4d] and [4d, d]
     expertsPerTokenFactor: int = 1  # experts per token (TopK of the router's softmax, Layers/MoEFeedForward.cs:84)
+    cross_attn: bool = False        # TransformerDecoder (Networks/TransformerDecoder.cs): every layer also attends to an encoder's output
+    max_src_tokens: int = 0         # capacity of the encoder output per sequence (cross_attn models)
 
     def is_moe_layer(self, k: int) -> bool:
         return self.expertNum > 1 and k > 1
@@ -111,6 +113,15 @@ class GPTConfig:
                 s[a + "K"], s[a + "Kb"] = (d, KVd), (1, KVd)
                 s[a + "V"], s[a + "Vb"] = (d, KVd), (1, KVd)
             s[a + "W0"], s[a + "b0"] = (Hd, d), (1, d)
+            if self.cross_attn:
+                # MultiHeadAttention without shared QKV (TransformerDecoder.cs:86-92, MultiHeadAttention.cs:76-86)
+                e = "GPTDecoder.EncAttn_%d." % k
+                s[e + "layerNormQ.m_alpha"] = (1, d)
+                if self.norm == NormEnums.LayerNorm:
+                    s[e + "layerNormQ.m_beta"] = (1, d)
+                for n in ("Q", "K", "V"):
+                    s[e + n], s[e + n + "b"] = (d, Hd), (1, Hd)
+                s[e + "W0"], s[e + "b0"] = (Hd, d), (1, d)
             if self.is_moe_layer(k):
                 # MoEFeedForward (Layers/MoEFeedForward.cs:31-52): always LayerNorm; experts without bias; 3-D tensors are
                 # handed over as [E * rows, cols]
@@ -215,6 +226,7 @@ class GPT:
         c.max_batch, c.max_tokens, c.device = max_batch, max_tokens, device_id
         c.tp_rank, c.tp_size = tp_rank, tp_size
         c.n_experts, c.experts_per_token = cfg.expertNum, cfg.expertsPerTokenFactor
+        c.cross_attn, c.max_src_tokens = (1 if cfg.cross_attn else 0), int(cfg.max_src_tokens)
         self.tp_rank, self.tp_size = tp_rank, tp_size
         self._h = C.c_void_p()
         N.call("TSB200_GptCreate", C.byref(c), C.byref(self._h))
@@ -323,6 +335,12 @@ class GPT:
         if ids.ndim != 2:
             raise ValueError("tokens must be [batch, prompt_len] with equal prompt lengths")
         B, S = ids.shape
+        if self.cfg.cross_attn and S > 1:
+            # the cross-attention block takes one new position per call: a longer target prefix goes in token by token
+            out = self.Prefill(ids[:, :1], opts)
+            for s in range(1, S):
+                out = self.StepHost(ids[:, s], opts)
+            return out
         out = np.zeros(B, dtype=np.int32)
         c = self._opts(opts)
         N.call("TSB200_GptPrefill", self._h, ids.ctypes.data_as(C.c_void_p), B, S, C.byref(c),
@@ -446,6 +464,20 @@ class GPT:
         c = self._opts(opts)
         N.call("TSB200_GptStepHost", self._h, ids.ctypes.data_as(C.c_void_p), C.byref(c), out.ctypes.data_as(C.c_void_p))
         return out
+
+    def SetEncoderOutput(self, enc, src_lens=None, replicas: int = 1):
+        """enc [B, S_src, d] (float32 or float16 array): the encoder's output for the sequences to come; src_lens: unpadded
+        source lengths (keys beyond them are not attended).  replicas > 1: sequence b + k * B reads source b (beam search).
+        Computes every layer's cross-attention K and V rows once; stays until the next call."""
+        enc = np.ascontiguousarray(enc)
+        if enc.dtype not in (np.float32, np.float16):
+            enc = enc.astype(np.float32)
+        if enc.ndim != 3 or enc.shape[2] != self.cfg.d:
+            raise ValueError("encoder output must be [batch, source_len, %d]" % self.cfg.d)
+        B, S = enc.shape[0], enc.shape[1]
+        lens = None if src_lens is None else np.ascontiguousarray(src_lens, dtype=np.int32)
+        N.call("TSB200_GptSetEncoderOutput", self._h, enc.ctypes.data_as(C.c_void_p), N.F16 if enc.dtype == np.float16 else N.F32, 0,
+               lens.ctypes.data_as(C.c_void_p) if lens is not None else None, B, S, int(replicas))
 
     def BeamCandidates(self, K: int, opts: DecodingOptions):
         """The K best next ids of every sequence after the latest forward, as the reference's beam loop finds them:
