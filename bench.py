@@ -10,7 +10,7 @@ path), timing is the max over ranks.
 Workloads (synthetic seeded weights and prompts of the named shapes; no dataset is involved):
     c5_b1   Llama-7B-class fp16, B=1,  prompt 512, Top-P 0.95     (headline: latency-bound decode)
     c5_b64  same model, B=64
-    c5_b2 .. c5_b8  same model, B=2, 3, 4, 8 (still one persistent launch per step on the fp16 tensor-core variant)
+    c5_b2 .. c5_b8  same model, B=2, 3, 4, 8 (one launch per operation on the tensor-core streaming linears)
     c3_b1 / c3_b2 / c3_b4 / c3_b8 / c3_b32  Llama-1B-class fp16, prompt 1024, greedy
     c4_b4   the same 1B-class model, B=4, 16384-token prompts, greedy (long-context KV-cache stress)
     c1      tiny fp32 model, B=1, prompt 32, greedy
