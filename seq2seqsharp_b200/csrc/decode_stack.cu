@@ -147,8 +147,16 @@ __device__ __forceinline__ void stack_linear(const StackArgs& a, const StackOp* 
         __threadfence();
         const float* all = a.partials + ((size_t)cur_ct * max_contrib * M) * NT;
         for (int idx = tid; idx < M * NT; idx += 256) {
+          // the slots are read eight at a time (one L2 round trip per batch) and added in slot order
           float v = 0.0f;
-          for (int j = 0; j < n_contrib; ++j) v += __ldcg(all + (size_t)j * M * NT + idx);
+          for (int j0 = 0; j0 < n_contrib; j0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) t[q] = j0 + q < n_contrib ? __ldcg(all + (size_t)(j0 + q) * M * NT + idx) : 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (j0 + q < n_contrib) v += t[q];
+          }
           red[idx] = v;
         }
         consumers_sync();

@@ -583,6 +583,17 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
       return r;
     }
   }
+  if (ng && dt == TSB200_F16 && rows <= 8) {
+    // up to eight rows: the tensor-core streaming kernel norms the rows itself (no norm launch)
+    prof_begin(g);
+    const int r = launch_gemm_stream_mma_norm(dev, g->st, x_resid, ng, c.norm_type == 0 ? nb : nullptr, c.norm_type, c.eps, Wp, rows, K, N, ep,
+                                              g->err_flag, g->pdl, g->lin_ws, g->lin_ws_bytes, g->s);
+    if (r != 2) {
+      g->lin_syms_used = true;
+      prof_end(g, KC_LINEAR);
+      return r;
+    }
+  }
   if (ng) {
     PROF(KC_NORM, launch_norm_residual(dev, g->st, dt, h_tmp, const_cast<float*>(x_resid), nullptr, ng, c.norm_type == 0 ? nb : nullptr,
                                        c.norm_type, c.eps, rows, K, g->s));

@@ -35,6 +35,12 @@ struct GsArgs {
   int M, K, N, KB, CT;
   int stages, max_contrib;
   int prefetch;             // 1: the first ring-full of weight tiles is requested before the wait on the previous kernel
+  // KQ > 0 instantiations: the rows come from the fp32 residual stream and are normed here (no activation tiles by TMA)
+  const float* xres;        // [M][K]
+  const __half* gamma;
+  const __half* beta;       // may be null
+  int norm_type;            // 0 LayerNorm, 1 RMSNorm
+  float eps;
   float* partials;          // [CT][max_contrib][M][256]
   unsigned int* counters;   // [CT], zero on entry, self-resetting
   int* error_flag;
@@ -79,15 +85,24 @@ __device__ __forceinline__ float gs_act(float v, int act) {
   }
 }
 
-template <int NB>  // row blocks of 8: M <= 8 * NB
+// KQ == 0: activation rows arrive as TMA tiles beside every weight tile.  KQ > 0 (NB == 1, K == KQ * 1024, M * KQ <= 16): the
+// rows are read from the fp32 residual stream, normed by the consumer warps (LayerNorm / RMSNorm, the arithmetic of
+// norm_kernel) and kept in shared memory as fp16 for the whole kernel - the norm launch in front of the linear disappears and
+// a stage is the weight tile alone.
+template <int NB, int KQ = 0>  // row blocks of 8: M <= 8 * NB
 __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(const __grid_constant__ CUtensorMap mapX, GsArgs a) {
   constexpr int NT = 256;
+  constexpr bool NORM = KQ > 0;
+  constexpr int STAGE = NORM ? kTileBytes : kGsStageBytes;
+  constexpr int XROW = KQ * 1024 * 2 + 16;   // bytes per normed row: 16 bytes of padding keep the ldmatrix row reads conflict-free
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int S = a.stages;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * kGsStageBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * STAGE);
   uint64_t* empty = full + 16;
+  unsigned char* xs = reinterpret_cast<unsigned char*>(empty + 16);   // NORM: [8][XROW]
   __shared__ int s_err, s_last;
+  __shared__ float s_red[8][16];
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int M = a.M, N = a.N, KB = a.KB;
@@ -114,24 +129,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
       long long issued = 0;
       // The weights do not depend on the previous kernel: the first ring-full of tiles is requested before the wait on it,
       // so the stream starts while that kernel's last CTAs still reduce and store (and while a norm kernel in between runs).
-      const int n_pre = a.prefetch ? min(S, u_end - u_begin) : 0;
+      constexpr unsigned TX = NORM ? kTileBytes : kTileBytes + NB * 8 * 64;
+      const int n_pre = (a.prefetch || NORM) ? min(S, u_end - u_begin) : 0;
       for (int i = 0; i < n_pre; ++i) {
-        mbar_expect_tx(&full[i], kTileBytes + NB * 8 * 64);
-        bulk_g2s(smem + (size_t)i * kGsStageBytes, src + (size_t)i * kTileBytes, kTileBytes, &full[i]);
+        mbar_expect_tx(&full[i], TX);
+        bulk_g2s(smem + (size_t)i * STAGE, src + (size_t)i * kTileBytes, kTileBytes, &full[i]);
       }
-      grid_dep_wait();  // the activation rows come from the previous kernel (read through TMA)
+      if (!NORM) grid_dep_wait();  // the activation rows come from the previous kernel (read through TMA)
       for (int u = u_begin; u < u_end; ++u) {
         if (round > 0 && !mbar_wait(&empty[s], (round - 1u) & 1u)) {
           s_err = 1;
           break;
         }
         if (*(volatile int*)&s_err) break;
-        unsigned char* dst = smem + (size_t)s * kGsStageBytes;
+        unsigned char* dst = smem + (size_t)s * STAGE;
         if (u - u_begin >= n_pre) {
-          mbar_expect_tx(&full[s], kTileBytes + NB * 8 * 64);
+          mbar_expect_tx(&full[s], TX);
           bulk_g2s(dst, src, kTileBytes, &full[s]);
         }
-        gs_tma_load_2d(dst + kTileBytes, &mapX, kb * kKT, 0, &full[s]);  // x = kb * 32 halves: a 64-byte multiple
+        if (!NORM) gs_tma_load_2d(dst + kTileBytes, &mapX, kb * kKT, 0, &full[s]);  // x = kb * 32 halves: a 64-byte multiple
         src += kTileBytes;
         ++issued;
         if (++kb == KB) kb = 0;
@@ -144,7 +160,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
         // stages whose weight tile was requested ahead still lack their activation tile: request it (any k block), so
         // that every copy into this CTA's shared memory has landed before the CTA returns
         for (long long j = issued; j < n_pre; ++j) {
-          gs_tma_load_2d(smem + (size_t)j * kGsStageBytes + kTileBytes, &mapX, 0, 0, &full[(int)j]);
+          if (!NORM) gs_tma_load_2d(smem + (size_t)j * STAGE + kTileBytes, &mapX, 0, 0, &full[(int)j]);
           ++issued;
         }
         const long long first = issued > S ? issued - S : 0;
@@ -156,6 +172,98 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
     return;
   }
   grid_dep_wait();  // consumers touch the scratch slots, counters and the residual rows of earlier kernels
+
+  if constexpr (NORM) {
+    // ---- norm of the M rows: thread t holds float4 t, t + 256, ... of every row (one round of loads), two block reductions
+    constexpr int R = 16 / KQ < 8 ? 16 / KQ : 8;   // rows a thread can hold
+    constexpr int K = KQ * 1024;
+    const int M_ = a.M;
+    float4 v[R][KQ];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < KQ; ++j)
+        v[r][j] = r < M_ ? __ldcg(reinterpret_cast<const float4*>(a.xres + (size_t)r * K) + tid + 256 * j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    auto reduce_rows = [&](float* part) {   // part[R] per thread -> totals over the 256 consumer threads, in every thread
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part[r] += __shfl_xor_sync(0xffffffffu, part[r], o);
+      gs_consumers_sync();
+      if (lane == 0)
+#pragma unroll
+        for (int r = 0; r < R; ++r) s_red[w][r] = part[r];
+      gs_consumers_sync();
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float t = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) t += s_red[q][r];
+        part[r] = t;
+      }
+    };
+    float sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      sum[r] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < KQ; ++j)
+        sum[r] += a.norm_type == 0 ? (v[r][j].x + v[r][j].y) + (v[r][j].z + v[r][j].w)
+                                   : (v[r][j].x * v[r][j].x + v[r][j].y * v[r][j].y) + (v[r][j].z * v[r][j].z + v[r][j].w * v[r][j].w);
+    }
+    reduce_rows(sum);
+    float shift[R], inv[R];
+    if (a.norm_type == 0) {
+      float sq[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        shift[r] = sum[r] / K;
+        sq[r] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < KQ; ++j) {
+          const float e0 = v[r][j].x - shift[r], e1 = v[r][j].y - shift[r], e2 = v[r][j].z - shift[r], e3 = v[r][j].w - shift[r];
+          sq[r] += (e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3);
+        }
+      }
+      reduce_rows(sq);
+#pragma unroll
+      for (int r = 0; r < R; ++r) inv[r] = sqrtf(a.eps + sq[r] / K);
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        shift[r] = 0.0f;
+        inv[r] = sqrtf(sum[r] / (float)K + a.eps);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < KQ; ++j) {
+      const int c4 = tid + 256 * j;   // float4 index inside a row
+      const __half2 g01 = reinterpret_cast<const __half2*>(a.gamma)[2 * c4], g23 = reinterpret_cast<const __half2*>(a.gamma)[2 * c4 + 1];
+      __half2 b01 = __floats2half2_rn(0.0f, 0.0f), b23 = b01;
+      if (a.beta) {
+        b01 = reinterpret_cast<const __half2*>(a.beta)[2 * c4];
+        b23 = reinterpret_cast<const __half2*>(a.beta)[2 * c4 + 1];
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        uint2 out = make_uint2(0u, 0u);   // rows beyond M are zero rows of the 8-row operand
+        if (r < R && r < M_) {
+          const int rr = r < R ? r : 0;
+          float t0 = __low2float(g01) * ((v[rr][j].x - shift[rr]) / inv[rr]), t1 = __high2float(g01) * ((v[rr][j].y - shift[rr]) / inv[rr]);
+          float t2 = __low2float(g23) * ((v[rr][j].z - shift[rr]) / inv[rr]), t3 = __high2float(g23) * ((v[rr][j].w - shift[rr]) / inv[rr]);
+          if (a.beta) {
+            t0 += __low2float(b01); t1 += __high2float(b01);
+            t2 += __low2float(b23); t3 += __high2float(b23);
+          }
+          const __half2 h01 = __floats2half2_rn(t0, t1), h23 = __floats2half2_rn(t2, t3);
+          out.x = *reinterpret_cast<const uint32_t*>(&h01);
+          out.y = *reinterpret_cast<const uint32_t*>(&h23);
+        }
+        *reinterpret_cast<uint2*>(xs + (size_t)r * XROW + (size_t)c4 * 8) = out;
+      }
+    }
+    gs_consumers_sync();
+  }
 
   // ---------------- consumer warps: warp w owns columns [w*32, w*32+32) of every tile
   const int chunk = w >> 1, hf = w & 1;
@@ -184,14 +292,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
       s_err = 1;
       dead = true;
     }
-    const uint32_t wbase = smem_u32(smem + (size_t)s * kGsStageBytes) + chunk * 4096;
-    const uint32_t xbase = smem_u32(smem + (size_t)s * kGsStageBytes + kTileBytes);
-    // activation fragments of all row blocks: [rows][32 k] with 64-byte rows, 16-byte chunks XOR-ed with (row / 2) & 3
+    const uint32_t wbase = smem_u32(smem + (size_t)s * STAGE) + chunk * 4096;
     uint32_t bf[NB][4];
+    if constexpr (NORM) {
+      // the normed rows stay in place: row xr, the four 16-byte chunks of k tile kb
+      gs_ldmatrix_x4(smem_u32(xs) + xr * XROW + kb * 64 + (xc << 4), bf[0][0], bf[0][1], bf[0][2], bf[0][3]);
+    } else {
+      const uint32_t xbase = smem_u32(smem + (size_t)s * STAGE + kTileBytes);
+      // activation fragments of all row blocks: [rows][32 k] with 64-byte rows, 16-byte chunks XOR-ed with (row / 2) & 3
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      const int n = nb * 8 + xr;
-      gs_ldmatrix_x4(xbase + n * 64 + ((xc ^ ((n >> 1) & 3)) << 4), bf[nb][0], bf[nb][1], bf[nb][2], bf[nb][3]);
+      for (int nb = 0; nb < NB; ++nb) {
+        const int n = nb * 8 + xr;
+        gs_ldmatrix_x4(xbase + n * 64 + ((xc ^ ((n >> 1) & 3)) << 4), bf[nb][0], bf[nb][1], bf[nb][2], bf[nb][3]);
+      }
     }
 #pragma unroll
     for (int kk = 0; kk < 2; ++kk) {
@@ -537,11 +650,11 @@ static GsEncodeTiledFn gs_get_encode() {
   return fn;
 }
 
-template <int NB>
+template <int NB, int KQ = 0>
 static int gs_launch(int device, const CUtensorMap& mapX, const GsArgs& a, int grid, size_t smem, bool pdl, cudaStream_t s) {
   static bool attr_done[kMaxDevices] = {};
   if (!attr_done[device]) {
-    TSB_CUDA(cudaFuncSetAttribute(gemm_stream_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    TSB_CUDA(cudaFuncSetAttribute(gemm_stream_mma_kernel<NB, KQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr_done[device] = true;
   }
   cudaLaunchConfig_t cfg{};
@@ -554,7 +667,7 @@ static int gs_launch(int device, const CUtensorMap& mapX, const GsArgs& a, int g
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
-  TSB_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_mma_kernel<NB>, mapX, a));
+  TSB_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_mma_kernel<NB, KQ>, mapX, a));
   count_launch(device);
   return 1;
 }
@@ -723,6 +836,59 @@ int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const voi
     case 2: return gs_launch<2>(device, mapX, a, (int)g, smem, pdl, s);
     case 4: return gs_launch<4>(device, mapX, a, (int)g, smem, pdl, s);
     default: return gs_launch<8>(device, mapX, a, (int)g, smem, pdl, s);
+  }
+}
+
+// y = epilogue(norm(x32[M,K]) * W[K,N]) in one launch, for up to 8 rows of a fp16 model whose width is 1024, 2048 or 4096
+// (M * K <= 16384): the consumer warps norm the rows themselves.  1 ok, 0 error, 2 shape not handled (the caller runs the
+// norm kernel and the plain linear).
+int launch_gemm_stream_mma_norm(int device, DeviceState* st, const float* x32, const void* gamma, const void* beta, int norm_type, float eps,
+                                const void* Wp, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws, int64_t ws_bytes,
+                                cudaStream_t s) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("TSB200_GEMM_FUSED_NORM");  // "0": a norm launch in front of every linear (A/B measurements)
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (!enabled || !gamma) return 2;
+  if (K != 1024 && K != 2048 && K != 4096) return 2;
+  const int KQ = K / 1024;
+  if (M < 1 || M > 8 || M * KQ > 16 || ((uintptr_t)x32 % 16) != 0 || ((uintptr_t)Wp % 16) != 0 || ((uintptr_t)gamma % 4) != 0 ||
+      (beta && ((uintptr_t)beta % 4) != 0))
+    return 2;
+  GsArgs a{};
+  a.Wp = reinterpret_cast<const unsigned char*>(Wp);
+  a.M = M; a.K = K; a.N = N;
+  a.KB = (K + kKT - 1) / kKT;
+  a.CT = (N + 255) / 256;
+  const long long U = (long long)a.KB * a.CT;
+  long long g = st->sm_count;
+  if (g > U) g = U;
+  a.max_contrib = (int)(a.KB / (U / g)) + 2;
+  const size_t xs_bytes = (size_t)8 * ((size_t)K * 2 + 16);
+  const size_t fixed = 32 * sizeof(uint64_t) + 1024 + 128 + xs_bytes;
+  int stages = (int)((225 * 1024 - fixed) / kTileBytes);
+  if (stages > 16) stages = 16;
+  if (stages < 4) return 2;
+  a.stages = stages;
+  a.prefetch = 1;
+  a.xres = x32;
+  a.gamma = reinterpret_cast<const __half*>(gamma);
+  a.beta = reinterpret_cast<const __half*>(beta);
+  a.norm_type = norm_type;
+  a.eps = eps;
+  const int64_t need = kWsCounterBytes + (int64_t)a.CT * a.max_contrib * M * 256 * 4;
+  if (!ws || ws_bytes < need) return 2;
+  a.counters = reinterpret_cast<unsigned int*>(ws);
+  a.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + kWsCounterBytes);
+  a.error_flag = error_flag;
+  a.ep = ep;
+  CUtensorMap none{};   // unused by these instantiations
+  const size_t smem = fixed + (size_t)stages * kTileBytes;
+  switch (KQ) {
+    case 1: return gs_launch<1, 1>(device, none, a, (int)g, smem, pdl, s);
+    case 2: return gs_launch<1, 2>(device, none, a, (int)g, smem, pdl, s);
+    default: return gs_launch<1, 4>(device, none, a, (int)g, smem, pdl, s);
   }
 }
 

@@ -156,6 +156,9 @@ int launch_gemm_stream_tc(int device, DeviceState* st, const void* x, const void
                           int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_stream_tc_workspace_bytes(int M, int K, int N, int sm_count);
 int stc_take_error();
+int launch_gemm_stream_mma_norm(int device, DeviceState* st, const float* x32, const void* gamma, const void* beta, int norm_type, float eps,
+                                const void* Wp, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws, int64_t ws_bytes,
+                                cudaStream_t s);
 int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
                            int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count);
