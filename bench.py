@@ -19,7 +19,8 @@ With N > 1 the 7B-class workloads (c5_*) run ONE model tensor-parallel over the 
 tokens/s of the one sharded model); the other workloads run N batch-sharded replicas (weak scaling).  `--parallelism`
 overrides.  After the timed region the benchmarked engine is checked against an independent engine (one GPU, one launch
 per operation) fed the same ids (`parity_check`; the run fails above the dtype's logit tolerance), and on one GPU a
-`secondary` block reports the large-batch decode and prefill figures the metric also names.
+`secondary` block reports the large-batch decode and prefill figures the metric also names, a small batch, the long-context
+configuration and a batch of sequences of different lengths.
 """
 import argparse
 import json
@@ -611,6 +612,8 @@ def run_b200(args):
         line["secondary"] = {
             "c5_b64": measure_secondary(local, "c5_llama7b_fp16", 64, 512, "topp", 0.95, want_prefill=True),
             "c3_b32": measure_secondary(local, "c3_llama1b_fp16", 32, 1024, "greedy", 1.0),
+            "c5_b4": measure_secondary(local, "c5_llama7b_fp16", 4, 512, "topp", 0.95),
+            "c4_b4": measure_secondary(local, "c4_llama1b_longctx_fp16", 4, 16384, "greedy", 1.0, want_prefill=True),
             "c5_mixed_b4": measure_mixed_batch(local, "c5_llama7b_fp16", [512, 384, 256, 128]),
         }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -191,7 +191,8 @@ TSB200_API int TSB200_PackWeight(int device, int dtype, void* packed, const void
                                  void* stream);
 /* y = act(bias + prologue(x) Wp) (+ residual) on packed weights.  norm_type -1: x [M,K] in `dtype`; 0 / 1: the input
  * is the fp32 residual stream x_f32 [M,K] and LayerNorm / RMSNorm (gamma, beta, eps) is applied first, fused into the
- * kernel (M <= 4 only).  M <= 4 runs the TMA-fed streaming GEMV; larger M the fallback kernels.  Replaces
+ * kernel (M <= 4; fp16 models of width 1024 / 2048 / 4096 also for M <= 8 while M * width <= 16384, in the tensor-core
+ * streaming kernel).  M <= 4 runs the TMA-fed streaming GEMV; larger M the tensor-core streaming kernels.  Replaces
  * LayerNorm/RMSNorm + Affine + activation/gate/residual of one layer (PositionwiseFeedForward.cs:72-98,
  * MultiHeadAttention.cs:130-137,234-237). */
 TSB200_API int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N);

@@ -550,7 +550,7 @@ int64_t TSB200_LinearPackedWorkspaceBytes(int dtype, int M, int K, int N) {
   int64_t b = linear_workspace_bytes(M, K, N);
   const int64_t c = dtype == TSB200_F16 && M > 16 ? gemm_tc_workspace_bytes(M, N, 132) : 0;
   if (c > b) b = c;
-  const int64_t d = dtype == TSB200_F16 && M > 4 && M <= 64 ? gemm_stream_mma_workspace_bytes(M, K, N, 132) : 0;
+  const int64_t d = dtype == TSB200_F16 && M >= 1 && M <= 64 ? gemm_stream_mma_workspace_bytes(M, K, N, 132) : 0;
   if (d > b) b = d;
   const int64_t e = dtype == TSB200_F16 && M > 16 && M <= 64 ? gemm_stream_tc_workspace_bytes(M, K, N, 160) : 0;
   if (e > b) b = e;
@@ -582,12 +582,24 @@ int TSB200_LinearPacked(int device, int dtype, void* y, float* y_f32, const void
   const int64_t z = workspace_bytes < kWsCounterBytes ? workspace_bytes : kWsCounterBytes;
   TSB_CUDA(cudaMemsetAsync(workspace, 0, (size_t)z, s));
   int* err = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + kWsCounterBytes - 256);
-  if (M <= 4) {
+  static int gemv_rows = -1;
+  if (gemv_rows < 0) {
+    const char* e = getenv("TSB200_GEMV_MAXROWS");  // rows served by the FMA streaming GEMV here (default 4; the engine has its own default)
+    gemv_rows = e ? atoi(e) : 4;
+  }
+  if (M <= 4 && M <= gemv_rows) {
     const int r = launch_gemv_stream(device, st, dtype, Wp, norm_type < 0 ? x : (const void*)x_f32, norm_type < 0 ? 0 : (norm_type == 0 ? 2 : 1),
                                      gamma, norm_type == 0 ? beta : nullptr, eps, M, K, N, ep, err, false, workspace, workspace_bytes - 256, s);
     if (r != 2) return r;
   }
-  TSB_CHECK(norm_type < 0, "linear_packed: the norm prologue is only fused for M <= 4; normalise separately for larger M");
+  if (norm_type >= 0 && dtype == TSB200_F16 && M <= 8) {
+    // up to eight rows of a fp16 model of width 1024 / 2048 / 4096: the tensor-core streaming kernel norms the rows itself
+    const int r = launch_gemm_stream_mma_norm(device, st, x_f32, gamma, norm_type == 0 ? beta : nullptr, norm_type, eps, Wp, M, K, N, ep, err, false,
+                                              workspace, workspace_bytes - 256, s);
+    if (r != 2) return r;
+  }
+  TSB_CHECK(norm_type < 0, "linear_packed: the norm prologue is fused for M <= 4 (and for M <= 8 on fp16 models of width 1024 / 2048 / 4096 "
+                           "with M * width <= 16384); normalise separately otherwise");
   return launch_linear(device, st, dtype, x, Wp, M, K, N, ep, workspace, workspace_bytes - 256, s, true);
 }
 

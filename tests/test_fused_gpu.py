@@ -300,3 +300,37 @@ def test_linear_packed_tensor_core_gemm(cuda, oracle, M, K, Nn):
         np.testing.assert_allclose(host(linear_packed(x, W, b, N.ACT_SWIGLU, dtype=dtype)), oracle.act(a, 1) * g, atol=tol * scale * scale)
     first = host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype))
     np.testing.assert_array_equal(host(linear_packed(x, W, b, N.ACT_NONE, dtype=dtype)), first)
+
+
+@pytest.mark.parametrize("M,K,N,norm", [(5, 2048, 3072, 1), (8, 2048, 512, 0), (8, 1024, 777, 1), (4, 4096, 6144, 1), (3, 4096, 1000, 0)])
+def test_linear_packed_norms_up_to_eight_rows_in_the_tensor_core_kernel(cuda, oracle, M, K, N, norm, monkeypatch):
+    """fp16, width 1024 / 2048 / 4096, M * width <= 16384: LayerNorm / RMSNorm of the fp32 rows inside the tensor-core
+    streaming kernel (no norm launch), against the oracle's norm + affine."""
+    from seq2seqsharp_b200 import _native as N_
+    from seq2seqsharp_b200.ops import Ops
+    import torch
+    monkeypatch.setenv("TSB200_GEMV_MAXROWS", "0")      # read once per process: only effective if this test is the first caller
+    rng = np.random.default_rng(M * 1000 + N)
+    x32 = (rng.standard_normal((M, K)) * 1.5 + 0.3).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * 0.03).astype(np.float16)
+    gamma = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    beta = (0.1 * rng.standard_normal(K)).astype(np.float16)
+    bias = (0.1 * rng.standard_normal(N)).astype(np.float16)
+    nd = N_.F16
+    dev = lambda a: torch.from_numpy(a).cuda()
+    Wd, xd, gd, bd, biasd = dev(W), dev(x32), dev(gamma), dev(beta), dev(bias)
+    pb = N_.lib().TSB200_PackedWeightBytes(nd, K, N)
+    Wp = torch.zeros(pb, dtype=torch.uint8, device="cuda")
+    N_.call("TSB200_PackWeight", 0, nd, Wp.data_ptr(), Wd.data_ptr(), nd, K, N, None)
+    y = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    wsb = N_.lib().TSB200_LinearPackedWorkspaceBytes(nd, M, K, N)
+    ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+    N_.call("TSB200_LinearPacked", 0, nd, y.data_ptr(), None, None, xd.data_ptr(), gd.data_ptr(), bd.data_ptr() if norm == 0 else None, norm, 1e-6,
+            Wp.data_ptr(), biasd.data_ptr(), None, M, K, N, N_.ACT_NONE, ws.data_ptr(), wsb, None)
+    torch.cuda.synchronize()
+    g32, b32 = gamma.astype(np.float32), beta.astype(np.float32)
+    h = oracle.layernorm(x32, g32, b32, 1e-6) if norm == 0 else oracle.rmsnorm(x32, g32, None, 1e-6)
+    h = h.astype(np.float16).astype(np.float32)
+    want = h @ W.astype(np.float32) + bias.astype(np.float32)
+    got = y.cpu().numpy().astype(np.float32)
+    assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
