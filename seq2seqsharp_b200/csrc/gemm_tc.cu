@@ -692,7 +692,10 @@ int launch_gemm_tc(int device, DeviceState* st, const void* x, const void* Wp, i
   {
     const int64_t tiles = (int64_t)grid.x * grid.y;
     const int k_total = (K + kBK - 1) / kBK;
-    if (tiles < st->sm_count && k_total >= 8 && ws) {
+    // Only with a single row tile: from two row tiles on (M > 128) the tiles of a weight column block already share its
+    // columns through L2 and the K slices' partial sums cost more than the idle SMs (512 x 4096 x 4096: 59.7 us with two
+    // slices, 39.9 us without; 256 x 4096 x 6144: 79.8 against 41.4 us).
+    if (tiles < st->sm_count && grid.y == 1 && k_total >= 8 && ws) {
       // about 1.5 CTAs per SM (two fit); every extra K slice costs the last arriver another partial to add
       int ks = (int)((3 * st->sm_count / 2 + tiles - 1) / tiles);
       if (ks > k_total / 4) ks = k_total / 4;
