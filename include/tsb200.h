@@ -437,7 +437,8 @@ TSB200_API int TSB200_GptStepHost(void* gpt, const int32_t* last_ids, const TSB2
  * attended, as under the reference's source/target mask (Decoder.cs:283, BuildSrcTgtMask).  Computes every layer's K and V
  * rows once (the reference caches them after the first step, MultiHeadAttention.cs:462-488).  replicas > 1 serves sequence
  * b + k * B (k < replicas) from source b: the hypotheses of a beam search.  Stays in place (TSB200_GptReset included) until
- * the next call. */
+ * the next call.  Engines with cross-attention take one new position per sequence and call: TSB200_GptPrefill with S = 1
+ * (<s>), then TSB200_GptDecode / TSB200_GptStepHost; a longer target prefix is fed through TSB200_GptStepHost. */
 TSB200_API int TSB200_GptSetEncoderOutput(void* gpt, const void* enc, int dtype, int on_device, const int32_t* src_lens, int B,
                                           int S_src, int replicas);
 TSB200_API int TSB200_GptBeamCandidates(void* gpt, int K, const TSB200DecodingOptions* opt, int32_t* ids, float* probs,

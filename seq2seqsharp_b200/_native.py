@@ -10,7 +10,8 @@ import os
 import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtsb200.so")
+# TSB200_LIB: another build of the library (e.g. libtsb200_checked.so from `python -m seq2seqsharp_b200.build --checked`)
+LIB_PATH = os.environ.get("TSB200_LIB") or os.path.join(_HERE, "libtsb200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "tsb200.h")
 
 F32, F16, F64, I32, U8 = 0, 1, 2, 3, 4

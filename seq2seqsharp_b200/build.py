@@ -1,6 +1,6 @@
 """Builds libtsb200.so (sm_100a only) from seq2seqsharp_b200/csrc with nvcc, in-tree.
 
-Usage: python -m seq2seqsharp_b200.build [--force] [--verbose]
+Usage: python -m seq2seqsharp_b200.build [--force] [--verbose] [--checked]
 """
 import hashlib
 import os
@@ -35,13 +35,28 @@ def _stamp():
     return h.hexdigest()
 
 
-def build(force=False, verbose=False):
+VARIANTS = {
+    "": [],
+    # device-side index / capacity checks that record a code and skip the access (see kernels.cuh), for bring-up and bug hunts
+    "checked": ["-DTSB200_CHECKED"],
+}
+
+
+def lib_path(variant=""):
+    return LIB if not variant else os.path.join(HERE, "libtsb200_%s.so" % variant)
+
+
+def build(force=False, verbose=False, variant=""):
+    """variant "": the product library; "checked": libtsb200_checked.so with -DTSB200_CHECKED (objects in build/checked)."""
+    vflags = VARIANTS[variant]
+    OBJ = os.path.join(HERE, "build", variant) if variant else globals()["OBJ"]
+    LIB = lib_path(variant)
     os.makedirs(OBJ, exist_ok=True)
     stamp_file = os.path.join(OBJ, "stamp")
-    stamp = _stamp()
+    stamp = _stamp() + " ".join(vflags)
     if not force and os.path.exists(LIB) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp:
         return LIB
-    extra = ["-Xptxas", "-v"] if verbose else []
+    extra = (["-Xptxas", "-v"] if verbose else []) + vflags
 
     def compile_one(src):
         obj = os.path.join(OBJ, src[:-3] + ".o")
@@ -65,4 +80,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, variant="checked" if "--checked" in sys.argv else ""))

@@ -20,8 +20,23 @@
 
 #include "decode_owner.cuh"
 #include "kernels.cuh"
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges cost a pointer test unless a profiler has injected itself
 
 namespace tsb {
+
+// NVTX range for the lifetime of the object: every engine entry point and the phases of a forward pass carry one, so a
+// timeline (Nsight Systems) shows prefill / decode / step / cache and beam operations by name.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+
+TSB_CHECKED_WORD(engine)
+#ifndef TSB200_CHECKED
+int chk_take_engine() { return 0; }
+#endif
 
 template <typename T>
 __global__ void embed_kernel(float* x, const T* E, const T* PE, const int* ids,
@@ -31,10 +46,12 @@ __global__ void embed_kernel(float* x, const T* E, const T* PE, const int* ids,
   pdl_wait();
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     int id = ids[r];
+    TSB_DEV_CHECK(engine, id >= 0 && id < V, 0x101, (void)0)          // token id outside the vocabulary (the row is embedded as id 0)
     if (id < 0 || id >= V) id = 0;
     const int s = r % S;
     const int T0 = state_len(dT0, r / S, T0_arg);
     int pos = (pe_mode == 1) ? s : T0 + s;  // pe_mode 1: the reference peeks APE rows [0, S) (PositionEmbedding.cs:30-33)
+    TSB_DEV_CHECK(engine, pe_mode == 0 || pos < pe_rows, 0x102, (void)0)   // position beyond the position table (clamped)
     if (pos >= pe_rows) pos = pe_rows - 1;
     const T* e = E + (int64_t)id * d;
     const T* p = (pe_mode != 0) ? PE + (int64_t)pos * d : nullptr;
@@ -73,6 +90,7 @@ __global__ void commit_kernel(int* ids_cur, const int* ids_new, int* hist,
     out[(int64_t)slot * B + b] = id;
     if (fin) continue;
     const int l = hist_len[b];
+    TSB_DEV_CHECK(engine, l >= 0 && l < hist_stride, 0x103, (void)0)   // token history full (the id is not recorded)
     if (l < hist_stride) hist[(int64_t)b * hist_stride + l] = id;
     hist_len[b] = l + 1;
     if (ragged) {
@@ -286,6 +304,7 @@ constexpr int kMaxBeam = 32;
 __global__ void __launch_bounds__(256) seq_copy_kernel(void* const* layers, const int* pairs, int Hkv, int64_t seq_bytes, int64_t head_pitch,
                                                        int64_t head_bytes, int* hist, int* hist_len, int* ids_cur, int hist_stride) {
   const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+  TSB_DEV_CHECK(engine, src >= 0 && dst >= 0 && src != dst && head_bytes <= head_pitch, 0x104, return)   // bad pair or rows beyond the cache
   const int lw = blockIdx.y / Hkv, kvh = blockIdx.y % Hkv;
   unsigned char* base = reinterpret_cast<unsigned char*>(layers[lw]);
   const uint4* from = reinterpret_cast<const uint4*>(base + (size_t)src * seq_bytes + (size_t)kvh * head_pitch);
@@ -757,6 +776,7 @@ static int ensure_stack(Gpt* g, int B) {
 // One forward pass over `rows = B*S` new tokens whose ids are in g->ids_in; leaves logits [B,V] in g->logits.
 // With use_state the cache length is read from g->state[0] by the kernels (graph replay), else from T0.
 static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int splits) {
+  NvtxRange nvtx_(S == 1 ? "tsb200.forward.step" : "tsb200.forward.prompt");
   PdlScope pdl_scope(g->pdl && S == 1);
   const TSB200GptConfig& c = g->c;
   const int dev = c.device, dt = c.dtype, d = c.d, rows = B * S;
@@ -886,6 +906,15 @@ static int check_err_flag(Gpt* g, const int* pre = nullptr) {
     g->lin_syms_used = false;
   }
   if (g->tp > 1) e |= comm_peer_take_error();
+#ifdef TSB200_CHECKED
+  {
+    int c = chk_take_engine();
+    if (!c) c = chk_take_attention();
+    if (!c) c = chk_take_moe();
+    if (!c) c = chk_take_sampling();
+    TSB_CHECK(c == 0, "checked build: device-side check 0x%x failed (an index or a capacity was out of range; the access was skipped)", c);
+  }
+#endif
   if (e) {
     cudaMemset(g->err_flag, 0, 2 * sizeof(int));
     if (g->stack_counters) cudaMemset(g->stack_counters, 0, (size_t)g->stack_counter_bytes);  // a kernel that gave up leaves them mid-count
@@ -1214,6 +1243,7 @@ int TSB200_GptDestroy(void* h) {
 }
 
 int TSB200_GptSetWeight(void* h, const char* name, const void* data, int dtype, int64_t rows, int64_t cols, int on_device) {
+  NvtxRange nvtx_("tsb200.gpt.set_weight");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && name && data, "gpt_set_weight: null argument");
   TSB_CHECK(dtype == TSB200_F32 || dtype == TSB200_F16, "gpt_set_weight: data must be F32 or F16");
@@ -1483,6 +1513,7 @@ static int run_prompt(Gpt* g, const int32_t* ids, int B, int S, const TSB200Deco
 extern "C" {
 
 int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  NvtxRange nvtx_("tsb200.gpt.prefill");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && ids && opt, "gpt_prefill: null argument");
   TSB_TRY(use_device(g->c.device, nullptr));
@@ -1491,6 +1522,7 @@ int TSB200_GptPrefill(void* h, const int32_t* ids, int B, int S, const TSB200Dec
 
 int TSB200_GptPrefillRagged(void* h, const int32_t* ids, const int32_t* lens, int B, int S, const TSB200DecodingOptions* opt,
                             int32_t* out_ids) {
+  NvtxRange nvtx_("tsb200.gpt.prefill_ragged");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && ids && lens && opt, "gpt_prefill_ragged: null argument");
   TSB_TRY(use_device(g->c.device, nullptr));
@@ -1498,6 +1530,7 @@ int TSB200_GptPrefillRagged(void* h, const int32_t* ids, const int32_t* lens, in
 }
 
 int TSB200_GptExtend(void* h, const int32_t* ids, int B, int S, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  NvtxRange nvtx_("tsb200.gpt.extend");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && ids && opt, "gpt_extend: null argument");
   TSB_TRY(use_device(g->c.device, nullptr));
@@ -1505,6 +1538,7 @@ int TSB200_GptExtend(void* h, const int32_t* ids, int B, int S, const TSB200Deco
 }
 
 int TSB200_GptDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, int stop_on_eos, int32_t* out_ids, int* steps_done) {
+  NvtxRange nvtx_("tsb200.gpt.decode");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && opt, "gpt_decode: null argument");
   const TSB200GptConfig& c = g->c;
@@ -1650,6 +1684,7 @@ struct GptSnapshot {
 extern "C" {
 
 int TSB200_GptCacheSnapshot(void* h, void** snap_out) {
+  NvtxRange nvtx_("tsb200.gpt.cache_snapshot");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && snap_out, "gpt_cache_snapshot: null argument");
   const TSB200GptConfig& c = g->c;
@@ -1712,6 +1747,7 @@ int TSB200_GptCacheSnapshotFree(void* snap) {
 }
 
 int TSB200_GptCacheRestore(void* h, void* snap, int B_new) {
+  NvtxRange nvtx_("tsb200.gpt.cache_restore");
   Gpt* g = (Gpt*)h;
   GptSnapshot* sn = (GptSnapshot*)snap;
   TSB_CHECK(g && sn, "gpt_cache_restore: null argument");
@@ -1754,6 +1790,7 @@ int TSB200_GptCacheRestore(void* h, void* snap, int B_new) {
 
 // ---- one sequence of the batch at a time: park it, replace it, give it more prompt, while the others keep their state
 int TSB200_GptSlotSnapshot(void* h, int slot, void** snap_out) {
+  NvtxRange nvtx_("tsb200.gpt.slot_snapshot");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && snap_out, "gpt_slot_snapshot: null argument");
   const TSB200GptConfig& c = g->c;
@@ -1832,6 +1869,7 @@ int TSB200_GptSetPerSequenceState(void* h, int on) {
 }
 
 int TSB200_GptSlotRestore(void* h, void* snap, int slot) {
+  NvtxRange nvtx_("tsb200.gpt.slot_restore");
   Gpt* g = (Gpt*)h;
   GptSnapshot* sn = (GptSnapshot*)snap;
   TSB_CHECK(g && sn, "gpt_slot_restore: null argument");
@@ -1865,6 +1903,7 @@ int TSB200_GptSlotRestore(void* h, void* snap, int slot) {
 // S prompt tokens for ONE sequence on top of what it has cached (nothing after TSB200_GptSlotReset), then its next id.
 // The run addresses the sequence's rows of every per-sequence buffer; the other sequences are not touched.
 int TSB200_GptSlotExtend(void* h, int slot, const int32_t* ids, int S, const TSB200DecodingOptions* opt, int32_t* out_id) {
+  NvtxRange nvtx_("tsb200.gpt.slot_extend");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && ids && opt, "gpt_slot_extend: null argument");
   const TSB200GptConfig& c = g->c;
@@ -1987,6 +2026,7 @@ int TSB200_GptGetStepTimes(void* h, float* ms, int n, int* n_out) {
 }
 
 int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOptions* opt, int32_t* out_ids) {
+  NvtxRange nvtx_("tsb200.gpt.step_host");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && last_ids && opt && out_ids, "gpt_step_host: null argument");
   const TSB200GptConfig& c = g->c;
@@ -2030,6 +2070,7 @@ int TSB200_GptStepHost(void* h, const int32_t* last_ids, const TSB200DecodingOpt
 
 // K and V rows of the encoder output for every layer's cross-attention block (see the header).
 int TSB200_GptSetEncoderOutput(void* h, const void* enc, int dtype, int on_device, const int32_t* src_lens, int B, int S_src, int replicas) {
+  NvtxRange nvtx_("tsb200.gpt.set_encoder_output");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && enc, "gpt_set_encoder_output: null argument");
   const TSB200GptConfig& c = g->c;
@@ -2096,10 +2137,23 @@ int TSB200_GptSetEncoderOutput(void* h, const void* enc, int dtype, int on_devic
   return 1;
 }
 
+#ifdef TSB200_CHECKED
+__global__ void chk_selftest_kernel(int code) { TSB_DEV_CHECK(engine, code == 0, code, return) }
+// Checked builds only: records `code` in the engine's check word the way a failing device-side check would (nothing faults),
+// so that a host can see the next engine call report it.
+__attribute__((visibility("default"))) int TSB200_DebugCheckedSelfTest(int device, int code) {
+  TSB_TRY(use_device(device, nullptr));
+  chk_selftest_kernel<<<1, 32>>>(code);
+  TSB_CUDA(cudaDeviceSynchronize());
+  return 1;
+}
+#endif
+
 // The K most probable next ids of every sequence after the latest forward (prefill, extend or step), taken as the
 // reference takes them in beam search: softmax of the logits, -1 on blocked ids, then K rounds of (first arg-max, zero it)
 // (Decoder.cs:447-517 / the same loop in GPTDecode).  ids, probs, log_probs: host arrays [sequences][K].
 int TSB200_GptBeamCandidates(void* h, int K, const TSB200DecodingOptions* opt, int32_t* ids, float* probs, float* log_probs) {
+  NvtxRange nvtx_("tsb200.gpt.beam_candidates");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && opt && ids && probs && log_probs, "gpt_beam_candidates: null argument");
   const TSB200GptConfig& c = g->c;
@@ -2127,6 +2181,7 @@ int TSB200_GptBeamCandidates(void* h, int K, const TSB200DecodingOptions* opt, i
 // equal to the number of sequences adds one (destinations in ascending order then).  No destination may also be a source:
 // a surviving hypothesis keeps its place, the copies fill the places of the ones that were dropped.
 int TSB200_GptBeamCopy(void* h, const int32_t* src, const int32_t* dst, int n) {
+  NvtxRange nvtx_("tsb200.gpt.beam_copy");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && (n == 0 || (src && dst)), "gpt_beam_copy: null argument");
   const TSB200GptConfig& c = g->c;
@@ -2193,6 +2248,7 @@ int TSB200_GptSetWaitLimit(void* h, int polls) {
 
 int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* opt, float* class_ms, int64_t* class_groups,
                             int n_classes) {
+  NvtxRange nvtx_("tsb200.gpt.profile_decode");
   Gpt* g = (Gpt*)h;
   TSB_CHECK(g && opt && class_ms && class_groups, "gpt_profile_decode: null argument");
   const TSB200GptConfig& c = g->c;

@@ -68,6 +68,40 @@ __device__ __forceinline__ int state_step(const int* st, int b, int fallback) {
   return st[kStateRagged] ? st[st[kStateStepsAt] + b] : st[1];
 }
 #endif
+// ---- checked build (-DTSB200_CHECKED): device-side index / capacity checks.  A failing check never traps: it records its
+// code in the translation unit's check word and SKIPS the access; the engine reads the words after every call
+// (TSB200_GptCheckDevice, and together with the wait-limit word after each step) and fails the call with the code.
+//   TSB_CHECKED_WORD(tag)            once per .cu that checks: the word and `int chk_take_<tag>()` (returns and clears it)
+//   TSB_DEV_CHECK(cond, code, stmt)  inside a kernel: if cond is false, record code and run stmt (continue / return / break)
+#ifdef TSB200_CHECKED
+#define TSB_CHECKED_WORD(tag)                                                      \
+  static __device__ int g_chk_word_##tag;                                          \
+  int chk_take_##tag() {                                                           \
+    int e = 0;                                                                     \
+    if (cudaMemcpyFromSymbol(&e, g_chk_word_##tag, sizeof(int)) != cudaSuccess) {  \
+      cudaGetLastError();                                                          \
+      return 0;                                                                    \
+    }                                                                              \
+    if (e) {                                                                       \
+      const int z = 0;                                                             \
+      cudaMemcpyToSymbol(g_chk_word_##tag, &z, sizeof(int));                       \
+    }                                                                              \
+    return e;                                                                      \
+  }
+#define TSB_DEV_CHECK(tag, cond, code, stmt)        \
+  if (!(cond)) {                                    \
+    atomicCAS(&g_chk_word_##tag, 0, (int)(code));   \
+    stmt;                                           \
+  }
+#else
+#define TSB_CHECKED_WORD(tag)
+#define TSB_DEV_CHECK(tag, cond, code, stmt)
+#endif
+int chk_take_engine();
+int chk_take_attention();
+int chk_take_moe();
+int chk_take_sampling();
+
 constexpr int kStackMaxRanks = 8;
 constexpr int kStackXchSites = 4;     // exchange buffers: {out-projection, FFN down} x layer parity
 constexpr int kStackXchRows = 8;      // rows per exchange slot

@@ -14,6 +14,11 @@
 
 namespace tsb {
 
+TSB_CHECKED_WORD(attention)
+#ifndef TSB200_CHECKED
+int chk_take_attention() { return 0; }
+#endif
+
 __device__ __forceinline__ void rope_cs(int i, int cols, int m, double base, float& c, float& s) {
   const float theta = (float)pow(base, -2.0 * i / cols);
   const float tm = theta * (float)m;
@@ -67,6 +72,7 @@ __global__ void rope_append_kernel(T* q, const T* k, const T* v, int64_t q_rs,
     const int b = (int)(row / S), s = (int)(row % S);
     const int T0 = state_len(dT0, b, T0_arg);  // the engine keeps the cache lengths on the device so one CUDA graph serves every step
     const int pos = T0 + s;
+    TSB_DEV_CHECK(attention, pos >= 0 && pos < Tmax, 0x201, (void)0)   // append position outside the cache (row skipped)
     if (pos >= Tmax) continue;  // capacity is checked on the host; never write past the cache
     const int head = rem / hp, i = rem % hp;
     float c = 1.0f, sn = 0.0f;
@@ -445,6 +451,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_mma_kernel(__half* out, flo
   pdl_trigger();
   pdl_wait();
   const int T0 = state_len(dT0, (int)blockIdx.z, T0_arg);
+  TSB_DEV_CHECK(attention, T0 >= 0 && T0 < Tmax, 0x202, (void)0)   // cache length beyond the capacity (keys are clamped to Tmax below)
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int G = H / Hkv;                // query heads per KV head (<= 8)

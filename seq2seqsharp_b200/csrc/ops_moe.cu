@@ -17,6 +17,11 @@
 
 namespace tsb {
 
+TSB_CHECKED_WORD(moe)
+#ifndef TSB200_CHECKED
+int chk_take_moe() { return 0; }
+#endif
+
 constexpr int kMoeMaxExperts = 256;
 constexpr int kMoeMaxPicks = 8;
 
@@ -93,6 +98,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(int* picks, float* score
         const int ti = idx[j]; idx[j] = idx[j - 1]; idx[j - 1] = ti;
       }
     for (int i = 0; i < k; ++i) {
+      TSB_DEV_CHECK(moe, idx[i] >= 0 && idx[i] < E, 0x301, (void)0)   // the router picked no expert for a slot (NaN scores): the slot is skipped downstream
       picks[(size_t)row * k + i] = idx[i];
       scores[(size_t)row * k + i] = idx[i] >= 0 ? s_r[idx[i]] : 0.0f;
     }

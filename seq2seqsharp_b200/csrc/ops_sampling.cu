@@ -14,6 +14,11 @@
 
 namespace tsb {
 
+TSB_CHECKED_WORD(sampling)
+#ifndef TSB200_CHECKED
+int chk_take_sampling() { return 0; }
+#endif
+
 struct ValIdx {
   float v;
   int i;
@@ -910,6 +915,7 @@ __global__ void __launch_bounds__(1024) beam_topk_kernel(int* __restrict__ out_i
       out_ids[(size_t)blockIdx.x * K + k] = best.i;
       out_p[(size_t)blockIdx.x * K + k] = best.v;
       out_logp[(size_t)blockIdx.x * K + k] = logf(best.v);
+      TSB_DEV_CHECK(sampling, best.i >= 0 && best.i < V, 0x401, (void)0)   // no candidate found (a row of NaNs): nothing is zeroed
       if (best.i < V) p[best.i] = 0.0f;
     }
     __syncthreads();   // the zero is in place (same CTA, global memory) before the next round reads the row

@@ -77,6 +77,16 @@ def test_greedy_loop_with_encoder_rows_matches_oracle(cuda, cfg):
     want_logits, _ = orc.step(prefix[:, :1])
     got = g.Logits(want_probs=False)[0]
     assert float(np.abs(got - want_logits).max()) <= _tol(cfg) * float(np.abs(want_logits).max())
+    # the graph-replayed loop (ids fed back on the device) gives what the host-fed steps give
+    g.Reset()
+    first = g.Prefill(prefix[:, :1], opts)
+    looped = g.Decode(6, opts)
+    g.Reset()
+    nxt = g.Prefill(prefix[:, :1], opts)
+    np.testing.assert_array_equal(nxt, first)
+    for i in range(6):
+        nxt = g.StepHost(nxt, opts)
+        np.testing.assert_array_equal(nxt, looped[:, i])
     with pytest.raises(Exception, match="max_src_tokens"):
         g.SetEncoderOutput(np.zeros((B, MAX_SRC + 1, cfg.d), dtype=np.float32))
     g.CheckGuards()
