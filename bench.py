@@ -241,18 +241,21 @@ def make_options(strat, topP, max_tokens, seed, seq_base):
 
 
 def per_operation_engine(cfg, device, max_batch, max_tokens, seed):
-    """An independent engine on ONE GPU that decodes with one launch per operation (no persistent decode-step kernel, no
-    tensor parallelism): the checker of the benchmarked engine."""
+    """An independent engine on ONE GPU that decodes with one launch per operation and none of the fusions of the
+    benchmarked path (no persistent decode-step kernel, no tensor parallelism; separate norm and RoPE-append launches; up to
+    four rows on the FMA streaming GEMV instead of the tensor-core kernel): the checker of the benchmarked engine."""
     from seq2seqsharp_b200.gpt import GPT
-    old = os.environ.get("TSB200_STACK")
-    os.environ["TSB200_STACK"] = "0"      # read when the engine is created
+    knobs = {"TSB200_STACK": "0", "TSB200_FUSED_STEP": "0", "TSB200_GEMV_MAXROWS": "4"}    # read when the engine is created
+    old = {k: os.environ.get(k) for k in knobs}
+    os.environ.update(knobs)
     try:
         ref = GPT(cfg, device_id=device, max_batch=max_batch, max_tokens=max_tokens)
     finally:
-        if old is None:
-            del os.environ["TSB200_STACK"]
-        else:
-            os.environ["TSB200_STACK"] = old
+        for k, v in old.items():
+            if v is None:
+                del os.environ[k]
+            else:
+                os.environ[k] = v
     ref.FillSynthetic(seed, 0.02, 0.0)
     return ref
 
@@ -288,7 +291,7 @@ def parity_check(gpt, ref, prompt, opts, n_steps, tol):
         cmp(i + 1)
         last = nxt
     return {"max_rel_logit_err": worst, "at_step": where, "steps": n_steps + 1, "tolerance": tol, "ids_equal": ids_equal,
-            "ok": bool(worst <= tol), "against": "one-GPU engine with one launch per operation, fed the same ids"}
+            "ok": bool(worst <= tol), "against": "one-GPU engine with one unfused launch per operation, fed the same ids"}
 
 
 def measure_secondary(local, name, B, S, strat, topP, steps=16, warm=3, want_prefill=False):

@@ -241,6 +241,8 @@ struct Gpt {
   bool pdl = true;         // programmatic dependent launch between the kernels of a decode step
   // persistent decode-step kernel (decode_stack.cu): the program of operations and its scratch
   bool use_stack = true;
+  bool fuse_step = true;       // per-operation path, up to eight rows: norm (and RoPE + cache append) inside the linear's launch
+                               // (TSB200_FUSED_STEP=0: separate norm / RoPE-append launches, e.g. for a checker engine)
   // Measured crossover on the 7B-class model (ms per step, persistent kernel against one launch per operation with the
   // mma.sync linears): 1 sequence 3.41 / 3.95, 2 sequences 3.79 / 3.92, 3 sequences 4.23 / 3.91, 4 sequences 4.62 / 3.96 --
   // the persistent kernel's dependency chain grows with every row, the per-operation path is flat up to 8 sequences.
@@ -602,7 +604,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
       return r;
     }
   }
-  if (ng && dt == TSB200_F16 && rows <= 8) {
+  if (ng && dt == TSB200_F16 && rows <= 8 && g->fuse_step) {
     // up to eight rows: the tensor-core streaming kernel norms the rows itself (no norm launch)
     prof_begin(g);
     const int r = launch_gemm_stream_mma_norm(dev, g->st, x_resid, ng, c.norm_type == 0 ? nb : nullptr, c.norm_type, c.eps, Wp, rows, K, N, ep,
@@ -829,11 +831,30 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   const int act = c.act;
   for (int k = 0; k < c.L; ++k) {
     LayerW& L = g->L[k];
-    TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n1_g, L.n1_b, g->h, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
     void* qp = g->qkv;
     void* kp = (char*)g->qkv + (int64_t)Hd * g->es;
     void* vp = (char*)g->qkv + (int64_t)(Hd + KVd) * g->es;
-    PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
+    bool appended = false;
+    if (S == 1 && dt == TSB200_F16 && rows <= 8 && g->fuse_step) {
+      // one new position per sequence, up to eight sequences: norm, q | k | v projection, RoPE and the cache append in one launch
+      RopeFuse rf{};
+      rf.cK = L.cK; rf.cV = L.cV; rf.Hd = Hd; rf.KVd = KVd; rf.hd = c.hd; rf.Tmax = c.max_tokens;
+      rf.use_rope = c.pe_type == 2 ? 1 : 0; rf.T0 = T0; rf.state = dT; rf.tab = g->rope_tab;
+      prof_begin(g);
+      const int r = launch_gemm_stream_mma_norm(dev, g->st, g->x, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, L.wqkv, rows, d,
+                                                g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->err_flag, g->pdl, g->lin_ws,
+                                                g->lin_ws_bytes, g->s, &rf);
+      if (r == 0) return 0;
+      if (r == 1) {
+        g->lin_syms_used = true;
+        prof_end(g, KC_LINEAR);
+        appended = true;
+      }
+    }
+    if (!appended) {
+      TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.n1_g, L.n1_b, g->h, L.wqkv, d, g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
+      PROF(KC_ROPE_APPEND, launch_rope_append(dev, g->st, dt, qp, kp, vp, g->Nqkv, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, c.pe_type == 2, (double)c.rope_base, g->rope_tab, g->s));
+    }
     PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, qp, g->Nqkv, L.cK, L.cV, B, S, c.H, c.Hkv, c.hd, T0, dT, c.max_tokens, splits, g->attn_ws, g->attn_ws_bytes, g->s));
     TSB_TRY(row_parallel_linear(g, rows, g->attn, L.wo, Hd, L.bo));
     if (c.cross_attn) {
@@ -1112,6 +1133,8 @@ int TSB200_GptCreate(const TSB200GptConfig* cfg, void** out) {
     g->tp_peer = !(e && e[0] == '0');
     e = getenv("TSB200_STACK");            // "0": one launch per operation instead of the persistent decode-step kernel
     g->use_stack = !(e && e[0] == '0');
+    e = getenv("TSB200_FUSED_STEP");
+    g->fuse_step = !(e && e[0] == '0');
     e = getenv("TSB200_STACK_MAXB");       // tuning knobs for the crossover between the three decode paths
     if (e) g->stack_cap = atoi(e);
     e = getenv("TSB200_GEMV_MAXROWS");

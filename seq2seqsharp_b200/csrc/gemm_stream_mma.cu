@@ -41,6 +41,8 @@ struct GsArgs {
   const __half* beta;       // may be null
   int norm_type;            // 0 LayerNorm, 1 RMSNorm
   float eps;
+  int rope_on;              // 1: the epilogue rotates q / k and appends k / v to the cache (see RopeFuse)
+  RopeFuse rope;
   float* partials;          // [CT][max_contrib][M][256]
   unsigned int* counters;   // [CT], zero on entry, self-resetting
   int* error_flag;
@@ -380,7 +382,35 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_mma_kernel(cons
           }
           const int row = idx >> 6, c = cur_ct * NT + (idx & 63) * 4;
           const float v[4] = {sum.x, sum.y, sum.z, sum.w};
-          if (!ep.glu) {
+          if (a.rope_on) {
+            // four columns = two rotation pairs of one head (hd and the section boundaries are multiples of four)
+            if (c + 3 < N) {
+              const RopeFuse& rf = a.rope;
+              const int pos = state_len(rf.state, row, rf.T0);
+              const int sec = c < rf.Hd ? 0 : (c < rf.Hd + rf.KVd ? 1 : 2);
+              const int cc = c - (sec == 0 ? 0 : (sec == 1 ? rf.Hd : rf.Hd + rf.KVd));
+              const int head = cc / rf.hd, e0 = cc % rf.hd;
+              float t[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) t[e] = __half2float(__float2half_rn(v[e] + (bias ? __half2float(bias[c + e]) : 0.0f)));
+              if (rf.use_rope && sec < 2 && pos < rf.Tmax) {
+                const float2 cs0 = rf.tab[(int64_t)pos * (rf.hd / 2) + e0 / 2], cs1 = rf.tab[(int64_t)pos * (rf.hd / 2) + e0 / 2 + 1];
+                const float a0 = t[0], b0 = t[1], a1 = t[2], b1 = t[3];
+                t[0] = a0 * cs0.x - b0 * cs0.y; t[1] = b0 * cs0.x + a0 * cs0.y;
+                t[2] = a1 * cs1.x - b1 * cs1.y; t[3] = b1 * cs1.x + a1 * cs1.y;
+              }
+              const __half2 h01 = __floats2half2_rn(t[0], t[1]), h23 = __floats2half2_rn(t[2], t[3]);
+              uint2 out;
+              out.x = *reinterpret_cast<const uint32_t*>(&h01);
+              out.y = *reinterpret_cast<const uint32_t*>(&h23);
+              if (sec == 0) {
+                *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(ep.y) + (size_t)row * N + c) = out;
+              } else if (pos < rf.Tmax) {   // capacity is checked on the host; never write past the cache
+                __half* dst = reinterpret_cast<__half*>(sec == 1 ? rf.cK : rf.cV) + (((int64_t)row * (rf.KVd / rf.hd) + head) * rf.Tmax + pos) * rf.hd + e0;
+                *reinterpret_cast<uint2*>(dst) = out;
+              }
+            }
+          } else if (!ep.glu) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               if (c + e < N) {
@@ -844,7 +874,7 @@ int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const voi
 // norm kernel and the plain linear).
 int launch_gemm_stream_mma_norm(int device, DeviceState* st, const float* x32, const void* gamma, const void* beta, int norm_type, float eps,
                                 const void* Wp, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws, int64_t ws_bytes,
-                                cudaStream_t s) {
+                                cudaStream_t s, const RopeFuse* rope) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("TSB200_GEMM_FUSED_NORM");  // "0": a norm launch in front of every linear (A/B measurements)
@@ -877,6 +907,15 @@ int launch_gemm_stream_mma_norm(int device, DeviceState* st, const float* x32, c
   a.beta = reinterpret_cast<const __half*>(beta);
   a.norm_type = norm_type;
   a.eps = eps;
+  if (rope) {
+    // q | k | v columns with whole heads of a multiple of four elements, fp16 output rows, no activation / gate / residual
+    if (rope->hd % 4 != 0 || rope->Hd % rope->hd != 0 || rope->KVd % rope->hd != 0 || rope->Hd + 2 * rope->KVd != N || N % 4 != 0 || !ep.y ||
+        ep.y32 || ep.residual || ep.glu || ep.act != TSB200_ACT_NONE || (rope->use_rope && !rope->tab) || ((uintptr_t)ep.y % 8) != 0 ||
+        ((uintptr_t)rope->cK % 8) != 0 || ((uintptr_t)rope->cV % 8) != 0)
+      return 2;
+    a.rope_on = 1;
+    a.rope = *rope;
+  }
   const int64_t need = kWsCounterBytes + (int64_t)a.CT * a.max_contrib * M * 256 * 4;
   if (!ws || ws_bytes < need) return 2;
   a.counters = reinterpret_cast<unsigned int*>(ws);

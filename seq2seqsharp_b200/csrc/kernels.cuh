@@ -190,9 +190,22 @@ int launch_gemm_stream_tc(int device, DeviceState* st, const void* x, const void
                           int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_stream_tc_workspace_bytes(int M, int K, int N, int sm_count);
 int stc_take_error();
+// The packed q | k | v projection of a decode step (one new position per sequence) with RoPE and the cache append done by
+// the linear's epilogue: q columns are rotated and go to the output rows, k columns are rotated and go to the K cache row of
+// the sequence's position, v columns go to the V cache row - the arithmetic of rope_append_kernel (the value is rounded to the
+// model type first, as when the linear stores it and a second kernel reads it back).
+struct RopeFuse {
+  void* cK;            // [sequences, Hkv, Tmax, hd]
+  void* cV;
+  int Hd, KVd, hd, Tmax;
+  int use_rope;        // 0: append only
+  int T0;              // cache length when `state` is null
+  const int* state;    // device step state (per-sequence lengths), may be null
+  const float2* tab;   // [Tmax, hd / 2] cos / sin
+};
 int launch_gemm_stream_mma_norm(int device, DeviceState* st, const float* x32, const void* gamma, const void* beta, int norm_type, float eps,
                                 const void* Wp, int M, int K, int N, const Epilogue& ep, int* error_flag, bool pdl, void* ws, int64_t ws_bytes,
-                                cudaStream_t s);
+                                cudaStream_t s, const RopeFuse* rope = nullptr);
 int launch_gemm_stream_mma(int device, DeviceState* st, const void* x, const void* Wp, int M, int K, int N, const Epilogue& ep,
                            int* error_flag, bool pdl, void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t gemm_stream_mma_workspace_bytes(int M, int K, int N, int sm_count);
