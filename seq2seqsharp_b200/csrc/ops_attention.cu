@@ -874,7 +874,9 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
       count_launch(device);
       return check_launch("attention_prefill_mma");
     }
-    if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv && B * Hkv * splits >= 2 * st->sm_count) {
+    // from one CTA per SM on (measured on the 7B-class model, one sequence of 530 tokens, 256 CTAs: 0.54 against 0.68 ms of
+    // attention per step for the shuffle / FMA kernel)
+    if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv && B * Hkv * splits >= st->sm_count) {
       const size_t sm3 = (size_t)kMmaStages * 2 * kMmaStageTokens * hd * 2;
       dim3 g3(splits, Hkv, B);
       static bool attr_done[kMaxDevices] = {};
