@@ -503,7 +503,8 @@ def run_b200(args):
     es = 2 if cfg.dtype == "float16" else 4
     lin_ms, lin_groups = prof["linear"]
     lin_bytes = linear_bytes_per_step(cfg, world if tp else 1)
-    dominant = "gemv_stream_kernel / gemm_tc_kernel (all linear layers of a decode step)"
+    dominant = ("gemm_stream_mma_kernel / gemm_stream_tc_kernel (all linear layers of a decode step: q|k|v with norm, RoPE and cache "
+                "append, out-projection, FFN-up with norm, FFN-down, LM head; timed launch by launch outside the graph)")
     if prof["decode_stack"][1] > 0:
         # one persistent launch per step runs every linear plus RoPE, cache append and attention; its
         # algorithmic bytes are the weights once plus the KV cache read and the appended rows

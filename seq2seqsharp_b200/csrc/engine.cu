@@ -247,8 +247,8 @@ struct Gpt {
   // mma.sync linears): 1 sequence 3.41 / 3.95, 2 sequences 3.79 / 3.92, 3 sequences 4.23 / 3.91, 4 sequences 4.62 / 3.96 --
   // the persistent kernel's dependency chain grows with every row, the per-operation path is flat up to 8 sequences.
   // Tensor-parallel engines keep the persistent kernel (the exchange lives there).
-  int stack_cap = -1;          // largest batch the persistent kernels are used for on one GPU (TSB200_STACK_MAXB); -1: fp16 one
-                               // sequence (from two on, one launch per operation on the tensor-core linears is faster), fp32 two
+  int stack_cap = -1;          // largest batch the persistent kernels are used for on one GPU (TSB200_STACK_MAXB); -1: fp16 none
+                               // (one launch per operation on the tensor-core linears is faster at every batch), fp32 two
   int gemv_rows = -1;          // largest row count of the FMA streaming GEMV in the per-operation path (TSB200_GEMV_MAXROWS);
                                // -1: fp16 none (the tensor-core streaming kernel is faster from one row on), fp32 four
   std::vector<StackOp> stack_host;
@@ -266,7 +266,7 @@ struct Gpt {
   // Measured on the 7B-class model (same GPU, ms per decode step, kernel only): one sequence 3.10 against 3.20 for the
   // stream-K persistent kernel; two sequences 3.82 against 3.63 (its staging, merges and emissions are per row); on the
   // 1B-class model 1.02 against 1.03.  So it serves single sequences; TSB200_OWNER_MAXB raises the limit (tests do).
-  int own_cap = 1;
+  int own_cap = -1;                  // -1: tensor-parallel engines one sequence, one-GPU engines none (TSB200_OWNER_MAXB)
   OwnerModel* own = nullptr;
   int own_B = 0;                     // batch the owner kernel serves for the current program (0: not in use)
 };
@@ -664,15 +664,16 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
 static int ensure_stack(Gpt* g, int B) {
   const TSB200GptConfig& c = g->c;
   g->stack_max_B = (c.dtype == TSB200_F16) ? 8 : 4;  // fp16: tensor-core consumers take up to 8 rows
-  const int cap = g->stack_cap >= 0 ? g->stack_cap : (c.dtype == TSB200_F16 ? 1 : 2);
-  if (g->tp == 1 && cap > 0 && cap < g->stack_max_B) g->stack_max_B = cap;
+  const int cap = g->stack_cap >= 0 ? g->stack_cap : (c.dtype == TSB200_F16 ? 0 : 2);
+  if (g->tp == 1 && cap < g->stack_max_B) g->stack_max_B = cap;
   g->own_B = 0;
   if (!g->use_stack || g->ragged) return 1;   // sequences of different lengths: one launch per operation
   if (g->c.n_experts > 1) return 1;           // mixture-of-experts layers exist only as separate launches
   if (g->c.cross_attn) return 1;              // so do the cross-attention blocks
   // tensor-parallel engines: one sequence, and only once the ranks' exchange regions are mapped into each other
   const bool own_tp_ok = g->tp == 1 || (g->xch_ready && g->tp_peer && B == 1 && g->xch_own_off != 0);
-  if (g->use_owner && own_tp_ok && B <= g->own_cap && B <= kOwnMaxRows) {
+  const int own_cap = g->own_cap >= 0 ? g->own_cap : (g->tp > 1 ? 1 : 0);
+  if (g->use_owner && own_tp_ok && B <= own_cap && B <= kOwnMaxRows) {
     OwnDims D{};
     D.L = c.L; D.d = c.d; D.H = c.H; D.Hkv = c.Hkv; D.hd = c.hd; D.F = c.F; D.V = c.V; D.glu = g->glu;
     if (owner_applicable(D, c.dtype, g->st->sm_count)) {
@@ -864,7 +865,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
       TSB_CHECK(S == 1, "cross-attention engines take one new token per sequence and call (got %d)", S);
       TSB_TRY(engine_linear(g, rows, nullptr, g->x, L.nx_g, L.nx_b, g->h, L.xq, d, (int)Hd, make_ep(L.xqb, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0)));
       PROF(KC_ATTENTION, launch_attention(dev, g->st, dt, g->attn, g->qkv, Hd, L.xK, L.xV, B, 1, c.H, c.H, c.hd, g->cross_T - 1, g->cross_state,
-                                          c.max_src_tokens, attn_pick_splits(g->st, B, c.H, c.H, g->cross_T), g->attn_ws, g->attn_ws_bytes, g->s));
+                                          c.max_src_tokens, attn_pick_splits(g->st, dt, B, c.H, c.H, c.hd, g->cross_T), g->attn_ws, g->attn_ws_bytes, g->s));
       TSB_TRY(row_parallel_linear(g, rows, g->attn, L.xo, Hd, L.xob));
     }
     if (L.moe) {
@@ -1037,7 +1038,7 @@ static int ensure_graph(Gpt* g, const TSB200DecodingOptions* opt, int n_steps) {
   while (Tp < g->T + n_steps) Tp <<= 1;
   TSB_TRY(ensure_stack(g, B));
   GraphKey key;
-  key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, B, c.H, c.Hkv, Tp);
+  key.B = B; key.strategy = opt->strategy; key.splits = attn_pick_splits(g->st, c.dtype, B, c.H, c.Hkv, c.hd, Tp);
   key.n_blocked = opt->n_blocked; key.blocked_hash = hash_blocked(opt->blocked, opt->n_blocked);
   key.topP = opt->topP; key.temperature = opt->temperature; key.penalty = opt->repeatPenalty;
   key.seed = opt->seed; key.seq_base = opt->seq_base;
@@ -2284,7 +2285,7 @@ int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* o
   TSB_TRY(set_state(g, 0));
   int Tp = 256;
   while (Tp < g->T + n_steps) Tp <<= 1;
-  const int splits = attn_pick_splits(g->st, g->B, c.H, c.Hkv, Tp);
+  const int splits = attn_pick_splits(g->st, c.dtype, g->B, c.H, c.Hkv, c.hd, Tp);
   TSB_TRY(ensure_stack(g, g->B));
   g->prof = true;
   g->prof_n = 0;

@@ -217,7 +217,7 @@ int launch_attention(int device, DeviceState* st, int dtype, void* out, const vo
                      const void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0, int Tmax, int splits_hint,
                      void* ws, int64_t ws_bytes, cudaStream_t s);
 int64_t attn_workspace_bytes(int B, int H, int hd, int T);
-int attn_pick_splits(DeviceState* st, int B, int H, int Hkv, int T);
+int attn_pick_splits(DeviceState* st, int dtype, int B, int H, int Hkv, int hd, int T);
 int launch_rope_table(int device, DeviceState* st, float2* tab, int Tmax, int hd, double base, cudaStream_t s);
 int launch_rope_append(int device, DeviceState* st, int dtype, void* q, const void* k, const void* v, int64_t q_rs,
                        int64_t kv_rs, void* cK, void* cV, int B, int S, int H, int Hkv, int hd, int T0, const int* dT0,

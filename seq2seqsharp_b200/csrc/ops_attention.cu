@@ -797,15 +797,24 @@ __global__ void attn_combine_kernel(T* out, const float* part, int hd, int split
   }
 }
 
-static int pick_splits(DeviceState* st, int B, int Hkv_groups, int T) {
-  // enough CTAs to cover the SMs about twice, at least 32 keys per split (a CTA covers 8..16 keys per iteration)
+static int pick_splits(DeviceState* st, int B, int Hkv_groups, int T, int min_keys = 32) {
+  // enough CTAs to cover the SMs about twice, at least min_keys keys per split (a CTA of the shuffle / FMA kernels covers
+  // 8..16 keys per iteration: 32; the tensor-core kernel stages 64 keys at a time: 128 - with 32 a 530-token context was cut
+  // into 17..32 splits whose start-up and merge cost more than they gained: 7B-class, two sequences, 3.38 against 3.20 ms per step)
   const int64_t base = (int64_t)B * Hkv_groups;
   int s = (int)((2LL * st->sm_count + base - 1) / base);
-  const int max_by_len = (T + 31) / 32;
+  const int max_by_len = (T + min_keys - 1) / min_keys;
   if (s > max_by_len) s = max_by_len;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
   return s;
+}
+
+// fp16, head size 64 / 128, 1, 2, 4 or 8 query heads per KV head: the tensor-core flash-decode kernel serves the shape
+static bool mma_decode_shape(int dtype, int H, int Hkv, int hd) {
+  if (Hkv <= 0 || H % Hkv != 0) return false;
+  const int group = H / Hkv;
+  return dtype == TSB200_F16 && (hd == 64 || hd == 128) && (group == 1 || group == 2 || group == 4 || group == 8);
 }
 
 int64_t attn_workspace_bytes(int B, int H, int hd, int T) {
@@ -831,7 +840,8 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   else if (group % 4 == 0) G = 4;
   else if (group % 2 == 0) G = 2;
   const int ygroups = Hkv * (group / G);
-  int splits = (S == 1) ? (splits_hint > 0 ? splits_hint : pick_splits(st, B, ygroups, T0 + 1)) : 1;
+  const bool mma_shape = mma_decode_shape(sizeof(T) == 2 ? TSB200_F16 : TSB200_F32, H, Hkv, hd);
+  int splits = (S == 1) ? (splits_hint > 0 ? splits_hint : pick_splits(st, B, ygroups, T0 + 1, mma_shape ? 256 : 32)) : 1;
   if (splits > 1) {
     const int64_t need = (int64_t)B * S * H * splits * (hd + 2) * sizeof(float);
     if (!ws || ws_bytes < need) splits = 1;
@@ -874,9 +884,8 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
       count_launch(device);
       return check_launch("attention_prefill_mma");
     }
-    // from one CTA per SM on (measured on the 7B-class model, one sequence of 530 tokens, 256 CTAs: 0.54 against 0.68 ms of
-    // attention per step for the shuffle / FMA kernel)
-    if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv && B * Hkv * splits >= st->sm_count) {
+    // at every grid size (7B-class model, sequences of 530 tokens: faster than the shuffle / FMA kernels from 16 CTAs on)
+    if (use_mma && staged && S == 1 && (hd == 64 || hd == 128) && group <= 8 && ygroups == Hkv) {
       const size_t sm3 = (size_t)kMmaStages * 2 * kMmaStageTokens * hd * 2;
       dim3 g3(splits, Hkv, B);
       static bool attr_done[kMaxDevices] = {};
@@ -950,13 +959,13 @@ static int launch_attn_t(int device, DeviceState* st, T* out, const T* q, int64_
   return 1;
 }
 
-int attn_pick_splits(DeviceState* st, int B, int H, int Hkv, int T) {
+int attn_pick_splits(DeviceState* st, int dtype, int B, int H, int Hkv, int hd, int T) {
   const int group = H / Hkv;
   int G = 1;
   if (group % 8 == 0) G = 8;
   else if (group % 4 == 0) G = 4;
   else if (group % 2 == 0) G = 2;
-  return pick_splits(st, B, Hkv * (group / G), T);
+  return pick_splits(st, B, Hkv * (group / G), T, mma_decode_shape(dtype, H, Hkv, hd) ? 256 : 32);
 }
 
 int launch_attention(int device, DeviceState* st, int dtype, void* out, const void* q, int64_t q_rs, const void* cK,

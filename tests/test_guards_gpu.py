@@ -74,6 +74,8 @@ def test_guards_of_a_wide_model_after_every_decode_path(cuda, monkeypatch):
     from seq2seqsharp_b200.configs import CONFIGS
     import dataclasses
     cfg = dataclasses.replace(CONFIGS["c5_llama7b_fp16"], L=2, V=4096)
+    monkeypatch.setenv("TSB200_OWNER_MAXB", "1")    # the persistent kernels are opt-in on one GPU
+    monkeypatch.setenv("TSB200_STACK_MAXB", "2")
     for owner, B in (("1", 1), ("0", 1), ("0", 2), ("1", 4), ("1", 64)):
         monkeypatch.setenv("TSB200_OWNER", owner)
         g = GPT(cfg, max_batch=B, max_tokens=160)

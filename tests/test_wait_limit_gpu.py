@@ -17,7 +17,9 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.timeout(300)
 @pytest.mark.parametrize("cfg", [ARCHS[1], ARCHS[0]], ids=["fp16_tensor_core_consumers", "fp32_cuda_core_consumers"])
 @pytest.mark.parametrize("call", ["decode", "step_host"])
-def test_a_wait_that_runs_out_fails_the_call_and_leaves_the_engine_usable(cuda, cfg, call):
+def test_a_wait_that_runs_out_fails_the_call_and_leaves_the_engine_usable(cuda, cfg, call, monkeypatch):
+    monkeypatch.setenv("TSB200_OWNER_MAXB", "1")    # one sequence on a persistent kernel (one-GPU fp16 engines default to one
+    monkeypatch.setenv("TSB200_STACK_MAXB", "1")    # launch per operation): the kernels whose cross-CTA waits are bounded
     w = synthetic_weights(cfg, 21, std=0.04)
     prompt = prompt_ids(9, 1, 24, cfg.V)
     opts = DecodingOptions(MaxTgtSentLength=64, BlockedTokens=[0])
