@@ -363,7 +363,7 @@ int launch_linear(int device, DeviceState* st, int dtype, const void* x, const v
     const int r = launch_gemm_stream_tc(device, st, x, W, M, K, N, ep, nullptr, true, ws, ws_bytes, s);
     if (r != 2) return r;
   }
-  if (packed && dtype == TSB200_F16 && M > 1 && M <= 64) {
+  if (packed && dtype == TSB200_F16 && M >= 1 && M <= 64) {
     // decode batches: weights streamed once through a ring, mma.sync consumers (measured: for 33..64 rows and wide
     // outputs the split-K tcgen05 kernel below is faster, its partial sums being a smaller share of the traffic)
     const int r = launch_gemm_stream_mma(device, st, x, W, M, K, N, ep, nullptr, true, ws, ws_bytes, s);
