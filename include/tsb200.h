@@ -266,7 +266,8 @@ typedef struct TSB200GptConfig {
    * block between self-attention and feed-forward that reads the encoder's output (weights <prefix>.EncAttn_k.{layerNormQ.*,
    * Q, Qb, K, Kb, V, Vb, W0, b0}, Layers/MultiHeadAttention.cs:434-527); max_src_tokens = capacity of its K/V rows per
    * sequence.  The encoder output arrives through TSB200_GptSetEncoderOutput.  One launch per operation; not tensor-parallel.
-   * The layer names may then start with "Decoder." instead of "GPTDecoder.". */
+   * The layer names may then start with "TransformerDecoder." (the reference's name for this network, Applications/Decoder.cs:49)
+ * instead of "GPTDecoder.", and the embedding table may be handed over as "SharedEmbeddings". */
   int32_t cross_attn, max_src_tokens;
 } TSB200GptConfig;
 

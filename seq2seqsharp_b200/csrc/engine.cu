@@ -416,11 +416,13 @@ static int resolve_local(Gpt* g, const std::string& name, Dest* out) {
   if (name == "GPTDecoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
   if (name == "FeedForward_Decoder_0.m_Whd") return setp(g->head_w, d, V, 0, 1);
   if (name == "FeedForward_Decoder_0.m_Bd") return set(g->head_b, 1, V, V, 1);
-  const bool dec_prefix = c.cross_attn && starts_with(name, "Decoder.");   // TransformerDecoder's own prefix
-  if (dec_prefix && name == "Decoder.layerNorm.m_alpha") return set(g->nf_g, 1, d, d, 1);
-  if (dec_prefix && name == "Decoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
+  // the reference names the decoder of its encoder-decoder models "TransformerDecoder" (Applications/Decoder.cs:49)
+  const bool dec_prefix = c.cross_attn && starts_with(name, "TransformerDecoder.");
+  if (dec_prefix && name == "TransformerDecoder.layerNorm.m_alpha") return set(g->nf_g, 1, d, d, 1);
+  if (dec_prefix && name == "TransformerDecoder.layerNorm.m_beta") return set(g->nf_b, 1, d, d, 1);
+  if (c.cross_attn && name == "SharedEmbeddings") return set(g->E, V, d, d, 1);   // one table for source and target (BaseSeq2SeqFramework.cs:365)
   TSB_CHECK(starts_with(name, "GPTDecoder.") || dec_prefix, "unknown weight name '%s'", name.c_str());
-  const std::string rest = name.substr(dec_prefix ? 8 : 11);
+  const std::string rest = name.substr(dec_prefix ? 19 : 11);
   const size_t us = rest.find('_'), dot = rest.find('.');
   TSB_CHECK(us != std::string::npos && dot != std::string::npos && us < dot, "unknown weight name '%s'", name.c_str());
   const int k = std::atoi(rest.substr(us + 1, dot - us - 1).c_str());

@@ -32,6 +32,7 @@ F_EXPERTS, F_ACT, F_VQTYPE, F_VQ, F_CODEBOOK, F_HALF, F_PE, F_NORM, F_MHA_TYPE, 
 F_EXPERTS_PER_TOKEN = 22
 VQ_NONE, VQ_INT4, VQ_INT8, VQ_FLOAT16 = 0, 16, 256, 65536          # Seq2SeqSharp/Utils/ModeEnums.cs:41-47
 DECODER_GPT = 2                                                    # DecoderTypeEnums.GPTDecoder
+DECODER_TRANSFORMER = 1                                            # DecoderTypeEnums.Transformer (Utils/ModeEnums.cs:33-39)
 
 
 class ModelFileError(ValueError):
@@ -187,6 +188,35 @@ class ModelFile:
                          attn=MultiHeadAttentionTypeEnums.GQA if gqa else MultiHeadAttentionTypeEnums.MHA, dtype=dtype, name="model_file",
                          expertNum=max(1, self.ExpertNum), expertsPerTokenFactor=max(1, self.ExpertsPerTokenFactor))
 
+    def seq2seq_decoder_config(self, max_src_tokens: int, dtype: Optional[str] = None) -> GPTConfig:
+        """The TransformerDecoder of an encoder-decoder model file (Applications/Decoder.cs:45-52 builds it from these fields):
+        MultiHeadAttention self-attention, attention over the encoder output, feed-forward.  The encoder's tensors of the same
+        file are not used by this backend: the encoder output is an input of the decoder path."""
+        if self.DecoderType != DECODER_TRANSFORMER:
+            raise ModelFileError("DecoderType %d is not the Transformer decoder of an encoder-decoder model" % self.DecoderType)
+        if self.MultiHeadNum <= 0 or self.HiddenDim % self.MultiHeadNum:
+            raise ModelFileError("HiddenDim %d is not divisible by MultiHeadNum %d" % (self.HiddenDim, self.MultiHeadNum))
+        if self.TgtVocab is None:
+            raise ModelFileError("the file holds no target vocabulary, so the LM head width is unknown")
+        pe = {0: PositionEmbeddingEnums.APE, 1: PositionEmbeddingEnums.NoPE, 2: PositionEmbeddingEnums.RoPE}[self.PEType]
+        if dtype is None:
+            dtype = "float16" if self.VQType == VQ_FLOAT16 else "float32"
+        return GPTConfig(L=self.DecoderLayerDepth, d=self.HiddenDim, H=self.MultiHeadNum, hd=self.HiddenDim // self.MultiHeadNum,
+                         F=self.IntermediateDim, V=len(self.TgtVocab), norm=NormEnums(self.NormType), act=ActivateFuncEnums(self.ActivateFunc),
+                         pe=pe, attn=MultiHeadAttentionTypeEnums.MHA, dtype=dtype, name="model_file_seq2seq_decoder", cross_attn=True,
+                         max_src_tokens=int(max_src_tokens))
+
+    def _file_name(self, cfg: GPTConfig, name: str) -> str:
+        """The key under which the file stores what the engine calls `name`: an encoder-decoder model names its decoder
+        "TransformerDecoder" and may keep one embedding table for both sides ("SharedEmbeddings")."""
+        if not cfg.cross_attn:
+            return name
+        if name.startswith("GPTDecoder."):
+            return "TransformerDecoder." + name[len("GPTDecoder."):]
+        if name == "TgtEmbeddings" and name not in self.names() and "SharedEmbeddings" in self.names():
+            return "SharedEmbeddings"
+        return name
+
     def weights_for(self, cfg: GPTConfig, max_pos: int = 0) -> Dict[str, np.ndarray]:
         """Every tensor the engine asks for, shaped [rows, cols], in the file's own precision (float16 arrays for a
         FLOAT16 file, float32 otherwise).  Missing tensors are an error; PosEmbedding is rebuilt."""
@@ -196,7 +226,7 @@ class ModelFile:
             if name == "PosEmbedding":
                 out[name] = position_embedding(shape[0], shape[1])
                 continue
-            w = self.get_weights(name, want_half=half)
+            w = self.get_weights(self._file_name(cfg, name), want_half=half)
             if w is None:
                 raise ModelFileError("weight '%s' is not in the model file" % name)
             if w.size != shape[0] * shape[1]:
@@ -269,6 +299,18 @@ def parse_model(data) -> ModelFile:
 def read_model(path: str) -> ModelFile:
     with open(path, "rb") as fh:
         return parse_model(fh.read())
+
+
+def load_seq2seq_decoder(path: str, max_src_tokens: int, device_id: int = 0, max_batch: int = 1, max_tokens: int = 512,
+                         dtype: Optional[str] = None):
+    """Encoder-decoder model file -> an engine holding its decoder (self-attention, attention over the encoder output,
+    feed-forward, LM head); the encoder output arrives through `GPT.SetEncoderOutput`.  Returns (GPT, ModelFile)."""
+    from .gpt import GPT
+    mf = read_model(path)
+    cfg = mf.seq2seq_decoder_config(max_src_tokens, dtype)
+    gpt = GPT(cfg, device_id=device_id, max_batch=max_batch, max_tokens=max_tokens)
+    gpt.LoadWeights(mf.weights_for(cfg, gpt.pos_embedding_rows if cfg.pe == PositionEmbeddingEnums.APE else 0))
+    return gpt, mf
 
 
 def load_gpt(path: str, device_id: int = 0, max_batch: int = 1, max_tokens: int = 512, dtype: Optional[str] = None):

@@ -95,3 +95,38 @@ def test_mixture_of_experts_model(tmp_path):
     assert shaped["GPTDecoder.MoEFFN_2.m_Router"].shape == (32, 3) and shaped["GPTDecoder.MoEFFN_2.m_RouterBias"].shape == (1, 3)
     for name, want in expect.items():
         np.testing.assert_array_equal(mf.get_weights(name).astype(np.float32), want, err_msg=name)
+
+
+def test_encoder_decoder_model_file_gives_the_decoder(tmp_path):
+    """A Seq2Seq model file (DecoderType Transformer): the decoder's tensors live under "TransformerDecoder.*", the embedding
+    table may be shared, and the encoder's tensors are simply not asked for."""
+    cfg = GPTConfig(L=2, d=64, H=4, hd=16, F=96, V=38, norm=Nm.LayerNorm, act=A.ReLU, pe=P.APE, attn=M.MHA, cross_attn=True,
+                    max_src_tokens=12)
+    w = {k: v for k, v in synthetic_weights(cfg, 7, std=0.1, bias_std=0.05).items() if k != "PosEmbedding"}
+    file_w = {}
+    for k, v in w.items():
+        if k.startswith("GPTDecoder."):
+            file_w["TransformerDecoder." + k[len("GPTDecoder."):]] = v
+        elif k == "TgtEmbeddings":
+            file_w["SharedEmbeddings"] = v
+        else:
+            file_w[k] = v
+    file_w["TransformerEncoder.SelfAttn_0.QKV"] = np.ones((64, 192), dtype=np.float32)      # the encoder side of the same file
+    path = str(tmp_path / "s2s.model")
+    expect = write_model(path, cfg, file_w, cfg.V, decoder_type=1)
+    mf = read_model(path)
+    with pytest.raises(ModelFileError, match="not GPTDecoder"):
+        mf.gpt_config()
+    got = mf.seq2seq_decoder_config(max_src_tokens=12)
+    assert got.cross_attn and got.max_src_tokens == 12 and (got.L, got.d, got.H, got.hd, got.F, got.V) == (2, 64, 4, 16, 96, 38)
+    assert got.attn == M.MHA and got.pe == P.APE and got.norm == Nm.LayerNorm
+    shaped = mf.weights_for(got, max_pos=20)
+    assert set(shaped) == set(cfg.weight_shapes(20))
+    np.testing.assert_array_equal(shaped["GPTDecoder.EncAttn_1.K"].reshape(-1), expect["TransformerDecoder.EncAttn_1.K"])
+    np.testing.assert_array_equal(shaped["TgtEmbeddings"].reshape(-1), expect["SharedEmbeddings"])
+    assert shaped["GPTDecoder.EncAttn_0.W0"].shape == (64, 64) and shaped["PosEmbedding"].shape == (20, 64)
+    # a GPT file is not an encoder-decoder file
+    gpt_path = str(tmp_path / "gpt.model")
+    write_model(gpt_path, CFG, saved_weights(CFG), CFG.V)
+    with pytest.raises(ModelFileError, match="Transformer decoder"):
+        read_model(gpt_path).seq2seq_decoder_config(8)

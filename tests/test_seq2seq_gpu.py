@@ -129,3 +129,38 @@ def test_beam_search_with_encoder_rows_matches_restated_loop(cuda, cfg):
         assert got.ids == want_ids
     g.CheckGuards()
     g.close()
+
+
+def test_decoder_of_an_encoder_decoder_model_file(cuda, tmp_path):
+    """A Seq2Seq model file (decoder tensors under "TransformerDecoder.*", one shared embedding table) loaded through
+    `load_seq2seq_decoder` decodes exactly like an engine given the same values under the engine's own names."""
+    from seq2seqsharp_b200.model_file import load_seq2seq_decoder
+    from tests.model_file_writer import write_model
+    cfg = CFGS[0]
+    w = synthetic_weights(cfg, 31, std=0.08, bias_std=0.02, max_pos=MAX_TOK + 2)
+    file_w = {}
+    for k, v in w.items():
+        if k == "PosEmbedding":
+            continue                                     # not saved: rebuilt by the loader (Utils/PositionEmbedding.cs:51-72)
+        if k.startswith("GPTDecoder."):
+            file_w["TransformerDecoder." + k[len("GPTDecoder."):]] = v
+        elif k == "TgtEmbeddings":
+            file_w["SharedEmbeddings"] = v
+        else:
+            file_w[k] = v
+    path = str(tmp_path / "s2s.model")
+    write_model(path, cfg, file_w, cfg.V, decoder_type=1)
+    g, mf = load_seq2seq_decoder(path, max_src_tokens=MAX_SRC, max_batch=2, max_tokens=MAX_TOK)
+    assert g.cfg.cross_attn and mf.DecoderType == 1
+    direct = GPT(g.cfg, max_batch=2, max_tokens=MAX_TOK)
+    direct.LoadWeights(mf.weights_for(g.cfg, g.pos_embedding_rows))
+    enc = _enc(cfg, 2, 6, 3)
+    opts = DecodingOptions(MaxTgtSentLength=MAX_TOK, DecodingStrategy=DS.GreedySearch)
+    for e in (g, direct):
+        e.SetEncoderOutput(enc, [6, 3])
+    a = g.RunForwardOnSingleDevice(np.asarray([[1], [1]], dtype=np.int32), DecodingOptions(MaxTgtSentLength=9), stop_on_eos=False)
+    b = direct.RunForwardOnSingleDevice(np.asarray([[1], [1]], dtype=np.int32), DecodingOptions(MaxTgtSentLength=9), stop_on_eos=False)
+    np.testing.assert_array_equal(a, b)
+    np.testing.assert_array_equal(g.Logits(want_probs=False)[0], direct.Logits(want_probs=False)[0])
+    g.close()
+    direct.close()
