@@ -160,3 +160,28 @@ def test_driver_refuses_what_it_does_not_offer():
         beam_search(eng, [[1, 2]], DecodingOptions(BeamSearchSize=3, MaxTgtSentLength=6))            # 3 beams need 3 sequences
     with pytest.raises(ValueError):
         beam_search(eng, [[1, 2]], DecodingOptions(BeamSearchSize=2, MaxTgtSentLength=6, DecodingStrategy=DS.Sampling))
+
+
+def test_placement_invariants_on_random_survivor_sets():
+    """Whatever the survivors' parents are: every hypothesis gets a sequence of its item's pool, no two share one, a copy's
+    destination is never a sequence that still serves as a source, and a parent with at least one child keeps its rows."""
+    rng = np.random.default_rng(77)
+    for trial in range(400):
+        K, B = int(rng.integers(1, 9)), int(rng.integers(1, 5))
+        pools = [[b + k * B for k in range(K)] for b in range(B)]
+        beams = []
+        for b in range(B):
+            n_parents = int(rng.integers(1, K + 1))
+            parents = rng.choice(pools[b], size=n_parents, replace=False)
+            beams.append([Hypothesis([0], np.float32(1), parent=int(rng.choice(parents))) for _ in range(K)])
+        copies = place(beams, pools)
+        dsts, srcs = [d for _, d in copies], [s for s, _ in copies]
+        assert dsts == sorted(dsts) and len(set(dsts)) == len(dsts) and not set(dsts) & set(srcs)
+        for b in range(B):
+            slots = [h.slot for h in beams[b]]
+            assert sorted(slots) == sorted(pools[b])                       # a permutation of the item's sequences
+            used_parents = {h.parent for h in beams[b]}
+            for p in used_parents:
+                assert any(h.slot == p and h.parent == p for h in beams[b])   # its first child stays in place
+            for h in beams[b]:
+                assert h.slot == h.parent or (h.parent, h.slot) in copies
