@@ -450,7 +450,8 @@ TSB200_API int TSB200_GptEnableStepTiming(void* gpt, int enable);
 TSB200_API int TSB200_GptGetStepTimes(void* gpt, float* ms, int n, int* n_out);
 /* Runs n_steps decode steps un-captured with CUDA events around every launch group and returns, per kernel class
  * (0 embed, 1 norm, 2 linear (GEMV/GEMM), 3 rope+append, 4 attention, 5 sampling, 6 commit), the summed device
- * time in ms and the number of launch groups.  n_classes >= 8. */
+ * time in ms and the number of launches.  Consecutive launches of one class are timed as one run (events only at its two
+ * ends), so that they chain as they do in the captured step.  n_classes >= 8. */
 TSB200_API int TSB200_GptProfileDecode(void* gpt, int n_steps, const TSB200DecodingOptions* opt, float* class_ms,
                                        int64_t* class_groups, int n_classes);
 /* the engine's stream (cudaStream_t) */

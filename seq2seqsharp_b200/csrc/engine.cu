@@ -230,7 +230,9 @@ struct Gpt {
   // instrumentation (TSB200_GptProfileDecode): events around every launch group, by kernel class
   bool prof = false;
   std::vector<cudaEvent_t> prof_ev;
-  std::vector<int> prof_cls;
+  std::vector<int> prof_cls, prof_cnt;   // class and number of launches of every timed run
+  bool prof_open = false;
+  int prof_open_cls = 0, prof_open_cnt = 0;
   size_t prof_n = 0;
   // per-step events of the last GptDecode (TSB200_GptEnableStepTiming)
   bool step_timing = false;
@@ -273,25 +275,47 @@ struct Gpt {
 
 enum KernelClass { KC_EMBED = 0, KC_NORM = 1, KC_LINEAR = 2, KC_ROPE_APPEND = 3, KC_ATTENTION = 4, KC_SAMPLE = 5, KC_COMMIT = 6, KC_ALLREDUCE = 7, KC_STACK = 8, KC_COUNT = 9 };
 
-static void prof_begin(Gpt* g) {
+// Profiling pass (TSB200_GptProfileDecode): CUDA events around RUNS of consecutive launches of one class.  Inside a run no
+// event is recorded between the launches, so they chain exactly as they do in the captured step (an event between two
+// launches would serialise them); a run ends when a launch of another class begins, or at prof_flush().
+static void prof_close_run(Gpt* g) {
+  if (!g->prof_open) return;
+  cudaEventRecord(g->prof_ev[2 * g->prof_n + 1], g->s);
+  if (g->prof_cls.size() <= g->prof_n) {
+    g->prof_cls.resize(g->prof_n + 512);
+    g->prof_cnt.resize(g->prof_n + 512);
+  }
+  g->prof_cls[g->prof_n] = g->prof_open_cls;
+  g->prof_cnt[g->prof_n] = g->prof_open_cnt;
+  ++g->prof_n;
+  g->prof_open = false;
+}
+static void prof_begin(Gpt* g, int cls) {
   if (!g->prof) return;
+  if (g->prof_open && g->prof_open_cls == cls) return;   // the run goes on
+  prof_close_run(g);
   if (g->prof_ev.size() < 2 * (g->prof_n + 1)) {
     const size_t old = g->prof_ev.size();
     g->prof_ev.resize(old + 512);
     for (size_t i = old; i < g->prof_ev.size(); ++i) cudaEventCreate(&g->prof_ev[i]);
   }
   cudaEventRecord(g->prof_ev[2 * g->prof_n], g->s);
+  g->prof_open = true;
+  g->prof_open_cls = cls;
+  g->prof_open_cnt = 0;
 }
+// a launch of class `cls` has been issued (after prof_begin of the same class; a begin whose launch did not happen - a
+// kernel that declined the shape - leaves the run open with nothing counted)
 static void prof_end(Gpt* g, int cls) {
   if (!g->prof) return;
-  cudaEventRecord(g->prof_ev[2 * g->prof_n + 1], g->s);
-  if (g->prof_cls.size() <= g->prof_n) g->prof_cls.resize(g->prof_n + 512);
-  g->prof_cls[g->prof_n] = cls;
-  ++g->prof_n;
+  if (g->prof_open && g->prof_open_cls == cls) ++g->prof_open_cnt;
+}
+static void prof_flush(Gpt* g) {
+  if (g->prof) prof_close_run(g);
 }
 #define PROF(cls, call)          \
   do {                           \
-    prof_begin(g);               \
+    prof_begin(g, cls);          \
     const int _ok = (call);      \
     prof_end(g, cls);            \
     if (!_ok) return 0;          \
@@ -597,7 +621,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
   const TSB200GptConfig& c = g->c;
   const int dev = c.device, dt = c.dtype;
   if (rows <= (g->gemv_rows >= 0 ? g->gemv_rows : (dt == TSB200_F16 ? 0 : 4))) {
-    prof_begin(g);
+    prof_begin(g, KC_LINEAR);
     const int r = launch_gemv_stream(dev, g->st, dt, Wp, ng ? (const void*)x_resid : x_T, ng ? (c.norm_type == 0 ? 2 : 1) : 0, ng,
                                      c.norm_type == 0 ? nb : nullptr, c.eps, rows, K, N, ep, g->err_flag, g->pdl, g->lin_ws,
                                      g->lin_ws_bytes, g->s);
@@ -608,7 +632,7 @@ static int engine_linear(Gpt* g, int rows, const void* x_T, const float* x_resid
   }
   if (ng && dt == TSB200_F16 && rows <= 8 && g->fuse_step) {
     // up to eight rows: the tensor-core streaming kernel norms the rows itself (no norm launch)
-    prof_begin(g);
+    prof_begin(g, KC_LINEAR);
     const int r = launch_gemm_stream_mma_norm(dev, g->st, x_resid, ng, c.norm_type == 0 ? nb : nullptr, c.norm_type, c.eps, Wp, rows, K, N, ep,
                                               g->err_flag, g->pdl, g->lin_ws, g->lin_ws_bytes, g->s);
     if (r != 2) {
@@ -639,18 +663,18 @@ static int row_parallel_linear(Gpt* g, int rows, const void* in, const void* Wp,
     // small messages (decode): the partial goes to this rank's peer buffer, one kernel exchanges flags over NVLink,
     // reads every rank's partial from its memory and adds the sum to the residual stream
     TSB_TRY(engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, nullptr, nullptr, pb, TSB200_ACT_NONE, 0)));
-    prof_begin(g);
+    prof_begin(g, KC_ALLREDUCE);
     const int ok = comm_peer_reduce(g->comm, g->x, (int64_t)rows * d, g->err_flag, g->st->sm_count, g->s);
     count_launch(g->c.device);
     prof_end(g, KC_ALLREDUCE);
     return ok;
   }
   TSB_TRY(engine_linear(g, rows, in, nullptr, nullptr, nullptr, nullptr, Wp, K, d, make_ep(bias, nullptr, nullptr, g->ar_buf, TSB200_ACT_NONE, 0)));
-  prof_begin(g);
+  prof_begin(g, KC_ALLREDUCE);
   int ok = comm_all_reduce_f32(g->comm, g->ar_buf, (int64_t)rows * d, g->s);
   prof_end(g, KC_ALLREDUCE);
   TSB_TRY(ok);
-  prof_begin(g);
+  prof_begin(g, KC_NORM);
   const int64_t n = (int64_t)rows * d;
   int64_t gsz = (n + 255) / 256;
   if (gsz > (int64_t)g->st->sm_count * 8) gsz = (int64_t)g->st->sm_count * 8;
@@ -790,7 +814,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
   const int pe_mode = (c.pe_type == 1) ? (c.ape_decode_pos0 ? 1 : 2) : 0;
   const float sf = (float)std::sqrt((double)d);
   {
-    prof_begin(g);
+    prof_begin(g, KC_EMBED);
     const int gsz = rows < g->st->sm_count * 8 ? rows : g->st->sm_count * 8;
     const int* ids = (S == 1 && use_state) ? g->ids_cur : g->ids_in;
     if (dt == TSB200_F32)
@@ -802,7 +826,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     TSB_TRY(check_launch("embed"));
   }
   if (S == 1 && use_state && g->use_stack && !g->ragged && g->own_B == B && owner_packed(g->own)) {
-    prof_begin(g);
+    prof_begin(g, KC_STACK);
     OwnTp otp{};
     otp.rank = g->tp_rank; otp.size = g->tp; otp.offset = (long long)g->xch_own_off;
     for (int q = 0; q < g->tp && q < kStackMaxRanks; ++q) otp.peer[q] = g->tp > 1 ? g->xch_peer[q] : nullptr;
@@ -822,7 +846,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
     sc.tp_rank = g->tp_rank; sc.tp_size = g->tp; sc.d = c.d;
     for (int r = 0; r < g->tp && r < kStackMaxRanks; ++r) sc.peer[r] = g->tp > 1 ? g->xch_peer[r] : nullptr;
     sc.poll_limit = g->poll_limit;
-    prof_begin(g);
+    prof_begin(g, KC_STACK);
     const int r = launch_decode_stack(dev, g->st, sc, g->stack_dev, g->stack_host.data(), (int)g->stack_host.size(),
                                       g->stack_partials, g->stack_counters, g->stack_attn, g->err_flag, g->stack_trace, g->pdl, g->s);
     if (r != 2) {
@@ -843,7 +867,7 @@ static int enqueue_forward(Gpt* g, int B, int S, int T0, bool use_state, int spl
       RopeFuse rf{};
       rf.cK = L.cK; rf.cV = L.cV; rf.Hd = Hd; rf.KVd = KVd; rf.hd = c.hd; rf.Tmax = c.max_tokens;
       rf.use_rope = c.pe_type == 2 ? 1 : 0; rf.T0 = T0; rf.state = dT; rf.tab = g->rope_tab;
-      prof_begin(g);
+      prof_begin(g, KC_LINEAR);
       const int r = launch_gemm_stream_mma_norm(dev, g->st, g->x, L.n1_g, c.norm_type == 0 ? L.n1_b : nullptr, c.norm_type, c.eps, L.wqkv, rows, d,
                                                 g->Nqkv, make_ep(L.bqkv, nullptr, g->qkv, nullptr, TSB200_ACT_NONE, 0), g->err_flag, g->pdl, g->lin_ws,
                                                 g->lin_ws_bytes, g->s, &rf);
@@ -903,7 +927,7 @@ static int enqueue_sample(Gpt* g, int B, const TSB200DecodingOptions* opt, bool 
     PROF(KC_SAMPLE, launch_philox(dev, g->u, B, opt->seed, opt->seq_base, g->step, use_state ? g->state : nullptr, g->s));
     PROF(KC_SAMPLE, launch_topp(dev, g->st, g->ids_new, g->probs, B, c.V, opt->topP, opt->repeatPenalty, g->hist, g->hist_len, c.max_tokens, g->u, g->topp_ws, g->s));
   }
-  prof_begin(g);
+  prof_begin(g, KC_COMMIT);
   TSB_CUDA(launch_k(commit_kernel, dim3(1), dim3(256), 0, g->s, g->ids_cur, (const int*)g->ids_new, g->hist, g->hist_len, c.max_tokens, g->out_dev, B, g->state, advance_T ? 1 : 0, g->seq0,
                     advance_T ? g->stop_fin : 0));
   count_launch(dev);
@@ -2293,7 +2317,9 @@ int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* o
   g->prof_n = 0;
   int ok = 1;
   for (int i = 0; i < n_steps && ok; ++i) ok = enqueue_forward(g, g->B, 1, g->T, true, splits) && enqueue_sample(g, g->B, opt, true, true);
+  prof_flush(g);
   g->prof = false;
+  g->prof_open = false;
   cudaError_t e = cudaStreamSynchronize(g->s);
   if (!ok) return 0;
   TSB_CUDA(e);
@@ -2302,7 +2328,7 @@ int TSB200_GptProfileDecode(void* h, int n_steps, const TSB200DecodingOptions* o
     float ms = 0.0f;
     TSB_CUDA(cudaEventElapsedTime(&ms, g->prof_ev[2 * i], g->prof_ev[2 * i + 1]));
     class_ms[g->prof_cls[i]] += ms;
-    class_groups[g->prof_cls[i]] += 1;
+    class_groups[g->prof_cls[i]] += g->prof_cnt[i];   // launches, however many of them shared a run
   }
   g->T += n_steps;
   g->step += (uint32_t)n_steps;
